@@ -1,0 +1,35 @@
+// Host-side helpers shared by the launchers of libb200_kernels.so: status
+// plumbing, cached device attributes and TMA tensor-map construction.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "b200_kernels.h"
+
+namespace b200 {
+
+// Number of SMs of the current device (cached per device ordinal).
+int sm_count();
+
+// Maps the last launch error (cudaPeekAtLastError) to a status code.
+inline int launch_status() {
+  return cudaPeekAtLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH_FAILED;
+}
+
+// Device status words of the translation units that contain bounded waits.
+cudaError_t sgemm_status_read_clear(uint32_t* word);
+cudaError_t umma_status_read_clear(uint32_t* word);
+
+enum class Swizzle { kNone, k128B };
+
+// Row-major FP32 matrix [rows][cols] with a row pitch of `ld` elements, tiled
+// in boxes of box_rows x box_cols (cols innermost). Out-of-range parts of a box
+// read as zero and are clipped on store. Requirements (checked, false on
+// failure): base 16-byte aligned, ld * 4 a multiple of 16, box_cols * 4 a
+// multiple of 16 (and <= 128 bytes with the 128-byte swizzle), boxes <= 256.
+bool make_tensor_map_2d(CUtensorMap* out, const float* base, uint64_t rows, uint64_t cols,
+                        uint64_t ld, uint32_t box_rows, uint32_t box_cols, Swizzle swizzle);
+
+}  // namespace b200

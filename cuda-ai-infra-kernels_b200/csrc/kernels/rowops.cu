@@ -1,0 +1,388 @@
+// RMSNorm and softmax over the last dimension of a row-major FP32 matrix.
+//
+// Both operators are HBM-bound: the algorithmic traffic is one read of x and
+// one write of y. Every fast path therefore keeps a whole row in registers
+// between the reduction and the scaling pass (the reference re-reads x from
+// global memory, csrc/rmsnorm/rmsnorm_naive.cu:70-89, or round-trips it through
+// shared memory, csrc/rmsnorm/rmsnorm_cache_x.cu; its softmax makes three
+// passes, csrc/softmax/softmax.cu:25-121). Paths, chosen by row length:
+//
+//   warp   : one warp per row, up to 8 x 128-bit vectors per lane
+//            (rows of <= 1024 floats); shuffle reductions only.
+//   block  : one 256-thread CTA per row, up to 8 vectors per thread
+//            (<= 8192 floats); shuffle + one shared-memory hop.
+//   cluster: 2/4/8 CTAs per row joined by a thread-block cluster; partial
+//            results are exchanged through distributed shared memory
+//            (<= 65536 floats).
+//   stream : any length / any alignment; re-reads the row (normally from L2).
+//
+// All offsets are 64-bit. 128-bit accesses are used only when the row length
+// is a multiple of four and the base pointers are 16-byte aligned.
+#include <cooperative_groups.h>
+#include <float.h>
+
+#include "host_common.h"
+
+namespace cg = cooperative_groups;
+
+namespace b200 {
+namespace {
+
+constexpr int kMaxVec = 8;        // 128-bit vectors held per thread
+constexpr int kBlockThreads = 256;
+constexpr int kWarpsPerBlock = kBlockThreads / 32;
+
+__device__ __forceinline__ float4 load_stream(const float4* p) { return __ldcs(p); }
+__device__ __forceinline__ void store_stream(float4* p, float4 v) { __stcs(p, v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+struct SumOp {
+  static __device__ __forceinline__ float identity() { return 0.f; }
+  static __device__ __forceinline__ float combine(float a, float b) { return a + b; }
+  static __device__ __forceinline__ float warp(float v) { return warp_sum(v); }
+};
+
+struct MaxOp {
+  static __device__ __forceinline__ float identity() { return -FLT_MAX; }
+  static __device__ __forceinline__ float combine(float a, float b) { return fmaxf(a, b); }
+  static __device__ __forceinline__ float warp(float v) { return warp_max(v); }
+};
+
+// Reduction scopes. Every thread receives the result.
+struct WarpScope {
+  template <class Op>
+  __device__ __forceinline__ float reduce(float v) const {
+    return Op::warp(v);
+  }
+};
+
+struct BlockScope {
+  float* scratch;  // kWarpsPerBlock floats per reduction, two slots
+  int slot = 0;
+  template <class Op>
+  __device__ __forceinline__ float reduce(float v) {
+    v = Op::warp(v);
+    float* s = scratch + slot * kWarpsPerBlock;
+    slot ^= 1;  // the next reduction uses the other slot: no trailing barrier needed
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = Op::identity();
+#pragma unroll
+    for (int w = 0; w < kWarpsPerBlock; ++w) r = Op::combine(r, s[w]);
+    return r;
+  }
+};
+
+struct ClusterScope {
+  float* scratch;   // kWarpsPerBlock floats + 1 per slot, two slots
+  int slot = 0;
+  template <class Op>
+  __device__ __forceinline__ float reduce(float v) {
+    cg::cluster_group cluster = cg::this_cluster();
+    v = Op::warp(v);
+    float* s = scratch + slot * (kWarpsPerBlock + 1);
+    slot ^= 1;
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float r = Op::identity();
+#pragma unroll
+      for (int w = 0; w < kWarpsPerBlock; ++w) r = Op::combine(r, s[w]);
+      s[kWarpsPerBlock] = r;  // this CTA's partial, read by its peers
+    }
+    cluster.sync();
+    float r = Op::identity();
+    const unsigned ranks = cluster.num_blocks();
+    for (unsigned peer = 0; peer < ranks; ++peer) {
+      const float* remote = cluster.map_shared_rank(s, peer);
+      r = Op::combine(r, remote[kWarpsPerBlock]);
+    }
+    return r;
+  }
+  // Peers may still be reading this CTA's shared memory: leave together.
+  __device__ __forceinline__ void finish() const { cg::this_cluster().sync(); }
+};
+
+// ---------------------------------------------------------------- row bodies
+// `x_row`/`y_row` point at the part of the row this scope's threads own,
+// `nvec` 128-bit vectors long; thread `t` of `nthreads` handles vectors
+// t, t + nthreads, ...; `row_len` is the full row length for the mean.
+
+template <int VPT, class Scope>
+__device__ __forceinline__ void rmsnorm_row(const float4* __restrict__ x_row, const float4* __restrict__ w_row,
+                                            float4* __restrict__ y_row, int nvec, int t, int nthreads,
+                                            int64_t row_len, double eps, Scope& scope) {
+  float4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = t + i * nthreads;
+    if (idx < nvec) {
+      v[i] = load_stream(x_row + idx);
+      ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+  }
+  ss = scope.template reduce<SumOp>(ss);
+  // Same arithmetic as the reference: FP32 mean, epsilon added in double,
+  // single-precision reciprocal square root (csrc/rmsnorm/rmsnorm_naive.cu:62-65).
+  const float inv_rms = rsqrtf(static_cast<float>(static_cast<double>(ss / static_cast<float>(row_len)) + eps));
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = t + i * nthreads;
+    if (idx < nvec) {
+      const float4 w = __ldg(w_row + idx);
+      store_stream(y_row + idx, make_float4(v[i].x * w.x * inv_rms, v[i].y * w.y * inv_rms,
+                                            v[i].z * w.z * inv_rms, v[i].w * w.w * inv_rms));
+    }
+  }
+}
+
+template <int VPT, class Scope>
+__device__ __forceinline__ void softmax_row(const float4* __restrict__ x_row, float4* __restrict__ y_row, int nvec,
+                                            int t, int nthreads, Scope& scope) {
+  float4 v[VPT];
+  float mx = -FLT_MAX;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = t + i * nthreads;
+    if (idx < nvec) {
+      v[i] = load_stream(x_row + idx);
+      mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    }
+  }
+  mx = scope.template reduce<MaxOp>(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = t + i * nthreads;
+    if (idx < nvec) {
+      v[i].x = __expf(v[i].x - mx), v[i].y = __expf(v[i].y - mx);
+      v[i].z = __expf(v[i].z - mx), v[i].w = __expf(v[i].w - mx);
+      sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+  }
+  sum = scope.template reduce<SumOp>(sum);
+  const float inv = __frcp_rn(sum);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = t + i * nthreads;
+    if (idx < nvec) store_stream(y_row + idx, make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv));
+  }
+}
+
+// -------------------------------------------------------------------- kernels
+
+enum class RowOp { kRmsNorm, kSoftmax };
+
+struct RowArgs {
+  const float* x;
+  const float* w;  // RMSNorm only
+  float* y;
+  int64_t rows;
+  int64_t cols;
+  double eps;      // RMSNorm only
+};
+
+template <RowOp kOp, int VPT>
+__global__ void __launch_bounds__(kBlockThreads) row_warp_kernel(const RowArgs a) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const int nvec = static_cast<int>(a.cols / 4);
+  const float4* x_row = reinterpret_cast<const float4*>(a.x + row * a.cols);
+  float4* y_row = reinterpret_cast<float4*>(a.y + row * a.cols);
+  WarpScope scope;
+  if constexpr (kOp == RowOp::kRmsNorm) {
+    rmsnorm_row<VPT>(x_row, reinterpret_cast<const float4*>(a.w), y_row, nvec, threadIdx.x & 31, 32, a.cols, a.eps,
+                     scope);
+  } else {
+    softmax_row<VPT>(x_row, y_row, nvec, threadIdx.x & 31, 32, scope);
+  }
+}
+
+template <RowOp kOp, int VPT>
+__global__ void __launch_bounds__(kBlockThreads) row_block_kernel(const RowArgs a) {
+  __shared__ float scratch[2 * kWarpsPerBlock];
+  const int64_t row = blockIdx.x;
+  const int nvec = static_cast<int>(a.cols / 4);
+  const float4* x_row = reinterpret_cast<const float4*>(a.x + row * a.cols);
+  float4* y_row = reinterpret_cast<float4*>(a.y + row * a.cols);
+  BlockScope scope{scratch};
+  if constexpr (kOp == RowOp::kRmsNorm) {
+    rmsnorm_row<VPT>(x_row, reinterpret_cast<const float4*>(a.w), y_row, nvec, threadIdx.x, kBlockThreads, a.cols,
+                     a.eps, scope);
+  } else {
+    softmax_row<VPT>(x_row, y_row, nvec, threadIdx.x, kBlockThreads, scope);
+  }
+}
+
+// One cluster per row; CTA `rank` owns vectors [rank * per_cta, ...).
+template <RowOp kOp>
+__global__ void __launch_bounds__(kBlockThreads) row_cluster_kernel(const RowArgs a) {
+  __shared__ float scratch[2 * (kWarpsPerBlock + 1)];
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned ranks = cluster.num_blocks();
+  const unsigned rank = cluster.block_rank();
+  const int64_t row = blockIdx.x / ranks;
+  const int nvec_row = static_cast<int>(a.cols / 4);
+  const int per_cta = (nvec_row + ranks - 1) / ranks;
+  const int begin = min(static_cast<int>(rank) * per_cta, nvec_row);
+  const int nvec = min(per_cta, nvec_row - begin);
+  const float4* x_row = reinterpret_cast<const float4*>(a.x + row * a.cols) + begin;
+  float4* y_row = reinterpret_cast<float4*>(a.y + row * a.cols) + begin;
+  ClusterScope scope{scratch};
+  if constexpr (kOp == RowOp::kRmsNorm) {
+    rmsnorm_row<kMaxVec>(x_row, reinterpret_cast<const float4*>(a.w) + begin, y_row, nvec, threadIdx.x,
+                         kBlockThreads, a.cols, a.eps, scope);
+  } else {
+    softmax_row<kMaxVec>(x_row, y_row, nvec, threadIdx.x, kBlockThreads, scope);
+  }
+  scope.finish();
+}
+
+// Any length, any alignment: scalar accesses, the row is re-read.
+template <RowOp kOp>
+__global__ void __launch_bounds__(kBlockThreads) row_stream_kernel(const RowArgs a) {
+  __shared__ float scratch[2 * kWarpsPerBlock];
+  const int64_t row = blockIdx.x;
+  const float* x_row = a.x + row * a.cols;
+  float* y_row = a.y + row * a.cols;
+  BlockScope scope{scratch};
+  if constexpr (kOp == RowOp::kRmsNorm) {
+    float ss = 0.f;
+    for (int64_t c = threadIdx.x; c < a.cols; c += kBlockThreads) {
+      const float v = x_row[c];
+      ss += v * v;
+    }
+    ss = scope.reduce<SumOp>(ss);
+    const float inv_rms = rsqrtf(static_cast<float>(static_cast<double>(ss / static_cast<float>(a.cols)) + a.eps));
+    for (int64_t c = threadIdx.x; c < a.cols; c += kBlockThreads) y_row[c] = x_row[c] * a.w[c] * inv_rms;
+  } else {
+    // Online maximum / rescaled sum: one read for both statistics.
+    float mx = -FLT_MAX, sum = 0.f;
+    for (int64_t c = threadIdx.x; c < a.cols; c += kBlockThreads) {
+      const float v = x_row[c];
+      const float m2 = fmaxf(mx, v);
+      sum = sum * __expf(mx - m2) + __expf(v - m2);
+      mx = m2;
+    }
+    const float row_max = scope.reduce<MaxOp>(mx);
+    sum = scope.reduce<SumOp>(sum * __expf(mx - row_max));
+    const float inv = __frcp_rn(sum);
+    for (int64_t c = threadIdx.x; c < a.cols; c += kBlockThreads) y_row[c] = __expf(x_row[c] - row_max) * inv;
+  }
+}
+
+// ------------------------------------------------------------------- dispatch
+
+template <RowOp kOp, int VPT>
+int launch_warp(const RowArgs& a, cudaStream_t s) {
+  const int64_t blocks = (a.rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  row_warp_kernel<kOp, VPT><<<static_cast<unsigned>(blocks), kBlockThreads, 0, s>>>(a);
+  return launch_status();
+}
+
+template <RowOp kOp, int VPT>
+int launch_block(const RowArgs& a, cudaStream_t s) {
+  row_block_kernel<kOp, VPT><<<static_cast<unsigned>(a.rows), kBlockThreads, 0, s>>>(a);
+  return launch_status();
+}
+
+template <RowOp kOp>
+int launch_cluster(const RowArgs& a, int ranks, cudaStream_t s) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(a.rows * ranks));
+  cfg.blockDim = dim3(kBlockThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = ranks;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, row_cluster_kernel<kOp>, a) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  return launch_status();
+}
+
+template <RowOp kOp>
+int launch_by_vectors_warp(int vpt, const RowArgs& a, cudaStream_t s) {
+  switch (vpt) {
+    case 1: return launch_warp<kOp, 1>(a, s);
+    case 2: return launch_warp<kOp, 2>(a, s);
+    case 3: case 4: return launch_warp<kOp, 4>(a, s);
+    case 5: case 6: return launch_warp<kOp, 6>(a, s);
+    default: return launch_warp<kOp, 8>(a, s);
+  }
+}
+
+template <RowOp kOp>
+int launch_by_vectors_block(int vpt, const RowArgs& a, cudaStream_t s) {
+  switch (vpt) {
+    case 1: return launch_block<kOp, 1>(a, s);
+    case 2: return launch_block<kOp, 2>(a, s);
+    case 3: case 4: return launch_block<kOp, 4>(a, s);
+    case 5: case 6: return launch_block<kOp, 6>(a, s);
+    default: return launch_block<kOp, 8>(a, s);
+  }
+}
+
+template <RowOp kOp>
+int launch_rows(const RowArgs& a, cudaStream_t s) {
+  if (a.rows == 0 || a.cols == 0) return B200_OK;
+  if (a.rows > 0x7fffffffLL / 8) return B200_ERR_INVALID_PROBLEM;  // grid.x with an 8-CTA cluster per row
+  const bool vector_ok = a.cols % 4 == 0 && reinterpret_cast<uintptr_t>(a.x) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(a.y) % 16 == 0 &&
+                         (kOp == RowOp::kSoftmax || reinterpret_cast<uintptr_t>(a.w) % 16 == 0);
+  const int64_t nvec = a.cols / 4;
+  if (vector_ok && nvec <= 32 * kMaxVec) {
+    return launch_by_vectors_warp<kOp>(static_cast<int>((nvec + 31) / 32), a, s);
+  }
+  if (vector_ok && nvec <= kBlockThreads * kMaxVec) {
+    return launch_by_vectors_block<kOp>(static_cast<int>((nvec + kBlockThreads - 1) / kBlockThreads), a, s);
+  }
+  if (vector_ok && nvec <= 8 * kBlockThreads * kMaxVec) {
+    const int64_t per_cluster_cta = kBlockThreads * kMaxVec;
+    const int needed = static_cast<int>((nvec + per_cluster_cta - 1) / per_cluster_cta);
+    const int ranks = needed <= 2 ? 2 : (needed <= 4 ? 4 : 8);
+    return launch_cluster<kOp>(a, ranks, s);
+  }
+  row_stream_kernel<kOp><<<static_cast<unsigned>(a.rows), kBlockThreads, 0, s>>>(a);
+  return launch_status();
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" {
+
+int b200_rmsnorm(int impl, const float* x, const float* weight, float* y, int64_t rows, int64_t hidden, double eps,
+                 b200_stream_t stream) {
+  if (impl != B200_RMSNORM_NAIVE && impl != B200_RMSNORM_CACHE_X) return B200_ERR_INVALID_ARGUMENT;
+  if (rows < 0 || hidden < 0) return B200_ERR_INVALID_ARGUMENT;
+  if (rows > 0 && hidden > 0 && (x == nullptr || weight == nullptr || y == nullptr)) return B200_ERR_INVALID_ARGUMENT;
+  if (impl == B200_RMSNORM_CACHE_X && hidden > 4096) return B200_ERR_NOT_SUPPORTED;
+  const b200::RowArgs args{x, weight, y, rows, hidden, eps};
+  return b200::launch_rows<b200::RowOp::kRmsNorm>(args, static_cast<cudaStream_t>(stream));
+}
+
+int b200_softmax(int impl, const float* x, float* y, int64_t rows, int64_t cols, b200_stream_t stream) {
+  if (impl != B200_SOFTMAX_NAIVE) return B200_ERR_INVALID_ARGUMENT;
+  if (rows < 0 || cols < 0) return B200_ERR_INVALID_ARGUMENT;
+  if (rows > 0 && cols > 0 && (x == nullptr || y == nullptr)) return B200_ERR_INVALID_ARGUMENT;
+  const b200::RowArgs args{x, nullptr, y, rows, cols, 0.0};
+  return b200::launch_rows<b200::RowOp::kSoftmax>(args, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,215 @@
+// FP32 SIMT GEMM ladder, stages 1-5: one output per thread, shared-memory
+// staging (scalar and 128-bit), register thread tiles and the warp-tiled
+// mapping. C[M,N] = A[M,K] * B[K,N] with A stored column-major (a contiguous
+// [K,M] array), B and C row-major. Full tiles only; sizes are validated on the
+// host (b200_sgemm_check) and the kernels do no bounds checks.
+//
+// Stages 2-5 share one kernel template: a CTA stages a [BK][BM] slab of A and a
+// [BK][BN] slab of B in shared memory, and every thread accumulates RM x RN
+// register blocks of CM x CN outputs whose origins inside the CTA tile come
+// from a mapping policy. The policies reproduce the work decomposition of each
+// ladder step of the reference (csrc/gemm/gemm_block_tile.cu,
+// gemm_block_tile_float4.cu, gemm_thread_tile.cu, gemm_warp_tile.cu).
+#include "sgemm.h"
+
+namespace b200 {
+namespace {
+
+// ---------------------------------------------------------------- stage 1
+
+__global__ void __launch_bounds__(256) sgemm_naive_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                          float* __restrict__ c, int m, int n, int k) {
+  const int col = blockIdx.x * 16 + threadIdx.x;
+  const int row = blockIdx.y * 16 + threadIdx.y;
+  const float* a_col = a + row;  // walks k with stride m
+  const float* b_col = b + col;  // walks k with stride n
+  float acc = 0.f;
+  for (int kk = 0; kk < k; ++kk) {
+    acc = fmaf(a_col[static_cast<int64_t>(kk) * m], b_col[static_cast<int64_t>(kk) * n], acc);
+  }
+  c[static_cast<int64_t>(row) * n + col] = acc;
+}
+
+// ------------------------------------------------------------ stages 2-5
+
+// One output per thread on a BM x BN thread grid (stages 2 and 3).
+template <int BM, int BN>
+struct MapOnePerThread {
+  static constexpr int kThreads = BM * BN;
+  static constexpr int kRowBlocks = 1, kColBlocks = 1, kBlockRows = 1, kBlockCols = 1;
+  int ty, tx;
+  __device__ explicit MapOnePerThread(int tid) : ty(tid / BN), tx(tid % BN) {}
+  __device__ int row_origin(int) const { return ty; }
+  __device__ int col_origin(int) const { return tx; }
+};
+
+// One contiguous TM x TN rectangle per thread (stage 4). With kWarp4x8 the
+// threads of a warp form 4 rows x 8 columns of rectangles instead of one row.
+template <int BM, int BN, int TM, int TN, bool kWarp4x8>
+struct MapThreadTile {
+  static_assert(TM % 4 == 0 && TN % 4 == 0, "register blocks are 4 wide");
+  static constexpr int kThreads = (BM / TM) * (BN / TN);
+  static constexpr int kRowBlocks = TM / 4, kColBlocks = TN / 4, kBlockRows = 4, kBlockCols = 4;
+  int ty, tx;
+  __device__ explicit MapThreadTile(int tid) {
+    if constexpr (kWarp4x8) {
+      constexpr int kWarpsAcross = BN / (8 * TN);
+      const int warp = tid >> 5, lane = tid & 31;
+      ty = (warp / kWarpsAcross) * 4 + (lane >> 3);
+      tx = (warp % kWarpsAcross) * 8 + (lane & 7);
+    } else {
+      ty = tid / (BN / TN);
+      tx = tid % (BN / TN);
+    }
+  }
+  __device__ int row_origin(int r) const { return ty * TM + 4 * r; }
+  __device__ int col_origin(int c) const { return tx * TN + 4 * c; }
+};
+
+// Stage 5: 2 x 4 warps of 64 x 32; inside a warp 8 x 4 lanes; each thread owns
+// 2 x 2 blocks of 4 x 4, the row blocks 32 apart and the column blocks 16
+// apart, so that a warp-wide 128-bit shared load touches one 128-byte line.
+struct MapWarpTile {
+  static constexpr int kThreads = 256;
+  static constexpr int kRowBlocks = 2, kColBlocks = 2, kBlockRows = 4, kBlockCols = 4;
+  int row0, col0;
+  __device__ explicit MapWarpTile(int tid) {
+    const int warp = tid >> 5, lane = tid & 31;
+    row0 = (warp >> 2) * 64 + (lane >> 2) * 4;
+    col0 = (warp & 3) * 32 + (lane & 3) * 4;
+  }
+  __device__ int row_origin(int r) const { return row0 + 32 * r; }
+  __device__ int col_origin(int c) const { return col0 + 16 * c; }
+};
+
+template <int BM, int BN, int BK, bool kVectorStaging, class Map>
+__global__ void __launch_bounds__(Map::kThreads) sgemm_smem_kernel(const float* __restrict__ a,
+                                                                     const float* __restrict__ b,
+                                                                     float* __restrict__ c, int m, int n, int k) {
+  constexpr int kThreads = Map::kThreads;
+  constexpr int RM = Map::kRowBlocks, RN = Map::kColBlocks, CM = Map::kBlockRows, CN = Map::kBlockCols;
+  __shared__ __align__(16) float a_s[BK][BM];
+  __shared__ __align__(16) float b_s[BK][BN];
+
+  const int tid = threadIdx.x;
+  const Map map(tid);
+  const int m0 = blockIdx.y * BM;
+  const int n0 = blockIdx.x * BN;
+
+  float acc[RM * CM][RN * CN];
+#pragma unroll
+  for (int i = 0; i < RM * CM; ++i)
+#pragma unroll
+    for (int j = 0; j < RN * CN; ++j) acc[i][j] = 0.f;
+
+  for (int k0 = 0; k0 < k; k0 += BK) {
+    // Stage the two slabs. Row kk of either slab is contiguous in global memory.
+    if constexpr (kVectorStaging) {
+      for (int v = tid; v < BK * BM / 4; v += kThreads) {
+        const int kk = v / (BM / 4), mm = (v % (BM / 4)) * 4;
+        *reinterpret_cast<float4*>(&a_s[kk][mm]) =
+            *reinterpret_cast<const float4*>(a + static_cast<int64_t>(k0 + kk) * m + m0 + mm);
+      }
+      for (int v = tid; v < BK * BN / 4; v += kThreads) {
+        const int kk = v / (BN / 4), nn = (v % (BN / 4)) * 4;
+        *reinterpret_cast<float4*>(&b_s[kk][nn]) =
+            *reinterpret_cast<const float4*>(b + static_cast<int64_t>(k0 + kk) * n + n0 + nn);
+      }
+    } else {
+      for (int e = tid; e < BK * BM; e += kThreads) {
+        const int kk = e / BM, mm = e % BM;
+        a_s[kk][mm] = a[static_cast<int64_t>(k0 + kk) * m + m0 + mm];
+      }
+      for (int e = tid; e < BK * BN; e += kThreads) {
+        const int kk = e / BN, nn = e % BN;
+        b_s[kk][nn] = b[static_cast<int64_t>(k0 + kk) * n + n0 + nn];
+      }
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float a_frag[RM * CM], b_frag[RN * CN];
+#pragma unroll
+      for (int r = 0; r < RM; ++r) {
+        if constexpr (CM == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(&a_s[kk][map.row_origin(r)]);
+          a_frag[4 * r + 0] = v.x, a_frag[4 * r + 1] = v.y, a_frag[4 * r + 2] = v.z, a_frag[4 * r + 3] = v.w;
+        } else {
+          a_frag[r] = a_s[kk][map.row_origin(r)];
+        }
+      }
+#pragma unroll
+      for (int cc = 0; cc < RN; ++cc) {
+        if constexpr (CN == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(&b_s[kk][map.col_origin(cc)]);
+          b_frag[4 * cc + 0] = v.x, b_frag[4 * cc + 1] = v.y, b_frag[4 * cc + 2] = v.z, b_frag[4 * cc + 3] = v.w;
+        } else {
+          b_frag[cc] = b_s[kk][map.col_origin(cc)];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < RM * CM; ++i)
+#pragma unroll
+        for (int j = 0; j < RN * CN; ++j) acc[i][j] = fmaf(a_frag[i], b_frag[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int r = 0; r < RM; ++r)
+#pragma unroll
+    for (int i = 0; i < CM; ++i) {
+      const int64_t row = m0 + map.row_origin(r) + i;
+#pragma unroll
+      for (int cc = 0; cc < RN; ++cc) {
+        const int col = n0 + map.col_origin(cc);
+        if constexpr (CN == 4) {
+          const float* v = acc[r * CM + i] + cc * 4;
+          *reinterpret_cast<float4*>(c + row * n + col) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+          c[row * n + col] = acc[r * CM + i][cc];
+        }
+      }
+    }
+}
+
+template <int BM, int BN, int BK, bool kVectorStaging, class Map>
+int launch_smem(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
+  sgemm_smem_kernel<BM, BN, BK, kVectorStaging, Map>
+      <<<dim3(n / BN, m / BM), Map::kThreads, 0, stream>>>(a, b, c, m, n, k);
+  return launch_status();
+}
+
+}  // namespace
+
+int sgemm_ladder_launch(int impl, const float* a, const float* b, float* c, int m, int n, int k,
+                        cudaStream_t stream) {
+  switch (impl) {
+    case B200_SGEMM_NAIVE:
+      sgemm_naive_kernel<<<dim3(n / 16, m / 16), dim3(16, 16), 0, stream>>>(a, b, c, m, n, k);
+      return launch_status();
+    case B200_SGEMM_BLOCK_TILE:
+      return launch_smem<16, 16, 8, false, MapOnePerThread<16, 16>>(a, b, c, m, n, k, stream);
+    case B200_SGEMM_BLOCK_TILE_F4_16x16:
+      return launch_smem<16, 16, 8, true, MapOnePerThread<16, 16>>(a, b, c, m, n, k, stream);
+    case B200_SGEMM_BLOCK_TILE_F4_16x32:
+      return launch_smem<16, 32, 8, true, MapOnePerThread<16, 32>>(a, b, c, m, n, k, stream);
+    case B200_SGEMM_BLOCK_TILE_F4_32x32:
+      return launch_smem<32, 32, 8, true, MapOnePerThread<32, 32>>(a, b, c, m, n, k, stream);
+    case B200_SGEMM_THREAD_TILE_4x4:
+      return launch_smem<128, 128, 8, true, MapThreadTile<128, 128, 4, 4, false>>(a, b, c, m, n, k, stream);
+    case B200_SGEMM_THREAD_TILE_4x8:
+      return launch_smem<128, 128, 8, true, MapThreadTile<128, 128, 4, 8, false>>(a, b, c, m, n, k, stream);
+    case B200_SGEMM_THREAD_TILE_8x8:
+      return launch_smem<128, 128, 8, true, MapThreadTile<128, 128, 8, 8, false>>(a, b, c, m, n, k, stream);
+    case B200_SGEMM_THREAD_TILE_8x8_WARP4x8:
+      return launch_smem<128, 128, 8, true, MapThreadTile<128, 128, 8, 8, true>>(a, b, c, m, n, k, stream);
+    case B200_SGEMM_WARP_TILE:
+      return launch_smem<128, 128, 8, true, MapWarpTile>(a, b, c, m, n, k, stream);
+    default:
+      return B200_ERR_INVALID_ARGUMENT;
+  }
+}
+
+}  // namespace b200

@@ -1,0 +1,547 @@
+// TF32 tensor-core GEMM with a fused epilogue, written for sm_100a:
+//   D = epilogue(alpha * A * B + beta * C),  A [M,K], B [K,N], C/D [M,N],
+// all row-major FP32; products in TF32 on tcgen05.mma, accumulation in FP32 in
+// tensor memory (TMEM); epilogue (scale, source add, optional ReLU) applied on
+// the TMEM -> register -> global path, so the accumulator never touches HBM.
+//
+// It stands in for the CUTLASS device::Gemm instantiations of the reference
+// (csrc/adaptive_gemm/kernel_sm80.h:4-171, launched through
+// csrc/adaptive_gemm/kernel_launcher.h:7-29).
+//
+// Operand staging. One pipeline stage holds a 128 x 32 slab of A and a
+// 32 x BN slab of B, 32 floats of K = 128 bytes per row, in the 128-byte
+// swizzled layout that both TMA and the MMA unit understand:
+//   A is K-major for the MMA (K contiguous in memory). The slab is one TMA box
+//     {32 (k), 128 (m)}: 128 rows of 128 bytes, 8-row groups 1024 bytes apart.
+//   B is N-major for the MMA (N contiguous in memory). The slab is BN/32 TMA
+//     boxes {32 (n), 32 (k)}: each 32 rows (k) of 128 bytes (32 n), boxes
+//     4096 bytes apart; inside a box, 8-row k groups are 1024 bytes apart.
+// One tcgen05.mma consumes 8 floats of K: the A descriptor advances 32 bytes
+// inside the swizzled row, the B descriptor advances one 8-row group.
+//
+// Two loaders feed that layout:
+//   TMA     - needs 16-byte aligned pointers and leading dimensions that are
+//             multiples of four floats; persistent, warp-specialised kernel
+//             (producer / MMA issuer / epilogue warps), double-buffered TMEM
+//             accumulator so the epilogue of one tile overlaps the main loop of
+//             the next.
+//   generic - any pointers, any sizes; predicated scalar loads written into the
+//             same swizzled layout, one tile per CTA.
+// Neither uses cluster multicast.
+#include <cstring>
+
+#include "host_common.h"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+
+cudaError_t umma_status_read_clear(uint32_t* word) { return status_word_read_clear(word); }
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kStageK = 32;                       // floats of K per stage (one 128-byte swizzle row)
+constexpr int kInstK = 8;                         // K of one tcgen05.mma kind::tf32
+constexpr uint32_t kASlabBytes = kTileM * kStageK * 4;  // 16 KiB
+constexpr uint32_t kBBoxBytes = 32 * kStageK * 4;       // 4 KiB: 32 (n) x 32 (k)
+
+struct UmmaParams {
+  CUtensorMap map_a;   // [M][K] boxes {32, 128}, 128-byte swizzle   (TMA loader only)
+  CUtensorMap map_b;   // [K][N] boxes {32, 32},  128-byte swizzle   (TMA loader only)
+  const float* a;      // generic loader only
+  const float* b;
+  const float* c;      // source, may be null when beta == 0
+  float* d;
+  int64_t lda, ldb, ldc, ldd;
+  int m, n, k;
+  float alpha, beta;
+  int vector_io;       // C/D rows allow 128-bit accesses
+};
+
+template <int BN>
+__host__ __device__ constexpr uint32_t stage_bytes() {
+  return kASlabBytes + (BN / 32) * kBBoxBytes;
+}
+
+template <int BN, int STAGES>
+__host__ __device__ constexpr size_t smem_bytes() {
+  return static_cast<size_t>(STAGES) * stage_bytes<BN>() + 1024 /*alignment slack*/ + 256 /*barriers + tmem ptr*/;
+}
+
+template <int BN>
+__host__ __device__ constexpr uint32_t tmem_columns() {
+  return 2 * BN < 32 ? 32 : 2 * BN;  // two accumulator buffers; BN in {64,128,256} keeps this a power of two
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int* tm, int* tn) {
+  constexpr int kBand = 8;
+  const int per_band = kBand * tiles_n;
+  const int band = tile / per_band;
+  const int first_m = band * kBand;
+  const int band_rows = min(kBand, tiles_m - first_m);
+  const int in_band = tile - band * per_band;
+  *tm = first_m + in_band % band_rows;
+  *tn = in_band / band_rows;
+}
+
+// Issues the four MMAs of one stage. `accumulate_first` is 0 only for the very
+// first MMA of an output tile.
+template <int BN>
+__device__ __forceinline__ void issue_stage_mmas(uint32_t tmem_acc, uint32_t a_addr, uint32_t b_addr,
+                                                 uint32_t accumulate_first) {
+  constexpr uint32_t idesc = umma_idesc_tf32(kTileM, BN, /*a_mn_major=*/false, /*b_mn_major=*/true);
+#pragma unroll
+  for (int j = 0; j < kStageK / kInstK; ++j) {
+    // A: K-major, 8-row groups 1024 bytes apart (SBO); LBO is not used by the
+    //    swizzled K-major form and carries the customary 16 bytes.
+    // B: N-major, 32-column groups 4096 bytes apart (LBO), 8-row k groups
+    //    1024 bytes apart (SBO).
+    const uint64_t desc_a = umma_smem_desc_sw128(a_addr + j * (kInstK * 4), 16, 1024);
+    const uint64_t desc_b = umma_smem_desc_sw128(b_addr + j * 1024, kBBoxBytes, 1024);
+    umma_tf32(tmem_acc, desc_a, desc_b, idesc, j == 0 ? accumulate_first : 1u);
+  }
+}
+
+// Epilogue of one 128 x BN tile for one warp: TMEM lanes [32 * quarter, +32)
+// are rows m0 + 32 * quarter + lane. Each thread owns one row and walks it in
+// chunks of 32 columns.
+template <int BN, bool kRelu>
+__device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem_acc, int quarter, int lane, int m0,
+                                              int n0) {
+  const int row = m0 + quarter * 32 + lane;
+  const bool row_ok = row < p.m;
+  const bool use_c = p.beta != 0.f;
+  const float* c_row = p.c + static_cast<int64_t>(row) * p.ldc;
+  float* d_row = p.d + static_cast<int64_t>(row) * p.ldd;
+#pragma unroll 1
+  for (int chunk = 0; chunk < BN / 32; ++chunk) {
+    const int col0 = n0 + chunk * 32;
+    if (col0 >= p.n) break;  // uniform across the warp
+    uint32_t raw[32];
+    tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 32, raw);
+    tmem_ld_wait();
+    if (!row_ok) continue;
+    if (p.vector_io) {
+      // n % 4 == 0 here, so a 4-wide group is entirely inside or outside.
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const int col = col0 + 4 * g;
+        if (col < p.n) {
+          float4 v = make_float4(p.alpha * __uint_as_float(raw[4 * g + 0]), p.alpha * __uint_as_float(raw[4 * g + 1]),
+                                 p.alpha * __uint_as_float(raw[4 * g + 2]), p.alpha * __uint_as_float(raw[4 * g + 3]));
+          if (use_c) {
+            const float4 s = __ldg(reinterpret_cast<const float4*>(c_row + col));
+            v.x = fmaf(p.beta, s.x, v.x), v.y = fmaf(p.beta, s.y, v.y);
+            v.z = fmaf(p.beta, s.z, v.z), v.w = fmaf(p.beta, s.w, v.w);
+          }
+          if (kRelu) v = make_float4(fmaxf(v.x, 0.f), fmaxf(v.y, 0.f), fmaxf(v.z, 0.f), fmaxf(v.w, 0.f));
+          *reinterpret_cast<float4*>(d_row + col) = v;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const int col = col0 + e;
+        if (col < p.n) {
+          float v = p.alpha * __uint_as_float(raw[e]);
+          if (use_c) v = fmaf(p.beta, __ldg(c_row + col), v);
+          if (kRelu) v = fmaxf(v, 0.f);
+          d_row[col] = v;
+        }
+      }
+    }
+  }
+}
+
+struct SmemCarve {
+  uint8_t* stages;
+  uint64_t* full;
+  uint64_t* empty;
+  uint64_t* acc_full;
+  uint64_t* acc_empty;
+  uint32_t* tmem_ptr;
+};
+
+template <int BN, int STAGES>
+__device__ __forceinline__ SmemCarve carve(uint8_t* raw) {
+  SmemCarve s;
+  s.stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  s.full = reinterpret_cast<uint64_t*>(s.stages + static_cast<size_t>(STAGES) * stage_bytes<BN>());
+  s.empty = s.full + STAGES;
+  s.acc_full = s.empty + STAGES;
+  s.acc_empty = s.acc_full + 2;
+  s.tmem_ptr = reinterpret_cast<uint32_t*>(s.acc_empty + 2);
+  return s;
+}
+
+// ------------------------------------------------------- TMA, persistent kernel
+// warp 0: TMA producer (one lane)      warp 1: TMEM owner + MMA issuer (one lane)
+// warps 2-5: epilogue; warp w reads the TMEM lane quarter w % 4.
+constexpr int kTmaThreads = 6 * 32;
+
+template <int BN, int STAGES, bool kRelu>
+__global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_constant__ UmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const SmemCarve sm = carve<BN, STAGES>(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.acc_full[b], 1);
+      mbar_init(&sm.acc_empty[b], 4);  // one arrive per epilogue warp
+    }
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc<tmem_columns<BN>()>(sm.tmem_ptr);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_ptr;
+
+  const int tiles_m = (p.m + kTileM - 1) / kTileM;
+  const int tiles_n = (p.n + BN - 1) / BN;
+  const int tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.k + kStageK - 1) / kStageK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&p.map_a);
+      prefetch_tensormap(&p.map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&sm.empty[stage], phase ^ 1u, kSiteUmmaEmpty)) { ok = false; break; }
+          uint8_t* a_dst = sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>();
+          uint8_t* b_dst = a_dst + kASlabBytes;
+          mbar_expect_tx(&sm.full[stage], stage_bytes<BN>());
+          tma_load_2d(a_dst, &p.map_a, &sm.full[stage], kb * kStageK, tm * kTileM);
+#pragma unroll
+          for (int j = 0; j < BN / 32; ++j) {
+            tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &sm.full[stage], tn * BN + j * 32, kb * kStageK);
+          }
+          if (++stage == STAGES) stage = 0, phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const uint32_t use_parity = (local >> 1) & 1u;
+        // The epilogue must have drained this accumulator buffer.
+        if (!mbar_wait(&sm.acc_empty[buf], use_parity ^ 1u, kSiteUmmaAccEmpty)) { ok = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + buf * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
+          tcgen05_fence_after_sync();
+          const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>());
+          issue_stage_mmas<BN>(tmem_acc, a_addr, a_addr + kASlabBytes, kb > 0 ? 1u : 0u);
+          umma_commit(&sm.empty[stage]);  // stage reusable once these MMAs have read it
+          if (++stage == STAGES) stage = 0, phase ^= 1u;
+        }
+        if (ok) umma_commit(&sm.acc_full[buf]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    bool ok = true;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const uint32_t use_parity = (local >> 1) & 1u;
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      if (!mbar_wait(&sm.acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
+      tcgen05_fence_after_sync();
+      epilogue_tile<BN, kRelu>(p, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN);
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
+    }
+  }
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc<tmem_columns<BN>()>(tmem_base);
+  }
+}
+
+// ------------------------------------------------------- generic loader kernel
+// One CTA per output tile, 128 threads. All threads fill the swizzled slabs
+// with predicated scalar loads (zeros outside the matrix), thread 0 issues the
+// MMAs, everyone waits for them before the slabs are overwritten. Two slabs
+// alternate so that the loads of stage i + 1 overlap the MMAs of stage i.
+constexpr int kGenericThreads = 128;
+
+template <int BN>
+__device__ __forceinline__ void fill_stage(const UmmaParams& p, uint8_t* a_dst, uint8_t* b_dst, int m0, int n0, int k0) {
+  // A slab: element (m, k) at m * 128 + ((k / 4) ^ (m % 8)) * 16 + (k % 4) * 4.
+  for (int e = threadIdx.x; e < kTileM * kStageK; e += kGenericThreads) {
+    const int mm = e / kStageK, kk = e % kStageK;
+    const int gm = m0 + mm, gk = k0 + kk;
+    const float v = (gm < p.m && gk < p.k) ? __ldg(p.a + static_cast<int64_t>(gm) * p.lda + gk) : 0.f;
+    *reinterpret_cast<float*>(a_dst + mm * 128 + (((kk >> 2) ^ (mm & 7)) << 4) + ((kk & 3) << 2)) = v;
+  }
+  // B slab: box j = n / 32; element (k, n) at j * 4096 + k * 128 + (((n % 32) / 4) ^ (k % 8)) * 16 + (n % 4) * 4.
+  for (int e = threadIdx.x; e < kStageK * BN; e += kGenericThreads) {
+    const int kk = e / BN, nn = e % BN;
+    const int gk = k0 + kk, gn = n0 + nn;
+    const float v = (gk < p.k && gn < p.n) ? __ldg(p.b + static_cast<int64_t>(gk) * p.ldb + gn) : 0.f;
+    const int j = nn >> 5, ni = nn & 31;
+    *reinterpret_cast<float*>(b_dst + j * kBBoxBytes + kk * 128 + (((ni >> 2) ^ (kk & 7)) << 4) + ((ni & 3) << 2)) = v;
+  }
+}
+
+template <int BN, bool kRelu>
+__global__ void __launch_bounds__(kGenericThreads) umma_generic_kernel(const __grid_constant__ UmmaParams p) {
+  constexpr int STAGES = 2;
+  extern __shared__ uint8_t smem_raw[];
+  const SmemCarve sm = carve<BN, STAGES>(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&sm.empty[s], 1);
+    mbar_init(&sm.acc_full[0], 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) {
+    tmem_alloc<tmem_columns<BN>()>(sm.tmem_ptr);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_ptr;
+
+  const int m0 = blockIdx.y * kTileM, n0 = blockIdx.x * BN;
+  const int k_blocks = (p.k + kStageK - 1) / kStageK;
+  bool ok = true;
+  for (int kb = 0; kb < k_blocks; ++kb) {
+    const int stage = kb & 1;
+    // MMAs that read this slab two iterations ago must be done.
+    if (kb >= 2) ok = mbar_wait(&sm.empty[stage], ((kb >> 1) - 1) & 1u, kSiteUmmaEmpty);
+    // The vote keeps the barrier below reachable by every thread.
+    if (!__syncthreads_and(ok)) { ok = false; break; }
+    uint8_t* a_dst = sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>();
+    fill_stage<BN>(p, a_dst, a_dst + kASlabBytes, m0, n0, kb * kStageK);
+    fence_proxy_async_smem();  // generic-proxy writes -> visible to the MMA unit
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      tcgen05_fence_after_sync();
+      issue_stage_mmas<BN>(tmem_base, smem_u32(a_dst), smem_u32(a_dst) + kASlabBytes, kb > 0 ? 1u : 0u);
+      umma_commit(&sm.empty[stage]);
+      if (kb == k_blocks - 1) umma_commit(&sm.acc_full[0]);
+    }
+  }
+  if (ok) ok = mbar_wait(&sm.acc_full[0], 0, kSiteUmmaAccFull);
+  if (ok) {
+    tcgen05_fence_after_sync();
+    epilogue_tile<BN, kRelu>(p, tmem_base, warp, lane, m0, n0);
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc<tmem_columns<BN>()>(tmem_base);
+  }
+}
+
+// ------------------------------------------------------------------ launchers
+
+bool aligned16(const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; }
+
+void fill_common(UmmaParams* p, const b200_gemm_problem& q) {
+  std::memset(p, 0, sizeof(*p));
+  p->a = q.a, p->b = q.b, p->d = q.d;
+  p->c = q.beta != 0.f ? q.c : nullptr;
+  p->lda = q.lda, p->ldb = q.ldb, p->ldc = q.ldc, p->ldd = q.ldd;
+  p->m = q.m, p->n = q.n, p->k = q.k;
+  p->alpha = q.alpha, p->beta = q.beta;
+  const bool c_ok = q.beta == 0.f || (aligned16(q.c) && q.ldc % 4 == 0);
+  p->vector_io = (q.n % 4 == 0 && aligned16(q.d) && q.ldd % 4 == 0 && c_ok) ? 1 : 0;
+}
+
+template <int BN, int STAGES, bool kRelu>
+int launch_tma(const b200_gemm_problem& q, cudaStream_t stream) {
+  auto kernel = umma_tma_kernel<BN, STAGES, kRelu>;
+  constexpr size_t smem = smem_bytes<BN, STAGES>();
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+    return B200_ERR_LAUNCH_FAILED;
+  }
+  UmmaParams p;
+  fill_common(&p, q);
+  if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
+      !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128B)) {
+    return B200_ERR_MISALIGNED_OPERAND;
+  }
+  const int sms = sm_count();
+  if (sms <= 0) return B200_ERR_INTERNAL;
+  const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + BN - 1) / BN);
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  kernel<<<grid, kTmaThreads, smem, stream>>>(p);
+  return launch_status();
+}
+
+template <int BN, bool kRelu>
+int launch_generic(const b200_gemm_problem& q, cudaStream_t stream) {
+  auto kernel = umma_generic_kernel<BN, kRelu>;
+  constexpr size_t smem = smem_bytes<BN, 2>();
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+    return B200_ERR_LAUNCH_FAILED;
+  }
+  UmmaParams p;
+  fill_common(&p, q);
+  const int64_t tiles_m = (q.m + kTileM - 1) / kTileM, tiles_n = (q.n + BN - 1) / BN;
+  if (tiles_m > 65535) return B200_ERR_INVALID_PROBLEM;
+  kernel<<<dim3(static_cast<unsigned>(tiles_n), static_cast<unsigned>(tiles_m)), kGenericThreads, smem, stream>>>(p);
+  return launch_status();
+}
+
+// ------------------------------------------------------------------- registry
+
+using LaunchFn = int (*)(const b200_gemm_problem&, cudaStream_t);
+
+struct RegistryEntry {
+  b200_tf32_kernel_meta meta;
+  LaunchFn launch;
+};
+
+constexpr b200_tf32_kernel_meta meta(int id, const char* name, const char* alias, int epilogue, int tile_n, int stages,
+                                     int alignment) {
+  return b200_tf32_kernel_meta{id,     name,       alias,     epilogue,  kTileM,    tile_n, kStageK,
+                               kTileM, tile_n,     kInstK,    stages,    alignment, alignment, alignment, 0};
+}
+
+// Dispatch order. The first eight entries carry the ids, alias names and the
+// order of the reference registry (csrc/adaptive_gemm/kernel_dispatch.cu:46-103,
+// parse_kernel in csrc/adaptive_gemm/adaptive_gemm.cu:61-97): "fast" entries
+// require 4-element alignment (here: the TMA loader), "fallback" entries accept
+// anything (here: the generic loader). What distinguished the reference's
+// variants (warp shape, stage count) maps onto tile width and pipeline depth.
+const RegistryEntry kRegistry[] = {
+    {meta(2, "umma128x128stage4tma", "fast", B200_EPILOGUE_LINEAR, 128, 4, 4), &launch_tma<128, 4, false>},
+    {meta(3, "umma128x128generic", "fallback", B200_EPILOGUE_LINEAR, 128, 2, 1), &launch_generic<128, false>},
+    {meta(4, "umma128x64stage4tma", "fast_mwarp", B200_EPILOGUE_LINEAR, 64, 4, 4), &launch_tma<64, 4, false>},
+    {meta(5, "umma128x64generic", "fallback_mwarp", B200_EPILOGUE_LINEAR, 64, 2, 1), &launch_generic<64, false>},
+    {meta(6, "umma128x128stage3tma", "fast_stage3", B200_EPILOGUE_LINEAR, 128, 3, 4), &launch_tma<128, 3, false>},
+    {meta(7, "umma128x128stage2tma", "fast_stage2", B200_EPILOGUE_LINEAR, 128, 2, 4), &launch_tma<128, 2, false>},
+    {meta(8, "umma128x128stage4tmaRelu", "fast_relu", B200_EPILOGUE_RELU, 128, 4, 4), &launch_tma<128, 4, true>},
+    {meta(9, "umma128x128genericRelu", "fallback_relu", B200_EPILOGUE_RELU, 128, 2, 1), &launch_generic<128, true>},
+    {meta(16, "umma128x256stage4tma", "wide", B200_EPILOGUE_LINEAR, 256, 4, 4), &launch_tma<256, 4, false>},
+    {meta(17, "umma128x256stage4tmaRelu", "wide_relu", B200_EPILOGUE_RELU, 256, 4, 4), &launch_tma<256, 4, true>},
+};
+constexpr int kRegistrySize = sizeof(kRegistry) / sizeof(kRegistry[0]);
+
+const RegistryEntry* find_entry(int id) {
+  for (const RegistryEntry& e : kRegistry)
+    if (e.meta.id == id) return &e;
+  return nullptr;
+}
+
+bool operand_aligned(const void* ptr, int64_t ld, int alignment_elements) {
+  if (alignment_elements <= 1) return true;
+  return reinterpret_cast<uintptr_t>(ptr) % (static_cast<uintptr_t>(alignment_elements) * sizeof(float)) == 0 &&
+         ld % alignment_elements == 0;
+}
+
+int check_problem(const b200_gemm_problem* q) {
+  if (q == nullptr || q->a == nullptr || q->b == nullptr || q->d == nullptr) return B200_ERR_INVALID_ARGUMENT;
+  if (q->m <= 0 || q->n <= 0 || q->k <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if (q->lda < q->k || q->ldb < q->n || q->ldd < q->n) return B200_ERR_INVALID_ARGUMENT;
+  if (q->beta != 0.f && (q->c == nullptr || q->ldc < q->n)) return B200_ERR_INVALID_ARGUMENT;
+  if (q->epilogue != B200_EPILOGUE_LINEAR && q->epilogue != B200_EPILOGUE_RELU) return B200_ERR_INVALID_ARGUMENT;
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" {
+
+int b200_tf32_registry_size(void) { return b200::kRegistrySize; }
+
+int b200_tf32_registry_entry(int index, b200_tf32_kernel_meta* out) {
+  if (index < 0 || index >= b200::kRegistrySize || out == nullptr) return B200_ERR_INVALID_ARGUMENT;
+  *out = b200::kRegistry[index].meta;
+  return B200_OK;
+}
+
+int b200_tf32_kernel_from_name(const char* name) {
+  if (name == nullptr) return -1;
+  if (std::strcmp(name, "auto") == 0) return B200_TF32_KERNEL_AUTO;
+  if (std::strcmp(name, "cublas") == 0) return B200_TF32_KERNEL_CUBLAS;
+  // The reference also accepts a capitalised spelling of the two ReLU kernels.
+  if (std::strcmp(name, "fast_Relu") == 0) name = "fast_relu";
+  if (std::strcmp(name, "fallback_Relu") == 0) name = "fallback_relu";
+  for (const b200::RegistryEntry& e : b200::kRegistry) {
+    if (std::strcmp(name, e.meta.alias) == 0 || std::strcmp(name, e.meta.name) == 0) return e.meta.id;
+  }
+  return -1;
+}
+
+int b200_tf32_can_implement(int kernel_id, const b200_gemm_problem* q) {
+  const b200::RegistryEntry* e = b200::find_entry(kernel_id);
+  if (e == nullptr) return B200_ERR_INVALID_ARGUMENT;
+  const int basic = b200::check_problem(q);
+  if (basic != B200_OK) return basic;
+  if (e->meta.epilogue != q->epilogue) return B200_ERR_NOT_SUPPORTED;
+  // Without a source the reference aliases C to D (adaptive_gemm.cu:152-154),
+  // so the source alignment test degenerates to the destination's.
+  const void* c_ptr = q->c != nullptr ? static_cast<const void*>(q->c) : static_cast<const void*>(q->d);
+  const int64_t ldc = q->c != nullptr ? q->ldc : q->ldd;
+  if (!b200::operand_aligned(q->a, q->lda, e->meta.alignment_a) ||
+      !b200::operand_aligned(q->b, q->ldb, e->meta.alignment_b) ||
+      !b200::operand_aligned(c_ptr, ldc, e->meta.alignment_c) ||
+      !b200::operand_aligned(q->d, q->ldd, e->meta.alignment_c)) {
+    return B200_ERR_MISALIGNED_OPERAND;
+  }
+  return B200_OK;
+}
+
+int b200_tf32_gemm_launch(int kernel_id, const b200_gemm_problem* q, b200_stream_t stream) {
+  const int status = b200_tf32_can_implement(kernel_id, q);
+  if (status != B200_OK) return status;
+  return b200::find_entry(kernel_id)->launch(*q, static_cast<cudaStream_t>(stream));
+}
+
+int b200_tf32_gemm_dispatch(int requested, const b200_gemm_problem* q, int* chosen, b200_stream_t stream) {
+  const int basic = b200::check_problem(q);
+  if (basic != B200_OK) return basic;
+  if (requested == B200_TF32_KERNEL_CUBLAS) return B200_ERR_INVALID_ARGUMENT;  // library baseline lives in the caller
+  for (const b200::RegistryEntry& e : b200::kRegistry) {
+    if (requested != B200_TF32_KERNEL_AUTO && e.meta.id != requested) continue;
+    const int status = b200_tf32_gemm_launch(e.meta.id, q, stream);
+    if (status == B200_OK) {
+      if (chosen != nullptr) *chosen = e.meta.id;
+      return B200_OK;
+    }
+    // Only "does not fit this kernel" moves on to the next entry; anything
+    // else is reported as is (kernel_dispatch.cu:125-132). An epilogue
+    // mismatch is a skipped entry in the reference, not an error.
+    if (status != B200_ERR_MISALIGNED_OPERAND && status != B200_ERR_INVALID_PROBLEM &&
+        status != B200_ERR_NOT_SUPPORTED) {
+      return status;
+    }
+  }
+  return B200_ERR_NOT_SUPPORTED;
+}
+
+}  // extern "C"

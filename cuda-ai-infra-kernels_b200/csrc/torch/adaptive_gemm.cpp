@@ -1,0 +1,141 @@
+// PyTorch-facing launcher of `cuda_ai_kernels.adaptive_gemm`:
+//   D = alpha * A @ B + beta * C, optionally followed by ReLU,
+// all operands row-major FP32, products on the tensor cores in TF32.
+// Validation order, accepted strings and error texts follow
+// csrc/adaptive_gemm/adaptive_gemm.cu:14-174; the kernel choice is delegated to
+// the registry behind b200_tf32_gemm_dispatch (first compatible entry wins).
+#include <ATen/cuda/CUDAContext.h>
+#include <cublas_v2.h>
+
+#include <limits>
+
+#include "op_common.h"
+#include "ops.h"
+
+namespace {
+
+using b200_torch::current_stream;
+
+thread_local std::string g_last_kernel;
+
+// Epilogue spellings the reference parses (adaptive_gemm.cu:39-59). Only the
+// first two have kernels; the rest are recognised so that they are refused
+// with the "supports only" message rather than as unknown strings.
+enum class ParsedEpilogue { kLinear, kRelu, kRecognisedButUnsupported };
+
+ParsedEpilogue parse_epilogue(const std::string& value) {
+  if (value == "linear") return ParsedEpilogue::kLinear;
+  if (value == "relu") return ParsedEpilogue::kRelu;
+  if (value == "bias" || value == "gelu" || value == "bias_relu" || value == "bias_gelu") {
+    return ParsedEpilogue::kRecognisedButUnsupported;
+  }
+  TORCH_CHECK(false, "unsupported epilogue: ", value);
+}
+
+int parse_kernel(const std::string& value) {
+  const int id = b200_tf32_kernel_from_name(value.c_str());
+  TORCH_CHECK(id >= 0, "unsupported adaptive_gemm kernel: ", value,
+              "; expected one of: auto, cublas, fast, fallback, fast_mwarp, "
+              "fallback_mwarp, fast_stage3, fast_stage2, fast_relu, fallback_relu");
+  return id;
+}
+
+void check_ab(const torch::Tensor& a, const torch::Tensor& b) {
+  B200_CHECK_INPUT(a);
+  B200_CHECK_INPUT(b);
+  B200_CHECK_FLOAT32(a);
+  B200_CHECK_FLOAT32(b);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "A and B must be 2D tensors");
+  TORCH_CHECK(a.size(1) == b.size(0), "Matrix multiplication shape mismatch: A has ", a.size(1),
+              " columns, but B has ", b.size(0), " rows");
+  TORCH_CHECK(a.device() == b.device(), "A and B must be on the same CUDA device");
+  TORCH_CHECK(a.size(0) > 0 && a.size(1) > 0 && b.size(1) > 0, "M, N, and K must be positive");
+  constexpr int64_t kIntMax = std::numeric_limits<int>::max();
+  TORCH_CHECK(a.size(0) <= kIntMax && a.size(1) <= kIntMax && b.size(1) <= kIntMax,
+              "M, N, and K must fit in the int32 problem size");
+}
+
+void check_source(const torch::Tensor& c, const torch::Tensor& a, int64_t m, int64_t n) {
+  B200_CHECK_INPUT(c);
+  B200_CHECK_FLOAT32(c);
+  TORCH_CHECK(c.device() == a.device(), "C must be on the same CUDA device as A");
+  TORCH_CHECK(c.dim() == 2, "C must be a 2D tensor");
+  TORCH_CHECK(c.size(0) == m && c.size(1) == n, "C must have shape [", m, ", ", n, "] but got ", c.sizes());
+}
+
+// Library baseline: cuBLAS with TF32 tensor-op math. The classic interface
+// updates its C operand in place, so a separate source is copied into D first
+// (csrc/adaptive_gemm/cublas_reference.cu:20-61).
+void launch_cublas_tf32(const b200_gemm_problem& q, cudaStream_t stream) {
+  if (q.beta != 0.f && q.c != q.d) {
+    const size_t bytes = static_cast<size_t>(q.m) * static_cast<size_t>(q.n) * sizeof(float);
+    const cudaError_t rc = cudaMemcpyAsync(q.d, q.c, bytes, cudaMemcpyDeviceToDevice, stream);
+    TORCH_CHECK(rc == cudaSuccess, "CUDA error: ", cudaGetErrorString(rc));
+  }
+  // Row-major D[M,N] is column-major D^T[N,M] = alpha * B^T * A^T + beta * D^T.
+  const cublasStatus_t rc =
+      cublasGemmEx(at::cuda::getCurrentCUDABlasHandle(), CUBLAS_OP_N, CUBLAS_OP_N, q.n, q.m, q.k, &q.alpha, q.b,
+                   CUDA_R_32F, static_cast<int>(q.ldb), q.a, CUDA_R_32F, static_cast<int>(q.lda), &q.beta, q.d,
+                   CUDA_R_32F, static_cast<int>(q.ldd), CUBLAS_COMPUTE_32F_FAST_TF32, CUBLAS_GEMM_DEFAULT_TENSOR_OP);
+  TORCH_CHECK(rc == CUBLAS_STATUS_SUCCESS, "cublasGemmEx failed with cuBLAS status ", static_cast<int>(rc));
+}
+
+const char* registry_name(int id) {
+  b200_tf32_kernel_meta meta;
+  for (int i = 0; i < b200_tf32_registry_size(); ++i) {
+    if (b200_tf32_registry_entry(i, &meta) == B200_OK && meta.id == id) return meta.name;
+  }
+  return "unknown";
+}
+
+}  // namespace
+
+std::string adaptive_gemm_last_kernel() { return g_last_kernel; }
+
+torch::Tensor adaptive_gemm(const torch::Tensor& a, const torch::Tensor& b, const c10::optional<at::Tensor>& c,
+                            const c10::optional<at::Tensor>& bias, double alpha, double beta,
+                            const std::string& epilogue, const std::string& kernel) {
+  check_ab(a, b);
+  const ParsedEpilogue parsed = parse_epilogue(epilogue);
+  const int requested = parse_kernel(kernel);
+  TORCH_CHECK(parsed != ParsedEpilogue::kRecognisedButUnsupported,
+              "adaptive_gemm currently supports only the linear and relu epilogues");
+  TORCH_CHECK(requested != B200_TF32_KERNEL_CUBLAS || parsed == ParsedEpilogue::kLinear,
+              "adaptive_gemm kernel='cublas' supports only the linear epilogue; "
+              "apply torch.relu to its output for an unfused ReLU baseline");
+  TORCH_CHECK(!(bias.has_value() && bias->defined()), "adaptive_gemm bias fusion is not implemented yet");
+
+  const int64_t m = a.size(0), n = b.size(1);
+  const bool has_c = c.has_value() && c->defined();
+  TORCH_CHECK(has_c || beta == 0.0, "C is required when beta is non-zero");
+  if (has_c) check_source(*c, a, m, n);
+
+  const c10::cuda::CUDAGuard guard(a.device());
+  auto d = torch::empty({m, n}, a.options());
+
+  b200_gemm_problem q{};
+  q.m = static_cast<int>(m), q.n = static_cast<int>(n), q.k = static_cast<int>(a.size(1));
+  q.a = a.data_ptr<float>(), q.b = b.data_ptr<float>(), q.d = d.data_ptr<float>();
+  // Without a source the destination stands in for it; beta is zero then, so
+  // it is never read (adaptive_gemm.cu:152-154).
+  q.c = has_c ? c->data_ptr<float>() : d.data_ptr<float>();
+  q.lda = a.stride(0), q.ldb = b.stride(0), q.ldd = d.stride(0);
+  q.ldc = has_c ? c->stride(0) : d.stride(0);
+  q.alpha = static_cast<float>(alpha), q.beta = static_cast<float>(beta);
+  q.epilogue = parsed == ParsedEpilogue::kRelu ? B200_EPILOGUE_RELU : B200_EPILOGUE_LINEAR;
+  constexpr int64_t kIntMax = std::numeric_limits<int>::max();
+  TORCH_CHECK(q.lda <= kIntMax && q.ldb <= kIntMax && q.ldc <= kIntMax && q.ldd <= kIntMax,
+              "leading dimension exceeds the int32 range");
+
+  if (requested == B200_TF32_KERNEL_CUBLAS) {
+    launch_cublas_tf32(q, static_cast<cudaStream_t>(current_stream(a)));
+    g_last_kernel = "cublas";
+    return d;
+  }
+
+  int chosen = -1;
+  const int status = b200_tf32_gemm_dispatch(requested, &q, &chosen, current_stream(a));
+  TORCH_CHECK(status == B200_OK, "adaptive GEMM dispatch failed: ", b200_status_string(status));
+  g_last_kernel = registry_name(chosen);
+  return d;
+}

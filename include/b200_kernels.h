@@ -1,0 +1,244 @@
+/*
+ * b200_kernels.h — C ABI of libb200_kernels.so.
+ *
+ * Hand-written sm_100a kernels for the operator set of the
+ * "cuda-ai-infra-kernels" project: the FP32 SIMT GEMM ladder, the TF32
+ * tensor-core GEMM with fused LinearCombination / ReLU epilogues and its
+ * compatibility registry, and the RMSNorm / softmax row operators.
+ *
+ * Conventions shared by every entry point
+ *   - plain pointers and sizes only; nothing in this header depends on PyTorch
+ *     or on the CUDA headers (a stream is passed as an opaque pointer that is
+ *     bit-identical to cudaStream_t);
+ *   - the caller has made the target device current; all pointers are device
+ *     pointers on that device unless a parameter says "host";
+ *   - work is enqueued on `stream` and the call returns without synchronising;
+ *     no entry point allocates or frees device memory, copies to the host or
+ *     synchronises, so every launch may be captured in a CUDA graph
+ *     (b200_device_status_read is the one exception and says so);
+ *   - the return value is a b200_status; nothing throws;
+ *   - inputs are never written.
+ *
+ * Each declaration names the reference interface it stands in for
+ * (path:line inside the cuda-ai-infra-kernels source tree).
+ */
+#ifndef B200_KERNELS_H_
+#define B200_KERNELS_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* b200_stream_t; /* cudaStream_t */
+
+/* ------------------------------------------------------------------ status */
+
+/*
+ * Status codes. The adaptive dispatcher of the reference walks its registry
+ * and moves on to the next entry only for "misaligned operand" and "invalid
+ * problem" (csrc/adaptive_gemm/kernel_dispatch.cu:125-132); the same two
+ * codes exist here with the same meaning, and the string forms match
+ * cutlassGetStatusString for the three codes the reference can surface
+ * (csrc/adaptive_gemm/adaptive_gemm.cu:169-172).
+ */
+typedef enum b200_status {
+  B200_OK = 0,
+  B200_ERR_MISALIGNED_OPERAND = 1,
+  B200_ERR_INVALID_PROBLEM = 2,
+  B200_ERR_NOT_SUPPORTED = 3,
+  B200_ERR_INVALID_ARGUMENT = 4,
+  B200_ERR_LAUNCH_FAILED = 5,
+  B200_ERR_DEVICE_TIMEOUT = 6,
+  B200_ERR_INTERNAL = 7
+} b200_status;
+
+/* Human-readable form of a status code (never NULL). */
+const char* b200_status_string(int status);
+
+/* Library version and the architecture the kernels were compiled for. */
+const char* b200_build_info(void);
+
+/*
+ * Every device-side wait in this library (mbarrier phases fed by TMA or by
+ * tcgen05.commit) is bounded. A kernel whose wait ran out records a non-zero
+ * word and returns instead of spinning. This call copies the word of the
+ * current device to *host_word and clears it. It synchronises `stream` and is
+ * therefore NOT capturable; call it from tests and after failures, not per
+ * launch. No reference counterpart (the reference has no device-side waits).
+ */
+int b200_device_status_read(uint32_t* host_word, b200_stream_t stream);
+
+/* ----------------------------------------------------- FP32 SIMT GEMM ladder */
+
+/*
+ * Ladder entries. C[M,N] = A[M,K] * B[K,N] in FP32 on the FMA pipe.
+ * A is logical [M,K] stored column-major (element (m,k) at A[k*M + m], i.e.
+ * a contiguous [K,M] array), B is row-major [K,N], C is row-major [M,N]
+ * (csrc/gemm/gemm_layout.h:5-9). Full tiles only: M % bm == 0, N % bn == 0,
+ * K % bk == 0 with (bm,bn,bk) from b200_sgemm_tile, all positive.
+ *
+ * ids 0..12 are the thirteen hand-written stages of the reference in ladder
+ * order (python/cuda_ai_kernels/gemm_stages.py:4-19; launchers declared in
+ * csrc/gemm/gemm.h:9-27).
+ */
+typedef enum b200_sgemm_impl {
+  B200_SGEMM_NAIVE = 0,                  /* gemm_naive            csrc/gemm/gemm_naive.cu:36-46 */
+  B200_SGEMM_BLOCK_TILE = 1,             /* gemm_block_tile       csrc/gemm/gemm_block_tile.cu:38-48 */
+  B200_SGEMM_BLOCK_TILE_F4_16x16 = 2,    /* gemm_block_tile_float4_16x16  gemm_block_tile_float4.cu:38-59 */
+  B200_SGEMM_BLOCK_TILE_F4_16x32 = 3,    /* gemm_block_tile_float4_16x32 */
+  B200_SGEMM_BLOCK_TILE_F4_32x32 = 4,    /* gemm_block_tile_float4_32x32 */
+  B200_SGEMM_THREAD_TILE_4x4 = 5,        /* gemm_thread_tile_4x4  csrc/gemm/gemm_thread_tile.cu:77-104 */
+  B200_SGEMM_THREAD_TILE_4x8 = 6,        /* gemm_thread_tile_4x8 */
+  B200_SGEMM_THREAD_TILE_8x8 = 7,        /* gemm_thread_tile_8x8 */
+  B200_SGEMM_THREAD_TILE_8x8_WARP4x8 = 8,/* gemm_thread_tile_8x8_warp4x8 */
+  B200_SGEMM_WARP_TILE = 9,              /* gemm_warp_tile        csrc/gemm/gemm_warp_tile.cu:108-119 */
+  B200_SGEMM_PREFETCH_SMEM = 10,         /* gemm_prefetchSmem     csrc/gemm/gemm_prefetchSmem.cu:176-199 */
+  B200_SGEMM_PREFETCH_REG = 11,          /* gemm_prefetchReg      csrc/gemm/gemm_prefetchRegister.cu:197-220 */
+  B200_SGEMM_SPLIT_K = 12,               /* gemm_splictK          csrc/gemm/gemm_splictK.cu:185-209 */
+  B200_SGEMM_IMPL_COUNT = 13
+} b200_sgemm_impl;
+
+/* Ladder name ("naive", "block_tile", ..., "split_k") or NULL. */
+const char* b200_sgemm_impl_name(int impl);
+/* Inverse of b200_sgemm_impl_name; -1 when unknown. */
+int b200_sgemm_impl_from_name(const char* name);
+
+/*
+ * Tile multiples an entry requires, and whether it needs 16-byte aligned A
+ * and B (all but naive and block_tile). Mirrors the (BM,BN,BK) column of
+ * python/cuda_ai_kernels/gemm_stages.py:4-19 and the `vectorized` flag of
+ * check_regular_gemm_inputs (csrc/gemm/gemm_regular.cuh:10-26).
+ */
+int b200_sgemm_tile(int impl, int* bm, int* bn, int* bk, int* needs_16b_alignment);
+
+/*
+ * Host-only validation in the order of csrc/gemm/gemm_regular.cuh:15-25:
+ * positive sizes -> B200_ERR_INVALID_ARGUMENT, divisibility or grid limit ->
+ * B200_ERR_INVALID_PROBLEM, pointer alignment -> B200_ERR_MISALIGNED_OPERAND.
+ * Does not touch the GPU.
+ */
+int b200_sgemm_check(int impl, const void* a, const void* b,
+                     int64_t m, int64_t n, int64_t k);
+
+/*
+ * Launch one ladder entry. For B200_SGEMM_SPLIT_K the output is cleared on
+ * `stream` inside the call before the K slices are reduced into it, which is
+ * what the reference does with torch::zeros (csrc/gemm/gemm_splictK.cu:201-202).
+ */
+int b200_sgemm(int impl, const float* a_colmajor, const float* b, float* c,
+               int m, int n, int k, b200_stream_t stream);
+
+/* ------------------------------------------- TF32 tensor-core GEMM + epilogue */
+
+/* Epilogues of csrc/adaptive_gemm/gemm_problem.h:6-15 that have kernels. */
+typedef enum b200_epilogue {
+  B200_EPILOGUE_LINEAR = 0, /* D = alpha * A*B + beta * C           */
+  B200_EPILOGUE_RELU = 1    /* D = max(0, alpha * A*B + beta * C)   */
+} b200_epilogue;
+
+/*
+ * Problem description: the POD part of GemmProblem + EpilogueDesc
+ * (csrc/adaptive_gemm/gemm_problem.h:17-57). All matrices are row-major FP32:
+ * A [M,K] with leading dimension lda, B [K,N] ldb, C [M,N] ldc (source, read
+ * only, never dereferenced when beta == 0), D [M,N] ldd (destination).
+ */
+typedef struct b200_gemm_problem {
+  int m, n, k;
+  const float* a;
+  const float* b;
+  const float* c;
+  float* d;
+  int64_t lda, ldb, ldc, ldd;
+  float alpha, beta;
+  int epilogue; /* b200_epilogue */
+} b200_gemm_problem;
+
+/*
+ * Registry record: KernelEntry + KernelMeta of
+ * csrc/adaptive_gemm/kernel_entry.h:7-61. `id` values 2..9 are the reference's
+ * KernelId enumerators in declaration order (0 = Auto, 1 = Cublas); ids >= 16
+ * are configurations that exist only here.
+ */
+typedef struct b200_tf32_kernel_meta {
+  int id;
+  const char* name;       /* registry name string */
+  const char* alias;      /* name accepted by the kernel= argument */
+  int epilogue;           /* b200_epilogue */
+  int tile_m, tile_n, tile_k;   /* CTA tile (tile_k = one pipeline stage of K) */
+  int inst_m, inst_n, inst_k;   /* tcgen05.mma instruction shape */
+  int stages;                   /* shared-memory pipeline depth */
+  int alignment_a, alignment_b, alignment_c; /* in elements: 4 = TMA path, 1 = any */
+  int supports_split_k;
+} b200_tf32_kernel_meta;
+
+enum { B200_TF32_KERNEL_AUTO = 0, B200_TF32_KERNEL_CUBLAS = 1 };
+
+/* Number of registry entries, in dispatch order (kKernelRegistry, kernel_dispatch.cu:46-103). */
+int b200_tf32_registry_size(void);
+/* Fill *out with entry `index`. */
+int b200_tf32_registry_entry(int index, b200_tf32_kernel_meta* out);
+/* Kernel id for a kernel= string (parse_kernel, adaptive_gemm.cu:61-97); -1 when unknown. */
+int b200_tf32_kernel_from_name(const char* name);
+
+/*
+ * Host-only compatibility test of one registry entry against a problem:
+ * epilogue kind, then pointer / leading-dimension alignment exactly as
+ * is_aligned / is_compatible do (kernel_dispatch.cu:13-44). Returns B200_OK,
+ * B200_ERR_MISALIGNED_OPERAND, B200_ERR_INVALID_PROBLEM or
+ * B200_ERR_NOT_SUPPORTED (epilogue mismatch). Does not touch the GPU.
+ */
+int b200_tf32_can_implement(int kernel_id, const b200_gemm_problem* problem);
+
+/* Launch exactly one registry entry (launch_gemm<Gemm>, kernel_launcher.h:7-29). */
+int b200_tf32_gemm_launch(int kernel_id, const b200_gemm_problem* problem,
+                          b200_stream_t stream);
+
+/*
+ * First-compatible-wins dispatch in registry order (dispatch_gemm,
+ * kernel_dispatch.cu:107-136). `requested` is B200_TF32_KERNEL_AUTO or a
+ * registry id. On success *chosen (may be NULL) receives the id that ran.
+ */
+int b200_tf32_gemm_dispatch(int requested, const b200_gemm_problem* problem,
+                            int* chosen, b200_stream_t stream);
+
+/* ------------------------------------------------------------ row operators */
+
+typedef enum b200_rmsnorm_impl {
+  B200_RMSNORM_NAIVE = 0,   /* rmsnorm_naive    csrc/rmsnorm/rmsnorm_naive.cu:94-109 */
+  B200_RMSNORM_CACHE_X = 1  /* rmsnorm_cache_x  csrc/rmsnorm/rmsnorm_cache_x.cu:97-117 */
+} b200_rmsnorm_impl;
+
+/*
+ * y[r,:] = x[r,:] * w * rsqrt(mean(x[r,:]^2) + eps), FP32, x and y row-major
+ * [rows, hidden], w [hidden]. Both impl ids run single-pass kernels that read x
+ * once; B200_RMSNORM_CACHE_X keeps the reference's limit of hidden <= 4096
+ * (rmsnorm_cache_x.cu:110-115) and returns B200_ERR_NOT_SUPPORTED beyond it.
+ */
+int b200_rmsnorm(int impl, const float* x, const float* weight, float* y,
+                 int64_t rows, int64_t hidden, double eps, b200_stream_t stream);
+
+typedef enum b200_softmax_impl {
+  B200_SOFTMAX_NAIVE = 0    /* softmax_naive    csrc/softmax/softmax.cu:124-133 */
+} b200_softmax_impl;
+
+/* y[r,:] = softmax(x[r,:]) over the last dimension, FP32, row-major [rows, cols]. */
+int b200_softmax(int impl, const float* x, float* y,
+                 int64_t rows, int64_t cols, b200_stream_t stream);
+
+/* ------------------------------------------------------ M-sharded large GEMM */
+
+/*
+ * Row partition of an M-row GEMM over `parts` devices: part p owns rows
+ * [row_begin[p], row_begin[p] + row_count[p]). Counts are multiples of
+ * `granule` (the CTA tile height) except possibly the last non-empty part.
+ * Host-only. The reference is single-GPU (README.md:34); this is new.
+ */
+int b200_shard_rows(int64_t m, int parts, int granule,
+                    int64_t* row_begin, int64_t* row_count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_KERNELS_H_ */

@@ -1,0 +1,297 @@
+"""The operator API (`cuda_ai_kernels.gemm / adaptive_gemm / rmsnorm / softmax`)
+on a GPU: error contract, stream and device behaviour, CUDA-graph capture. The
+cases follow the reference suite (tests/test_gemm.py, test_gemm_prefetch_smem.py,
+test_gemm_split_k.py, test_adaptive_gemm.py) so that a user switching over sees
+the same acceptances, refusals and messages."""
+import pytest
+import torch
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+from cuda_ai_kernels.gemm_stages import GEMM_STAGES  # noqa: E402
+
+REGULAR = [name for stage, name, _ in GEMM_STAGES if stage <= 5] + ["thread_tile"]
+VECTOR = [name for stage, name, _ in GEMM_STAGES if 3 <= stage <= 5]
+NAMED = ["prefetch_smem", "prefetch_reg", "split_k"]
+ALL_LADDER = REGULAR + NAMED
+
+
+def gemm(*args, **kwargs):
+    import cuda_ai_kernels
+
+    return cuda_ai_kernels.gemm(*args, **kwargs)
+
+
+def adaptive_gemm(*args, **kwargs):
+    import cuda_ai_kernels
+
+    return cuda_ai_kernels.adaptive_gemm(*args, **kwargs)
+
+
+def ladder_inputs(m=128, n=128, k=32):
+    return torch.randn(k, m, device="cuda").t(), torch.randn(k, n, device="cuda")
+
+
+def test_native_module_is_the_one_in_tree():
+    from cuda_ai_kernels import _C
+    from conftest import PACKAGE
+
+    assert str(PACKAGE) in _C.__file__
+
+
+@pytest.mark.parametrize("impl", ALL_LADDER + ["cublas"])
+def test_gemm_matches_fp64(impl):
+    torch.manual_seed(7)
+    a, b = ladder_inputs(256, 384, 80)
+    out = gemm(a, b, impl=impl)
+    assert out.shape == (256, 384) and out.is_contiguous() and out.dtype == torch.float32 and out.device == a.device
+    torch.testing.assert_close(out.cpu(), oracle.gemm_fp64(a, b), atol=1e-3, rtol=1e-3)
+
+
+def test_unknown_impl_is_a_value_error():
+    a, b = ladder_inputs()
+    with pytest.raises(ValueError, match="unknown GEMM impl"):
+        gemm(a, b, impl="nope")
+    import cuda_ai_kernels
+
+    with pytest.raises(ValueError, match="unknown RMSNorm impl"):
+        cuda_ai_kernels.rmsnorm(torch.zeros(2, 8, device="cuda"), torch.zeros(8, device="cuda"), impl="nope")
+    with pytest.raises(ValueError, match="unknown softmax impl"):
+        cuda_ai_kernels.softmax(torch.zeros(2, 8, device="cuda"), impl="nope")
+
+
+@pytest.mark.parametrize("impl", REGULAR)
+@pytest.mark.parametrize("bad", ["row_major_a", "column_major_b", "partial_m", "partial_n", "empty_k"])
+def test_regular_stages_reject_bad_inputs(impl, bad):
+    m = 127 if bad == "partial_m" else 128
+    n = 127 if bad == "partial_n" else 128
+    k = 0 if bad == "empty_k" else 16
+    a = torch.empty(k, m, device="cuda").t()
+    b = torch.empty(k, n, device="cuda")
+    if bad == "row_major_a":
+        a = a.contiguous()
+    if bad == "column_major_b":
+        b = b.t().contiguous().t()
+    with pytest.raises(RuntimeError):
+        gemm(a, b, impl=impl)
+
+
+@pytest.mark.parametrize("impl", [i for i in REGULAR if i != "naive"])
+def test_regular_stages_reject_partial_k(impl):
+    with pytest.raises(RuntimeError, match="divisible"):
+        gemm(torch.empty(7, 128, device="cuda").t(), torch.empty(7, 128, device="cuda"), impl=impl)
+
+
+@pytest.mark.parametrize("impl", VECTOR + NAMED)
+@pytest.mark.parametrize("operand", ["a", "b"])
+def test_vectorised_stages_reject_misaligned_storage(impl, operand):
+    a, b = ladder_inputs(128, 128, 16)
+    shifted = torch.empty(16 * 128 + 1, device="cuda")[1:].view(16, 128)
+    if operand == "a":
+        a = shifted.t()
+    else:
+        b = shifted
+    with pytest.raises(RuntimeError, match="16-byte aligned"):
+        gemm(a, b, impl=impl)
+
+
+@pytest.mark.parametrize("impl", NAMED)
+@pytest.mark.parametrize("case,message", [
+    ("row_a", "column-major"), ("column_b", "row-major"), ("dtype", "float32"), ("rank", "2D"),
+    ("shape", "shape mismatch"), ("zero_m", "positive"), ("partial_m", "divisible"), ("partial_k", "divisible"),
+])
+def test_named_stages_report_the_first_violated_rule(impl, case, message):
+    a, b = ladder_inputs(128, 128, 32)
+    if case == "row_a":
+        a = a.contiguous()
+    elif case == "column_b":
+        b = b.t().contiguous().t()
+    elif case == "dtype":
+        a = a.half()
+    elif case == "rank":
+        a = a.unsqueeze(0)
+    elif case == "shape":
+        b = b[:-1]
+    elif case == "zero_m":
+        a, b = ladder_inputs(0, 128, 32)
+    elif case == "partial_m":
+        a, b = ladder_inputs(127, 128, 32)
+    elif case == "partial_k":
+        a, b = ladder_inputs(128, 128, 36)
+    with pytest.raises(RuntimeError, match=message):
+        gemm(a, b, impl=impl)
+
+
+@pytest.mark.parametrize("k", [8, 24, 40])
+def test_split_k_rejects_k_that_cannot_be_halved_into_eights(k):
+    a, b = ladder_inputs(128, 128, k)
+    with pytest.raises(RuntimeError, match="divisible"):
+        gemm(a, b, impl="split_k")
+
+
+@pytest.mark.parametrize("impl", NAMED + ["cublas"])
+def test_aligned_storage_offsets_are_accepted(impl):
+    a = torch.randn(128 * 32 + 4, device="cuda")[4:].view(32, 128).t()
+    b = torch.randn(32 * 128 + 4, device="cuda")[4:].view(32, 128)
+    torch.testing.assert_close(gemm(a, b, impl=impl).cpu(), oracle.gemm_fp64(a, b), atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("impl", ALL_LADDER + ["cublas"])
+def test_work_is_enqueued_on_the_current_stream(impl):
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        a, b = ladder_inputs(128, 256, 48)
+        # A long-running producer ahead of the fills: a launch on any other
+        # stream would read the tensors before they are written.
+        torch.cuda._sleep(5_000_000)
+        a.fill_(2)
+        b.fill_(3)
+        out = gemm(a, b, impl=impl).clone()
+    stream.synchronize()
+    torch.testing.assert_close(out, torch.full_like(out, 288), atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("impl", ALL_LADDER)
+def test_cuda_graph_capture_and_replay(impl):
+    a = torch.ones(16, 128, device="cuda").t()
+    b = torch.ones(16, 256, device="cuda")
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        gemm(a, b, impl=impl)
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        out = gemm(a, b, impl=impl)
+    for value in (2.0, 3.0):
+        a.fill_(value)
+        graph.replay()
+        torch.cuda.synchronize()
+        torch.testing.assert_close(out, torch.full_like(out, value * 16), atol=0, rtol=0)
+
+
+def test_split_k_output_is_cleared_even_when_the_allocator_recycles_storage():
+    a, b = ladder_inputs(128, 256, 32)
+    b.fill_(1)
+    for value in (2, 0, 3, 0):
+        a.fill_(value)
+        out = gemm(a, b, impl="split_k")
+        torch.testing.assert_close(out, torch.full_like(out, value * 32), atol=0, rtol=0)
+        out.fill_(12345)
+        del out
+
+
+def test_cublas_baseline_stays_fp32_when_tf32_is_enabled():
+    a, b = ladder_inputs(128, 128, 24)
+    a.fill_(1.0001)
+    b.fill_(1)
+    previous = torch.backends.cuda.matmul.allow_tf32
+    try:
+        torch.backends.cuda.matmul.allow_tf32 = True
+        torch.testing.assert_close(gemm(a, b, impl="cublas").cpu(), oracle.gemm_fp64(a, b), atol=1e-5, rtol=1e-6)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = previous
+
+
+@pytest.mark.parametrize("shape", [(64, 64, 64), (128, 96, 64), (33, 65, 17)])
+def test_cublas_accepts_row_major_a_and_any_shape(shape):
+    m, n, k = shape
+    torch.manual_seed(0)
+    a, b = torch.randn(m, k, device="cuda"), torch.randn(k, n, device="cuda")
+    torch.testing.assert_close(gemm(a, b, impl="cublas").cpu(), oracle.gemm_fp64(a, b), atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("impl", ["tensor_core", "cutlass"])
+@pytest.mark.parametrize("shape", [(64, 64, 64), (128, 96, 64), (33, 65, 17), (1024, 1024, 1024)])
+def test_row_major_tf32_side_entries(impl, shape):
+    m, n, k = shape
+    torch.manual_seed(0)
+    a, b = torch.randn(m, k, device="cuda"), torch.randn(k, n, device="cuda")
+    torch.testing.assert_close(gemm(a, b, impl=impl).cpu(), oracle.gemm_fp64(a, b), atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("impl", NAMED + ["cublas"])
+def test_inputs_on_another_device_are_honoured(impl):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    a = torch.randn(32, 128, device="cuda:1").t()
+    b = torch.randn(32, 128, device="cuda:1")
+    with torch.cuda.device(0):
+        out = gemm(a, b, impl=impl)
+        assert torch.cuda.current_device() == 0
+    assert out.device == a.device
+    torch.testing.assert_close(out.cpu(), oracle.gemm_fp64(a, b), atol=1e-3, rtol=1e-3)
+
+
+# ------------------------------------------------------------- adaptive_gemm
+
+@pytest.mark.parametrize("kernel", ["fast", "fast_mwarp", "fast_stage3", "fast_stage2"])
+@pytest.mark.parametrize("shape", [(33, 65, 20), (33, 68, 17)])
+def test_forced_fast_kernels_refuse_misaligned_shapes(kernel, shape):
+    m, n, k = shape
+    a, b = torch.randn(m, k, device="cuda"), torch.randn(k, n, device="cuda")
+    with pytest.raises(RuntimeError, match="adaptive GEMM dispatch failed"):
+        adaptive_gemm(a, b, kernel=kernel)
+
+
+@pytest.mark.parametrize("kernel,epilogue", [("fast", "relu"), ("fallback", "relu"), ("fast_relu", "linear"),
+                                             ("fallback_relu", "linear")])
+def test_kernel_and_epilogue_must_agree(kernel, epilogue):
+    eye = torch.eye(4, device="cuda")
+    with pytest.raises(RuntimeError, match="adaptive GEMM dispatch failed"):
+        adaptive_gemm(eye, eye, epilogue=epilogue, kernel=kernel)
+
+
+def test_adaptive_argument_errors():
+    eye = torch.eye(4, device="cuda")
+    with pytest.raises(RuntimeError, match="unsupported adaptive_gemm kernel"):
+        adaptive_gemm(eye, eye, kernel="unknown")
+    with pytest.raises(RuntimeError, match="float32"):
+        adaptive_gemm(eye.half(), eye.half())
+    with pytest.raises(RuntimeError, match="supports only the linear epilogue"):
+        adaptive_gemm(eye, eye, epilogue="relu", kernel="cublas")
+    with pytest.raises(RuntimeError, match="C is required"):
+        adaptive_gemm(eye, eye, beta=1.0, epilogue="relu")
+    with pytest.raises(RuntimeError, match="supports only the linear and relu"):
+        adaptive_gemm(eye, eye, epilogue="gelu")
+    with pytest.raises(RuntimeError, match="unsupported epilogue"):
+        adaptive_gemm(eye, eye, epilogue="swish")
+    with pytest.raises(RuntimeError, match="bias fusion is not implemented"):
+        adaptive_gemm(eye, eye, bias=torch.zeros(4, device="cuda"))
+    with pytest.raises(RuntimeError, match="C must have shape"):
+        adaptive_gemm(eye, eye, c=torch.zeros(4, 5, device="cuda"), beta=1.0)
+
+
+@pytest.mark.parametrize("kernel", ["auto", "cublas", "fast", "fallback"])
+def test_adaptive_alpha_beta_matches_oracle(kernel):
+    torch.manual_seed(0)
+    m, n, k = (64, 68, 36) if kernel == "fast" else (65, 67, 33)
+    a, b, c = torch.randn(m, k, device="cuda"), torch.randn(k, n, device="cuda"), torch.randn(m, n, device="cuda")
+    before = c.clone()
+    out = adaptive_gemm(a, b, c=c, alpha=0.75, beta=0.25, kernel=kernel)
+    torch.testing.assert_close(out.cpu(), oracle.adaptive_gemm_fp64(a, b, c, 0.75, 0.25), atol=3e-2, rtol=3e-2)
+    assert torch.equal(c, before)
+
+
+def test_auto_dispatch_reports_the_first_compatible_entry():
+    from cuda_ai_kernels import _C
+
+    a, b = torch.randn(128, 64, device="cuda"), torch.randn(64, 128, device="cuda")
+    adaptive_gemm(a, b)
+    assert "tma" in _C.adaptive_gemm_last_kernel()
+    adaptive_gemm(torch.randn(33, 17, device="cuda"), torch.randn(17, 65, device="cuda"))
+    assert "generic" in _C.adaptive_gemm_last_kernel()
+    adaptive_gemm(a, b, epilogue="relu")
+    assert _C.adaptive_gemm_last_kernel().endswith("Relu")
+
+
+def test_rope_and_attention_decode_are_declared_but_refuse():
+    import cuda_ai_kernels
+
+    x = torch.zeros(2, 4, device="cuda")
+    with pytest.raises(RuntimeError, match="planned for v0.2"):
+        cuda_ai_kernels.rope(x, x, x)
+    with pytest.raises(RuntimeError, match="planned for v0.3"):
+        cuda_ai_kernels.attention_decode(x, x, x)

@@ -1,0 +1,175 @@
+"""Parity of the tcgen05 TF32 GEMM + fused epilogue with the CPU oracle, through
+the C ABI. Tolerances: relative Frobenius error <= 5e-3 (north star) and the
+reference suite's atol = rtol = 3e-2; exact for inputs that TF32 represents
+exactly (small integers), which is what checks the shared-memory descriptors,
+the swizzled layouts and the TMEM addressing element by element."""
+import ctypes
+
+import pytest
+import torch
+
+from conftest import GemmProblem, KernelMeta, assert_device_clean, current_stream_ptr
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+LINEAR, RELU = 0, 1
+
+
+def registry(abi):
+    out = []
+    for i in range(abi.b200_tf32_registry_size()):
+        meta = KernelMeta()
+        abi.b200_tf32_registry_entry(i, ctypes.byref(meta))
+        out.append((meta.id, meta.alias.decode(), meta.epilogue, meta.alignment_a))
+    return out
+
+
+def run(abi, kernel_id, a, b, c=None, alpha=1.0, beta=0.0, epilogue=LINEAR, dispatch=False):
+    m, k = a.shape
+    n = b.shape[1]
+    d = torch.full((m, n), float("nan"), device=a.device)
+    q = GemmProblem(m, n, k, a.data_ptr(), b.data_ptr(), c.data_ptr() if c is not None else None, d.data_ptr(),
+                    a.stride(0), b.stride(0), c.stride(0) if c is not None else n, d.stride(0), alpha, beta, epilogue)
+    if dispatch:
+        chosen = ctypes.c_int(-1)
+        status = abi.b200_tf32_gemm_dispatch(kernel_id, ctypes.byref(q), ctypes.byref(chosen), current_stream_ptr())
+        return status, d, chosen.value
+    status = abi.b200_tf32_gemm_launch(kernel_id, ctypes.byref(q), current_stream_ptr())
+    return status, d, kernel_id
+
+
+def check(actual, expected):
+    assert oracle.rel_frobenius(actual, expected) <= oracle.TF32_REL_FROBENIUS
+    torch.testing.assert_close(actual.cpu(), expected, atol=3e-2, rtol=3e-2)
+
+
+def entries(align=None, epilogue=None):
+    import conftest
+
+    lib = conftest.load_abi()
+    return [e for e in registry(lib) if (align is None or e[3] == align) and (epilogue is None or e[2] == epilogue)]
+
+
+@pytest.mark.parametrize("entry", entries(), ids=lambda e: e[1])
+@pytest.mark.parametrize("shape", [(128, 128, 32), (128, 256, 64), (256, 512, 96), (384, 320, 160)])
+def test_integer_inputs_are_reproduced_exactly(abi, entry, shape):
+    # Values in [-4, 4] are exact in TF32 and every partial sum is exact in
+    # FP32, so any element that comes from the wrong (m, k) or (k, n) shows.
+    kernel_id, _, epilogue, _ = entry
+    m, n, k = shape
+    g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
+    a = torch.randint(-4, 5, (m, k), generator=g).float()
+    b = torch.randint(-4, 5, (k, n), generator=g).float()
+    status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), epilogue=epilogue)
+    assert status == 0, abi.b200_status_string(status)
+    expected = oracle.adaptive_gemm_fp64(a, b, epilogue="relu" if epilogue == RELU else "linear")
+    torch.testing.assert_close(d.cpu(), expected, atol=0, rtol=0)
+    assert_device_clean(abi)
+
+
+@pytest.mark.parametrize("entry", entries(), ids=lambda e: e[1])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (33, 68, 20), (200, 264, 1000), (1024, 1024, 1024)])
+def test_aligned_shapes_match_oracle(abi, entry, shape):
+    kernel_id, _, epilogue, _ = entry
+    a, b, c = oracle.adaptive_inputs(*shape)
+    status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c.cuda(), alpha=1.0, beta=0.5, epilogue=epilogue)
+    assert status == 0, abi.b200_status_string(status)
+    check(d, oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, "relu" if epilogue == RELU else "linear"))
+    assert_device_clean(abi)
+
+
+@pytest.mark.parametrize("entry", entries(align=1), ids=lambda e: e[1])
+@pytest.mark.parametrize("shape", [(33, 65, 17), (1, 1, 1), (33, 65, 20), (33, 68, 17), (130, 259, 70), (5, 300, 33)])
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (0.75, 0.25), (-0.5, 1.0), (0.0, -1.0)])
+def test_generic_loader_takes_any_shape(abi, entry, shape, alpha, beta):
+    kernel_id, _, epilogue, _ = entry
+    a, b, c = oracle.adaptive_inputs(*shape)
+    c_dev = c.cuda() if beta else None
+    status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c_dev, alpha, beta, epilogue)
+    assert status == 0, abi.b200_status_string(status)
+    expected = oracle.adaptive_gemm_fp64(a, b, c, alpha, beta, "relu" if epilogue == RELU else "linear")
+    torch.testing.assert_close(d.cpu(), expected, atol=3e-2, rtol=3e-2)
+    if epilogue == RELU:
+        assert bool((d >= 0).all())
+    assert_device_clean(abi)
+
+
+@pytest.mark.parametrize("entry", entries(align=4), ids=lambda e: e[1])
+@pytest.mark.parametrize("shape", [(33, 65, 20), (33, 68, 17)])
+def test_tma_entries_refuse_misaligned_shapes(abi, entry, shape):
+    a, b, _ = oracle.adaptive_inputs(*shape)
+    status, _, _ = run(abi, entry[0], a.cuda(), b.cuda(), epilogue=entry[2])
+    assert status == 1  # misaligned operand
+
+
+def test_misaligned_pointer_falls_through_to_the_generic_loader(abi):
+    a, b, _ = oracle.adaptive_inputs(128, 128, 64)
+    a_dev = torch.empty(128 * 64 + 1, device="cuda")[1:].view(128, 64).copy_(a)
+    status, d, chosen = run(abi, 0, a_dev, b.cuda(), dispatch=True)
+    assert status == 0 and chosen == 3
+    check(d, oracle.adaptive_gemm_fp64(a, b))
+
+
+@pytest.mark.parametrize("kernel", [0, 8, 9])
+def test_relu_is_applied_after_scale_and_source_add(abi, kernel):
+    a = torch.eye(4, device="cuda")
+    b = torch.tensor([[-2.0, -1.0, 1.0, 2.0]], device="cuda").repeat(4, 1)
+    c = torch.tensor([[-2.0, -2.0, 2.0, 2.0]], device="cuda").repeat(4, 1)
+    status, d, _ = run(abi, kernel, a, b, c, alpha=-1.0, beta=1.0, epilogue=RELU, dispatch=True)
+    assert status == 0
+    expected = torch.tensor([[0.0, 0.0, 1.0, 0.0]], device="cuda").repeat(4, 1)
+    torch.testing.assert_close(d, expected, atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("kernel", [0, 8, 9])
+def test_beta_zero_never_reads_the_source(abi, kernel):
+    a = torch.eye(4, device="cuda")
+    b = torch.tensor([[-2.0, -1.0, 1.0, 2.0]], device="cuda").repeat(4, 1)
+    c = torch.full((4, 4), float("nan"), device="cuda")
+    status, d, _ = run(abi, kernel, a, b, c, beta=0.0, epilogue=RELU, dispatch=True)
+    assert status == 0
+    torch.testing.assert_close(d, b.relu(), atol=0, rtol=0)
+
+
+def test_auto_dispatch_order(abi):
+    a, b, _ = oracle.adaptive_inputs(256, 256, 64)
+    assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 2               # fast
+    assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 8  # fast_relu
+    a, b, _ = oracle.adaptive_inputs(33, 65, 17)
+    assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 3               # fallback
+    assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 9  # fallback_relu
+
+
+def test_strided_operands(abi):
+    # Leading dimensions larger than the logical width (sub-matrices of wider buffers).
+    big_a = torch.randn(256, 192, device="cuda")
+    big_b = torch.randn(192, 512, device="cuda")
+    big_c = torch.randn(256, 640, device="cuda")
+    a, b, c = big_a[:, :128], big_b[:128, :384], big_c[:, :384]
+    status, d, chosen = run(abi, 0, a, b, c, alpha=0.5, beta=2.0, dispatch=True)
+    assert status == 0 and chosen == 2
+    check(d, oracle.adaptive_gemm_fp64(a, b, c, 0.5, 2.0))
+
+
+@pytest.mark.parametrize("epilogue", [LINEAR, RELU])
+def test_baseline_config_8192_sampled_rows(abi, epilogue):
+    # D = relu(1.0 * A @ B + 0.5 * C) at M = N = K = 8192. The FP64 oracle is
+    # evaluated on 96 sampled rows (and therefore every column and the whole K
+    # range); a row of a GEMM depends on nothing outside that row of A and C.
+    n = 8192
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(n, n, generator=g)
+    b = torch.randn(n, n, generator=g)
+    c = torch.randn(n, n, generator=g)
+    status, d, chosen = run(abi, 0, a.cuda(), b.cuda(), c.cuda(), 1.0, 0.5, epilogue, dispatch=True)
+    assert status == 0
+    rows = torch.randperm(n, generator=g)[:96]
+    expected = oracle.adaptive_gemm_fp64(a[rows], b, c[rows], 1.0, 0.5, "relu" if epilogue == RELU else "linear")
+    check(d[rows.cuda()], expected)
+    # Size-independent property: with beta = 0 the ReLU output is the positive
+    # part of the linear output, element for element.
+    if epilogue == RELU:
+        lin = run(abi, 0, a.cuda(), b.cuda(), c.cuda(), 1.0, 0.5, LINEAR, dispatch=True)[1]
+        assert torch.equal(d, lin.clamp_min(0))
+    assert_device_clean(abi)
