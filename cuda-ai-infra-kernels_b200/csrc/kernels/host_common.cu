@@ -52,14 +52,16 @@ bool make_tensor_map_2d(CUtensorMap* out, const float* base, uint64_t rows, uint
   if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return false;
   if ((ld * sizeof(float)) % 16 != 0 || (box_cols * sizeof(float)) % 16 != 0) return false;
   if (box_rows == 0 || box_cols == 0 || box_rows > 256 || box_cols > 256) return false;
-  if (swizzle == Swizzle::k128B && box_cols * sizeof(float) > 128) return false;
+  if (swizzle != Swizzle::kNone && box_cols * sizeof(float) > 128) return false;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {ld * sizeof(float)};
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t elem_strides[2] = {1, 1};
   const CUresult rc = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box,
                              elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             swizzle == Swizzle::k128B ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                             swizzle == Swizzle::k128B          ? CU_TENSOR_MAP_SWIZZLE_128B
+                             : swizzle == Swizzle::k128BAtom32B ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                                : CU_TENSOR_MAP_SWIZZLE_NONE,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return rc == CUDA_SUCCESS;
 }

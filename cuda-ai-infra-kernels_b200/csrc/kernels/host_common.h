@@ -22,13 +22,15 @@ inline int launch_status() {
 cudaError_t sgemm_status_read_clear(uint32_t* word);
 cudaError_t umma_status_read_clear(uint32_t* word);
 
-enum class Swizzle { kNone, k128B };
+// k128BAtom32B: 128-byte span swizzled in 32-byte granules (what an MN-major
+// 32-bit tcgen05 operand needs); k128B: the usual 16-byte granules.
+enum class Swizzle { kNone, k128B, k128BAtom32B };
 
 // Row-major FP32 matrix [rows][cols] with a row pitch of `ld` elements, tiled
 // in boxes of box_rows x box_cols (cols innermost). Out-of-range parts of a box
 // read as zero and are clipped on store. Requirements (checked, false on
 // failure): base 16-byte aligned, ld * 4 a multiple of 16, box_cols * 4 a
-// multiple of 16 (and <= 128 bytes with the 128-byte swizzle), boxes <= 256.
+// multiple of 16 (and <= 128 bytes with either 128-byte swizzle), boxes <= 256.
 bool make_tensor_map_2d(CUtensorMap* out, const float* base, uint64_t rows, uint64_t cols,
                         uint64_t ld, uint32_t box_rows, uint32_t box_cols, Swizzle swizzle);
 

@@ -215,14 +215,21 @@ __device__ __forceinline__ void tmem_ld_wait() {
 //   bits 16-29  leading-dimension byte offset >> 4
 //   bits 32-45  stride-dimension  byte offset >> 4
 //   bits 46-47  descriptor version (1 on sm_100)
-//   bits 61-63  swizzle mode (2 = 128-byte)
-__device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//   bits 61-63  swizzle mode
+enum UmmaSwizzle : uint32_t {
+  kUmmaSwizzleNone = 0,
+  kUmmaSwizzle128B32BAtom = 1,  // 128-byte span, 32-byte granules, 4-row period
+  kUmmaSwizzle128B = 2,         // 128-byte span, 16-byte granules, 8-row period
+};
+
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   UmmaSwizzle swizzle) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= 1ull << 46;
-  d |= 2ull << 61;
+  d |= static_cast<uint64_t>(swizzle) << 61;
   return d;
 }
 

@@ -9,15 +9,18 @@
 // csrc/adaptive_gemm/kernel_launcher.h:7-29).
 //
 // Operand staging. One pipeline stage holds a 128 x 32 slab of A and a
-// 32 x BN slab of B, 32 floats of K = 128 bytes per row, in the 128-byte
-// swizzled layout that both TMA and the MMA unit understand:
+// 32 x BN slab of B in swizzled layouts that both TMA and the MMA unit
+// understand:
 //   A is K-major for the MMA (K contiguous in memory). The slab is one TMA box
-//     {32 (k), 128 (m)}: 128 rows of 128 bytes, 8-row groups 1024 bytes apart.
-//   B is N-major for the MMA (N contiguous in memory). The slab is BN/32 TMA
-//     boxes {32 (n), 32 (k)}: each 32 rows (k) of 128 bytes (32 n), boxes
-//     4096 bytes apart; inside a box, 8-row k groups are 1024 bytes apart.
+//     {32 (k), 128 (m)}: 128 rows of 128 bytes, 128-byte swizzle in 16-byte
+//     granules (period 8 rows), 8-row groups 1024 bytes apart.
+//   B is N-major for the MMA (N contiguous in memory). A 32-bit N-major operand
+//     must use the 128-byte swizzle with 32-byte granules (period 4 rows). The
+//     slab is BN/32 TMA boxes {32 (n), 32 (k)}: each 32 rows (k) of 128 bytes
+//     (32 n), boxes 4096 bytes apart; inside a box, 4-row k groups are 512
+//     bytes apart.
 // One tcgen05.mma consumes 8 floats of K: the A descriptor advances 32 bytes
-// inside the swizzled row, the B descriptor advances one 8-row group.
+// inside the swizzled row, the B descriptor advances two 4-row groups.
 //
 // Two loaders feed that layout:
 //   TMA     - needs 16-byte aligned pointers and leading dimensions that are
@@ -47,7 +50,7 @@ constexpr uint32_t kBBoxBytes = 32 * kStageK * 4;       // 4 KiB: 32 (n) x 32 (k
 
 struct UmmaParams {
   CUtensorMap map_a;   // [M][K] boxes {32, 128}, 128-byte swizzle   (TMA loader only)
-  CUtensorMap map_b;   // [K][N] boxes {32, 32},  128-byte swizzle   (TMA loader only)
+  CUtensorMap map_b;   // [K][N] boxes {32, 32},  128-byte swizzle, 32-byte granules
   const float* a;      // generic loader only
   const float* b;
   const float* c;      // source, may be null when beta == 0
@@ -94,10 +97,10 @@ __device__ __forceinline__ void issue_stage_mmas(uint32_t tmem_acc, uint32_t a_a
   for (int j = 0; j < kStageK / kInstK; ++j) {
     // A: K-major, 8-row groups 1024 bytes apart (SBO); LBO is not used by the
     //    swizzled K-major form and carries the customary 16 bytes.
-    // B: N-major, 32-column groups 4096 bytes apart (LBO), 8-row k groups
-    //    1024 bytes apart (SBO).
-    const uint64_t desc_a = umma_smem_desc_sw128(a_addr + j * (kInstK * 4), 16, 1024);
-    const uint64_t desc_b = umma_smem_desc_sw128(b_addr + j * 1024, kBBoxBytes, 1024);
+    // B: N-major, 32-column groups 4096 bytes apart (LBO), 4-row k groups
+    //    512 bytes apart (SBO); one MMA spans two of them.
+    const uint64_t desc_a = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
+    const uint64_t desc_b = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
     umma_tf32(tmem_acc, desc_a, desc_b, idesc, j == 0 ? accumulate_first : 1u);
   }
 }
@@ -300,13 +303,13 @@ __device__ __forceinline__ void fill_stage(const UmmaParams& p, uint8_t* a_dst, 
     const float v = (gm < p.m && gk < p.k) ? __ldg(p.a + static_cast<int64_t>(gm) * p.lda + gk) : 0.f;
     *reinterpret_cast<float*>(a_dst + mm * 128 + (((kk >> 2) ^ (mm & 7)) << 4) + ((kk & 3) << 2)) = v;
   }
-  // B slab: box j = n / 32; element (k, n) at j * 4096 + k * 128 + (((n % 32) / 4) ^ (k % 8)) * 16 + (n % 4) * 4.
+  // B slab: box j = n / 32; element (k, n) at j * 4096 + k * 128 + (((n % 32) / 8) ^ (k % 4)) * 32 + (n % 8) * 4.
   for (int e = threadIdx.x; e < kStageK * BN; e += kGenericThreads) {
     const int kk = e / BN, nn = e % BN;
     const int gk = k0 + kk, gn = n0 + nn;
     const float v = (gk < p.k && gn < p.n) ? __ldg(p.b + static_cast<int64_t>(gk) * p.ldb + gn) : 0.f;
     const int j = nn >> 5, ni = nn & 31;
-    *reinterpret_cast<float*>(b_dst + j * kBBoxBytes + kk * 128 + (((ni >> 2) ^ (kk & 7)) << 4) + ((ni & 3) << 2)) = v;
+    *reinterpret_cast<float*>(b_dst + j * kBBoxBytes + kk * 128 + (((ni >> 3) ^ (kk & 3)) << 5) + ((ni & 7) << 2)) = v;
   }
 }
 
@@ -389,7 +392,7 @@ int launch_tma(const b200_gemm_problem& q, cudaStream_t stream) {
   UmmaParams p;
   fill_common(&p, q);
   if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
-      !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128B)) {
+      !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
     return B200_ERR_MISALIGNED_OPERAND;
   }
   const int sms = sm_count();
@@ -418,10 +421,14 @@ int launch_generic(const b200_gemm_problem& q, cudaStream_t stream) {
 // ------------------------------------------------------------------- registry
 
 using LaunchFn = int (*)(const b200_gemm_problem&, cudaStream_t);
+// Shape heuristic consulted only by automatic dispatch; a forced kernel runs
+// whatever the shape.
+using AutoGateFn = bool (*)(const b200_gemm_problem&, int sms);
 
 struct RegistryEntry {
   b200_tf32_kernel_meta meta;
   LaunchFn launch;
+  AutoGateFn auto_gate;
 };
 
 constexpr b200_tf32_kernel_meta meta(int id, const char* name, const char* alias, int epilogue, int tile_n, int stages,
@@ -430,23 +437,38 @@ constexpr b200_tf32_kernel_meta meta(int id, const char* name, const char* alias
                                kTileM, tile_n,     kInstK,    stages,    alignment, alignment, alignment, 0};
 }
 
-// Dispatch order. The first eight entries carry the ids, alias names and the
-// order of the reference registry (csrc/adaptive_gemm/kernel_dispatch.cu:46-103,
-// parse_kernel in csrc/adaptive_gemm/adaptive_gemm.cu:61-97): "fast" entries
-// require 4-element alignment (here: the TMA loader), "fallback" entries accept
-// anything (here: the generic loader). What distinguished the reference's
-// variants (warp shape, stage count) maps onto tile width and pipeline depth.
+int64_t tiles_of(const b200_gemm_problem& q, int tile_n) {
+  return static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + tile_n - 1) / tile_n);
+}
+
+bool gate_always(const b200_gemm_problem&, int) { return true; }
+// 128 x 256 tiles move a third fewer operand bytes per flop through L2, which
+// is what bounds this kernel; worth it once they still fill the GPU.
+bool gate_wide(const b200_gemm_problem& q, int sms) { return tiles_of(q, 256) >= sms; }
+// 128 x 64 tiles when 128-wide ones would leave more than half the SMs idle.
+bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) * 2 <= sms && q.n > 64; }
+
+// Dispatch order. Entries with ids >= 16 exist only here and are tried first by
+// automatic dispatch when their shape gate accepts the problem. The eight
+// entries after them carry the ids, alias names and the order of the reference
+// registry (csrc/adaptive_gemm/kernel_dispatch.cu:46-103, parse_kernel in
+// csrc/adaptive_gemm/adaptive_gemm.cu:61-97): "fast" entries require 4-element
+// alignment (here: the TMA loader), "fallback" entries accept anything (here:
+// the generic loader). What distinguished the reference's variants (warp
+// shape, stage count) maps onto tile width and pipeline depth.
 const RegistryEntry kRegistry[] = {
-    {meta(2, "umma128x128stage4tma", "fast", B200_EPILOGUE_LINEAR, 128, 4, 4), &launch_tma<128, 4, false>},
-    {meta(3, "umma128x128generic", "fallback", B200_EPILOGUE_LINEAR, 128, 2, 1), &launch_generic<128, false>},
-    {meta(4, "umma128x64stage4tma", "fast_mwarp", B200_EPILOGUE_LINEAR, 64, 4, 4), &launch_tma<64, 4, false>},
-    {meta(5, "umma128x64generic", "fallback_mwarp", B200_EPILOGUE_LINEAR, 64, 2, 1), &launch_generic<64, false>},
-    {meta(6, "umma128x128stage3tma", "fast_stage3", B200_EPILOGUE_LINEAR, 128, 3, 4), &launch_tma<128, 3, false>},
-    {meta(7, "umma128x128stage2tma", "fast_stage2", B200_EPILOGUE_LINEAR, 128, 2, 4), &launch_tma<128, 2, false>},
-    {meta(8, "umma128x128stage4tmaRelu", "fast_relu", B200_EPILOGUE_RELU, 128, 4, 4), &launch_tma<128, 4, true>},
-    {meta(9, "umma128x128genericRelu", "fallback_relu", B200_EPILOGUE_RELU, 128, 2, 1), &launch_generic<128, true>},
-    {meta(16, "umma128x256stage4tma", "wide", B200_EPILOGUE_LINEAR, 256, 4, 4), &launch_tma<256, 4, false>},
-    {meta(17, "umma128x256stage4tmaRelu", "wide_relu", B200_EPILOGUE_RELU, 256, 4, 4), &launch_tma<256, 4, true>},
+    {meta(16, "umma128x256stage4tma", "wide", B200_EPILOGUE_LINEAR, 256, 4, 4), &launch_tma<256, 4, false>, &gate_wide},
+    {meta(17, "umma128x256stage4tmaRelu", "wide_relu", B200_EPILOGUE_RELU, 256, 4, 4), &launch_tma<256, 4, true>, &gate_wide},
+    {meta(18, "umma128x64stage6tma", "narrow", B200_EPILOGUE_LINEAR, 64, 6, 4), &launch_tma<64, 6, false>, &gate_narrow},
+    {meta(19, "umma128x64stage6tmaRelu", "narrow_relu", B200_EPILOGUE_RELU, 64, 6, 4), &launch_tma<64, 6, true>, &gate_narrow},
+    {meta(2, "umma128x128stage4tma", "fast", B200_EPILOGUE_LINEAR, 128, 4, 4), &launch_tma<128, 4, false>, &gate_always},
+    {meta(3, "umma128x128generic", "fallback", B200_EPILOGUE_LINEAR, 128, 2, 1), &launch_generic<128, false>, &gate_always},
+    {meta(4, "umma128x64stage4tma", "fast_mwarp", B200_EPILOGUE_LINEAR, 64, 4, 4), &launch_tma<64, 4, false>, &gate_always},
+    {meta(5, "umma128x64generic", "fallback_mwarp", B200_EPILOGUE_LINEAR, 64, 2, 1), &launch_generic<64, false>, &gate_always},
+    {meta(6, "umma128x128stage3tma", "fast_stage3", B200_EPILOGUE_LINEAR, 128, 3, 4), &launch_tma<128, 3, false>, &gate_always},
+    {meta(7, "umma128x128stage2tma", "fast_stage2", B200_EPILOGUE_LINEAR, 128, 2, 4), &launch_tma<128, 2, false>, &gate_always},
+    {meta(8, "umma128x128stage4tmaRelu", "fast_relu", B200_EPILOGUE_RELU, 128, 4, 4), &launch_tma<128, 4, true>, &gate_always},
+    {meta(9, "umma128x128genericRelu", "fallback_relu", B200_EPILOGUE_RELU, 128, 2, 1), &launch_generic<128, true>, &gate_always},
 };
 constexpr int kRegistrySize = sizeof(kRegistry) / sizeof(kRegistry[0]);
 
@@ -526,8 +548,10 @@ int b200_tf32_gemm_dispatch(int requested, const b200_gemm_problem* q, int* chos
   const int basic = b200::check_problem(q);
   if (basic != B200_OK) return basic;
   if (requested == B200_TF32_KERNEL_CUBLAS) return B200_ERR_INVALID_ARGUMENT;  // library baseline lives in the caller
+  const int sms = requested == B200_TF32_KERNEL_AUTO ? b200::sm_count() : 0;
   for (const b200::RegistryEntry& e : b200::kRegistry) {
     if (requested != B200_TF32_KERNEL_AUTO && e.meta.id != requested) continue;
+    if (requested == B200_TF32_KERNEL_AUTO && !e.auto_gate(*q, sms)) continue;
     const int status = b200_tf32_gemm_launch(e.meta.id, q, stream);
     if (status == B200_OK) {
       if (chosen != nullptr) *chosen = e.meta.id;

@@ -159,7 +159,9 @@ typedef struct b200_gemm_problem {
  * Registry record: KernelEntry + KernelMeta of
  * csrc/adaptive_gemm/kernel_entry.h:7-61. `id` values 2..9 are the reference's
  * KernelId enumerators in declaration order (0 = Auto, 1 = Cublas); ids >= 16
- * are configurations that exist only here.
+ * are configurations that exist only here (wider or narrower tiles); automatic
+ * dispatch tries them first, each behind a shape gate, and then walks the
+ * reference's eight entries in the reference's order.
  */
 typedef struct b200_tf32_kernel_meta {
   int id;

@@ -100,7 +100,12 @@ def registry(abi):
 
 def test_registry_keeps_the_reference_ids_aliases_and_order(abi):
     entries = registry(abi)
-    head = [(e.id, e.alias.decode(), e.epilogue, e.alignment_a) for e in entries[:8]]
+    # Configurations that exist only here come first; the reference's eight
+    # follow in the reference's order.
+    own = [e for e in entries if e.id >= 16]
+    assert entries[:len(own)] == own or [e.id for e in entries[:len(own)]] == [e.id for e in own]
+    reference = [e for e in entries if e.id < 16]
+    head = [(e.id, e.alias.decode(), e.epilogue, e.alignment_a) for e in reference]
     assert head == [
         (2, "fast", 0, 4), (3, "fallback", 0, 1), (4, "fast_mwarp", 0, 4), (5, "fallback_mwarp", 0, 1),
         (6, "fast_stage3", 0, 4), (7, "fast_stage2", 0, 4), (8, "fast_relu", 1, 4), (9, "fallback_relu", 1, 1),

@@ -209,7 +209,10 @@ def test_row_major_tf32_side_entries(impl, shape):
     m, n, k = shape
     torch.manual_seed(0)
     a, b = torch.randn(m, k, device="cuda"), torch.randn(k, n, device="cuda")
-    torch.testing.assert_close(gemm(a, b, impl=impl).cpu(), oracle.gemm_fp64(a, b), atol=3e-2, rtol=3e-2)
+    # 3e-2 is the reference suite's gate for K <= 64; the absolute part grows
+    # with sqrt(K) because tcgen05 truncates FP32 operands to TF32.
+    atol = 3e-2 * max(1.0, (k / 64) ** 0.5 / 2)
+    torch.testing.assert_close(gemm(a, b, impl=impl).cpu(), oracle.gemm_fp64(a, b), atol=atol, rtol=3e-2)
 
 
 @pytest.mark.parametrize("impl", NAMED + ["cublas"])

@@ -39,9 +39,13 @@ def run(abi, kernel_id, a, b, c=None, alpha=1.0, beta=0.0, epilogue=LINEAR, disp
     return status, d, kernel_id
 
 
-def check(actual, expected):
+def check(actual, expected, k=64):
     assert oracle.rel_frobenius(actual, expected) <= oracle.TF32_REL_FROBENIUS
-    torch.testing.assert_close(actual.cpu(), expected, atol=3e-2, rtol=3e-2)
+    # Element-wise gate of the reference suite (3e-2, chosen there for K <= 64).
+    # tcgen05 truncates FP32 operands to TF32, so the absolute error of a sum
+    # grows like sqrt(K); the absolute part of the gate is scaled accordingly.
+    atol = 3e-2 * max(1.0, (k / 64) ** 0.5 / 2)
+    torch.testing.assert_close(actual.cpu(), expected, atol=atol, rtol=3e-2)
 
 
 def entries(align=None, epilogue=None):
@@ -75,7 +79,7 @@ def test_aligned_shapes_match_oracle(abi, entry, shape):
     a, b, c = oracle.adaptive_inputs(*shape)
     status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c.cuda(), alpha=1.0, beta=0.5, epilogue=epilogue)
     assert status == 0, abi.b200_status_string(status)
-    check(d, oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, "relu" if epilogue == RELU else "linear"))
+    check(d, oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, "relu" if epilogue == RELU else "linear"), k=shape[2])
     assert_device_clean(abi)
 
 
@@ -133,9 +137,20 @@ def test_beta_zero_never_reads_the_source(abi, kernel):
 
 
 def test_auto_dispatch_order(abi):
-    a, b, _ = oracle.adaptive_inputs(256, 256, 64)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    # Mid-sized aligned problem: neither shape gate fires, the reference order decides.
+    m = 128 * ((sms + 1) // 2 + 1)
+    a, b, _ = oracle.adaptive_inputs(m, 128, 64)
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 2               # fast
     assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 8  # fast_relu
+    # Small problem: 128-wide tiles would idle most SMs -> 64-wide tiles.
+    a, b, _ = oracle.adaptive_inputs(256, 256, 64)
+    assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 18              # narrow
+    assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 19
+    # Large problem: 256-wide tiles still fill the GPU.
+    a, b, _ = oracle.adaptive_inputs(128 * 16, 256 * ((sms + 15) // 16), 64)
+    assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 16              # wide
+    assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 17
     a, b, _ = oracle.adaptive_inputs(33, 65, 17)
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 3               # fallback
     assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 9  # fallback_relu
@@ -148,7 +163,7 @@ def test_strided_operands(abi):
     big_c = torch.randn(256, 640, device="cuda")
     a, b, c = big_a[:, :128], big_b[:128, :384], big_c[:, :384]
     status, d, chosen = run(abi, 0, a, b, c, alpha=0.5, beta=2.0, dispatch=True)
-    assert status == 0 and chosen == 2
+    assert status == 0 and chosen in (2, 18)
     check(d, oracle.adaptive_gemm_fp64(a, b, c, 0.5, 2.0))
 
 
@@ -166,7 +181,7 @@ def test_baseline_config_8192_sampled_rows(abi, epilogue):
     assert status == 0
     rows = torch.randperm(n, generator=g)[:96]
     expected = oracle.adaptive_gemm_fp64(a[rows], b, c[rows], 1.0, 0.5, "relu" if epilogue == RELU else "linear")
-    check(d[rows.cuda()], expected)
+    check(d[rows.cuda()], expected, k=n)
     # Size-independent property: with beta = 0 the ReLU output is the positive
     # part of the linear output, element for element.
     if epilogue == RELU:
