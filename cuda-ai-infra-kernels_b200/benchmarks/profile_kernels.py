@@ -1,0 +1,52 @@
+"""Launches each hot-path kernel a few times at its benchmark shape, for ncu.
+
+    python cuda-ai-infra-kernels_b200/benchmarks/profile_kernels.py [sgemm] [tf32] [rows] [--small]
+
+Meant to be wrapped by Nsight Compute, one kernel family per capture, e.g.
+
+    ncu --set full --clock-control none -k regex:sgemm_pipeline -c 3 -o prof \
+        python cuda-ai-infra-kernels_b200/benchmarks/profile_kernels.py sgemm
+
+The role of the reference's profiling/profile_*.sh wrappers. `--small` halves
+the GEMM edge (2048) so that a multi-pass capture stays short; the row-operator
+shapes (256 MiB and 128 MiB per tensor) are already small enough.
+"""
+import sys
+from pathlib import Path
+
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1] / "python"))
+import cuda_ai_kernels as pkg  # noqa: E402
+
+
+def main(argv):
+    small = "--small" in argv
+    which = [a for a in argv if not a.startswith("--")] or ["sgemm", "tf32", "rows"]
+    edge = 2048 if small else 4096
+    dev = "cuda"
+    if "sgemm" in which:
+        a = torch.randn(edge, edge, device=dev).t()
+        b = torch.randn(edge, edge, device=dev)
+        for impl in ("prefetch_reg", "prefetch_reg", "split_k", "prefetch_smem"):
+            pkg.gemm(a, b, impl=impl)
+    if "tf32" in which:
+        a = torch.randn(edge, edge, device=dev)
+        b = torch.randn(edge, edge, device=dev)
+        c = torch.randn(edge, edge, device=dev)
+        for _ in range(2):
+            pkg.adaptive_gemm(a, b, c=c, alpha=1.0, beta=0.5, epilogue="relu")
+    if "rows" in which:
+        x = torch.randn(16384, 4096, device=dev)
+        w = torch.rand(4096, device=dev) + 0.5
+        for _ in range(2):
+            pkg.rmsnorm(x, w, 1e-6)
+        logits = torch.randn(32768, 1024, device=dev)
+        for _ in range(2):
+            pkg.softmax(logits)
+    torch.cuda.synchronize()
+    print("profiled:", " ".join(which))
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
