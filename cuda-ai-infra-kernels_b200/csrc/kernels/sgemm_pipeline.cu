@@ -5,7 +5,7 @@
 //
 //   prefetch_smem : the ring alone (the reference's cp.async double buffer,
 //                   csrc/gemm/gemm_prefetchSmem.cu:100-169, becomes N stages);
-//                   a dedicated producer warp, scalar FMAs.
+//                   fragments are loaded where they are used.
 //   prefetch_reg  : ring + register double buffer of the shared-memory
 //                   fragments carried across stage boundaries, and packed
 //                   two-wide FMAs (csrc/gemm/gemm_prefetchRegister.cu:125-190).
@@ -362,7 +362,7 @@ int sgemm_pipeline_launch(int impl, const float* a, const float* b, float* c, in
   // producer measured slower (50 TFLOP/s) and are kept out of the dispatch.
   switch (impl) {
     case B200_SGEMM_PREFETCH_SMEM:
-      return launch_pipeline<WarpGrid<2, 2>, 32, 5, false, false, 1, 1>(a, b, c, m, n, k, stream);
+      return launch_pipeline<WarpGrid<2, 2>, 64, 3, false, true, 1, 1>(a, b, c, m, n, k, stream);
     case B200_SGEMM_PREFETCH_REG:
       return launch_pipeline<WarpGrid<2, 2>, 64, 3, true, true, 1, 1>(a, b, c, m, n, k, stream);
     case B200_SGEMM_SPLIT_K:

@@ -287,6 +287,159 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_c
   }
 }
 
+// ---------------------------------------------------- TMA, CTA-pair kernel
+// Two CTAs of a cluster share one 256 x 256 output tile through
+// tcgen05.mma.cta_group::2: CTA r of the pair holds rows [128 r, 128 r + 128) of
+// A, columns [128 r, 128 r + 128) of B and the accumulator rows [128 r, +128)
+// (all 256 columns). Per CTA a stage is 16 KiB of A + 16 KiB of B for a
+// 256 x 256 x 32 product, a third fewer operand bytes through L2 per flop than
+// the single-CTA 128 x 256 tile. The even CTA issues the MMAs for both.
+// Signals that both CTAs need (stage free, accumulator ready) are committed
+// twice, once per CTA; no multicast form is used anywhere.
+constexpr int kPairN = 256;
+constexpr uint32_t kPairStageBytes = kASlabBytes + (kPairN / 2 / 32) * kBBoxBytes;  // 32 KiB per CTA
+
+template <int STAGES>
+__host__ __device__ constexpr size_t pair_smem_bytes() {
+  return static_cast<size_t>(STAGES) * kPairStageBytes + 1024 + 256;
+}
+
+template <int STAGES, bool kRelu>
+__global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_constant__ UmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // Same carve-up in both CTAs: the MMA addresses the peer's shared memory by
+  // the same offsets as its own.
+  uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(STAGES) * kPairStageBytes);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();  // 0: issues the MMAs, 1: peer
+  const uint32_t peer = rank ^ 1u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);   // used in CTA 0 only: one expect_tx arrival, bytes of both CTAs
+      mbar_init(&empty[s], 1);  // one tcgen05.commit per use, sent to each CTA
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);  // used in CTA 0 only: four epilogue warps of each CTA
+    }
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair<512>(tmem_ptr);
+    tmem_relinquish_pair();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before any remote arrival
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  const int tiles_m = (p.m + 2 * kTileM - 1) / (2 * kTileM);
+  const int tiles_n = (p.n + kPairN - 1) / kPairN;
+  const int tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.k + kStageK - 1) / kStageK;
+  const int first_tile = blockIdx.x >> 1, tile_stride = gridDim.x >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&p.map_a);
+      prefetch_tensormap(&p.map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < tiles && ok; tile += tile_stride) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        const int row0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
+        const int col0 = tn * kPairN + static_cast<int>(rank) * (kPairN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, kSiteUmmaEmpty)) { ok = false; break; }
+          // Completion bytes of both CTAs are counted on CTA 0's barrier.
+          const uint32_t full_addr = map_to_cta(smem_u32(&full[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * kPairStageBytes);
+          uint8_t* a_dst = stages + static_cast<size_t>(stage) * kPairStageBytes;
+          uint8_t* b_dst = a_dst + kASlabBytes;
+          tma_load_2d_pair(a_dst, &p.map_a, full_addr, kb * kStageK, row0);
+#pragma unroll
+          for (int j = 0; j < kPairN / 2 / 32; ++j) {
+            tma_load_2d_pair(b_dst + j * kBBoxBytes, &p.map_b, full_addr, col0 + j * 32, kb * kStageK);
+          }
+          if (++stage == STAGES) stage = 0, phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(2 * kTileM, kPairN, /*a_mn_major=*/false, /*b_mn_major=*/true);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = first_tile; tile < tiles && ok; tile += tile_stride, ++local) {
+        const int buf = local & 1;
+        const uint32_t use_parity = (local >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[buf], use_parity ^ 1u, kSiteUmmaAccEmpty)) { ok = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + buf * kPairN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
+          tcgen05_fence_after_sync();
+          const uint32_t a_addr = smem_u32(stages + static_cast<size_t>(stage) * kPairStageBytes);
+          const uint32_t b_addr = a_addr + kASlabBytes;
+#pragma unroll
+          for (int j = 0; j < kStageK / kInstK; ++j) {
+            const uint64_t desc_a = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
+            const uint64_t desc_b = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
+            umma_tf32_pair(tmem_acc, desc_a, desc_b, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          // The stage is reusable in both CTAs once these MMAs have read it.
+          umma_commit_pair(smem_u32(&empty[stage]));
+          umma_commit_pair(map_to_cta(smem_u32(&empty[stage]), 1));
+          if (++stage == STAGES) stage = 0, phase ^= 1u;
+        }
+        if (ok) {
+          umma_commit_pair(smem_u32(&acc_full[buf]));
+          umma_commit_pair(map_to_cta(smem_u32(&acc_full[buf]), 1));
+        }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    bool ok = true;
+    int local = 0;
+    for (int tile = first_tile; tile < tiles && ok; tile += tile_stride, ++local) {
+      const int buf = local & 1;
+      const uint32_t use_parity = (local >> 1) & 1u;
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
+      tcgen05_fence_after_sync();
+      epilogue_tile<kPairN, kRelu>(p, tmem_base + buf * kPairN, quarter, lane,
+                                   tm * 2 * kTileM + static_cast<int>(rank) * kTileM, tn * kPairN);
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      // The MMA issuer (CTA 0) waits for the epilogues of both CTAs.
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+    }
+  }
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer may still be signalling this CTA's barriers or reading its operands
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc_pair<512>(tmem_base);
+  }
+  (void)peer;
+}
+
 // ------------------------------------------------------- generic loader kernel
 // One CTA per output tile, 128 threads. All threads fill the swizzled slabs
 // with predicated scalar loads (zeros outside the matrix), thread 0 issues the
@@ -403,6 +556,39 @@ int launch_tma(const b200_gemm_problem& q, cudaStream_t stream) {
   return launch_status();
 }
 
+template <int STAGES, bool kRelu>
+int launch_pair(const b200_gemm_problem& q, cudaStream_t stream) {
+  auto kernel = umma_pair_kernel<STAGES, kRelu>;
+  constexpr size_t smem = pair_smem_bytes<STAGES>();
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+    return B200_ERR_LAUNCH_FAILED;
+  }
+  UmmaParams p;
+  fill_common(&p, q);
+  if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
+      !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
+    return B200_ERR_MISALIGNED_OPERAND;
+  }
+  const int sms = sm_count();
+  if (sms < 2) return B200_ERR_INTERNAL;
+  const int64_t tiles = static_cast<int64_t>((q.m + 2 * kTileM - 1) / (2 * kTileM)) * ((q.n + kPairN - 1) / kPairN);
+  const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  cfg.blockDim = dim3(kTmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  return launch_status();
+}
+
 template <int BN, bool kRelu>
 int launch_generic(const b200_gemm_problem& q, cudaStream_t stream) {
   auto kernel = umma_generic_kernel<BN, kRelu>;
@@ -437,6 +623,12 @@ constexpr b200_tf32_kernel_meta meta(int id, const char* name, const char* alias
                                kTileM, tile_n,     kInstK,    stages,    alignment, alignment, alignment, 0};
 }
 
+// A CTA pair: 256 x 256 tile and a 256 x 256 x 8 instruction across two CTAs.
+constexpr b200_tf32_kernel_meta meta_pair(int id, const char* name, const char* alias, int epilogue, int stages) {
+  return b200_tf32_kernel_meta{id, name, alias, epilogue, 2 * kTileM, kPairN, kStageK, 2 * kTileM, kPairN, kInstK,
+                               stages, 4, 4, 4, 0};
+}
+
 int64_t tiles_of(const b200_gemm_problem& q, int tile_n) {
   return static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + tile_n - 1) / tile_n);
 }
@@ -446,6 +638,11 @@ bool gate_always(const b200_gemm_problem&, int) { return true; }
 // is what bounds this kernel; worth it once they still fill the GPU.
 bool gate_wide(const b200_gemm_problem& q, int sms) { return tiles_of(q, 256) >= sms; }
 // 128 x 64 tiles when 128-wide ones would leave more than half the SMs idle.
+// CTA pairs (256 x 256 per pair) when they fill at least one wave of pairs.
+bool gate_pair(const b200_gemm_problem& q, int sms) {
+  const int64_t tiles = static_cast<int64_t>((q.m + 255) / 256) * ((q.n + 255) / 256);
+  return tiles >= sms / 2;
+}
 bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) * 2 <= sms && q.n > 64; }
 
 // Dispatch order. Entries with ids >= 16 exist only here and are tried first by
@@ -457,6 +654,8 @@ bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) 
 // the generic loader). What distinguished the reference's variants (warp
 // shape, stage count) maps onto tile width and pipeline depth.
 const RegistryEntry kRegistry[] = {
+    {meta_pair(20, "umma256x256stage6pair", "pair", B200_EPILOGUE_LINEAR, 6), &launch_pair<6, false>, &gate_pair},
+    {meta_pair(21, "umma256x256stage6pairRelu", "pair_relu", B200_EPILOGUE_RELU, 6), &launch_pair<6, true>, &gate_pair},
     {meta(16, "umma128x256stage4tma", "wide", B200_EPILOGUE_LINEAR, 256, 4, 4), &launch_tma<256, 4, false>, &gate_wide},
     {meta(17, "umma128x256stage4tmaRelu", "wide_relu", B200_EPILOGUE_RELU, 256, 4, 4), &launch_tma<256, 4, true>, &gate_wide},
     {meta(18, "umma128x64stage6tma", "narrow", B200_EPILOGUE_LINEAR, 64, 6, 4), &launch_tma<64, 6, false>, &gate_narrow},

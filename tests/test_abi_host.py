@@ -111,8 +111,9 @@ def test_registry_keeps_the_reference_ids_aliases_and_order(abi):
         (6, "fast_stage3", 0, 4), (7, "fast_stage2", 0, 4), (8, "fast_relu", 1, 4), (9, "fallback_relu", 1, 1),
     ]
     for e in entries:
-        assert e.tile_m == 128 and e.inst_m == 128 and e.inst_k == 8 and e.tile_k == 32
+        assert e.tile_m in (128, 256) and e.inst_m == e.tile_m and e.inst_k == 8 and e.tile_k == 32
         assert e.tile_n in (64, 128, 256) and e.inst_n == e.tile_n
+        assert (e.tile_m == 256) == e.alias.decode().startswith("pair")   # 256 rows only as a CTA pair
         assert e.alignment_a == e.alignment_b == e.alignment_c and e.alignment_a in (1, 4)
         assert abi.b200_tf32_kernel_from_name(e.alias) == e.id
         assert abi.b200_tf32_kernel_from_name(e.name) == e.id
