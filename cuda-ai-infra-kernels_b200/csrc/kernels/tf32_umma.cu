@@ -24,10 +24,12 @@
 //
 // Two loaders feed that layout:
 //   TMA     - needs 16-byte aligned pointers and leading dimensions that are
-//             multiples of four floats; persistent, warp-specialised kernel
+//             multiples of four floats; persistent, warp-specialised kernels
 //             (producer / MMA issuer / epilogue warps), double-buffered TMEM
 //             accumulator so the epilogue of one tile overlaps the main loop of
-//             the next.
+//             the next. Two forms: one CTA per 128 x BN tile, and CTA pairs
+//             (cta_group::2) that share a 256 x 256 tile and halve the B bytes
+//             each CTA pulls through L2.
 //   generic - any pointers, any sizes; predicated scalar loads written into the
 //             same swizzled layout, one tile per CTA.
 // Neither uses cluster multicast.
@@ -318,7 +320,6 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();  // 0: issues the MMAs, 1: peer
-  const uint32_t peer = rank ^ 1u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -437,7 +438,6 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
     tcgen05_fence_after_sync();
     tmem_dealloc_pair<512>(tmem_base);
   }
-  (void)peer;
 }
 
 // ------------------------------------------------------- generic loader kernel
