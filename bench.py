@@ -54,6 +54,16 @@ FP32_LANES_PER_SM = 128
 # The reference's published figure for this metric: split_k at 4096^3 on an
 # A800 80GB PCIe, 17.206 TFLOP/s (its README.md:17). Other hardware; per GPU.
 PUBLISHED_A800_SPLIT_K_TFLOPS = 17.206
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the
+# committed Nsight Compute captures of exactly these workloads (profiles/*.md).
+# bench.py cannot run ncu on itself; the figures are carried here so that the
+# roofline objects can set traffic beside the algorithmic bytes.
+NCU_TRAFFIC_BYTES = {
+    "sgemm_4096": 334.2e6 + 54.9e6,      # profiles/sgemm_pipeline_4096.md (algorithmic: 201 MB of operands + output)
+    "tf32_4096": 413.0e6 + 49.8e6,       # profiles/tf32_umma_4096.md
+    "rmsnorm_16384x4096": 268.5e6 + 213.0e6,   # profiles/rowops_c4.md (writes partly still in L2 at kernel end)
+    "softmax_32768x1024": 134.2e6 + 78.2e6,
+}
 
 
 def load_peaks() -> dict:
@@ -227,7 +237,8 @@ def measure_extras(pkg, peaks: dict, steps: int, warmup: int) -> dict:
         del a, b, c
     out["tf32_roofline"] = {"bound": "tensor", "achieved": out["tf32_relu_4096_tflops"], "peak": tf32_peak,
                             "unit": "TFLOP/s", "frac": out["tf32_relu_4096_tflops"] / tf32_peak,
-                            "peak_source": f"{peaks['source']} bf16 burst / 2", "traffic": None}
+                            "peak_source": f"{peaks['source']} bf16 burst / 2",
+                            "traffic": NCU_TRAFFIC_BYTES["tf32_4096"]}
 
     # Row operators: bytes = one read of x + one write of y (+ weight once).
     rows, hidden = 16384, 4096
@@ -250,7 +261,8 @@ def measure_extras(pkg, peaks: dict, steps: int, warmup: int) -> dict:
     for key in ("rmsnorm_16384x4096_gbs", "softmax_32768x1024_gbs"):
         out[key.replace("_gbs", "_roofline")] = {
             "bound": "hbm", "achieved": out[key], "peak": peaks["hbm_gbs"], "unit": "GB/s",
-            "frac": out[key] / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth", "traffic": None}
+            "frac": out[key] / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth",
+            "traffic": NCU_TRAFFIC_BYTES[key.replace("_gbs", "")]}
     return out
 
 
@@ -395,7 +407,7 @@ def main() -> None:
         roofline = {"bound": "fp32_fma", "achieved": per_gpu_tflops, "peak": fma_peak, "unit": "TFLOP/s",
                     "frac": per_gpu_tflops / fma_peak,
                     "peak_source": f"2 flop x {FP32_LANES_PER_SM} lanes x {sms} SMs x {sm_max:.0f} MHz (max SM clock)",
-                    "traffic": None}
+                    "traffic": NCU_TRAFFIC_BYTES["sgemm_4096"]}
         if clk.get("sm_mhz"):
             roofline["frac_at_observed_clock"] = per_gpu_tflops / (fma_peak * clk["sm_mhz"] / sm_max)
         line = {

@@ -9,14 +9,17 @@
 //   prefetch_reg  : ring + register double buffer of the shared-memory
 //                   fragments carried across stage boundaries, and packed
 //                   two-wide FMAs (csrc/gemm/gemm_prefetchRegister.cu:125-190).
-//   split_k       : prefetch_reg on two K slices per output tile, reduced with
-//                   128-bit vector reductions into an output that the launcher
-//                   clears on the same stream (csrc/gemm/gemm_splictK.cu:101-209).
+//   split_k       : prefetch_reg with K split across CTAs and the partial sums
+//                   reduced with 128-bit vector reductions into an output that
+//                   the launcher clears on the same stream. The reference cuts
+//                   every tile's K in two (csrc/gemm/gemm_splictK.cu:101-209) to
+//                   balance waves; here the whole (tile, k block) iteration
+//                   space is cut into one equal range per CTA (stream-K), which
+//                   balances any shape.
 //
 // Layout in shared memory per stage: A slab [BK][128] (row kk = 128 consecutive
 // m of storage row k) and B slab [BK][128]; both arrive exactly as one TMA box.
-// K tails and K slices are handled by the tensor maps: rows past a slice's
-// extent read as zeros.
+// K tails are handled by the tensor maps: rows past K read as zeros.
 //
 // What bounds the kernel: a 128-bit shared-memory load costs four cycles of the
 // SM's single shared-memory pipe whatever its addresses, and with 8 x 8
@@ -38,12 +41,12 @@ namespace {
 constexpr int kTile = 128;  // CTA tile is kTile x kTile
 
 struct PipelineParams {
-  CUtensorMap map_a[2];  // per K slice: [k_slice][M] view of A storage
-  CUtensorMap map_b[2];  // per K slice: [k_slice][N] view of B
+  CUtensorMap map_a;  // [K][M] view of A storage, boxes {128 m, BK k}
+  CUtensorMap map_b;  // [K][N] view of B, boxes {128 n, BK k}
   float* c;
   int n;
   int tiles_m, tiles_n;
-  int k_blocks;          // ceil(k_slice / BK)
+  int k_blocks;       // ceil(K / BK)
 };
 
 // Work decomposition of the consumer warps. Inside a warp the lanes form an
@@ -137,38 +140,99 @@ __device__ __forceinline__ void outer_product(float (&acc)[4 * RM][4 * RN], cons
   }
 }
 
-// Position of the TMA producer in the CTA's sequence of (work unit, k block).
+// A run of consecutive k blocks of one output tile.
+struct Segment {
+  int tile;
+  int kb_begin, kb_end;
+};
+
+// Hands a CTA its segments. Two schedules:
+//   whole tiles - tile = blockIdx.x, + gridDim.x, ...; every segment is a full K
+//                 range and its result is stored;
+//   stream-K    - the (tile, k block) iteration space is cut into gridDim.x
+//                 equal contiguous ranges, so every CTA does the same number of
+//                 k blocks whatever the tile count; a range covers the tail of
+//                 one tile, some whole tiles and the head of another, and every
+//                 segment is reduced into the output.
+// Producer and consumers walk identical copies.
+template <bool kStreamK>
+struct WorkIterator {
+  int k_blocks;
+  int tile, tile_end, tile_stride;  // whole tiles
+  int64_t it, it_end;               // stream-K
+
+  __device__ WorkIterator(int tiles, int k_blocks_) : k_blocks(k_blocks_) {
+    if constexpr (kStreamK) {
+      const int64_t total = static_cast<int64_t>(tiles) * k_blocks;
+      it = total * blockIdx.x / gridDim.x;
+      it_end = total * (blockIdx.x + 1) / gridDim.x;
+      tile = tile_end = tile_stride = 0;
+    } else {
+      tile = blockIdx.x, tile_end = tiles, tile_stride = gridDim.x;
+      it = it_end = 0;
+    }
+  }
+
+  __device__ bool next(Segment* s) {
+    if constexpr (kStreamK) {
+      if (it >= it_end) return false;
+      s->tile = static_cast<int>(it / k_blocks);
+      s->kb_begin = static_cast<int>(it - static_cast<int64_t>(s->tile) * k_blocks);
+      const int64_t room = it_end - it;
+      s->kb_end = room < k_blocks - s->kb_begin ? s->kb_begin + static_cast<int>(room) : k_blocks;
+      it += s->kb_end - s->kb_begin;
+      return true;
+    } else {
+      if (tile >= tile_end) return false;
+      s->tile = tile, s->kb_begin = 0, s->kb_end = k_blocks;
+      tile += tile_stride;
+      return true;
+    }
+  }
+};
+
+// Position of the TMA producer: its own copy of the work iterator plus the
+// ring slot it fills next.
+template <bool kStreamK>
 struct ProducerCursor {
-  int unit;
+  WorkIterator<kStreamK> work;
+  Segment seg{0, 0, 0};
   int kb = 0;
-  int tm = 0, tn = 0, slice = 0;
+  int tm = 0, tn = 0;
+  bool active;
   int stage = 0;
   uint32_t phase = 0;
+
+  __device__ ProducerCursor(const PipelineParams& p) : work(p.tiles_m * p.tiles_n, p.k_blocks) { advance_segment(p); }
+
+  __device__ void advance_segment(const PipelineParams& p) {
+    active = work.next(&seg);
+    if (active) {
+      kb = seg.kb_begin;
+      tile_coords(seg.tile, p.tiles_m, p.tiles_n, &tm, &tn);
+    }
+  }
 };
 
 // Issues the loads of the cursor's stage and advances it. Returns false only
 // when the bounded wait for a free stage expired.
-template <int BK, int STAGES, int SPLIT>
-__device__ __forceinline__ bool produce_stage(const PipelineParams& p, ProducerCursor& c, int units, int unit_stride,
-                                              float* slabs, uint64_t* full_bar, uint64_t* empty_bar) {
+template <int BK, int STAGES, bool kStreamK>
+__device__ __forceinline__ bool produce_stage(const PipelineParams& p, ProducerCursor<kStreamK>& c, float* slabs,
+                                              uint64_t* full_bar, uint64_t* empty_bar) {
   using Layout = SmemLayout<BK, STAGES>;
-  if (c.unit >= units) return true;  // nothing left to fetch
-  if (c.kb == 0) {
-    c.slice = c.unit % SPLIT;
-    tile_coords(c.unit / SPLIT, p.tiles_m, p.tiles_n, &c.tm, &c.tn);
-  }
+  if (!c.active) return true;  // nothing left to fetch
   // A stage is free once every consumer warp released its previous use.
   if (!mbar_wait(&empty_bar[c.stage], c.phase ^ 1u, kSiteSgemmEmpty)) return false;
   mbar_expect_tx(&full_bar[c.stage], Layout::kStageBytes);
   float* a_slab = slabs + static_cast<size_t>(c.stage) * 2 * Layout::kSlabFloats;
-  tma_load_2d(a_slab, &p.map_a[c.slice], &full_bar[c.stage], c.tm * kTile, c.kb * BK);
-  tma_load_2d(a_slab + Layout::kSlabFloats, &p.map_b[c.slice], &full_bar[c.stage], c.tn * kTile, c.kb * BK);
+  tma_load_2d(a_slab, &p.map_a, &full_bar[c.stage], c.tm * kTile, c.kb * BK);
+  tma_load_2d(a_slab + Layout::kSlabFloats, &p.map_b, &full_bar[c.stage], c.tn * kTile, c.kb * BK);
   if (++c.stage == STAGES) c.stage = 0, c.phase ^= 1u;
-  if (++c.kb == p.k_blocks) c.kb = 0, c.unit += unit_stride;
+  if (++c.kb == c.seg.kb_end) c.advance_segment(p);
   return true;
 }
 
-template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, int SPLIT, int kCtasPerSm>
+template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, bool kStreamK, int kCtasPerSm>
 __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_kernel(const __grid_constant__ PipelineParams p) {
   using Layout = SmemLayout<BK, STAGES>;
   constexpr int RM = Grid::RM, RN = Grid::RN;
@@ -197,17 +261,14 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
   }
   __syncthreads();
 
-  const int units = p.tiles_m * p.tiles_n * SPLIT;
-  const int unit_stride = gridDim.x;
-
   if (Grid::kProducerWarp && tid >= Grid::kConsumerThreads) {
     // ------------------------------------------------- dedicated producer warp
     if (tid != Grid::kConsumerThreads) return;
-    prefetch_tensormap(&p.map_a[0]);
-    prefetch_tensormap(&p.map_b[0]);
-    ProducerCursor cursor{static_cast<int>(blockIdx.x)};
-    while (cursor.unit < units) {
-      if (!produce_stage<BK, STAGES, SPLIT>(p, cursor, units, unit_stride, slabs, full_bar, empty_bar)) return;
+    prefetch_tensormap(&p.map_a);
+    prefetch_tensormap(&p.map_b);
+    ProducerCursor<kStreamK> cursor(p);
+    while (cursor.active) {
+      if (!produce_stage<BK, STAGES>(p, cursor, slabs, full_bar, empty_bar)) return;
     }
     return;
   }
@@ -218,21 +279,24 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
   const int col0 = (warp % Grid::kWarpsN) * (16 * RN) + (lane & 3) * 4;
 
   const bool produces = kInlineProducer && tid == 0;
-  ProducerCursor cursor{static_cast<int>(blockIdx.x)};
+  ProducerCursor<kStreamK> cursor(p);
   if (produces) {
-    prefetch_tensormap(&p.map_a[0]);
-    prefetch_tensormap(&p.map_b[0]);
+    prefetch_tensormap(&p.map_a);
+    prefetch_tensormap(&p.map_b);
 #pragma unroll 1
     for (int i = 0; i < kLookahead; ++i) {
-      if (!produce_stage<BK, STAGES, SPLIT>(p, cursor, units, unit_stride, slabs, full_bar, empty_bar)) return;
+      if (!produce_stage<BK, STAGES>(p, cursor, slabs, full_bar, empty_bar)) return;
     }
   }
 
   int stage = 0;
   uint32_t phase = 0;
-  for (int unit = blockIdx.x; unit < units; unit += unit_stride) {
+  WorkIterator<kStreamK> work(p.tiles_m * p.tiles_n, p.k_blocks);
+  Segment seg;
+  while (work.next(&seg)) {
     int tm, tn;
-    tile_coords(unit / SPLIT, p.tiles_m, p.tiles_n, &tm, &tn);
+    tile_coords(seg.tile, p.tiles_m, p.tiles_n, &tm, &tn);
+    const int seg_blocks = seg.kb_end - seg.kb_begin;
 
     float acc[4 * RM][4 * RN];
 #pragma unroll
@@ -246,9 +310,9 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
       const float* a_slab = slabs + static_cast<size_t>(stage) * 2 * Layout::kSlabFloats + row0;
       const float* b_slab = slabs + static_cast<size_t>(stage) * 2 * Layout::kSlabFloats + Layout::kSlabFloats + col0;
       load_fragment(frag[0], a_slab, b_slab, 0);
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int kb = 0; kb < seg_blocks; ++kb) {
         if (produces) {
-          if (!produce_stage<BK, STAGES, SPLIT>(p, cursor, units, unit_stride, slabs, full_bar, empty_bar)) return;
+          if (!produce_stage<BK, STAGES>(p, cursor, slabs, full_bar, empty_bar)) return;
         }
         const int this_stage = stage;
         if (++stage == STAGES) stage = 0, phase ^= 1u;
@@ -256,7 +320,7 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
         for (int kk = 0; kk < BK; ++kk) {
           if (kk + 1 < BK) {
             load_fragment(frag[(kk + 1) & 1], a_slab, b_slab, kk + 1);
-          } else if (kb + 1 < p.k_blocks) {
+          } else if (kb + 1 < seg_blocks) {
             // First fragment of the next stage is fetched before the last
             // k of this one is multiplied.
             if (!mbar_wait(&full_bar[stage], phase, kSiteSgemmFull)) return;
@@ -270,9 +334,9 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
         if (lane == 0) mbar_arrive(&empty_bar[this_stage]);
       }
     } else {
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int kb = 0; kb < seg_blocks; ++kb) {
         if (produces) {
-          if (!produce_stage<BK, STAGES, SPLIT>(p, cursor, units, unit_stride, slabs, full_bar, empty_bar)) return;
+          if (!produce_stage<BK, STAGES>(p, cursor, slabs, full_bar, empty_bar)) return;
         }
         if (!mbar_wait(&full_bar[stage], phase, kSiteSgemmFull)) return;
         const float* a_slab = slabs + static_cast<size_t>(stage) * 2 * Layout::kSlabFloats + row0;
@@ -290,7 +354,8 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
     }
 
     // Epilogue straight from registers: every store instruction of a warp
-    // covers eight rows x 64 contiguous bytes.
+    // covers eight rows x 64 contiguous bytes. Stream-K segments are partial
+    // sums and are reduced into the cleared output instead.
     float* c_tile = p.c + static_cast<int64_t>(tm * kTile + row0) * p.n + tn * kTile + col0;
 #pragma unroll
     for (int rb = 0; rb < RM; ++rb)
@@ -300,7 +365,7 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
         const float* v = acc[rb * 4 + i];
 #pragma unroll
         for (int cb = 0; cb < RN; ++cb) {
-          if constexpr (SPLIT == 1) {
+          if constexpr (!kStreamK) {
             *reinterpret_cast<float4*>(c_row + 16 * cb) = make_float4(v[4 * cb], v[4 * cb + 1], v[4 * cb + 2], v[4 * cb + 3]);
           } else {
             red_add_v4(c_row + 16 * cb, v[4 * cb], v[4 * cb + 1], v[4 * cb + 2], v[4 * cb + 3]);
@@ -310,10 +375,10 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
   }
 }
 
-template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, int SPLIT, int kCtasPerSm>
+template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, bool kStreamK, int kCtasPerSm>
 int launch_pipeline(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
   using Layout = SmemLayout<BK, STAGES>;
-  auto kernel = sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, SPLIT, kCtasPerSm>;
+  auto kernel = sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, kStreamK, kCtasPerSm>;
   // Function attributes are per device; setting them again is cheap and keeps
   // the launcher free of per-device state.
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Layout::kBytes)) !=
@@ -324,28 +389,25 @@ int launch_pipeline(const float* a, const float* b, float* c, int m, int n, int 
   if (sms <= 0) return B200_ERR_INTERNAL;
 
   PipelineParams p;
-  const int k_slice = k / SPLIT;
-  for (int s = 0; s < SPLIT; ++s) {
-    const float* a_slice = a + static_cast<int64_t>(s) * k_slice * m;
-    const float* b_slice = b + static_cast<int64_t>(s) * k_slice * n;
-    if (!make_tensor_map_2d(&p.map_a[s], a_slice, k_slice, m, m, BK, kTile, Swizzle::kNone) ||
-        !make_tensor_map_2d(&p.map_b[s], b_slice, k_slice, n, n, BK, kTile, Swizzle::kNone)) {
-      return B200_ERR_MISALIGNED_OPERAND;
-    }
+  // Rows past K read as zeros, which takes care of a K that is not a multiple
+  // of the ring's stage depth.
+  if (!make_tensor_map_2d(&p.map_a, a, k, m, m, BK, kTile, Swizzle::kNone) ||
+      !make_tensor_map_2d(&p.map_b, b, k, n, n, BK, kTile, Swizzle::kNone)) {
+    return B200_ERR_MISALIGNED_OPERAND;
   }
-  for (int s = SPLIT; s < 2; ++s) p.map_a[s] = p.map_a[0], p.map_b[s] = p.map_b[0];
   p.c = c;
   p.n = n;
   p.tiles_m = m / kTile;
   p.tiles_n = n / kTile;
-  p.k_blocks = (k_slice + BK - 1) / BK;
+  p.k_blocks = (k + BK - 1) / BK;
 
-  if (SPLIT > 1) {
+  if (kStreamK) {
     if (cudaMemsetAsync(c, 0, static_cast<size_t>(m) * n * sizeof(float), stream) != cudaSuccess) {
       return B200_ERR_LAUNCH_FAILED;
     }
   }
-  const int64_t units = static_cast<int64_t>(p.tiles_m) * p.tiles_n * SPLIT;
+  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  const int64_t units = kStreamK ? tiles * p.k_blocks : tiles;
   const int64_t slots = static_cast<int64_t>(sms) * kCtasPerSm;
   const int grid = static_cast<int>(units < slots ? units : slots);
   kernel<<<grid, Grid::kThreads, Layout::kBytes, stream>>>(p);
@@ -362,11 +424,11 @@ int sgemm_pipeline_launch(int impl, const float* a, const float* b, float* c, in
   // producer measured slower (50 TFLOP/s) and are kept out of the dispatch.
   switch (impl) {
     case B200_SGEMM_PREFETCH_SMEM:
-      return launch_pipeline<WarpGrid<2, 2>, 64, 3, false, true, 1, 1>(a, b, c, m, n, k, stream);
+      return launch_pipeline<WarpGrid<2, 2>, 64, 3, false, true, false, 1>(a, b, c, m, n, k, stream);
     case B200_SGEMM_PREFETCH_REG:
-      return launch_pipeline<WarpGrid<2, 2>, 64, 3, true, true, 1, 1>(a, b, c, m, n, k, stream);
+      return launch_pipeline<WarpGrid<2, 2>, 64, 3, true, true, false, 1>(a, b, c, m, n, k, stream);
     case B200_SGEMM_SPLIT_K:
-      return launch_pipeline<WarpGrid<2, 2>, 64, 3, true, true, 2, 1>(a, b, c, m, n, k, stream);
+      return launch_pipeline<WarpGrid<2, 2>, 64, 3, true, true, true, 1>(a, b, c, m, n, k, stream);
     default:
       return B200_ERR_INVALID_ARGUMENT;
   }

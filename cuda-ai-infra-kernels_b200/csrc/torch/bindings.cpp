@@ -22,7 +22,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_warp_tile", &gemm_warp_tile, ladder_doc);
   m.def("gemm_prefetch_smem", &gemm_prefetch_smem, "FP32 SIMT GEMM fed by a TMA + mbarrier ring");
   m.def("gemm_prefetch_reg", &gemm_prefetch_reg, "TMA ring + register double buffer + packed FMAs");
-  m.def("gemm_split_k", &gemm_split_k, "Two K slices per tile reduced into a cleared output");
+  m.def("gemm_split_k", &gemm_split_k, "K split across CTAs (stream-K), partial sums reduced into a cleared output");
   m.def("gemm_tensor_core", &gemm_tensor_core, "Row-major TF32 GEMM on tcgen05 tensor cores");
   m.def("gemm_cutlass", &gemm_cutlass, "Row-major TF32 GEMM on tcgen05 tensor cores");
   m.def("rmsnorm_naive", &rmsnorm_naive, "RMSNorm forward");
