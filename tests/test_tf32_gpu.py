@@ -138,8 +138,8 @@ def test_beta_zero_never_reads_the_source(abi, kernel):
 
 def test_auto_dispatch_order(abi):
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    # Mid-sized aligned problem: neither shape gate fires, the reference order decides.
-    m = 128 * ((sms + 1) // 2 + 1)
+    # Mid-sized aligned problem: no shape gate fires, the reference order decides.
+    m = 128 * ((sms + 1) // 2 + 1)          # too many 128-wide tiles for "narrow", too few 256 x 256 for "pair"
     a, b, _ = oracle.adaptive_inputs(m, 128, 64)
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 2               # fast
     assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 8  # fast_relu
