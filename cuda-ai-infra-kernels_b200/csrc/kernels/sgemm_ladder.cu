@@ -102,55 +102,27 @@ __global__ void __launch_bounds__(Map::kThreads) sgemm_smem_kernel(const float* 
 #pragma unroll
     for (int j = 0; j < RN * CN; ++j) acc[i][j] = 0.f;
 
-  // Staging plan. Which element of a slab a thread copies does not depend on
-  // the k step, so source pointers and shared-memory slots are fixed up front
-  // and the loop only advances the pointers by BK storage rows.
-  constexpr int kVec = kVectorStaging ? 4 : 1;
-  constexpr int kACopies = (BK * BM / kVec + kThreads - 1) / kThreads;
-  constexpr int kBCopies = (BK * BN / kVec + kThreads - 1) / kThreads;
-  const float* a_src[kACopies];
-  const float* b_src[kBCopies];
-  float* a_dst[kACopies];
-  float* b_dst[kBCopies];
-#pragma unroll
-  for (int i = 0; i < kACopies; ++i) {
-    const int e = (tid + i * kThreads) * kVec;
-    const int kk = e / BM, mm = e % BM;
-    const bool mine = e < BK * BM;
-    a_src[i] = mine ? a + static_cast<int64_t>(kk) * m + m0 + mm : nullptr;
-    a_dst[i] = &a_s[mine ? kk : 0][mine ? mm : 0];
-  }
-#pragma unroll
-  for (int i = 0; i < kBCopies; ++i) {
-    const int e = (tid + i * kThreads) * kVec;
-    const int kk = e / BN, nn = e % BN;
-    const bool mine = e < BK * BN;
-    b_src[i] = mine ? b + static_cast<int64_t>(kk) * n + n0 + nn : nullptr;
-    b_dst[i] = &b_s[mine ? kk : 0][mine ? nn : 0];
-  }
-  const int64_t a_step = static_cast<int64_t>(BK) * m, b_step = static_cast<int64_t>(BK) * n;
-
   for (int k0 = 0; k0 < k; k0 += BK) {
-#pragma unroll
-    for (int i = 0; i < kACopies; ++i) {
-      if (a_src[i] != nullptr) {
-        if constexpr (kVectorStaging) {
-          *reinterpret_cast<float4*>(a_dst[i]) = *reinterpret_cast<const float4*>(a_src[i]);
-        } else {
-          *a_dst[i] = *a_src[i];
-        }
-        a_src[i] += a_step;
+    // Stage the two slabs. Row kk of either slab is contiguous in global memory.
+    if constexpr (kVectorStaging) {
+      for (int v = tid; v < BK * BM / 4; v += kThreads) {
+        const int kk = v / (BM / 4), mm = (v % (BM / 4)) * 4;
+        *reinterpret_cast<float4*>(&a_s[kk][mm]) =
+            *reinterpret_cast<const float4*>(a + static_cast<int64_t>(k0 + kk) * m + m0 + mm);
       }
-    }
-#pragma unroll
-    for (int i = 0; i < kBCopies; ++i) {
-      if (b_src[i] != nullptr) {
-        if constexpr (kVectorStaging) {
-          *reinterpret_cast<float4*>(b_dst[i]) = *reinterpret_cast<const float4*>(b_src[i]);
-        } else {
-          *b_dst[i] = *b_src[i];
-        }
-        b_src[i] += b_step;
+      for (int v = tid; v < BK * BN / 4; v += kThreads) {
+        const int kk = v / (BN / 4), nn = (v % (BN / 4)) * 4;
+        *reinterpret_cast<float4*>(&b_s[kk][nn]) =
+            *reinterpret_cast<const float4*>(b + static_cast<int64_t>(k0 + kk) * n + n0 + nn);
+      }
+    } else {
+      for (int e = tid; e < BK * BM; e += kThreads) {
+        const int kk = e / BM, mm = e % BM;
+        a_s[kk][mm] = a[static_cast<int64_t>(k0 + kk) * m + m0 + mm];
+      }
+      for (int e = tid; e < BK * BN; e += kThreads) {
+        const int kk = e / BN, nn = e % BN;
+        b_s[kk][nn] = b[static_cast<int64_t>(k0 + kk) * n + n0 + nn];
       }
     }
     __syncthreads();
