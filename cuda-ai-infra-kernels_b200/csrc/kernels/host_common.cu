@@ -66,6 +66,25 @@ bool make_tensor_map_2d(CUtensorMap* out, const float* base, uint64_t rows, uint
   return rc == CUDA_SUCCESS;
 }
 
+bool make_tensor_map_strips(CUtensorMap* out, const float* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                            uint32_t box_rows, uint32_t box_groups, Swizzle swizzle) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || (ld * sizeof(float)) % 16 != 0) return false;
+  if (cols == 0 || cols % 32 != 0 || box_rows == 0 || box_rows > 256 || box_groups == 0 || box_groups > 256) return false;
+  const cuuint64_t dims[3] = {32, rows, cols / 32};
+  const cuuint64_t strides[2] = {ld * sizeof(float), 32 * sizeof(float)};
+  const cuuint32_t box[3] = {32, box_rows, box_groups};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult rc = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box,
+                             elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             swizzle == Swizzle::k128B          ? CU_TENSOR_MAP_SWIZZLE_128B
+                             : swizzle == Swizzle::k128BAtom32B ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                                : CU_TENSOR_MAP_SWIZZLE_NONE,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
+
 }  // namespace b200
 
 extern "C" {

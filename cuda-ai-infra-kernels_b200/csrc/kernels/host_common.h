@@ -34,4 +34,11 @@ enum class Swizzle { kNone, k128B, k128BAtom32B };
 bool make_tensor_map_2d(CUtensorMap* out, const float* base, uint64_t rows, uint64_t cols,
                         uint64_t ld, uint32_t box_rows, uint32_t box_cols, Swizzle swizzle);
 
+// Row-major FP32 matrix [rows][cols] (cols a multiple of 32) viewed as
+// [cols / 32][rows][32]: a box of `box_groups` x `box_rows` x 32 gathers
+// `box_groups` adjacent 32-column strips of the same rows with ONE copy and
+// lays them out strip after strip (box_rows * 128 bytes each) in shared memory.
+bool make_tensor_map_strips(CUtensorMap* out, const float* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                            uint32_t box_rows, uint32_t box_groups, Swizzle swizzle);
+
 }  // namespace b200

@@ -53,6 +53,8 @@ constexpr uint32_t kBBoxBytes = 32 * kStageK * 4;       // 4 KiB: 32 (n) x 32 (k
 struct UmmaParams {
   CUtensorMap map_a;   // [M][K] boxes {32, 128}, 128-byte swizzle   (TMA loader only)
   CUtensorMap map_b;   // [K][N] boxes {32, 32},  128-byte swizzle, 32-byte granules
+  CUtensorMap map_b_strips;  // [N/32][K][32] boxes {32, 32, strips}: a whole B slab in one copy (N % 32 == 0)
+  int b_strips;        // strips per map_b_strips box, 0 when that map is not usable
   const float* a;      // generic loader only
   const float* b;
   const float* c;      // source, may be null when beta == 0
@@ -231,9 +233,14 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_c
           uint8_t* b_dst = a_dst + kASlabBytes;
           mbar_expect_tx(&sm.full[stage], stage_bytes<BN>());
           tma_load_2d(a_dst, &p.map_a, &sm.full[stage], kb * kStageK, tm * kTileM);
+          if (p.b_strips == BN / 32) {
+            // The producer thread's issue rate matters: one copy instead of BN / 32.
+            tma_load_3d(b_dst, &p.map_b_strips, &sm.full[stage], 0, kb * kStageK, tn * (BN / 32));
+          } else {
 #pragma unroll
-          for (int j = 0; j < BN / 32; ++j) {
-            tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &sm.full[stage], tn * BN + j * 32, kb * kStageK);
+            for (int j = 0; j < BN / 32; ++j) {
+              tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &sm.full[stage], tn * BN + j * 32, kb * kStageK);
+            }
           }
           if (++stage == STAGES) stage = 0, phase ^= 1u;
         }
@@ -368,9 +375,13 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
           uint8_t* a_dst = stages + static_cast<size_t>(stage) * kPairStageBytes;
           uint8_t* b_dst = a_dst + kASlabBytes;
           tma_load_2d_pair(a_dst, &p.map_a, full_addr, kb * kStageK, row0);
+          if (p.b_strips == kPairN / 2 / 32) {
+            tma_load_3d_pair(b_dst, &p.map_b_strips, full_addr, 0, kb * kStageK, col0 / 32);
+          } else {
 #pragma unroll
-          for (int j = 0; j < kPairN / 2 / 32; ++j) {
-            tma_load_2d_pair(b_dst + j * kBBoxBytes, &p.map_b, full_addr, col0 + j * 32, kb * kStageK);
+            for (int j = 0; j < kPairN / 2 / 32; ++j) {
+              tma_load_2d_pair(b_dst + j * kBBoxBytes, &p.map_b, full_addr, col0 + j * 32, kb * kStageK);
+            }
           }
           if (++stage == STAGES) stage = 0, phase ^= 1u;
         }
@@ -548,6 +559,11 @@ int launch_tma(const b200_gemm_problem& q, cudaStream_t stream) {
       !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
     return B200_ERR_MISALIGNED_OPERAND;
   }
+  // One copy per B slab when the columns split into whole 32-wide strips.
+  p.b_strips = (q.n % 32 == 0 && make_tensor_map_strips(&p.map_b_strips, q.b, q.k, q.n, q.ldb, kStageK, BN / 32,
+                                                        Swizzle::k128BAtom32B))
+                   ? BN / 32
+                   : 0;
   const int sms = sm_count();
   if (sms <= 0) return B200_ERR_INTERNAL;
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + BN - 1) / BN);
@@ -569,6 +585,10 @@ int launch_pair(const b200_gemm_problem& q, cudaStream_t stream) {
       !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
     return B200_ERR_MISALIGNED_OPERAND;
   }
+  p.b_strips = (q.n % 32 == 0 && make_tensor_map_strips(&p.map_b_strips, q.b, q.k, q.n, q.ldb, kStageK,
+                                                        kPairN / 2 / 32, Swizzle::k128BAtom32B))
+                   ? kPairN / 2 / 32
+                   : 0;
   const int sms = sm_count();
   if (sms < 2) return B200_ERR_INTERNAL;
   const int64_t tiles = static_cast<int64_t>((q.m + 2 * kTileM - 1) / (2 * kTileM)) * ((q.n + kPairN - 1) / kPairN);
@@ -635,14 +655,15 @@ int64_t tiles_of(const b200_gemm_problem& q, int tile_n) {
 
 bool gate_always(const b200_gemm_problem&, int) { return true; }
 // 128 x 256 tiles move a third fewer operand bytes per flop through L2, which
-// is what bounds this kernel; worth it once they still fill the GPU.
-bool gate_wide(const b200_gemm_problem& q, int sms) { return tiles_of(q, 256) >= sms; }
+// is what bounds this kernel; worth it once they occupy three quarters of the
+// SMs (measured at 2048^3: 128 tiles on 148 SMs beat both 128 x 128 tiles and
+// 64 CTA pairs).
+bool gate_wide(const b200_gemm_problem& q, int sms) { return tiles_of(q, 256) * 4 >= sms * 3; }
 // 128 x 64 tiles when 128-wide ones would leave more than half the SMs idle.
-// CTA pairs (256 x 256 per pair) once they occupy two thirds of the SM pairs:
-// measured at 2048^3 (64 tiles on 74 pairs) they already beat 128 x 128 tiles.
+// CTA pairs (256 x 256 per pair) when they fill at least one round of pairs.
 bool gate_pair(const b200_gemm_problem& q, int sms) {
   const int64_t tiles = static_cast<int64_t>((q.m + 255) / 256) * ((q.n + 255) / 256);
-  return tiles * 3 >= sms;
+  return tiles >= sms / 2;
 }
 bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) * 2 <= sms && q.n > 64; }
 

@@ -147,10 +147,14 @@ def test_auto_dispatch_order(abi):
     a, b, _ = oracle.adaptive_inputs(256, 256, 64)
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 18              # narrow
     assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 19
-    # Large problem: 256 x 256 CTA pairs fill at least one wave of pairs.
+    # Large problem: 256 x 256 CTA pairs fill at least one round of pairs.
     a, b, _ = oracle.adaptive_inputs(256 * 8, 256 * ((sms // 2 + 7) // 8), 64)
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 20              # pair
     assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 21
+    # In between: 128 x 256 tiles on at least three quarters of the SMs.
+    a, b, _ = oracle.adaptive_inputs(128 * 8, 256 * ((3 * sms // 4 + 7) // 8), 64)
+    assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 16              # wide
+    assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 17
     a, b, _ = oracle.adaptive_inputs(33, 65, 17)
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 3               # fallback
     assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 9  # fallback_relu
