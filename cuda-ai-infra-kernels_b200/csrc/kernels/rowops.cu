@@ -9,11 +9,12 @@
 //
 //   warp   : one warp per row, up to 8 x 128-bit vectors per lane
 //            (rows of <= 1024 floats); shuffle reductions only.
-//   block  : one 256-thread CTA per row, up to 8 vectors per thread
-//            (<= 8192 floats); shuffle + one shared-memory hop.
+//   block  : one CTA per row, up to 4 vectors per thread: 256 or 512 threads
+//            (<= 4096 / 8192 floats); shuffle + one shared-memory hop.
 //   cluster: 2/4/8 CTAs per row joined by a thread-block cluster; partial
-//            results are exchanged through distributed shared memory
-//            (<= 65536 floats).
+//            results are exchanged through distributed shared memory. 256
+//            threads and 4 vectors per thread up to 32768 floats, 8 vectors up
+//            to 65536, 1024 threads up to 262144.
 //   stream : any length / any alignment; re-reads the row (normally from L2).
 //
 // All offsets are 64-bit. 128-bit accesses are used only when the row length
@@ -31,6 +32,7 @@ namespace {
 constexpr int kMaxVec = 8;        // 128-bit vectors held per thread
 constexpr int kBlockThreads = 256;
 constexpr int kWarpsPerBlock = kBlockThreads / 32;
+constexpr int kBigBlockThreads = 1024;  // rows longer than 8192 floats, and every CTA of a cluster
 
 __device__ __forceinline__ float4 load_stream(const float4* p) { return __ldcs(p); }
 __device__ __forceinline__ void store_stream(float4* p, float4 v) { __stcs(p, v); }
@@ -67,46 +69,48 @@ struct WarpScope {
   }
 };
 
+template <int kWarps>
 struct BlockScope {
-  float* scratch;  // kWarpsPerBlock floats per reduction, two slots
+  float* scratch;  // kWarps floats per reduction, two slots
   int slot = 0;
   template <class Op>
   __device__ __forceinline__ float reduce(float v) {
     v = Op::warp(v);
-    float* s = scratch + slot * kWarpsPerBlock;
+    float* s = scratch + slot * kWarps;
     slot ^= 1;  // the next reduction uses the other slot: no trailing barrier needed
     if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
     __syncthreads();
     float r = Op::identity();
 #pragma unroll
-    for (int w = 0; w < kWarpsPerBlock; ++w) r = Op::combine(r, s[w]);
+    for (int w = 0; w < kWarps; ++w) r = Op::combine(r, s[w]);
     return r;
   }
 };
 
+template <int kWarps>
 struct ClusterScope {
-  float* scratch;   // kWarpsPerBlock floats + 1 per slot, two slots
+  float* scratch;   // kWarps floats + 1 per slot, two slots
   int slot = 0;
   template <class Op>
   __device__ __forceinline__ float reduce(float v) {
     cg::cluster_group cluster = cg::this_cluster();
     v = Op::warp(v);
-    float* s = scratch + slot * (kWarpsPerBlock + 1);
+    float* s = scratch + slot * (kWarps + 1);
     slot ^= 1;
     if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
     __syncthreads();
     if (threadIdx.x == 0) {
       float r = Op::identity();
 #pragma unroll
-      for (int w = 0; w < kWarpsPerBlock; ++w) r = Op::combine(r, s[w]);
-      s[kWarpsPerBlock] = r;  // this CTA's partial, read by its peers
+      for (int w = 0; w < kWarps; ++w) r = Op::combine(r, s[w]);
+      s[kWarps] = r;  // this CTA's partial, read by its peers
     }
     cluster.sync();
     float r = Op::identity();
     const unsigned ranks = cluster.num_blocks();
     for (unsigned peer = 0; peer < ranks; ++peer) {
       const float* remote = cluster.map_shared_rank(s, peer);
-      r = Op::combine(r, remote[kWarpsPerBlock]);
+      r = Op::combine(r, remote[kWarps]);
     }
     return r;
   }
@@ -210,26 +214,26 @@ __global__ void __launch_bounds__(kBlockThreads) row_warp_kernel(const RowArgs a
   }
 }
 
-template <RowOp kOp, int VPT>
-__global__ void __launch_bounds__(kBlockThreads) row_block_kernel(const RowArgs a) {
-  __shared__ float scratch[2 * kWarpsPerBlock];
+template <RowOp kOp, int VPT, int kThreads>
+__global__ void __launch_bounds__(kThreads) row_block_kernel(const RowArgs a) {
+  __shared__ float scratch[2 * (kThreads / 32)];
   const int64_t row = blockIdx.x;
   const int nvec = static_cast<int>(a.cols / 4);
   const float4* x_row = reinterpret_cast<const float4*>(a.x + row * a.cols);
   float4* y_row = reinterpret_cast<float4*>(a.y + row * a.cols);
-  BlockScope scope{scratch};
+  BlockScope<kThreads / 32> scope{scratch};
   if constexpr (kOp == RowOp::kRmsNorm) {
-    rmsnorm_row<VPT>(x_row, reinterpret_cast<const float4*>(a.w), y_row, nvec, threadIdx.x, kBlockThreads, a.cols,
-                     a.eps, scope);
+    rmsnorm_row<VPT>(x_row, reinterpret_cast<const float4*>(a.w), y_row, nvec, threadIdx.x, kThreads, a.cols, a.eps,
+                     scope);
   } else {
-    softmax_row<VPT>(x_row, y_row, nvec, threadIdx.x, kBlockThreads, scope);
+    softmax_row<VPT>(x_row, y_row, nvec, threadIdx.x, kThreads, scope);
   }
 }
 
 // One cluster per row; CTA `rank` owns vectors [rank * per_cta, ...).
-template <RowOp kOp>
-__global__ void __launch_bounds__(kBlockThreads) row_cluster_kernel(const RowArgs a) {
-  __shared__ float scratch[2 * (kWarpsPerBlock + 1)];
+template <RowOp kOp, int VPT, int kThreads>
+__global__ void __launch_bounds__(kThreads) row_cluster_kernel(const RowArgs a) {
+  __shared__ float scratch[2 * (kThreads / 32 + 1)];
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned ranks = cluster.num_blocks();
   const unsigned rank = cluster.block_rank();
@@ -240,12 +244,12 @@ __global__ void __launch_bounds__(kBlockThreads) row_cluster_kernel(const RowArg
   const int nvec = min(per_cta, nvec_row - begin);
   const float4* x_row = reinterpret_cast<const float4*>(a.x + row * a.cols) + begin;
   float4* y_row = reinterpret_cast<float4*>(a.y + row * a.cols) + begin;
-  ClusterScope scope{scratch};
+  ClusterScope<kThreads / 32> scope{scratch};
   if constexpr (kOp == RowOp::kRmsNorm) {
-    rmsnorm_row<kMaxVec>(x_row, reinterpret_cast<const float4*>(a.w) + begin, y_row, nvec, threadIdx.x,
-                         kBlockThreads, a.cols, a.eps, scope);
+    rmsnorm_row<VPT>(x_row, reinterpret_cast<const float4*>(a.w) + begin, y_row, nvec, threadIdx.x, kThreads, a.cols,
+                     a.eps, scope);
   } else {
-    softmax_row<kMaxVec>(x_row, y_row, nvec, threadIdx.x, kBlockThreads, scope);
+    softmax_row<VPT>(x_row, y_row, nvec, threadIdx.x, kThreads, scope);
   }
   scope.finish();
 }
@@ -257,14 +261,14 @@ __global__ void __launch_bounds__(kBlockThreads) row_stream_kernel(const RowArgs
   const int64_t row = blockIdx.x;
   const float* x_row = a.x + row * a.cols;
   float* y_row = a.y + row * a.cols;
-  BlockScope scope{scratch};
+  BlockScope<kWarpsPerBlock> scope{scratch};
   if constexpr (kOp == RowOp::kRmsNorm) {
     float ss = 0.f;
     for (int64_t c = threadIdx.x; c < a.cols; c += kBlockThreads) {
       const float v = x_row[c];
       ss += v * v;
     }
-    ss = scope.reduce<SumOp>(ss);
+    ss = scope.template reduce<SumOp>(ss);
     const float inv_rms = rsqrtf(static_cast<float>(static_cast<double>(ss / static_cast<float>(a.cols)) + a.eps));
     for (int64_t c = threadIdx.x; c < a.cols; c += kBlockThreads) y_row[c] = x_row[c] * a.w[c] * inv_rms;
   } else {
@@ -276,8 +280,8 @@ __global__ void __launch_bounds__(kBlockThreads) row_stream_kernel(const RowArgs
       sum = sum * __expf(mx - m2) + __expf(v - m2);
       mx = m2;
     }
-    const float row_max = scope.reduce<MaxOp>(mx);
-    sum = scope.reduce<SumOp>(sum * __expf(mx - row_max));
+    const float row_max = scope.template reduce<MaxOp>(mx);
+    sum = scope.template reduce<SumOp>(sum * __expf(mx - row_max));
     const float inv = __frcp_rn(sum);
     for (int64_t c = threadIdx.x; c < a.cols; c += kBlockThreads) y_row[c] = __expf(x_row[c] - row_max) * inv;
   }
@@ -292,17 +296,17 @@ int launch_warp(const RowArgs& a, cudaStream_t s) {
   return launch_status();
 }
 
-template <RowOp kOp, int VPT>
+template <RowOp kOp, int VPT, int kThreads>
 int launch_block(const RowArgs& a, cudaStream_t s) {
-  row_block_kernel<kOp, VPT><<<static_cast<unsigned>(a.rows), kBlockThreads, 0, s>>>(a);
+  row_block_kernel<kOp, VPT, kThreads><<<static_cast<unsigned>(a.rows), kThreads, 0, s>>>(a);
   return launch_status();
 }
 
-template <RowOp kOp>
+template <RowOp kOp, int VPT, int kThreads>
 int launch_cluster(const RowArgs& a, int ranks, cudaStream_t s) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(a.rows * ranks));
-  cfg.blockDim = dim3(kBlockThreads);
+  cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = s;
   cudaLaunchAttribute attr;
@@ -312,7 +316,7 @@ int launch_cluster(const RowArgs& a, int ranks, cudaStream_t s) {
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, row_cluster_kernel<kOp>, a) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  if (cudaLaunchKernelEx(&cfg, row_cluster_kernel<kOp, VPT, kThreads>, a) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
   return launch_status();
 }
 
@@ -327,14 +331,14 @@ int launch_by_vectors_warp(int vpt, const RowArgs& a, cudaStream_t s) {
   }
 }
 
-template <RowOp kOp>
+template <RowOp kOp, int kThreads>
 int launch_by_vectors_block(int vpt, const RowArgs& a, cudaStream_t s) {
   switch (vpt) {
-    case 1: return launch_block<kOp, 1>(a, s);
-    case 2: return launch_block<kOp, 2>(a, s);
-    case 3: case 4: return launch_block<kOp, 4>(a, s);
-    case 5: case 6: return launch_block<kOp, 6>(a, s);
-    default: return launch_block<kOp, 8>(a, s);
+    case 1: return launch_block<kOp, 1, kThreads>(a, s);
+    case 2: return launch_block<kOp, 2, kThreads>(a, s);
+    case 3: case 4: return launch_block<kOp, 4, kThreads>(a, s);
+    case 5: case 6: return launch_block<kOp, 6, kThreads>(a, s);
+    default: return launch_block<kOp, 8, kThreads>(a, s);
   }
 }
 
@@ -349,15 +353,21 @@ int launch_rows(const RowArgs& a, cudaStream_t s) {
   if (vector_ok && nvec <= 32 * kMaxVec) {
     return launch_by_vectors_warp<kOp>(static_cast<int>((nvec + 31) / 32), a, s);
   }
-  if (vector_ok && nvec <= kBlockThreads * kMaxVec) {
-    return launch_by_vectors_block<kOp>(static_cast<int>((nvec + kBlockThreads - 1) / kBlockThreads), a, s);
+  // Beyond one warp per row, many small CTAs work best: with at most four
+  // vectors per thread 2048 threads stay resident per SM, and the load phase of
+  // one CTA overlaps the store phase of another. Longer rows therefore get more
+  // CTAs (a cluster of 256-thread CTAs exchanging partials through DSMEM)
+  // rather than fatter ones; only the longest rows use eight vectors per thread
+  // and 1024-thread CTAs.
+  constexpr int kLightVec = 4;
+  if (vector_ok && nvec <= 256 * kLightVec) return launch_by_vectors_block<kOp, 256>(static_cast<int>((nvec + 255) / 256), a, s);
+  if (vector_ok && nvec <= 512 * kLightVec) return launch_by_vectors_block<kOp, 512>(static_cast<int>((nvec + 511) / 512), a, s);
+  if (vector_ok && nvec <= 8 * 256 * kLightVec) {
+    const int needed = static_cast<int>((nvec + 256 * kLightVec - 1) / (256 * kLightVec));
+    return launch_cluster<kOp, kLightVec, 256>(a, needed <= 2 ? 2 : (needed <= 4 ? 4 : 8), s);
   }
-  if (vector_ok && nvec <= 8 * kBlockThreads * kMaxVec) {
-    const int64_t per_cluster_cta = kBlockThreads * kMaxVec;
-    const int needed = static_cast<int>((nvec + per_cluster_cta - 1) / per_cluster_cta);
-    const int ranks = needed <= 2 ? 2 : (needed <= 4 ? 4 : 8);
-    return launch_cluster<kOp>(a, ranks, s);
-  }
+  if (vector_ok && nvec <= 8 * 256 * kMaxVec) return launch_cluster<kOp, kMaxVec, 256>(a, 8, s);
+  if (vector_ok && nvec <= 8 * kBigBlockThreads * kMaxVec) return launch_cluster<kOp, kMaxVec, kBigBlockThreads>(a, 8, s);
   row_stream_kernel<kOp><<<static_cast<unsigned>(a.rows), kBlockThreads, 0, s>>>(a);
   return launch_status();
 }

@@ -10,10 +10,12 @@ from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
-# (rows, cols): warp path, block path, cluster path (2/4/8 CTAs), streaming
-# path, lengths that are not a multiple of four, single row / single column.
+# (rows, cols): warp path (<= 1024), block path (256 / 512 threads, <= 4096 /
+# 8192), cluster paths (2/4/8 CTAs, <= 32768 / 65536 / 262144), streaming path,
+# lengths that are not a multiple of four, single row / single column.
 SHAPES = [(16, 128), (16, 768), (32, 1024), (33, 516), (8, 2048), (8, 4096), (5, 8192), (4, 12288), (3, 16384),
-          (3, 33000), (2, 65536), (2, 70000), (5, 1001), (7, 3), (1, 1), (300, 4), (0, 16)]
+          (3, 32768), (3, 33000), (2, 65536), (2, 70000), (2, 140000), (1, 262144), (1, 300000), (5, 1001), (7, 3),
+          (1, 1), (300, 4), (0, 16)]
 
 
 def rmsnorm(abi, x, w, eps, impl=0):
