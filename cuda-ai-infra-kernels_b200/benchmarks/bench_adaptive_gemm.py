@@ -32,6 +32,7 @@ from cuda_ai_kernels.env import collect_env  # noqa: E402
 LINEAR_KERNELS = ["auto", "pair", "wide", "narrow", "fast", "fallback", "fast_mwarp", "fallback_mwarp", "fast_stage3",
                   "fast_stage2", "cublas"]
 RELU_KERNELS = ["auto", "pair_relu", "wide_relu", "narrow_relu", "fast_relu", "fallback_relu", "cublas"]
+GELU_KERNELS = ["auto", "pair_gelu", "wide_gelu", "narrow_gelu", "fast_gelu", "fallback_gelu"]
 REL_FROBENIUS = 5e-3
 
 
@@ -68,7 +69,10 @@ def benchmark_problem(m: int, n: int, k: int, args) -> dict:
         expected = expected + args.beta * c.double()
     if args.epilogue == "relu":
         expected = expected.relu()
-    names = (RELU_KERNELS if args.epilogue == "relu" else LINEAR_KERNELS) if args.kernel == "all" else [args.kernel]
+    elif args.epilogue == "gelu":
+        expected = torch.nn.functional.gelu(expected)
+    by_epilogue = {"linear": LINEAR_KERNELS, "relu": RELU_KERNELS, "gelu": GELU_KERNELS}
+    names = by_epilogue[args.epilogue] if args.kernel == "all" else [args.kernel]
     timer = cuda_graph_benchmark if args.timing == "graph" else cuda_event_benchmark
     peak, peak_source = tf32_peak_tflops()
     flops = 2.0 * m * n * k
@@ -112,7 +116,7 @@ def main(argv=None) -> dict:
     parser.add_argument("--sizes", default="1024,4096,8192")
     parser.add_argument("--shape", default="")
     parser.add_argument("--kernel", default="all")
-    parser.add_argument("--epilogue", choices=["linear", "relu"], default="relu")
+    parser.add_argument("--epilogue", choices=["linear", "relu", "gelu"], default="relu")
     parser.add_argument("--alpha", type=float, default=1.0)
     parser.add_argument("--beta", type=float, default=0.5)
     parser.add_argument("--timing", choices=["graph", "event"], default="graph")

@@ -58,6 +58,7 @@ struct UmmaParams {
   const float* a;      // generic loader only
   const float* b;
   const float* c;      // source, may be null when beta == 0
+  const float* bias;   // [N] added to every row before the activation, or null
   float* d;
   int64_t lda, ldb, ldc, ldd;
   int m, n, k;
@@ -109,15 +110,24 @@ __device__ __forceinline__ void issue_stage_mmas(uint32_t tmem_acc, uint32_t a_a
   }
 }
 
+// Activation applied last: after scaling, source add and bias.
+template <int kAct>
+__device__ __forceinline__ float activate(float v) {
+  if constexpr (kAct == B200_EPILOGUE_RELU) return fmaxf(v, 0.f);
+  if constexpr (kAct == B200_EPILOGUE_GELU) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));  // exact (erf) GELU
+  return v;
+}
+
 // Epilogue of one 128 x BN tile for one warp: TMEM lanes [32 * quarter, +32)
 // are rows m0 + 32 * quarter + lane. Each thread owns one row and walks it in
 // chunks of 32 columns.
-template <int BN, bool kRelu>
+template <int BN, int kAct>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem_acc, int quarter, int lane, int m0,
                                               int n0) {
   const int row = m0 + quarter * 32 + lane;
   const bool row_ok = row < p.m;
   const bool use_c = p.beta != 0.f;
+  const bool use_bias = p.bias != nullptr;
   const float* c_row = p.c + static_cast<int64_t>(row) * p.ldc;
   float* d_row = p.d + static_cast<int64_t>(row) * p.ldd;
 #pragma unroll 1
@@ -141,7 +151,11 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
             v.x = fmaf(p.beta, s.x, v.x), v.y = fmaf(p.beta, s.y, v.y);
             v.z = fmaf(p.beta, s.z, v.z), v.w = fmaf(p.beta, s.w, v.w);
           }
-          if (kRelu) v = make_float4(fmaxf(v.x, 0.f), fmaxf(v.y, 0.f), fmaxf(v.z, 0.f), fmaxf(v.w, 0.f));
+          if (use_bias) {
+            const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+            v.x += bv.x, v.y += bv.y, v.z += bv.z, v.w += bv.w;
+          }
+          v = make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
           *reinterpret_cast<float4*>(d_row + col) = v;
         }
       }
@@ -152,7 +166,8 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
         if (col < p.n) {
           float v = p.alpha * __uint_as_float(raw[e]);
           if (use_c) v = fmaf(p.beta, __ldg(c_row + col), v);
-          if (kRelu) v = fmaxf(v, 0.f);
+          if (use_bias) v += __ldg(p.bias + col);
+          v = activate<kAct>(v);
           d_row[col] = v;
         }
       }
@@ -186,7 +201,7 @@ __device__ __forceinline__ SmemCarve carve(uint8_t* raw) {
 // warps 2-5: epilogue; warp w reads the TMEM lane quarter w % 4.
 constexpr int kTmaThreads = 6 * 32;
 
-template <int BN, int STAGES, bool kRelu>
+template <int BN, int STAGES, int kAct>
 __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
   const SmemCarve sm = carve<BN, STAGES>(smem_raw);
@@ -281,7 +296,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_c
       tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
       if (!mbar_wait(&sm.acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
-      epilogue_tile<BN, kRelu>(p, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN);
+      epilogue_tile<BN, kAct>(p, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN);
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
@@ -313,7 +328,7 @@ __host__ __device__ constexpr size_t pair_smem_bytes() {
   return static_cast<size_t>(STAGES) * kPairStageBytes + 1024 + 256;
 }
 
-template <int STAGES, bool kRelu>
+template <int STAGES, int kAct>
 __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
   // Same carve-up in both CTAs: the MMA addresses the peer's shared memory by
@@ -433,7 +448,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
       tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
       if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
-      epilogue_tile<kPairN, kRelu>(p, tmem_base + buf * kPairN, quarter, lane,
+      epilogue_tile<kPairN, kAct>(p, tmem_base + buf * kPairN, quarter, lane,
                                    tm * 2 * kTileM + static_cast<int>(rank) * kTileM, tn * kPairN);
       tcgen05_fence_before_sync();
       __syncwarp();
@@ -477,7 +492,7 @@ __device__ __forceinline__ void fill_stage(const UmmaParams& p, uint8_t* a_dst, 
   }
 }
 
-template <int BN, bool kRelu>
+template <int BN, int kAct>
 __global__ void __launch_bounds__(kGenericThreads) umma_generic_kernel(const __grid_constant__ UmmaParams p) {
   constexpr int STAGES = 2;
   extern __shared__ uint8_t smem_raw[];
@@ -521,7 +536,7 @@ __global__ void __launch_bounds__(kGenericThreads) umma_generic_kernel(const __g
   if (ok) ok = mbar_wait(&sm.acc_full[0], 0, kSiteUmmaAccFull);
   if (ok) {
     tcgen05_fence_after_sync();
-    epilogue_tile<BN, kRelu>(p, tmem_base, warp, lane, m0, n0);
+    epilogue_tile<BN, kAct>(p, tmem_base, warp, lane, m0, n0);
   }
   tcgen05_fence_before_sync();
   __syncthreads();
@@ -539,16 +554,18 @@ void fill_common(UmmaParams* p, const b200_gemm_problem& q) {
   std::memset(p, 0, sizeof(*p));
   p->a = q.a, p->b = q.b, p->d = q.d;
   p->c = q.beta != 0.f ? q.c : nullptr;
+  p->bias = q.bias;
   p->lda = q.lda, p->ldb = q.ldb, p->ldc = q.ldc, p->ldd = q.ldd;
   p->m = q.m, p->n = q.n, p->k = q.k;
   p->alpha = q.alpha, p->beta = q.beta;
   const bool c_ok = q.beta == 0.f || (aligned16(q.c) && q.ldc % 4 == 0);
-  p->vector_io = (q.n % 4 == 0 && aligned16(q.d) && q.ldd % 4 == 0 && c_ok) ? 1 : 0;
+  const bool bias_ok = q.bias == nullptr || aligned16(q.bias);
+  p->vector_io = (q.n % 4 == 0 && aligned16(q.d) && q.ldd % 4 == 0 && c_ok && bias_ok) ? 1 : 0;
 }
 
-template <int BN, int STAGES, bool kRelu>
+template <int BN, int STAGES, int kAct>
 int launch_tma(const b200_gemm_problem& q, cudaStream_t stream) {
-  auto kernel = umma_tma_kernel<BN, STAGES, kRelu>;
+  auto kernel = umma_tma_kernel<BN, STAGES, kAct>;
   constexpr size_t smem = smem_bytes<BN, STAGES>();
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
@@ -572,9 +589,9 @@ int launch_tma(const b200_gemm_problem& q, cudaStream_t stream) {
   return launch_status();
 }
 
-template <int STAGES, bool kRelu>
+template <int STAGES, int kAct>
 int launch_pair(const b200_gemm_problem& q, cudaStream_t stream) {
-  auto kernel = umma_pair_kernel<STAGES, kRelu>;
+  auto kernel = umma_pair_kernel<STAGES, kAct>;
   constexpr size_t smem = pair_smem_bytes<STAGES>();
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
@@ -609,9 +626,9 @@ int launch_pair(const b200_gemm_problem& q, cudaStream_t stream) {
   return launch_status();
 }
 
-template <int BN, bool kRelu>
+template <int BN, int kAct>
 int launch_generic(const b200_gemm_problem& q, cudaStream_t stream) {
-  auto kernel = umma_generic_kernel<BN, kRelu>;
+  auto kernel = umma_generic_kernel<BN, kAct>;
   constexpr size_t smem = smem_bytes<BN, 2>();
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
@@ -676,20 +693,26 @@ bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) 
 // the generic loader). What distinguished the reference's variants (warp
 // shape, stage count) maps onto tile width and pipeline depth.
 const RegistryEntry kRegistry[] = {
-    {meta_pair(20, "umma256x256stage6pair", "pair", B200_EPILOGUE_LINEAR, 6), &launch_pair<6, false>, &gate_pair},
-    {meta_pair(21, "umma256x256stage6pairRelu", "pair_relu", B200_EPILOGUE_RELU, 6), &launch_pair<6, true>, &gate_pair},
-    {meta(16, "umma128x256stage4tma", "wide", B200_EPILOGUE_LINEAR, 256, 4, 4), &launch_tma<256, 4, false>, &gate_wide},
-    {meta(17, "umma128x256stage4tmaRelu", "wide_relu", B200_EPILOGUE_RELU, 256, 4, 4), &launch_tma<256, 4, true>, &gate_wide},
-    {meta(18, "umma128x64stage6tma", "narrow", B200_EPILOGUE_LINEAR, 64, 6, 4), &launch_tma<64, 6, false>, &gate_narrow},
-    {meta(19, "umma128x64stage6tmaRelu", "narrow_relu", B200_EPILOGUE_RELU, 64, 6, 4), &launch_tma<64, 6, true>, &gate_narrow},
-    {meta(2, "umma128x128stage4tma", "fast", B200_EPILOGUE_LINEAR, 128, 4, 4), &launch_tma<128, 4, false>, &gate_always},
-    {meta(3, "umma128x128generic", "fallback", B200_EPILOGUE_LINEAR, 128, 2, 1), &launch_generic<128, false>, &gate_always},
-    {meta(4, "umma128x64stage4tma", "fast_mwarp", B200_EPILOGUE_LINEAR, 64, 4, 4), &launch_tma<64, 4, false>, &gate_always},
-    {meta(5, "umma128x64generic", "fallback_mwarp", B200_EPILOGUE_LINEAR, 64, 2, 1), &launch_generic<64, false>, &gate_always},
-    {meta(6, "umma128x128stage3tma", "fast_stage3", B200_EPILOGUE_LINEAR, 128, 3, 4), &launch_tma<128, 3, false>, &gate_always},
-    {meta(7, "umma128x128stage2tma", "fast_stage2", B200_EPILOGUE_LINEAR, 128, 2, 4), &launch_tma<128, 2, false>, &gate_always},
-    {meta(8, "umma128x128stage4tmaRelu", "fast_relu", B200_EPILOGUE_RELU, 128, 4, 4), &launch_tma<128, 4, true>, &gate_always},
-    {meta(9, "umma128x128genericRelu", "fallback_relu", B200_EPILOGUE_RELU, 128, 2, 1), &launch_generic<128, true>, &gate_always},
+    {meta_pair(20, "umma256x256stage6pair", "pair", B200_EPILOGUE_LINEAR, 6), &launch_pair<6, B200_EPILOGUE_LINEAR>, &gate_pair},
+    {meta_pair(21, "umma256x256stage6pairRelu", "pair_relu", B200_EPILOGUE_RELU, 6), &launch_pair<6, B200_EPILOGUE_RELU>, &gate_pair},
+    {meta(16, "umma128x256stage4tma", "wide", B200_EPILOGUE_LINEAR, 256, 4, 4), &launch_tma<256, 4, B200_EPILOGUE_LINEAR>, &gate_wide},
+    {meta(17, "umma128x256stage4tmaRelu", "wide_relu", B200_EPILOGUE_RELU, 256, 4, 4), &launch_tma<256, 4, B200_EPILOGUE_RELU>, &gate_wide},
+    {meta(18, "umma128x64stage6tma", "narrow", B200_EPILOGUE_LINEAR, 64, 6, 4), &launch_tma<64, 6, B200_EPILOGUE_LINEAR>, &gate_narrow},
+    {meta(19, "umma128x64stage6tmaRelu", "narrow_relu", B200_EPILOGUE_RELU, 64, 6, 4), &launch_tma<64, 6, B200_EPILOGUE_RELU>, &gate_narrow},
+    {meta_pair(22, "umma256x256stage6pairGelu", "pair_gelu", B200_EPILOGUE_GELU, 6), &launch_pair<6, B200_EPILOGUE_GELU>, &gate_pair},
+    {meta(23, "umma128x256stage4tmaGelu", "wide_gelu", B200_EPILOGUE_GELU, 256, 4, 4), &launch_tma<256, 4, B200_EPILOGUE_GELU>, &gate_wide},
+    {meta(24, "umma128x64stage6tmaGelu", "narrow_gelu", B200_EPILOGUE_GELU, 64, 6, 4), &launch_tma<64, 6, B200_EPILOGUE_GELU>, &gate_narrow},
+    {meta(2, "umma128x128stage4tma", "fast", B200_EPILOGUE_LINEAR, 128, 4, 4), &launch_tma<128, 4, B200_EPILOGUE_LINEAR>, &gate_always},
+    {meta(3, "umma128x128generic", "fallback", B200_EPILOGUE_LINEAR, 128, 2, 1), &launch_generic<128, B200_EPILOGUE_LINEAR>, &gate_always},
+    {meta(4, "umma128x64stage4tma", "fast_mwarp", B200_EPILOGUE_LINEAR, 64, 4, 4), &launch_tma<64, 4, B200_EPILOGUE_LINEAR>, &gate_always},
+    {meta(5, "umma128x64generic", "fallback_mwarp", B200_EPILOGUE_LINEAR, 64, 2, 1), &launch_generic<64, B200_EPILOGUE_LINEAR>, &gate_always},
+    {meta(6, "umma128x128stage3tma", "fast_stage3", B200_EPILOGUE_LINEAR, 128, 3, 4), &launch_tma<128, 3, B200_EPILOGUE_LINEAR>, &gate_always},
+    {meta(7, "umma128x128stage2tma", "fast_stage2", B200_EPILOGUE_LINEAR, 128, 2, 4), &launch_tma<128, 2, B200_EPILOGUE_LINEAR>, &gate_always},
+    {meta(8, "umma128x128stage4tmaRelu", "fast_relu", B200_EPILOGUE_RELU, 128, 4, 4), &launch_tma<128, 4, B200_EPILOGUE_RELU>, &gate_always},
+    {meta(9, "umma128x128genericRelu", "fallback_relu", B200_EPILOGUE_RELU, 128, 2, 1), &launch_generic<128, B200_EPILOGUE_RELU>, &gate_always},
+    // GELU has no entry in the reference registry (the epilogue is parsed but refused there).
+    {meta(25, "umma128x128stage4tmaGelu", "fast_gelu", B200_EPILOGUE_GELU, 128, 4, 4), &launch_tma<128, 4, B200_EPILOGUE_GELU>, &gate_always},
+    {meta(26, "umma128x128genericGelu", "fallback_gelu", B200_EPILOGUE_GELU, 128, 2, 1), &launch_generic<128, B200_EPILOGUE_GELU>, &gate_always},
 };
 constexpr int kRegistrySize = sizeof(kRegistry) / sizeof(kRegistry[0]);
 
@@ -710,7 +733,9 @@ int check_problem(const b200_gemm_problem* q) {
   if (q->m <= 0 || q->n <= 0 || q->k <= 0) return B200_ERR_INVALID_ARGUMENT;
   if (q->lda < q->k || q->ldb < q->n || q->ldd < q->n) return B200_ERR_INVALID_ARGUMENT;
   if (q->beta != 0.f && (q->c == nullptr || q->ldc < q->n)) return B200_ERR_INVALID_ARGUMENT;
-  if (q->epilogue != B200_EPILOGUE_LINEAR && q->epilogue != B200_EPILOGUE_RELU) return B200_ERR_INVALID_ARGUMENT;
+  if (q->epilogue != B200_EPILOGUE_LINEAR && q->epilogue != B200_EPILOGUE_RELU && q->epilogue != B200_EPILOGUE_GELU) {
+    return B200_ERR_INVALID_ARGUMENT;
+  }
   return B200_OK;
 }
 

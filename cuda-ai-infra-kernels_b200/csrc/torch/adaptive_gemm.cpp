@@ -1,5 +1,5 @@
 // PyTorch-facing launcher of `cuda_ai_kernels.adaptive_gemm`:
-//   D = alpha * A @ B + beta * C, optionally followed by ReLU,
+//   D = act(alpha * A @ B + beta * C [+ bias]),  act in {identity, ReLU, GELU},
 // all operands row-major FP32, products on the tensor cores in TF32.
 // Validation order, accepted strings and error texts follow
 // csrc/adaptive_gemm/adaptive_gemm.cu:14-174; the kernel choice is delegated to
@@ -18,17 +18,22 @@ using b200_torch::current_stream;
 
 thread_local std::string g_last_kernel;
 
-// Epilogue spellings the reference parses (adaptive_gemm.cu:39-59). Only the
-// first two have kernels; the rest are recognised so that they are refused
-// with the "supports only" message rather than as unknown strings.
-enum class ParsedEpilogue { kLinear, kRelu, kRecognisedButUnsupported };
+// Epilogue spellings the reference parses (adaptive_gemm.cu:39-59). The
+// reference runs only "linear" and "relu" and refuses the rest at run time
+// (adaptive_gemm.cu:124-133); here all six run: the bias term and the GELU are
+// applied in the same TMEM -> register pass as the scaling.
+struct ParsedEpilogue {
+  int activation;   // b200_epilogue
+  bool wants_bias;
+};
 
 ParsedEpilogue parse_epilogue(const std::string& value) {
-  if (value == "linear") return ParsedEpilogue::kLinear;
-  if (value == "relu") return ParsedEpilogue::kRelu;
-  if (value == "bias" || value == "gelu" || value == "bias_relu" || value == "bias_gelu") {
-    return ParsedEpilogue::kRecognisedButUnsupported;
-  }
+  if (value == "linear") return {B200_EPILOGUE_LINEAR, false};
+  if (value == "relu") return {B200_EPILOGUE_RELU, false};
+  if (value == "gelu") return {B200_EPILOGUE_GELU, false};
+  if (value == "bias") return {B200_EPILOGUE_LINEAR, true};
+  if (value == "bias_relu") return {B200_EPILOGUE_RELU, true};
+  if (value == "bias_gelu") return {B200_EPILOGUE_GELU, true};
   TORCH_CHECK(false, "unsupported epilogue: ", value);
 }
 
@@ -98,17 +103,24 @@ torch::Tensor adaptive_gemm(const torch::Tensor& a, const torch::Tensor& b, cons
   check_ab(a, b);
   const ParsedEpilogue parsed = parse_epilogue(epilogue);
   const int requested = parse_kernel(kernel);
-  TORCH_CHECK(parsed != ParsedEpilogue::kRecognisedButUnsupported,
-              "adaptive_gemm currently supports only the linear and relu epilogues");
-  TORCH_CHECK(requested != B200_TF32_KERNEL_CUBLAS || parsed == ParsedEpilogue::kLinear,
+  const bool has_bias = bias.has_value() && bias->defined();
+  TORCH_CHECK(requested != B200_TF32_KERNEL_CUBLAS || (parsed.activation == B200_EPILOGUE_LINEAR && !parsed.wants_bias),
               "adaptive_gemm kernel='cublas' supports only the linear epilogue; "
               "apply torch.relu to its output for an unfused ReLU baseline");
-  TORCH_CHECK(!(bias.has_value() && bias->defined()), "adaptive_gemm bias fusion is not implemented yet");
+  TORCH_CHECK(has_bias == parsed.wants_bias,
+              parsed.wants_bias ? "bias is required by the '" : "a bias tensor needs a bias epilogue, not '", epilogue,
+              "' epilogue");
 
   const int64_t m = a.size(0), n = b.size(1);
   const bool has_c = c.has_value() && c->defined();
   TORCH_CHECK(has_c || beta == 0.0, "C is required when beta is non-zero");
   if (has_c) check_source(*c, a, m, n);
+  if (has_bias) {
+    B200_CHECK_INPUT((*bias));
+    B200_CHECK_FLOAT32((*bias));
+    TORCH_CHECK(bias->device() == a.device(), "bias must be on the same CUDA device as A");
+    TORCH_CHECK(bias->dim() == 1 && bias->size(0) == n, "bias must have shape [", n, "] but got ", bias->sizes());
+  }
 
   const c10::cuda::CUDAGuard guard(a.device());
   auto d = torch::empty({m, n}, a.options());
@@ -122,7 +134,8 @@ torch::Tensor adaptive_gemm(const torch::Tensor& a, const torch::Tensor& b, cons
   q.lda = a.stride(0), q.ldb = b.stride(0), q.ldd = d.stride(0);
   q.ldc = has_c ? c->stride(0) : d.stride(0);
   q.alpha = static_cast<float>(alpha), q.beta = static_cast<float>(beta);
-  q.epilogue = parsed == ParsedEpilogue::kRelu ? B200_EPILOGUE_RELU : B200_EPILOGUE_LINEAR;
+  q.epilogue = parsed.activation;
+  q.bias = has_bias ? bias->data_ptr<float>() : nullptr;
   constexpr int64_t kIntMax = std::numeric_limits<int>::max();
   TORCH_CHECK(q.lda <= kIntMax && q.ldb <= kIntMax && q.ldc <= kIntMax && q.ldd <= kIntMax,
               "leading dimension exceeds the int32 range");

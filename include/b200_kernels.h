@@ -132,10 +132,18 @@ int b200_sgemm(int impl, const float* a_colmajor, const float* b, float* c,
 
 /* ------------------------------------------- TF32 tensor-core GEMM + epilogue */
 
-/* Epilogues of csrc/adaptive_gemm/gemm_problem.h:6-15 that have kernels. */
+/*
+ * Epilogues of csrc/adaptive_gemm/gemm_problem.h:6-15 that have kernels. With
+ * z = alpha * A*B + beta * C (+ bias[n] when the problem carries a bias):
+ * Linear, Relu are the two the reference implements; Gelu (exact, erf-based)
+ * and the bias term are declared by the reference (EpilogueKind::Gelu, ::Bias,
+ * ::BiasRelu, ::BiasGelu, parse_epilogue in adaptive_gemm.cu:39-59) but refused
+ * at run time there (adaptive_gemm.cu:124-133).
+ */
 typedef enum b200_epilogue {
-  B200_EPILOGUE_LINEAR = 0, /* D = alpha * A*B + beta * C           */
-  B200_EPILOGUE_RELU = 1    /* D = max(0, alpha * A*B + beta * C)   */
+  B200_EPILOGUE_LINEAR = 0, /* D = z            */
+  B200_EPILOGUE_RELU = 1,   /* D = max(0, z)    */
+  B200_EPILOGUE_GELU = 2    /* D = 0.5 z (1 + erf(z / sqrt 2)) */
 } b200_epilogue;
 
 /*
@@ -143,6 +151,8 @@ typedef enum b200_epilogue {
  * (csrc/adaptive_gemm/gemm_problem.h:17-57). All matrices are row-major FP32:
  * A [M,K] with leading dimension lda, B [K,N] ldb, C [M,N] ldc (source, read
  * only, never dereferenced when beta == 0), D [M,N] ldd (destination).
+ * `bias` is NULL or a vector of N floats added to every row before the
+ * activation (EpilogueDesc::bias, gemm_problem.h:17-23).
  */
 typedef struct b200_gemm_problem {
   int m, n, k;
@@ -153,6 +163,7 @@ typedef struct b200_gemm_problem {
   int64_t lda, ldb, ldc, ldd;
   float alpha, beta;
   int epilogue; /* b200_epilogue */
+  const float* bias;
 } b200_gemm_problem;
 
 /*

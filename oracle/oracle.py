@@ -34,8 +34,8 @@ def gemm_fp64(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 def adaptive_gemm_fp64(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, alpha: float = 1.0,
-                       beta: float = 0.0, epilogue: str = "linear") -> torch.Tensor:
-    """``alpha * A @ B + beta * C`` then optional ReLU, in FP64, cast to FP32.
+                       beta: float = 0.0, epilogue: str = "linear", bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(alpha * A @ B + beta * C [+ bias])`` in FP64, cast to FP32.
 
     Reference: tests/test_adaptive_gemm.py:221-224 (ReLU applied after scaling
     and source add) and benchmarks/bench_adaptive_gemm.py:38-46. alpha and beta
@@ -43,7 +43,21 @@ def adaptive_gemm_fp64(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tenso
     (csrc/adaptive_gemm/adaptive_gemm.cu:163-164). With beta == 0 the source is
     not read at all, so a NaN-filled C must not propagate
     (tests/test_adaptive_gemm.py:247-254).
+
+    ``gelu`` and the ``bias*`` epilogues are named by the reference
+    (adaptive_gemm.cu:39-59) but refused by it at run time, so it holds no
+    expression or vector for them. They are stated here with the meaning of the
+    CUTLASS functors its kernel_config.h:41-46 aliases: the bias is a length-N
+    vector added to every row before the activation, GELU is the exact
+    erf-based form ``0.5 z (1 + erf(z / sqrt 2))``.
     """
+    kinds = {"linear": ("linear", False), "relu": ("relu", False), "gelu": ("gelu", False),
+             "bias": ("linear", True), "bias_relu": ("relu", True), "bias_gelu": ("gelu", True)}
+    if epilogue not in kinds:
+        raise ValueError(f"unsupported epilogue: {epilogue}")
+    activation, wants_bias = kinds[epilogue]
+    if wants_bias != (bias is not None):
+        raise ValueError("bias tensor and epilogue do not agree")
     alpha32 = float(torch.tensor(alpha, dtype=torch.float32))
     beta32 = float(torch.tensor(beta, dtype=torch.float32))
     out = alpha32 * (a.detach().cpu().double() @ b.detach().cpu().double())
@@ -51,10 +65,12 @@ def adaptive_gemm_fp64(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tenso
         if c is None:
             raise ValueError("C is required when beta is non-zero")
         out = out + beta32 * c.detach().cpu().double()
-    if epilogue == "relu":
+    if bias is not None:
+        out = out + bias.detach().cpu().double()[None, :]
+    if activation == "relu":
         out = torch.relu(out)
-    elif epilogue != "linear":
-        raise ValueError(f"unsupported epilogue: {epilogue}")
+    elif activation == "gelu":
+        out = 0.5 * out * (1.0 + torch.erf(out / math.sqrt(2.0)))
     return out.float()
 
 

@@ -39,6 +39,7 @@ class GemmProblem(ctypes.Structure):
         ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldc", ctypes.c_int64), ("ldd", ctypes.c_int64),
         ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
         ("epilogue", ctypes.c_int),
+        ("bias", ctypes.c_void_p),
     ]
 
 

@@ -100,10 +100,14 @@ def registry(abi):
 
 def test_registry_keeps_the_reference_ids_aliases_and_order(abi):
     entries = registry(abi)
-    # Configurations that exist only here come first; the reference's eight
-    # follow in the reference's order.
-    own = [e for e in entries if e.id >= 16]
-    assert entries[:len(own)] == own or [e.id for e in entries[:len(own)]] == [e.id for e in own]
+    # Shape-gated configurations that exist only here come first, then the
+    # reference's eight as one block in the reference's order, then the entries
+    # that close the dispatch order for GELU (which the reference never runs).
+    ids = [e.id for e in entries]
+    first, last = ids.index(2), ids.index(9)
+    assert ids[first:last + 1] == [2, 3, 4, 5, 6, 7, 8, 9]
+    assert all(i >= 16 for i in ids[:first] + ids[last + 1:])
+    assert all(e.epilogue == 2 for e in entries[last + 1:])
     reference = [e for e in entries if e.id < 16]
     head = [(e.id, e.alias.decode(), e.epilogue, e.alignment_a) for e in reference]
     assert head == [
@@ -151,6 +155,10 @@ def test_can_implement_alignment_rules(abi):
     assert abi.b200_tf32_can_implement(fast_relu, ctypes.byref(problem(128, 128, 64, epilogue=1))) == OK
     assert abi.b200_tf32_can_implement(fast_relu, ctypes.byref(problem(128, 128, 64, epilogue=0))) == NOT_SUPPORTED
     # Malformed problems.
+    gelu = abi.b200_tf32_kernel_from_name(b"fast_gelu")
+    assert gelu == 25 and abi.b200_tf32_can_implement(gelu, ctypes.byref(problem(128, 128, 64, epilogue=2))) == OK
+    assert abi.b200_tf32_can_implement(gelu, ctypes.byref(problem(128, 128, 64, epilogue=1))) == NOT_SUPPORTED
+    assert abi.b200_tf32_can_implement(fast, ctypes.byref(problem(128, 128, 64, epilogue=3))) == INVALID_ARGUMENT
     assert abi.b200_tf32_can_implement(fast, ctypes.byref(problem(0, 128, 64))) == INVALID_ARGUMENT
     assert abi.b200_tf32_can_implement(fast, ctypes.byref(problem(128, 128, 64, c=0, beta=1.0))) == INVALID_ARGUMENT
     assert abi.b200_tf32_can_implement(fast, ctypes.byref(problem(128, 128, 64, lda=60))) == INVALID_ARGUMENT

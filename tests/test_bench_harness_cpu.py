@@ -157,9 +157,10 @@ def test_kernel_lists_cover_the_registry_aliases(adaptive_harness, abi):
     from conftest import KernelMeta
 
     module, _ = adaptive_harness
-    aliases = {0: set(), 1: set()}
+    aliases = {0: set(), 1: set(), 2: set()}
     for i in range(abi.b200_tf32_registry_size()):
         meta = KernelMeta()
         abi.b200_tf32_registry_entry(i, ctypes.byref(meta))
         aliases[meta.epilogue].add(meta.alias.decode())
     assert aliases[0] <= set(module.LINEAR_KERNELS) and aliases[1] <= set(module.RELU_KERNELS)
+    assert aliases[2] <= set(module.GELU_KERNELS)

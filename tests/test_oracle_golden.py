@@ -46,6 +46,26 @@ def test_adaptive_oracle_ignores_nan_source_when_beta_is_zero():
     torch.testing.assert_close(actual, b.relu(), atol=0, rtol=0)
 
 
+def test_adaptive_oracle_bias_and_gelu_agree_with_torch_functional():
+    # No reference vectors exist for these epilogues (the reference refuses them);
+    # the oracle is cross-checked against PyTorch's own FP64 GELU instead.
+    a, b, c = t("adaptive_a"), t("adaptive_b"), t("adaptive_c")
+    bias = torch.linspace(-1, 1, b.shape[1])
+    z = 0.75 * (a.double() @ b.double()) + 0.25 * c.double()
+    torch.testing.assert_close(oracle.adaptive_gemm_fp64(a, b, c, 0.75, 0.25, "gelu"),
+                               torch.nn.functional.gelu(z).float(), atol=0, rtol=1e-6)
+    zb = z + bias.double()
+    torch.testing.assert_close(oracle.adaptive_gemm_fp64(a, b, c, 0.75, 0.25, "bias", bias), zb.float(), atol=0, rtol=0)
+    torch.testing.assert_close(oracle.adaptive_gemm_fp64(a, b, c, 0.75, 0.25, "bias_relu", bias), zb.relu().float(),
+                               atol=0, rtol=0)
+    torch.testing.assert_close(oracle.adaptive_gemm_fp64(a, b, c, 0.75, 0.25, "bias_gelu", bias),
+                               torch.nn.functional.gelu(zb).float(), atol=0, rtol=1e-6)
+    with pytest.raises(ValueError):
+        oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.0, "bias")           # bias epilogue without a bias
+    with pytest.raises(ValueError):
+        oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.0, "relu", bias)     # bias without a bias epilogue
+
+
 def test_rmsnorm_oracle_matches_reference_module_and_inline_form():
     x, w = t("rmsnorm_x"), t("rmsnorm_w")
     # Both forms are the same value up to the last FP64 bit; after the cast to

@@ -257,12 +257,18 @@ def test_adaptive_argument_errors():
         adaptive_gemm(eye, eye, epilogue="relu", kernel="cublas")
     with pytest.raises(RuntimeError, match="C is required"):
         adaptive_gemm(eye, eye, beta=1.0, epilogue="relu")
-    with pytest.raises(RuntimeError, match="supports only the linear and relu"):
-        adaptive_gemm(eye, eye, epilogue="gelu")
     with pytest.raises(RuntimeError, match="unsupported epilogue"):
         adaptive_gemm(eye, eye, epilogue="swish")
-    with pytest.raises(RuntimeError, match="bias fusion is not implemented"):
+    with pytest.raises(RuntimeError, match="a bias tensor needs a bias epilogue"):
         adaptive_gemm(eye, eye, bias=torch.zeros(4, device="cuda"))
+    with pytest.raises(RuntimeError, match="bias is required"):
+        adaptive_gemm(eye, eye, epilogue="bias_relu")
+    with pytest.raises(RuntimeError, match="bias must have shape"):
+        adaptive_gemm(eye, eye, bias=torch.zeros(5, device="cuda"), epilogue="bias")
+    with pytest.raises(RuntimeError, match="supports only the linear epilogue"):
+        adaptive_gemm(eye, eye, bias=torch.zeros(4, device="cuda"), epilogue="bias", kernel="cublas")
+    with pytest.raises(RuntimeError, match="adaptive GEMM dispatch failed"):
+        adaptive_gemm(eye, eye, epilogue="gelu", kernel="fast_relu")
     with pytest.raises(RuntimeError, match="C must have shape"):
         adaptive_gemm(eye, eye, c=torch.zeros(4, 5, device="cuda"), beta=1.0)
 
@@ -276,6 +282,19 @@ def test_adaptive_alpha_beta_matches_oracle(kernel):
     out = adaptive_gemm(a, b, c=c, alpha=0.75, beta=0.25, kernel=kernel)
     torch.testing.assert_close(out.cpu(), oracle.adaptive_gemm_fp64(a, b, c, 0.75, 0.25), atol=3e-2, rtol=3e-2)
     assert torch.equal(c, before)
+
+
+@pytest.mark.parametrize("epilogue", ["gelu", "bias", "bias_relu", "bias_gelu"])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (33, 65, 17)])
+def test_epilogues_the_reference_declares_but_refuses(epilogue, shape):
+    # D = act(alpha * A @ B + beta * C + bias): bias before the activation, erf GELU.
+    m, n, k = shape
+    torch.manual_seed(0)
+    a, b, c = torch.randn(m, k, device="cuda"), torch.randn(k, n, device="cuda"), torch.randn(m, n, device="cuda")
+    bias = torch.randn(n, device="cuda") if epilogue.startswith("bias") else None
+    out = adaptive_gemm(a, b, c=c, bias=bias, alpha=0.75, beta=0.25, epilogue=epilogue)
+    expected = oracle.adaptive_gemm_fp64(a, b, c, 0.75, 0.25, epilogue, bias)
+    torch.testing.assert_close(out.cpu(), expected, atol=3e-2, rtol=3e-2)
 
 
 def test_auto_dispatch_reports_the_first_compatible_entry():

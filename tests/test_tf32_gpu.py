@@ -13,7 +13,8 @@ from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
-LINEAR, RELU = 0, 1
+LINEAR, RELU, GELU = 0, 1, 2
+EPILOGUE_NAME = {LINEAR: "linear", RELU: "relu", GELU: "gelu"}
 
 
 def registry(abi):
@@ -25,12 +26,13 @@ def registry(abi):
     return out
 
 
-def run(abi, kernel_id, a, b, c=None, alpha=1.0, beta=0.0, epilogue=LINEAR, dispatch=False):
+def run(abi, kernel_id, a, b, c=None, alpha=1.0, beta=0.0, epilogue=LINEAR, dispatch=False, bias=None):
     m, k = a.shape
     n = b.shape[1]
     d = torch.full((m, n), float("nan"), device=a.device)
     q = GemmProblem(m, n, k, a.data_ptr(), b.data_ptr(), c.data_ptr() if c is not None else None, d.data_ptr(),
-                    a.stride(0), b.stride(0), c.stride(0) if c is not None else n, d.stride(0), alpha, beta, epilogue)
+                    a.stride(0), b.stride(0), c.stride(0) if c is not None else n, d.stride(0), alpha, beta, epilogue,
+                    bias.data_ptr() if bias is not None else None)
     if dispatch:
         chosen = ctypes.c_int(-1)
         status = abi.b200_tf32_gemm_dispatch(kernel_id, ctypes.byref(q), ctypes.byref(chosen), current_stream_ptr())
@@ -67,8 +69,10 @@ def test_integer_inputs_are_reproduced_exactly(abi, entry, shape):
     b = torch.randint(-4, 5, (k, n), generator=g).float()
     status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), epilogue=epilogue)
     assert status == 0, abi.b200_status_string(status)
-    expected = oracle.adaptive_gemm_fp64(a, b, epilogue="relu" if epilogue == RELU else "linear")
-    torch.testing.assert_close(d.cpu(), expected, atol=0, rtol=0)
+    expected = oracle.adaptive_gemm_fp64(a, b, epilogue=EPILOGUE_NAME[epilogue])
+    # The accumulator is exact; only the erf of the GELU entries is rounded.
+    tol = 1e-5 if epilogue == GELU else 0
+    torch.testing.assert_close(d.cpu(), expected, atol=tol, rtol=tol)
     assert_device_clean(abi)
 
 
@@ -79,7 +83,7 @@ def test_aligned_shapes_match_oracle(abi, entry, shape):
     a, b, c = oracle.adaptive_inputs(*shape)
     status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c.cuda(), alpha=1.0, beta=0.5, epilogue=epilogue)
     assert status == 0, abi.b200_status_string(status)
-    check(d, oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, "relu" if epilogue == RELU else "linear"), k=shape[2])
+    check(d, oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, EPILOGUE_NAME[epilogue]), k=shape[2])
     assert_device_clean(abi)
 
 
@@ -92,7 +96,7 @@ def test_generic_loader_takes_any_shape(abi, entry, shape, alpha, beta):
     c_dev = c.cuda() if beta else None
     status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c_dev, alpha, beta, epilogue)
     assert status == 0, abi.b200_status_string(status)
-    expected = oracle.adaptive_gemm_fp64(a, b, c, alpha, beta, "relu" if epilogue == RELU else "linear")
+    expected = oracle.adaptive_gemm_fp64(a, b, c, alpha, beta, EPILOGUE_NAME[epilogue])
     torch.testing.assert_close(d.cpu(), expected, atol=3e-2, rtol=3e-2)
     if epilogue == RELU:
         assert bool((d >= 0).all())
@@ -184,7 +188,7 @@ def test_baseline_config_8192_sampled_rows(abi, epilogue):
     status, d, chosen = run(abi, 0, a.cuda(), b.cuda(), c.cuda(), 1.0, 0.5, epilogue, dispatch=True)
     assert status == 0
     rows = torch.randperm(n, generator=g)[:96]
-    expected = oracle.adaptive_gemm_fp64(a[rows], b, c[rows], 1.0, 0.5, "relu" if epilogue == RELU else "linear")
+    expected = oracle.adaptive_gemm_fp64(a[rows], b, c[rows], 1.0, 0.5, EPILOGUE_NAME[epilogue])
     check(d[rows.cuda()], expected, k=n)
     # Size-independent property: with beta = 0 the ReLU output is the positive
     # part of the linear output, element for element.
@@ -192,3 +196,58 @@ def test_baseline_config_8192_sampled_rows(abi, epilogue):
         lin = run(abi, 0, a.cuda(), b.cuda(), c.cuda(), 1.0, 0.5, LINEAR, dispatch=True)[1]
         assert torch.equal(d, lin.clamp_min(0))
     assert_device_clean(abi)
+
+
+# ------------------------------------------------ bias and GELU epilogues
+# Declared by the reference, refused by it at run time; no reference vectors
+# exist, the oracle states them (bias added before the activation, erf GELU).
+
+@pytest.mark.parametrize("entry", entries(), ids=lambda e: e[1])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (300, 520, 100)])
+def test_bias_is_added_before_the_activation(abi, entry, shape):
+    kernel_id, _, epilogue, align = entry
+    m, n, k = shape
+    if align == 1:
+        m, n, k = m + 1, n + 3, k + 1          # the generic loader's territory
+    a, b, c = oracle.adaptive_inputs(m, n, k)
+    bias = torch.linspace(-2, 2, n)
+    status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c.cuda(), 0.5, 0.25, epilogue, bias=bias.cuda())
+    assert status == 0, abi.b200_status_string(status)
+    expected = oracle.adaptive_gemm_fp64(a, b, c, 0.5, 0.25, "bias" if epilogue == LINEAR else "bias_" + EPILOGUE_NAME[epilogue],
+                                         bias)
+    check(d, expected, k=k)
+    assert_device_clean(abi)
+
+
+def test_exact_bias_and_gelu_values(abi):
+    # Identity A: the accumulator is B exactly; bias and GELU act on known values.
+    a = torch.eye(4, device="cuda")
+    b = torch.tensor([[-2.0, -1.0, 0.0, 2.0]], device="cuda").repeat(4, 1)
+    bias = torch.tensor([1.0, 1.0, -3.0, 0.5], device="cuda")
+    status, d, _ = run(abi, 0, a, b, epilogue=RELU, dispatch=True, bias=bias)
+    assert status == 0
+    torch.testing.assert_close(d, torch.tensor([[0.0, 0.0, 0.0, 2.5]], device="cuda").repeat(4, 1), atol=0, rtol=0)
+    status, d, chosen = run(abi, 0, a, b, epilogue=GELU, dispatch=True)
+    assert status == 0 and chosen in (24, 25)
+    expected = torch.nn.functional.gelu(b.double()).float()
+    torch.testing.assert_close(d, expected, atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("size", [1024, 4096])
+def test_gelu_auto_dispatch_at_benchmark_sizes(abi, size):
+    a, b, c = oracle.adaptive_inputs(size, size, size)
+    rows = torch.arange(0, size, max(1, size // 64))
+    bias = torch.randn(size)
+    status, d, chosen = run(abi, 0, a.cuda(), b.cuda(), c.cuda(), 1.0, 0.5, GELU, dispatch=True, bias=bias.cuda())
+    assert status == 0 and chosen in (22, 23, 24, 25)
+    expected = oracle.adaptive_gemm_fp64(a[rows], b, c[rows], 1.0, 0.5, "bias_gelu", bias)
+    check(d[rows.cuda()], expected, k=size)
+
+
+def test_misaligned_bias_pointer_uses_scalar_epilogue(abi):
+    a, b, c = oracle.adaptive_inputs(128, 128, 64)
+    bias = torch.randn(128)
+    bias_dev = torch.empty(129, device="cuda")[1:].copy_(bias)
+    status, d, chosen = run(abi, 0, a.cuda(), b.cuda(), c.cuda(), 1.0, 1.0, LINEAR, dispatch=True, bias=bias_dev)
+    assert status == 0
+    check(d, oracle.adaptive_gemm_fp64(a, b, c, 1.0, 1.0, "bias", bias))
