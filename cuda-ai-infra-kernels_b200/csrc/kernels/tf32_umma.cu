@@ -196,6 +196,54 @@ __device__ __forceinline__ SmemCarve carve(uint8_t* raw) {
   return s;
 }
 
+// MMA issuer of the persistent single-CTA kernels (one thread): for every tile
+// of this CTA, waits until the epilogue has drained the accumulator buffer,
+// then consumes the operand ring stage by stage.
+template <int BN, int STAGES>
+__device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base, int tiles, int k_blocks) {
+  int stage = 0;
+  uint32_t phase = 0;
+  bool ok = true;
+  int local = 0;
+  for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+    const int buf = local & 1;
+    const uint32_t use_parity = (local >> 1) & 1u;
+    // The epilogue must have drained this accumulator buffer.
+    if (!mbar_wait(&sm.acc_empty[buf], use_parity ^ 1u, kSiteUmmaAccEmpty)) { ok = false; break; }
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_acc = tmem_base + buf * BN;
+    for (int kb = 0; kb < k_blocks; ++kb) {
+      if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
+      tcgen05_fence_after_sync();
+      const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>());
+      issue_stage_mmas<BN>(tmem_acc, a_addr, a_addr + kASlabBytes, kb > 0 ? 1u : 0u);
+      umma_commit(&sm.empty[stage]);  // stage reusable once these MMAs have read it
+      if (++stage == STAGES) stage = 0, phase ^= 1u;
+    }
+    if (ok) umma_commit(&sm.acc_full[buf]);
+  }
+}
+
+// One of the four epilogue warps of the persistent single-CTA kernels.
+template <int BN, int kAct>
+__device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCarve& sm, uint32_t tmem_base, int quarter,
+                                              int lane, int tiles, int tiles_m, int tiles_n) {
+  bool ok = true;
+  int local = 0;
+  for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+    const int buf = local & 1;
+    const uint32_t use_parity = (local >> 1) & 1u;
+    int tm, tn;
+    tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+    if (!mbar_wait(&sm.acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
+    tcgen05_fence_after_sync();
+    epilogue_tile<BN, kAct>(p, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN);
+    tcgen05_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
+  }
+}
+
 // ------------------------------------------------------- TMA, persistent kernel
 // warp 0: TMA producer (one lane)      warp 1: TMEM owner + MMA issuer (one lane)
 // warps 2-5: epilogue; warp w reads the TMEM lane quarter w % 4.
@@ -262,45 +310,9 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_c
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int local = 0;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
-        const int buf = local & 1;
-        const uint32_t use_parity = (local >> 1) & 1u;
-        // The epilogue must have drained this accumulator buffer.
-        if (!mbar_wait(&sm.acc_empty[buf], use_parity ^ 1u, kSiteUmmaAccEmpty)) { ok = false; break; }
-        tcgen05_fence_after_sync();
-        const uint32_t tmem_acc = tmem_base + buf * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
-          tcgen05_fence_after_sync();
-          const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>());
-          issue_stage_mmas<BN>(tmem_acc, a_addr, a_addr + kASlabBytes, kb > 0 ? 1u : 0u);
-          umma_commit(&sm.empty[stage]);  // stage reusable once these MMAs have read it
-          if (++stage == STAGES) stage = 0, phase ^= 1u;
-        }
-        if (ok) umma_commit(&sm.acc_full[buf]);
-      }
-    }
+    if (lane == 0) mma_role<BN, STAGES>(sm, tmem_base, tiles, k_blocks);
   } else {
-    const int quarter = warp & 3;
-    bool ok = true;
-    int local = 0;
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
-      const int buf = local & 1;
-      const uint32_t use_parity = (local >> 1) & 1u;
-      int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
-      if (!mbar_wait(&sm.acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
-      tcgen05_fence_after_sync();
-      epilogue_tile<BN, kAct>(p, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN);
-      tcgen05_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
-    }
+    epilogue_role<BN, kAct>(p, sm, tmem_base, warp & 3, lane, tiles, tiles_m, tiles_n);
   }
 
   tcgen05_fence_before_sync();
@@ -467,41 +479,103 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
 }
 
 // ------------------------------------------------------- generic loader kernel
-// One CTA per output tile, 128 threads. All threads fill the swizzled slabs
-// with predicated scalar loads (zeros outside the matrix), thread 0 issues the
-// MMAs, everyone waits for them before the slabs are overwritten. Two slabs
-// alternate so that the loads of stage i + 1 overlap the MMAs of stage i.
-constexpr int kGenericThreads = 128;
+// For operands TMA cannot describe (base not 16-byte aligned, leading dimension
+// not a multiple of four floats). Persistent like the TMA kernel, same MMA and
+// epilogue roles, but the operand ring is filled by eight loader warps with
+// predicated scalar loads (zeros outside the matrix):
+//   warp 0: TMEM owner + MMA issuer     warps 1-4: epilogue     warps 5-12: loaders
+// A loader warp moves one 128-byte row of a slab per instruction: coalesced in
+// global memory, and conflict-free in shared memory because the swizzle only
+// permutes the 16- or 32-byte granules inside that row. Each thread keeps the
+// values of the next stage in registers while it stores the current one, so
+// 32 loads per thread are in flight across the wait for a free slot.
+constexpr int kLoaderWarps = 8;
+constexpr int kGenericThreads = (1 + 4 + kLoaderWarps) * 32;
+constexpr int kGenericARows = kTileM / kLoaderWarps;  // A rows per loader warp and stage
 
+// Work split of one stage over the loader warps. Warp lw owns
+//   A rows  m = lw + 8 i                      (m % 8 == lw for all of them),
+//   B rows  k = lw % 4 + 4 (i % 8) of strips j = (lw / 4) * (BN / 64) + i / 8   (k % 4 == lw % 4),
+// so the swizzle term of every store is a per-thread constant and the stores
+// are a base address plus immediates.
 template <int BN>
-__device__ __forceinline__ void fill_stage(const UmmaParams& p, uint8_t* a_dst, uint8_t* b_dst, int m0, int n0, int k0) {
-  // A slab: element (m, k) at m * 128 + ((k / 4) ^ (m % 8)) * 16 + (k % 4) * 4.
-  for (int e = threadIdx.x; e < kTileM * kStageK; e += kGenericThreads) {
-    const int mm = e / kStageK, kk = e % kStageK;
-    const int gm = m0 + mm, gk = k0 + kk;
-    const float v = (gm < p.m && gk < p.k) ? __ldg(p.a + static_cast<int64_t>(gm) * p.lda + gk) : 0.f;
-    *reinterpret_cast<float*>(a_dst + mm * 128 + (((kk >> 2) ^ (mm & 7)) << 4) + ((kk & 3) << 2)) = v;
-  }
-  // B slab: box j = n / 32; element (k, n) at j * 4096 + k * 128 + (((n % 32) / 8) ^ (k % 4)) * 32 + (n % 8) * 4.
-  for (int e = threadIdx.x; e < kStageK * BN; e += kGenericThreads) {
-    const int kk = e / BN, nn = e % BN;
-    const int gk = k0 + kk, gn = n0 + nn;
-    const float v = (gk < p.k && gn < p.n) ? __ldg(p.b + static_cast<int64_t>(gk) * p.ldb + gn) : 0.f;
-    const int j = nn >> 5, ni = nn & 31;
-    *reinterpret_cast<float*>(b_dst + j * kBBoxBytes + kk * 128 + (((ni >> 3) ^ (kk & 3)) << 5) + ((ni & 7) << 2)) = v;
+struct StageRegs {
+  static constexpr int kBRows = kStageK * (BN / 32) / kLoaderWarps;  // 128-byte B rows per loader warp and stage
+  float a[kGenericARows];
+  float b[kBRows];
+};
+
+// Loads this thread's share of stage (m0, n0, k0) into registers.
+template <int BN>
+__device__ __forceinline__ void load_stage_regs(const UmmaParams& p, StageRegs<BN>& r, int lw, int lane, int m0, int n0,
+                                                int k0) {
+  constexpr int kStripsPerWarpHalf = BN / 64;
+  const float* a_ptr = p.a + static_cast<int64_t>(m0 + lw) * p.lda + k0 + lane;
+  const int kb0 = k0 + (lw & 3), nb0 = n0 + (lw >> 2) * kStripsPerWarpHalf * 32 + lane;
+  const float* b_ptr = p.b + static_cast<int64_t>(kb0) * p.ldb + nb0;
+  const int64_t a_step = static_cast<int64_t>(kLoaderWarps) * p.lda, b_step = 4 * p.ldb;
+  if (m0 + kTileM <= p.m && n0 + BN <= p.n && k0 + kStageK <= p.k) {  // interior stage: no predicates
+#pragma unroll
+    for (int i = 0; i < kGenericARows; ++i) r.a[i] = __ldg(a_ptr + i * a_step);
+#pragma unroll
+    for (int i = 0; i < StageRegs<BN>::kBRows; ++i) r.b[i] = __ldg(b_ptr + (i & 7) * b_step + (i >> 3) * 32);
+  } else {
+    const bool k_ok = k0 + lane < p.k;
+#pragma unroll
+    for (int i = 0; i < kGenericARows; ++i) {
+      r.a[i] = (k_ok && m0 + lw + kLoaderWarps * i < p.m) ? __ldg(a_ptr + i * a_step) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < StageRegs<BN>::kBRows; ++i) {
+      const bool ok = kb0 + 4 * (i & 7) < p.k && nb0 + (i >> 3) * 32 < p.n;
+      r.b[i] = ok ? __ldg(b_ptr + (i & 7) * b_step + (i >> 3) * 32) : 0.f;
+    }
   }
 }
 
-template <int BN, int kAct>
-__global__ void __launch_bounds__(kGenericThreads) umma_generic_kernel(const __grid_constant__ UmmaParams p) {
-  constexpr int STAGES = 2;
+// Stores them into the swizzled slabs.
+//   A: element (m, k) at m * 128 + ((k / 4) ^ (m % 8)) * 16 + (k % 4) * 4.
+//   B: box j = n / 32; element (k, n) at j * 4096 + k * 128 + (((n % 32) / 8) ^ (k % 4)) * 32 + (n % 8) * 4.
+template <int BN>
+__device__ __forceinline__ void store_stage_regs(const StageRegs<BN>& r, uint8_t* a_dst, uint8_t* b_dst, int lw, int lane) {
+  constexpr int kStripsPerWarpHalf = BN / 64;
+  float* a_base = reinterpret_cast<float*>(a_dst + lw * 128 + (((lane >> 2) ^ lw) << 4) + ((lane & 3) << 2));
+#pragma unroll
+  for (int i = 0; i < kGenericARows; ++i) a_base[i * (kLoaderWarps * 128 / 4)] = r.a[i];
+  float* b_base = reinterpret_cast<float*>(b_dst + (lw >> 2) * kStripsPerWarpHalf * kBBoxBytes + (lw & 3) * 128 +
+                                           (((lane >> 3) ^ (lw & 3)) << 5) + ((lane & 7) << 2));
+#pragma unroll
+  for (int i = 0; i < StageRegs<BN>::kBRows; ++i) b_base[(i >> 3) * (kBBoxBytes / 4) + (i & 7) * (4 * 128 / 4)] = r.b[i];
+}
+
+// Position of a loader in the (tile, k block) sequence of its CTA.
+struct LoaderCursor {
+  int tile, kb, tm, tn;
+  __device__ __forceinline__ bool valid(int tiles) const { return tile < tiles; }
+  __device__ __forceinline__ void advance(int tiles, int tiles_m, int tiles_n, int k_blocks) {
+    if (++kb == k_blocks) {
+      kb = 0;
+      tile += gridDim.x;
+      if (tile < tiles) tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+    }
+  }
+};
+
+template <int BN, int STAGES, int kAct>
+__global__ void __launch_bounds__(kGenericThreads, 1) umma_generic_kernel(const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
   const SmemCarve sm = carve<BN, STAGES>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) mbar_init(&sm.empty[s], 1);
-    mbar_init(&sm.acc_full[0], 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], kLoaderWarps);  // one arrive per loader warp
+      mbar_init(&sm.empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.acc_full[b], 1);
+      mbar_init(&sm.acc_empty[b], 4);
+    }
     mbar_init_fence();
   }
   if (warp == 0) {
@@ -513,31 +587,52 @@ __global__ void __launch_bounds__(kGenericThreads) umma_generic_kernel(const __g
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *sm.tmem_ptr;
 
-  const int m0 = blockIdx.y * kTileM, n0 = blockIdx.x * BN;
+  const int tiles_m = (p.m + kTileM - 1) / kTileM;
+  const int tiles_n = (p.n + BN - 1) / BN;
+  const int tiles = tiles_m * tiles_n;
   const int k_blocks = (p.k + kStageK - 1) / kStageK;
-  bool ok = true;
-  for (int kb = 0; kb < k_blocks; ++kb) {
-    const int stage = kb & 1;
-    // MMAs that read this slab two iterations ago must be done.
-    if (kb >= 2) ok = mbar_wait(&sm.empty[stage], ((kb >> 1) - 1) & 1u, kSiteUmmaEmpty);
-    // The vote keeps the barrier below reachable by every thread.
-    if (!__syncthreads_and(ok)) { ok = false; break; }
-    uint8_t* a_dst = sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>();
-    fill_stage<BN>(p, a_dst, a_dst + kASlabBytes, m0, n0, kb * kStageK);
-    fence_proxy_async_smem();  // generic-proxy writes -> visible to the MMA unit
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      tcgen05_fence_after_sync();
-      issue_stage_mmas<BN>(tmem_base, smem_u32(a_dst), smem_u32(a_dst) + kASlabBytes, kb > 0 ? 1u : 0u);
-      umma_commit(&sm.empty[stage]);
-      if (kb == k_blocks - 1) umma_commit(&sm.acc_full[0]);
+
+  if (warp == 0) {
+    if (lane == 0) mma_role<BN, STAGES>(sm, tmem_base, tiles, k_blocks);
+  } else if (warp <= 4) {
+    epilogue_role<BN, kAct>(p, sm, tmem_base, warp & 3, lane, tiles, tiles_m, tiles_n);
+  } else {
+    const int lw = warp - 5;
+    LoaderCursor cursor{static_cast<int>(blockIdx.x), 0, 0, 0};  // the next stage to load
+    if (cursor.valid(tiles)) tile_coords(cursor.tile, tiles_m, tiles_n, &cursor.tm, &cursor.tn);
+    int stage = 0;
+    uint32_t phase = 0;
+    auto load = [&](StageRegs<BN>& r) {
+      const bool have = cursor.valid(tiles);
+      if (have) {
+        load_stage_regs<BN>(p, r, lw, lane, cursor.tm * kTileM, cursor.tn * BN, cursor.kb * kStageK);
+        cursor.advance(tiles, tiles_m, tiles_n, k_blocks);
+      }
+      return have;
+    };
+    auto commit = [&](const StageRegs<BN>& r) {
+      if (!mbar_wait(&sm.empty[stage], phase ^ 1u, kSiteUmmaEmpty)) return false;
+      uint8_t* a_dst = sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>();
+      store_stage_regs<BN>(r, a_dst, a_dst + kASlabBytes, lw, lane);
+      fence_proxy_async_smem();  // generic-proxy writes -> visible to the MMA unit
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.full[stage]);
+      if (++stage == STAGES) stage = 0, phase ^= 1u;
+      return true;
+    };
+    // Two register sets alternate, written out rather than copied, so that the
+    // loads of one stage stay in flight while the other is being stored.
+    StageRegs<BN> r0, r1;
+    bool have0 = load(r0);
+    while (have0) {
+      const bool have1 = load(r1);
+      if (!commit(r0)) break;
+      if (!have1) break;
+      have0 = load(r0);
+      if (!commit(r1)) break;
     }
   }
-  if (ok) ok = mbar_wait(&sm.acc_full[0], 0, kSiteUmmaAccFull);
-  if (ok) {
-    tcgen05_fence_after_sync();
-    epilogue_tile<BN, kAct>(p, tmem_base, warp, lane, m0, n0);
-  }
+
   tcgen05_fence_before_sync();
   __syncthreads();
   if (warp == 0) {
@@ -626,18 +721,20 @@ int launch_pair(const b200_gemm_problem& q, cudaStream_t stream) {
   return launch_status();
 }
 
-template <int BN, int kAct>
+template <int BN, int STAGES, int kAct>
 int launch_generic(const b200_gemm_problem& q, cudaStream_t stream) {
-  auto kernel = umma_generic_kernel<BN, kAct>;
-  constexpr size_t smem = smem_bytes<BN, 2>();
+  auto kernel = umma_generic_kernel<BN, STAGES, kAct>;
+  constexpr size_t smem = smem_bytes<BN, STAGES>();
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
   }
   UmmaParams p;
   fill_common(&p, q);
-  const int64_t tiles_m = (q.m + kTileM - 1) / kTileM, tiles_n = (q.n + BN - 1) / BN;
-  if (tiles_m > 65535) return B200_ERR_INVALID_PROBLEM;
-  kernel<<<dim3(static_cast<unsigned>(tiles_n), static_cast<unsigned>(tiles_m)), kGenericThreads, smem, stream>>>(p);
+  const int sms = sm_count();
+  if (sms <= 0) return B200_ERR_INTERNAL;
+  const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + BN - 1) / BN);
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  kernel<<<grid, kGenericThreads, smem, stream>>>(p);
   return launch_status();
 }
 
@@ -703,16 +800,16 @@ const RegistryEntry kRegistry[] = {
     {meta(23, "umma128x256stage4tmaGelu", "wide_gelu", B200_EPILOGUE_GELU, 256, 4, 4), &launch_tma<256, 4, B200_EPILOGUE_GELU>, &gate_wide},
     {meta(24, "umma128x64stage6tmaGelu", "narrow_gelu", B200_EPILOGUE_GELU, 64, 6, 4), &launch_tma<64, 6, B200_EPILOGUE_GELU>, &gate_narrow},
     {meta(2, "umma128x128stage4tma", "fast", B200_EPILOGUE_LINEAR, 128, 4, 4), &launch_tma<128, 4, B200_EPILOGUE_LINEAR>, &gate_always},
-    {meta(3, "umma128x128generic", "fallback", B200_EPILOGUE_LINEAR, 128, 2, 1), &launch_generic<128, B200_EPILOGUE_LINEAR>, &gate_always},
+    {meta(3, "umma128x128stage4generic", "fallback", B200_EPILOGUE_LINEAR, 128, 4, 1), &launch_generic<128, 4, B200_EPILOGUE_LINEAR>, &gate_always},
     {meta(4, "umma128x64stage4tma", "fast_mwarp", B200_EPILOGUE_LINEAR, 64, 4, 4), &launch_tma<64, 4, B200_EPILOGUE_LINEAR>, &gate_always},
-    {meta(5, "umma128x64generic", "fallback_mwarp", B200_EPILOGUE_LINEAR, 64, 2, 1), &launch_generic<64, B200_EPILOGUE_LINEAR>, &gate_always},
+    {meta(5, "umma128x64stage4generic", "fallback_mwarp", B200_EPILOGUE_LINEAR, 64, 4, 1), &launch_generic<64, 4, B200_EPILOGUE_LINEAR>, &gate_always},
     {meta(6, "umma128x128stage3tma", "fast_stage3", B200_EPILOGUE_LINEAR, 128, 3, 4), &launch_tma<128, 3, B200_EPILOGUE_LINEAR>, &gate_always},
     {meta(7, "umma128x128stage2tma", "fast_stage2", B200_EPILOGUE_LINEAR, 128, 2, 4), &launch_tma<128, 2, B200_EPILOGUE_LINEAR>, &gate_always},
     {meta(8, "umma128x128stage4tmaRelu", "fast_relu", B200_EPILOGUE_RELU, 128, 4, 4), &launch_tma<128, 4, B200_EPILOGUE_RELU>, &gate_always},
-    {meta(9, "umma128x128genericRelu", "fallback_relu", B200_EPILOGUE_RELU, 128, 2, 1), &launch_generic<128, B200_EPILOGUE_RELU>, &gate_always},
+    {meta(9, "umma128x128stage4genericRelu", "fallback_relu", B200_EPILOGUE_RELU, 128, 4, 1), &launch_generic<128, 4, B200_EPILOGUE_RELU>, &gate_always},
     // GELU has no entry in the reference registry (the epilogue is parsed but refused there).
     {meta(25, "umma128x128stage4tmaGelu", "fast_gelu", B200_EPILOGUE_GELU, 128, 4, 4), &launch_tma<128, 4, B200_EPILOGUE_GELU>, &gate_always},
-    {meta(26, "umma128x128genericGelu", "fallback_gelu", B200_EPILOGUE_GELU, 128, 2, 1), &launch_generic<128, B200_EPILOGUE_GELU>, &gate_always},
+    {meta(26, "umma128x128stage4genericGelu", "fallback_gelu", B200_EPILOGUE_GELU, 128, 4, 1), &launch_generic<128, 4, B200_EPILOGUE_GELU>, &gate_always},
 };
 constexpr int kRegistrySize = sizeof(kRegistry) / sizeof(kRegistry[0]);
 
