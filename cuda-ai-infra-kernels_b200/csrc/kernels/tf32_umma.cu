@@ -33,9 +33,12 @@
 //   generic - any pointers, any sizes; predicated scalar loads written into the
 //             same swizzled layout, one tile per CTA.
 // Neither uses cluster multicast.
+#include <cooperative_groups.h>
+
 #include <cstring>
 
 #include "host_common.h"
+#include "tf32_gemm.h"
 #include "ptx_sm100.cuh"
 
 namespace b200 {
@@ -49,6 +52,22 @@ constexpr int kStageK = 32;                       // floats of K per stage (one 
 constexpr int kInstK = 8;                         // K of one tcgen05.mma kind::tf32
 constexpr uint32_t kASlabBytes = kTileM * kStageK * 4;  // 16 KiB
 constexpr uint32_t kBBoxBytes = 32 * kStageK * 4;       // 4 KiB: 32 (n) x 32 (k)
+
+// Build-time instrumentation (-DB200_PROBE_TIMING, never in the shipped library):
+// one thread per CTA stamps the global timer at the phase boundaries of a kernel.
+#ifdef B200_PROBE_TIMING
+#define B200_PROBE(params, slot)                                                              \
+  do {                                                                                        \
+    if ((params).probe != nullptr && threadIdx.x == 64) {                                     \
+      uint64_t t_;                                                                            \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
+      (params).probe[static_cast<size_t>(blockIdx.x) * 8 + (slot)] = t_;                      \
+      (params).probe[2048 + static_cast<size_t>(blockIdx.x) * 8 + (slot)] = clock64();        \
+    }                                                                                         \
+  } while (0)
+#else
+#define B200_PROBE(params, slot) do { } while (0)
+#endif
 
 struct UmmaParams {
   CUtensorMap map_a;   // [M][K] boxes {32, 128}, 128-byte swizzle   (TMA loader only)
@@ -64,7 +83,28 @@ struct UmmaParams {
   int m, n, k;
   float alpha, beta;
   int vector_io;       // C/D rows allow 128-bit accesses
+#ifdef B200_PROBE_TIMING
+  uint64_t* probe;     // [grid][8] time stamps, or null
+#endif
 };
+
+// The epilogue's view of the problem, copied into registers once per thread. The kernel parameter
+// block is memory as far as the compiler can tell, memory that the epilogue's own stores might
+// alias: reading it inside the store loops would reload every field after every store, a chain of
+// dependent loads that the few epilogue warps cannot hide.
+struct EpilogueArgs {
+  const float* c;      // null when beta == 0
+  const float* bias;   // or null
+  float* d;
+  int64_t ldc, ldd;
+  int m, n;
+  float alpha, beta;
+  int vector_io;
+};
+
+__device__ __forceinline__ EpilogueArgs epilogue_args(const UmmaParams& p) {
+  return EpilogueArgs{p.c, p.bias, p.d, p.ldc, p.ldd, p.m, p.n, p.alpha, p.beta, p.vector_io};
+}
 
 template <int BN>
 __host__ __device__ constexpr uint32_t stage_bytes() {
@@ -122,7 +162,7 @@ __device__ __forceinline__ float activate(float v) {
 // are rows m0 + 32 * quarter + lane. Each thread owns one row and walks it in
 // chunks of 32 columns.
 template <int BN, int kAct>
-__device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem_acc, int quarter, int lane, int m0,
+__device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tmem_acc, int quarter, int lane, int m0,
                                               int n0) {
   const int row = m0 + quarter * 32 + lane;
   const bool row_ok = row < p.m;
@@ -228,6 +268,7 @@ __device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base
 template <int BN, int kAct>
 __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCarve& sm, uint32_t tmem_base, int quarter,
                                               int lane, int tiles, int tiles_m, int tiles_n) {
+  const EpilogueArgs ep = epilogue_args(p);
   bool ok = true;
   int local = 0;
   for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
@@ -237,7 +278,7 @@ __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCar
     tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
     if (!mbar_wait(&sm.acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
     tcgen05_fence_after_sync();
-    epilogue_tile<BN, kAct>(p, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN);
+    epilogue_tile<BN, kAct>(ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN);
     tcgen05_fence_before_sync();
     __syncwarp();
     if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
@@ -450,6 +491,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
       }
     }
   } else {
+    const EpilogueArgs ep = epilogue_args(p);
     const int quarter = warp & 3;
     bool ok = true;
     int local = 0;
@@ -460,7 +502,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
       tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
       if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
-      epilogue_tile<kPairN, kAct>(p, tmem_base + buf * kPairN, quarter, lane,
+      epilogue_tile<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane,
                                    tm * 2 * kTileM + static_cast<int>(rank) * kTileM, tn * kPairN);
       tcgen05_fence_before_sync();
       __syncwarp();
@@ -475,6 +517,260 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
   if (warp == 1) {
     tcgen05_fence_after_sync();
     tmem_dealloc_pair<512>(tmem_base);
+  }
+}
+
+// ------------------------------------------------ TMA, split-K cluster kernel
+// For problems with too few 128 x 128 output tiles to occupy the SMs (few rows,
+// or small M x N with a long K): the 1, 2, 4 or 8 CTAs of a cluster share one
+// output tile and each reduces a contiguous range of K blocks into its own TMEM
+// accumulator (same producer / MMA roles as above, one tile per CTA, up to
+// two CTAs per SM). The partial tiles then meet in shared memory across the cluster:
+//   1. cluster barrier: every main loop is finished, so every operand ring is
+//      idle and becomes the exchange buffer;
+//   2. each epilogue thread (one accumulator row) sends the columns
+//      [r * W, (r + 1) * W), W = 128 / cluster, of its partial row to CTA r
+//      (distributed-shared-memory stores), rows outside the matrix are skipped;
+//   3. cluster barrier; CTA r adds the partials of its W columns in rank order
+//      (a fixed order: results do not depend on timing) and applies the fused
+//      epilogue. No scratch buffer, no atomics, no second launch.
+namespace cg = cooperative_groups;
+
+constexpr int kSplitN = 128;
+
+// Scaling, source, bias and activation for four adjacent outputs of one row.
+template <int kAct>
+__device__ __forceinline__ void finish_quad(const EpilogueArgs& p, int row, int col, float4 acc) {
+  float v[4] = {p.alpha * acc.x, p.alpha * acc.y, p.alpha * acc.z, p.alpha * acc.w};
+  const float* c_row = p.c + static_cast<int64_t>(row) * p.ldc;
+  float* d_row = p.d + static_cast<int64_t>(row) * p.ldd;
+  if (p.vector_io) {  // n % 4 == 0: the quad is inside the matrix as a whole
+    if (p.beta != 0.f) {
+      const float4 s = __ldg(reinterpret_cast<const float4*>(c_row + col));
+      v[0] = fmaf(p.beta, s.x, v[0]), v[1] = fmaf(p.beta, s.y, v[1]);
+      v[2] = fmaf(p.beta, s.z, v[2]), v[3] = fmaf(p.beta, s.w, v[3]);
+    }
+    if (p.bias != nullptr) {
+      const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+      v[0] += bv.x, v[1] += bv.y, v[2] += bv.z, v[3] += bv.w;
+    }
+    *reinterpret_cast<float4*>(d_row + col) =
+        make_float4(activate<kAct>(v[0]), activate<kAct>(v[1]), activate<kAct>(v[2]), activate<kAct>(v[3]));
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (col + e < p.n) {
+        float out = v[e];
+        if (p.beta != 0.f) out = fmaf(p.beta, __ldg(c_row + col + e), out);
+        if (p.bias != nullptr) out += __ldg(p.bias + col + e);
+        d_row[col + e] = activate<kAct>(out);
+      }
+    }
+  }
+}
+
+// Exchange buffer of a CTA: float4 elements [source][column quad of its share][row], kExchangePitch
+// elements per (source, quad). Senders own a row each, so a warp writes 32 consecutive elements;
+// the finishing pass reads row-wise (lanes = adjacent quads of one row) and the odd pitch spreads
+// those reads over the banks.
+constexpr int kExchangePitch = kTileM + 1;
+
+// Step 2 of the split-K kernels for one epilogue thread (one accumulator row of kCols columns in
+// TMEM at `tmem_row`): the columns of share s go to the CTA with cluster rank
+// s * rank_stride + rank_offset, into that CTA's buffer for source `my_slice`. The next 32 columns
+// are fetched from TMEM while the current ones are being sent; a share is at least 16 columns
+// wide, so each half chunk (four quads) has a single destination.
+template <int kCols>
+__device__ __forceinline__ void send_partial_row(cg::cluster_group& cluster, uint32_t tmem_row, bool have_acc,
+                                                 float4* exchange, int my_slice, int quads_log2, int rank_stride,
+                                                 int rank_offset, int row_in_tile) {
+  constexpr int kChunks = kCols / 32;
+  const int quads = 1 << quads_log2;
+  uint32_t raw[2][32];
+  if (have_acc) {
+    tmem_ld_32x32(tmem_row, raw[0]);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) raw[0][e] = raw[1][e] = 0u;   // an empty K range contributes zeros
+  }
+#pragma unroll
+  for (int chunk = 0; chunk < kChunks; ++chunk) {
+    if (have_acc) {
+      tmem_ld_wait();
+      if (chunk + 1 < kChunks) tmem_ld_32x32(tmem_row + (chunk + 1) * 32, raw[(chunk + 1) & 1]);
+    }
+    const uint32_t(&cur)[32] = raw[chunk & 1];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int quad0 = chunk * 8 + half * 4;
+      const int dest_slice = quad0 >> quads_log2, local_quad0 = quad0 & (quads - 1);
+      float4* dst = cluster.map_shared_rank(exchange, dest_slice * rank_stride + rank_offset) +
+                    (my_slice * quads + local_quad0) * kExchangePitch + row_in_tile;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = half * 16 + j * 4;
+        dst[j * kExchangePitch] = make_float4(__uint_as_float(cur[e + 0]), __uint_as_float(cur[e + 1]),
+                                              __uint_as_float(cur[e + 2]), __uint_as_float(cur[e + 3]));
+      }
+    }
+  }
+}
+
+// Step 3 of the split-K kernels for thread t of `threads`: adds the partials of this CTA's column
+// share in source order and writes finished rows with lanes along the row, so that C is read and
+// D is written in contiguous segments. Only a few warps run this, so four outputs per thread are
+// kept in flight to cover the latencies.
+template <int kAct>
+__device__ __forceinline__ void exchange_finish(const EpilogueArgs& p, const float4* exchange, int sources, int quads_log2,
+                                                int row0, int col_base, int t, int threads) {
+  constexpr int kBatch = 4;
+  const int quads = 1 << quads_log2;
+  const int items = kTileM << quads_log2;
+  for (int base = t; base < items; base += kBatch * threads) {
+    float4 sum[kBatch];
+    const float4* src_ptr[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int item = min(base + u * threads, items - 1);   // clamped: a duplicate read, no duplicate write below
+      src_ptr[u] = exchange + (item & (quads - 1)) * kExchangePitch + (item >> quads_log2);
+      sum[u] = *src_ptr[u];
+    }
+    for (int src = 1; src < sources; ++src) {
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const float4 v = src_ptr[u][src * quads * kExchangePitch];
+        sum[u].x += v.x, sum[u].y += v.y, sum[u].z += v.z, sum[u].w += v.w;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int item = base + u * threads;
+      const int row = row0 + (item >> quads_log2), col = col_base + 4 * (item & (quads - 1));
+      if (item < items && row < p.m && col < p.n) finish_quad<kAct>(p, row, col, sum[u]);
+    }
+  }
+}
+
+template <int STAGES, int kAct>
+__global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __grid_constant__ UmmaParams p) {
+  constexpr int BN = kSplitN;
+  static_assert(static_cast<size_t>(STAGES) * stage_bytes<BN>() >= sizeof(float4) * kExchangePitch * (BN / 4),
+                "the idle operand ring must hold one exchanged tile");
+  cg::cluster_group cluster = cg::this_cluster();
+  const int ranks = static_cast<int>(cluster.num_blocks());
+  const int rank = static_cast<int>(cluster.block_rank());
+  extern __shared__ uint8_t smem_raw[];
+  const SmemCarve sm = carve<BN, STAGES>(smem_raw);
+  B200_PROBE(p, 0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    mbar_init(&sm.acc_full[0], 1);
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc<BN>(sm.tmem_ptr);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_ptr;
+  B200_PROBE(p, 1);
+
+  const int tiles_m = (p.m + kTileM - 1) / kTileM;
+  const int tiles_n = (p.n + BN - 1) / BN;
+  int tm, tn;
+  tile_coords(static_cast<int>(blockIdx.x) / ranks, tiles_m, tiles_n, &tm, &tn);
+  const int k_blocks = (p.k + kStageK - 1) / kStageK;
+  const int per_rank = (k_blocks + ranks - 1) / ranks;
+  const int kb_begin = min(k_blocks, rank * per_rank);
+  const int kb_end = min(k_blocks, kb_begin + per_rank);
+  const bool has_work = kb_begin < kb_end;   // an empty range contributes zeros
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&p.map_a);
+      prefetch_tensormap(p.b_strips == BN / 32 ? &p.map_b_strips : &p.map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&sm.empty[stage], phase ^ 1u, kSiteUmmaEmpty)) break;
+        uint8_t* a_dst = sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>();
+        uint8_t* b_dst = a_dst + kASlabBytes;
+        mbar_expect_tx(&sm.full[stage], stage_bytes<BN>());
+        tma_load_2d(a_dst, &p.map_a, &sm.full[stage], kb * kStageK, tm * kTileM);
+        if (p.b_strips == BN / 32) {
+          tma_load_3d(b_dst, &p.map_b_strips, &sm.full[stage], 0, kb * kStageK, tn * (BN / 32));
+        } else {
+#pragma unroll
+          for (int j = 0; j < BN / 32; ++j) {
+            tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &sm.full[stage], tn * BN + j * 32, kb * kStageK);
+          }
+        }
+        if (++stage == STAGES) stage = 0, phase ^= 1u;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && has_work) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool fed = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { fed = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>());
+        issue_stage_mmas<BN>(tmem_base, a_addr, a_addr + kASlabBytes, kb > kb_begin ? 1u : 0u);
+        umma_commit(&sm.empty[stage]);
+        if (++stage == STAGES) stage = 0, phase ^= 1u;
+      }
+      if (fed) umma_commit(&sm.acc_full[0]);
+    }
+  } else if (has_work) {
+    ok = mbar_wait(&sm.acc_full[0], 0, kSiteUmmaAccFull);
+    tcgen05_fence_after_sync();
+  }
+
+  B200_PROBE(p, 2);
+  // 1. Every CTA of the cluster is past its main loop.
+  tcgen05_fence_before_sync();
+  cluster.sync();
+  tcgen05_fence_after_sync();
+
+  B200_PROBE(p, 3);
+  // Exchange buffer of a CTA: float4 elements [source rank][column quad of its W columns][row]. Rows are
+  // innermost so that the 32 lanes of a warp (32 rows) touch 512 contiguous bytes: no bank conflicts
+  // on either side.
+  float4* exchange = reinterpret_cast<float4*>(sm.stages);
+  const int width = BN / ranks;                            // W: 128, 64, 32 or 16 columns per CTA
+  const int quads = width / 4;
+  const int quarter = warp & 3;
+  const int row_in_tile = quarter * 32 + lane;
+  const bool warp_rows = tm * kTileM + quarter * 32 < p.m;   // any row of this warp inside the matrix
+  const int quads_log2 = 31 - __clz(quads);
+  if (warp >= 2 && warp_rows) {
+    // 2. Send this CTA's partial row, W columns to each CTA.
+    send_partial_row<BN>(cluster, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), has_work && ok, exchange,
+                         rank, quads_log2, 1, 0, row_in_tile);
+  }
+  B200_PROBE(p, 4);
+  tcgen05_fence_before_sync();
+  cluster.sync();
+  B200_PROBE(p, 5);
+
+  // 3. Add the partials of this CTA's columns in rank order and finish them.
+  exchange_finish<kAct>(epilogue_args(p), exchange, ranks, quads_log2, tm * kTileM, tn * BN + rank * width, threadIdx.x, kTmaThreads);
+
+  B200_PROBE(p, 6);
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc<BN>(tmem_base);
   }
 }
 
@@ -721,6 +1017,98 @@ int launch_pair(const b200_gemm_problem& q, cudaStream_t stream) {
   return launch_status();
 }
 
+// Most clusters of `cluster_size` CTAs of the split-K kernel that the device keeps resident at once
+// (cached per device; clusters of eight fit far fewer CTAs than the SM count suggests).
+int splitk_max_clusters(int cluster_size) {
+  static int cache[64][4];   // [device][log2 cluster size], 0 = not asked yet
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  const int slot = cluster_size == 1 ? 0 : cluster_size == 2 ? 1 : cluster_size == 4 ? 2 : 3;
+  if (cache[device][slot] != 0) return cache[device][slot];
+  auto kernel = umma_splitk_kernel<3, B200_EPILOGUE_LINEAR>;   // the activation does not change the footprint
+  constexpr size_t smem = smem_bytes<kSplitN, 3>();
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(cluster_size) * 64);
+  cfg.blockDim = dim3(kTmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(cluster_size);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) clusters = 0;
+  cache[device][slot] = clusters > 0 ? clusters : -1;
+  return cache[device][slot];
+}
+
+// Cluster size of the split-K kernel, from a cost model fitted to phase timings of the kernel on a
+// B200 (microseconds): a K block costs 0.34 with one CTA per SM and 0.53 per CTA with two; barriers,
+// exchange and the finishing pass cost 4.5 / 6.0 / 7.2 for clusters of 2 / 4 / 8 (half as much again when
+// two CTAs share an SM). A candidate must keep
+// two K blocks per range and fit the device in one wave (two CTAs per SM: twice the cluster count the
+// occupancy query reports for one). `estimate_us` receives the modelled time of the choice.
+int splitk_ranks(const b200_gemm_problem& q, int sms, float* estimate_us = nullptr) {
+  const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
+  const int k_blocks = (q.k + kStageK - 1) / kStageK;
+  constexpr float kExchangeUs[4] = {4.7f, 4.5f, 6.0f, 7.2f};
+  int best = 1;
+  float best_us = 1e30f;
+  for (int log2r = 0; log2r < 4; ++log2r) {
+    const int ranks = 1 << log2r;
+    const int64_t ctas = tiles * ranks;
+    if (ctas > 2LL * sms) break;
+    if (ranks > 1 && (k_blocks / ranks < 2 || tiles > 2LL * splitk_max_clusters(ranks))) break;
+    const bool shared_sm = ctas > sms;   // two CTAs per SM also share its exchange and store bandwidth
+    const float us = static_cast<float>((k_blocks + ranks - 1) / ranks) * (shared_sm ? 0.53f : 0.34f) +
+                     kExchangeUs[log2r] * (shared_sm ? 1.5f : 1.0f);
+    if (us < best_us) best_us = us, best = ranks;
+  }
+  if (estimate_us != nullptr) *estimate_us = best_us;
+  return best;
+}
+
+template <int STAGES, int kAct>
+int launch_splitk(const b200_gemm_problem& q, cudaStream_t stream) {
+  auto kernel = umma_splitk_kernel<STAGES, kAct>;
+  constexpr size_t smem = smem_bytes<kSplitN, STAGES>();
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+    return B200_ERR_LAUNCH_FAILED;
+  }
+  UmmaParams p;
+  fill_common(&p, q);
+  if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
+      !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
+    return B200_ERR_MISALIGNED_OPERAND;
+  }
+  p.b_strips = (q.n % 32 == 0 && make_tensor_map_strips(&p.map_b_strips, q.b, q.k, q.n, q.ldb, kStageK, kSplitN / 32,
+                                                        Swizzle::k128BAtom32B))
+                   ? kSplitN / 32
+                   : 0;
+  const int sms = sm_count();
+  if (sms <= 0) return B200_ERR_INTERNAL;
+  const int ranks = splitk_ranks(q, sms);
+  const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
+  if (tiles * ranks > 0x7fffffffLL) return B200_ERR_INVALID_PROBLEM;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * ranks));
+  cfg.blockDim = dim3(kTmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(ranks);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  return launch_status();
+}
+
 template <int BN, int STAGES, int kAct>
 int launch_generic(const b200_gemm_problem& q, cudaStream_t stream) {
   auto kernel = umma_generic_kernel<BN, STAGES, kAct>;
@@ -763,6 +1151,16 @@ constexpr b200_tf32_kernel_meta meta_pair(int id, const char* name, const char* 
                                stages, 4, 4, 4, 0};
 }
 
+// One 128 x 128 tile per cluster, K split over the cluster's CTAs.
+constexpr b200_tf32_kernel_meta meta_splitk(int id, const char* name, const char* alias, int epilogue, int stages) {
+  return b200_tf32_kernel_meta{id, name, alias, epilogue, kTileM, kSplitN, kStageK, kTileM, kSplitN, kInstK, stages, 4, 4, 4, 1};
+}
+
+// Skinny rows: FP32 FMA stream over B, 16 x 128 outputs per CTA, K split over warps and a cluster.
+constexpr b200_tf32_kernel_meta meta_skinny(int id, const char* name, const char* alias, int epilogue) {
+  return b200_tf32_kernel_meta{id, name, alias, epilogue, kSkinnyMaxRows, 128, 64, kSkinnyMaxRows, 128, 1, 1, 1, 4, 1, 0};
+}
+
 int64_t tiles_of(const b200_gemm_problem& q, int tile_n) {
   return static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + tile_n - 1) / tile_n);
 }
@@ -779,6 +1177,23 @@ bool gate_pair(const b200_gemm_problem& q, int sms) {
   const int64_t tiles = static_cast<int64_t>((q.m + 255) / 256) * ((q.n + 255) / 256);
   return tiles >= sms / 2;
 }
+// Up to four rows the FP32 stream over B is the fastest entry (1 x 4096 x 4096:
+// 8.0 us against 17.1 us for the split-K tensor-core tile); from eight rows on
+// its FMA work per byte of B exceeds what hides behind the memory stream and the
+// tensor-core split-K entry takes over (16 x 4096 x 4096: 22.1 vs 14.7 us).
+bool gate_skinny(const b200_gemm_problem& q, int) { return q.m <= 4; }
+// Split K when the model above predicts a shorter run than the unsplit tile kernels, which stream a
+// K block in about 0.23 us (128 x 64 tiles, when those fit the SMs in one round) or 0.34 us (128 x 128)
+// on top of 3.5 us of prologue and epilogue. Measured on a B200: 1024 x 1024 x 8192 39.8 us split
+// four ways against 73.0 us unsplit, 16 x 4096 x 4096 14.1 against 38.1, while 512^3 and 1024^3 stay
+// within 1 us of the 128 x 64 tile kernel either way.
+bool gate_splitk(const b200_gemm_problem& q, int sms) {
+  float split_us = 0.f;
+  if (splitk_ranks(q, sms, &split_us) < 2) return false;
+  const int k_blocks = (q.k + kStageK - 1) / kStageK;
+  const float unsplit_us = static_cast<float>(k_blocks) * (tiles_of(q, 64) <= sms ? 0.23f : 0.34f) + 3.5f;
+  return split_us < unsplit_us;
+}
 bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) * 2 <= sms && q.n > 64; }
 
 // Dispatch order. Entries with ids >= 16 exist only here and are tried first by
@@ -790,6 +1205,12 @@ bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) 
 // the generic loader). What distinguished the reference's variants (warp
 // shape, stage count) maps onto tile width and pipeline depth.
 const RegistryEntry kRegistry[] = {
+    {meta_skinny(27, "simt16x128splitk", "skinny", B200_EPILOGUE_LINEAR), &launch_skinny, &gate_skinny},
+    {meta_skinny(28, "simt16x128splitkRelu", "skinny_relu", B200_EPILOGUE_RELU), &launch_skinny, &gate_skinny},
+    {meta_skinny(29, "simt16x128splitkGelu", "skinny_gelu", B200_EPILOGUE_GELU), &launch_skinny, &gate_skinny},
+    {meta_splitk(30, "umma128x128stage3splitk", "splitk", B200_EPILOGUE_LINEAR, 3), &launch_splitk<3, B200_EPILOGUE_LINEAR>, &gate_splitk},
+    {meta_splitk(31, "umma128x128stage3splitkRelu", "splitk_relu", B200_EPILOGUE_RELU, 3), &launch_splitk<3, B200_EPILOGUE_RELU>, &gate_splitk},
+    {meta_splitk(32, "umma128x128stage3splitkGelu", "splitk_gelu", B200_EPILOGUE_GELU, 3), &launch_splitk<3, B200_EPILOGUE_GELU>, &gate_splitk},
     {meta_pair(20, "umma256x256stage6pair", "pair", B200_EPILOGUE_LINEAR, 6), &launch_pair<6, B200_EPILOGUE_LINEAR>, &gate_pair},
     {meta_pair(21, "umma256x256stage6pairRelu", "pair_relu", B200_EPILOGUE_RELU, 6), &launch_pair<6, B200_EPILOGUE_RELU>, &gate_pair},
     {meta(16, "umma128x256stage4tma", "wide", B200_EPILOGUE_LINEAR, 256, 4, 4), &launch_tma<256, 4, B200_EPILOGUE_LINEAR>, &gate_wide},

@@ -114,7 +114,15 @@ def test_registry_keeps_the_reference_ids_aliases_and_order(abi):
         (2, "fast", 0, 4), (3, "fallback", 0, 1), (4, "fast_mwarp", 0, 4), (5, "fallback_mwarp", 0, 1),
         (6, "fast_stage3", 0, 4), (7, "fast_stage2", 0, 4), (8, "fast_relu", 1, 4), (9, "fallback_relu", 1, 1),
     ]
+    skinny = [e for e in entries if e.alias.decode().startswith("skinny")]
+    assert [(e.id, e.epilogue, e.tile_m, e.tile_n, e.alignment_a, e.alignment_b) for e in skinny] == [
+        (27, 0, 16, 128, 1, 4), (28, 1, 16, 128, 1, 4), (29, 2, 16, 128, 1, 4)]
+    assert entries[:3] == skinny or [e.id for e in entries[:3]] == [27, 28, 29]   # tried first, behind an M <= 16 gate
     for e in entries:
+        assert abi.b200_tf32_kernel_from_name(e.alias) == e.id
+        assert abi.b200_tf32_kernel_from_name(e.name) == e.id
+        if e in skinny:
+            continue
         assert e.tile_m in (128, 256) and e.inst_m == e.tile_m and e.inst_k == 8 and e.tile_k == 32
         assert e.tile_n in (64, 128, 256) and e.inst_n == e.tile_n
         assert (e.tile_m == 256) == e.alias.decode().startswith("pair")   # 256 rows only as a CTA pair

@@ -50,11 +50,13 @@ def check(actual, expected, k=64):
     torch.testing.assert_close(actual.cpu(), expected, atol=atol, rtol=3e-2)
 
 
-def entries(align=None, epilogue=None):
+def entries(align=None, epilogue=None, skinny=False):
+    """Registry entries as (id, alias, epilogue, alignment of A); the tensor-core ones unless `skinny`."""
     import conftest
 
     lib = conftest.load_abi()
-    return [e for e in registry(lib) if (align is None or e[3] == align) and (epilogue is None or e[2] == epilogue)]
+    return [e for e in registry(lib) if (align is None or e[3] == align) and (epilogue is None or e[2] == epilogue)
+            and e[1].startswith("skinny") == skinny]
 
 
 @pytest.mark.parametrize("entry", entries(), ids=lambda e: e[1])
@@ -228,7 +230,7 @@ def test_exact_bias_and_gelu_values(abi):
     assert status == 0
     torch.testing.assert_close(d, torch.tensor([[0.0, 0.0, 0.0, 2.5]], device="cuda").repeat(4, 1), atol=0, rtol=0)
     status, d, chosen = run(abi, 0, a, b, epilogue=GELU, dispatch=True)
-    assert status == 0 and chosen in (24, 25)
+    assert status == 0 and chosen == 29   # four rows: the skinny entry under automatic dispatch
     expected = torch.nn.functional.gelu(b.double()).float()
     torch.testing.assert_close(d, expected, atol=1e-6, rtol=1e-6)
 
@@ -239,7 +241,7 @@ def test_gelu_auto_dispatch_at_benchmark_sizes(abi, size):
     rows = torch.arange(0, size, max(1, size // 64))
     bias = torch.randn(size)
     status, d, chosen = run(abi, 0, a.cuda(), b.cuda(), c.cuda(), 1.0, 0.5, GELU, dispatch=True, bias=bias.cuda())
-    assert status == 0 and chosen in (22, 23, 24, 25)
+    assert status == 0 and chosen in (22, 23, 24, 25, 32)   # narrow or pair entries at these sizes
     expected = oracle.adaptive_gemm_fp64(a[rows], b, c[rows], 1.0, 0.5, "bias_gelu", bias)
     check(d[rows.cuda()], expected, k=size)
 
@@ -251,3 +253,122 @@ def test_misaligned_bias_pointer_uses_scalar_epilogue(abi):
     status, d, chosen = run(abi, 0, a.cuda(), b.cuda(), c.cuda(), 1.0, 1.0, LINEAR, dispatch=True, bias=bias_dev)
     assert status == 0
     check(d, oracle.adaptive_gemm_fp64(a, b, c, 1.0, 1.0, "bias", bias))
+
+
+# ----------------------------------------------------------------- skinny rows
+# M <= 16: FP32 FMA stream over B with K split over warps and a cluster. FP32
+# arithmetic, so besides the TF32 gates the result has to be FP32-accurate.
+
+
+@pytest.mark.parametrize("entry", entries(skinny=True), ids=lambda e: e[1])
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 13, 16])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (132, 100), (4, 7), (260, 1000), (1024, 8)])
+def test_skinny_rows_match_oracle(abi, entry, m, n, k):
+    kernel_id, _, epilogue, _ = entry
+    a, b, c = oracle.adaptive_inputs(m, n, k, seed=m)
+    bias = torch.linspace(-1.0, 1.0, n)
+    status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c.cuda(), alpha=0.75, beta=0.25, epilogue=epilogue,
+                       bias=bias.cuda())
+    assert status == 0, abi.b200_status_string(status)
+    name = "bias" if epilogue == LINEAR else "bias_" + EPILOGUE_NAME[epilogue]
+    expected = oracle.adaptive_gemm_fp64(a, b, c, 0.75, 0.25, name, bias=bias)
+    check(d, expected, k=k)
+    tol = oracle.sgemm_abs_tolerance(a, b)   # the FP32 ladder's bound
+    assert float((d.cpu() - expected).abs().max()) <= tol
+    assert_device_clean(abi)
+
+
+@pytest.mark.parametrize("m", [1, 7, 16])
+def test_skinny_rows_reproduce_integers_exactly(abi, m):
+    g = torch.Generator().manual_seed(m)
+    a = torch.randint(-4, 5, (m, 777), generator=g).float()
+    b = torch.randint(-4, 5, (777, 520), generator=g).float()
+    status, d, _ = run(abi, 27, a.cuda(), b.cuda())
+    assert status == 0
+    torch.testing.assert_close(d.cpu(), oracle.adaptive_gemm_fp64(a, b), atol=0, rtol=0)
+
+
+def test_skinny_dispatch_and_refusals(abi):
+    a, b, _ = oracle.adaptive_inputs(4, 4096, 4096)
+    for epilogue, expected_id in ((LINEAR, 27), (RELU, 28), (GELU, 29)):
+        status, _, chosen = run(abi, 0, a.cuda(), b.cuda(), epilogue=epilogue, dispatch=True)
+        assert status == 0 and chosen == expected_id
+    # From five rows on automatic dispatch prefers the tensor-core entries (here: split K).
+    a5, b5, _ = oracle.adaptive_inputs(16, 4096, 4096)
+    assert run(abi, 0, a5.cuda(), b5.cuda(), dispatch=True)[2] == 30
+    # More than 16 rows: a forced call is refused.
+    a17, b17, _ = oracle.adaptive_inputs(17, 256, 64)
+    assert run(abi, 27, a17.cuda(), b17.cuda())[0] == 2          # invalid problem
+    assert run(abi, 0, a17.cuda(), b17.cuda(), dispatch=True)[2] not in (27, 28, 29)
+    # Columns that are not whole float4 groups, or a misaligned B: refused, dispatch moves on.
+    a1, b1, _ = oracle.adaptive_inputs(4, 66, 32)
+    assert run(abi, 27, a1.cuda(), b1.cuda())[0] in (1, 2)
+    status, d, chosen = run(abi, 0, a1.cuda(), b1.cuda(), dispatch=True)
+    assert status == 0 and chosen == 3
+    check(d, oracle.adaptive_gemm_fp64(a1, b1))
+    b_off = torch.empty(64 * 128 + 1, device="cuda")[1:].view(64, 128)
+    a2, b2, _ = oracle.adaptive_inputs(4, 128, 64)
+    b_off.copy_(b2)
+    assert run(abi, 27, a2.cuda(), b_off)[0] == 1                # misaligned operand
+    # A may sit anywhere: only B is read with 128-bit loads.
+    a_off = torch.empty(4 * 64 + 1, device="cuda")[1:].view(4, 64).copy_(a2)
+    status, d, _ = run(abi, 27, a_off, b2.cuda())
+    assert status == 0
+    check(d, oracle.adaptive_gemm_fp64(a2, b2))
+    assert_device_clean(abi)
+
+
+def test_skinny_beta_zero_never_reads_the_source(abi):
+    a, b, _ = oracle.adaptive_inputs(8, 512, 256)
+    poison = torch.full((8, 512), float("nan"), device="cuda")
+    status, d, _ = run(abi, 27, a.cuda(), b.cuda(), poison, alpha=1.0, beta=0.0)
+    assert status == 0
+    check(d, oracle.adaptive_gemm_fp64(a, b), k=256)
+
+
+# --------------------------------------------------------------- split-K cluster
+# One 128 x 128 tile per cluster of 1/2/4/8 CTAs; partial tiles are exchanged
+# through distributed shared memory and added in rank order.
+
+
+@pytest.mark.parametrize("entry", [e for e in entries() if e[1].startswith("splitk")], ids=lambda e: e[1])
+@pytest.mark.parametrize("shape", [
+    (16, 4096, 4096),    # decode-like: 32 tiles x 8 ranks
+    (64, 128, 288),      # 9 K blocks over 4 ranks: the last rank has an empty range
+    (100, 200, 200),     # 7 K blocks over 2 ranks, ragged rows, columns and K
+    (512, 512, 2048),    # 16 tiles x 8 ranks
+    (1024, 1024, 1024),  # 64 tiles x 4 ranks
+    (130, 132, 4100),    # tile edges inside a cluster's column shares
+])
+def test_split_k_cluster_matches_oracle(abi, entry, shape):
+    kernel_id, _, epilogue, _ = entry
+    a, b, c = oracle.adaptive_inputs(*shape, seed=shape[0])
+    bias = torch.linspace(-1.0, 1.0, shape[1])
+    status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c.cuda(), alpha=0.75, beta=0.25, epilogue=epilogue,
+                       bias=bias.cuda())
+    assert status == 0, abi.b200_status_string(status)
+    name = "bias" if epilogue == LINEAR else "bias_" + EPILOGUE_NAME[epilogue]
+    check(d, oracle.adaptive_gemm_fp64(a, b, c, 0.75, 0.25, name, bias=bias), k=shape[2])
+    assert_device_clean(abi)
+
+
+def test_split_k_cluster_is_deterministic_and_exact_on_integers(abi):
+    g = torch.Generator().manual_seed(5)
+    a = torch.randint(-4, 5, (48, 1024), generator=g).float()
+    b = torch.randint(-4, 5, (1024, 384), generator=g).float()
+    first = run(abi, 30, a.cuda(), b.cuda())[1]
+    torch.testing.assert_close(first.cpu(), oracle.adaptive_gemm_fp64(a, b), atol=0, rtol=0)
+    a2, b2, _ = oracle.adaptive_inputs(48, 384, 1024)
+    runs = [run(abi, 30, a2.cuda(), b2.cuda())[1] for _ in range(3)]
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])
+
+
+def test_split_k_auto_dispatch(abi):
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    a, b, _ = oracle.adaptive_inputs(64, 1024, 2048)       # 8 tiles, 64 K blocks
+    for epilogue, expected_id in ((LINEAR, 30), (RELU, 31), (GELU, 32)):
+        status, _, chosen = run(abi, 0, a.cuda(), b.cuda(), epilogue=epilogue, dispatch=True)
+        assert status == 0 and chosen == expected_id
+    # Enough tiles for every SM: no split.
+    a, b, _ = oracle.adaptive_inputs(128 * 8, 128 * ((sms + 7) // 8), 256)
+    assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] not in (30, 31, 32)
