@@ -8,10 +8,14 @@ The benchmark configuration: M = 32768, N = K = 8192, FP32 N(0,1) inputs. Rank r
 owns rows [r*M/G, (r+1)*M/G) of A (a column-major shard for the FP32 SIMT path,
 a contiguous row slab for the TF32 path), B is replicated, C stays sharded: no
 collective on the data path. Timing: CUDA events around `steps` calls on each
-rank between barriers, MAX over ranks. The all-gather of C over NCCL is timed
-separately. Every rank checks sampled rows of its shard against the FP64 oracle
-expression on the CPU before anything is timed. Rank 0 prints one JSON line;
-scaling = T(1) / (G * T(G)) is left to the reader of the per-G lines.
+rank between barriers, MAX over ranks. Gathering C on every rank is timed three
+ways: the NCCL all-gather alone, GEMM followed by that all-gather, and the fused
+kernels whose epilogues store every tile into every rank's copy of C over
+NVLink (`sharded.sharded_gemm_gather`), each step closed by the device-side
+barrier that makes the copies readable. Every rank checks sampled rows of its
+shard against the FP64 oracle expression on the CPU before anything is timed,
+and the fused result against the collective one bit for bit. Rank 0 prints one
+JSON line; scaling = T(1) / (G * T(G)) is left to the reader of the per-G lines.
 """
 from __future__ import annotations
 
@@ -107,6 +111,7 @@ def main() -> None:
         results[name] = {"ms": ms, "tflops_total": 2.0 * args.m * args.n * args.k / ms / 1e9}
 
     gather = None
+    fused = None
     if distributed:
         counts = [count for _, count in plan]
         for _ in range(2):
@@ -116,12 +121,44 @@ def main() -> None:
         received = (args.m - rows) * args.n * 4
         gather = {"ms": ms, "received_gb_per_rank": received / 1e9, "gbs_per_rank": received / ms / 1e6}
 
+        # GEMM + all-gather: two launches (kernel, then NCCL) against one fused kernel + barrier.
+        out = sharded.GatheredOutput(args.m, args.n, plan)
+        arms = {
+            "fp32_simt_then_allgather": lambda: sharded.all_gather_rows(pkg.gemm(a_colmajor, b, impl=args.sgemm_impl), counts),
+            "fp32_simt_fused": lambda: (sharded.sharded_gemm_gather(a_colmajor, b, out, impl=args.sgemm_impl), out.barrier()),
+            "tf32_then_allgather": lambda: sharded.all_gather_rows(pkg.adaptive_gemm(a_rows, b), counts),
+            "tf32_fused": lambda: (sharded.sharded_adaptive_gemm_gather(a_rows, b, out), out.barrier()),
+        }
+        # Parity of the fused result with the collective one, on every rank.
+        reference = arms["fp32_simt_then_allgather"]()
+        arms["fp32_simt_fused"]()
+        torch.cuda.synchronize()
+        same_fp32 = bool(torch.equal(out.full, reference))
+        out.barrier()
+        reference = arms["tf32_then_allgather"]()
+        arms["tf32_fused"]()
+        torch.cuda.synchronize()
+        same_tf32 = bool(torch.equal(out.full, reference))
+        del reference
+        flags = torch.tensor([int(same_fp32), int(same_tf32)], device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        if not bool(flags.min().item()):
+            raise SystemExit(f"rank {rank}: fused all-gather differs from GEMM + NCCL all-gather ({flags.tolist()})")
+        fused = {"bit_identical_to_collective": True}
+        for name, fn in arms.items():
+            for _ in range(args.warmup):
+                fn()
+            dist.barrier()
+            ms = reduce_max(timed_ms(fn, args.steps))
+            fused[name] = {"ms": ms, "tflops_total": 2.0 * args.m * args.n * args.k / ms / 1e9}
+
     if rank == 0:
         print(json.dumps({"benchmark": "m_sharded_gemm", "m": args.m, "n": args.n, "k": args.k, "n_gpus": world,
                           "rows_per_rank": rows, "steps": args.steps, "warmup": args.warmup,
                           "sgemm_impl": args.sgemm_impl, "tf32_kernel": tf32_kernel, "parity": {
                               "fp32_max_abs_error": err32, "fp32_tolerance": tol, "tf32_rel_frobenius": rel_tf32},
-                          "fp32_simt": results["fp32_simt"], "tf32": results["tf32"], "allgather_c": gather}))
+                          "fp32_simt": results["fp32_simt"], "tf32": results["tf32"], "allgather_c": gather,
+                          "gemm_plus_allgather": fused}))
     if distributed:
         dist.destroy_process_group()
 

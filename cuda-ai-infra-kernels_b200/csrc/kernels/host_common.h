@@ -10,6 +10,27 @@
 
 namespace b200 {
 
+// Destinations of a fused "GEMM + all-gather" store: besides its own output a
+// kernel writes every finished tile to the same position of up to
+// B200_MAX_PEERS other buffers (peer GPUs' memory mapped into this process,
+// plain st.global over NVLink; never loaded from, never handed to TMA).
+struct PeerOutputs {
+  float* ptr[B200_MAX_PEERS];
+  int count;
+};
+
+inline bool make_peer_outputs(PeerOutputs* out, float* const* peers, int n_peers) {
+  out->count = 0;
+  for (int i = 0; i < B200_MAX_PEERS; ++i) out->ptr[i] = nullptr;
+  if (n_peers < 0 || n_peers > B200_MAX_PEERS || (n_peers > 0 && peers == nullptr)) return false;
+  for (int i = 0; i < n_peers; ++i) {
+    if (peers[i] == nullptr) return false;
+    out->ptr[i] = peers[i];
+  }
+  out->count = n_peers;
+  return true;
+}
+
 // Number of SMs of the current device (cached per device ordinal).
 int sm_count();
 

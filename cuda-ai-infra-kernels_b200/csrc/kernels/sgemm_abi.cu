@@ -79,7 +79,24 @@ int b200_sgemm(int impl, const float* a_colmajor, const float* b, float* c, int 
   if (check != B200_OK) return check;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (impl <= B200_SGEMM_WARP_TILE) return b200::sgemm_ladder_launch(impl, a_colmajor, b, c, m, n, k, s);
-  return b200::sgemm_pipeline_launch(impl, a_colmajor, b, c, m, n, k, s);
+  b200::PeerOutputs none;
+  b200::make_peer_outputs(&none, nullptr, 0);
+  return b200::sgemm_pipeline_launch(impl, a_colmajor, b, c, none, m, n, k, s);
+}
+
+int b200_sgemm_gather(int impl, const float* a_colmajor, const float* b, float* c, float* const* peer_c, int n_peers,
+                      int m, int n, int k, b200_stream_t stream) {
+  if (a_colmajor == nullptr || b == nullptr || c == nullptr) return B200_ERR_INVALID_ARGUMENT;
+  b200::PeerOutputs peers;
+  if (!b200::make_peer_outputs(&peers, peer_c, n_peers)) return B200_ERR_INVALID_ARGUMENT;
+  const int check = b200_sgemm_check(impl, a_colmajor, b, m, n, k);
+  if (check != B200_OK) return check;
+  // Only the persistent pipeline kernels that store finished tiles once can fan them out.
+  if (impl != B200_SGEMM_PREFETCH_SMEM && impl != B200_SGEMM_PREFETCH_REG) return B200_ERR_NOT_SUPPORTED;
+  for (int i = 0; i < n_peers; ++i) {
+    if (reinterpret_cast<uintptr_t>(peer_c[i]) % 16 != 0) return B200_ERR_MISALIGNED_OPERAND;
+  }
+  return b200::sgemm_pipeline_launch(impl, a_colmajor, b, c, peers, m, n, k, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -44,6 +44,7 @@ struct PipelineParams {
   CUtensorMap map_a;  // [K][M] view of A storage, boxes {128 m, BK k}
   CUtensorMap map_b;  // [K][N] view of B, boxes {128 n, BK k}
   float* c;
+  PeerOutputs peers;  // further destinations of every output tile (fused all-gather), usually none
   int n;
   int tiles_m, tiles_n;
   int k_blocks;       // ceil(K / BK)
@@ -356,27 +357,34 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
     // Epilogue straight from registers: every store instruction of a warp
     // covers eight rows x 64 contiguous bytes. Stream-K segments are partial
     // sums and are reduced into the cleared output instead.
-    float* c_tile = p.c + static_cast<int64_t>(tm * kTile + row0) * p.n + tn * kTile + col0;
+    const int64_t tile_offset = static_cast<int64_t>(tm * kTile + row0) * p.n + tn * kTile + col0;
+    // Destination 0 is this GPU's output; the others (fused all-gather) are the
+    // same tile in peer GPUs' buffers, written with the same plain stores.
+    const int destinations = kStreamK ? 1 : 1 + p.peers.count;
+    for (int dest = 0; dest < destinations; ++dest) {
+      float* c_tile = (dest == 0 ? p.c : p.peers.ptr[dest - 1]) + tile_offset;
 #pragma unroll
-    for (int rb = 0; rb < RM; ++rb)
+      for (int rb = 0; rb < RM; ++rb)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float* c_row = c_tile + static_cast<int64_t>(rb * 32 + i) * p.n;
-        const float* v = acc[rb * 4 + i];
+        for (int i = 0; i < 4; ++i) {
+          float* c_row = c_tile + static_cast<int64_t>(rb * 32 + i) * p.n;
+          const float* v = acc[rb * 4 + i];
 #pragma unroll
-        for (int cb = 0; cb < RN; ++cb) {
-          if constexpr (!kStreamK) {
-            *reinterpret_cast<float4*>(c_row + 16 * cb) = make_float4(v[4 * cb], v[4 * cb + 1], v[4 * cb + 2], v[4 * cb + 3]);
-          } else {
-            red_add_v4(c_row + 16 * cb, v[4 * cb], v[4 * cb + 1], v[4 * cb + 2], v[4 * cb + 3]);
+          for (int cb = 0; cb < RN; ++cb) {
+            if constexpr (!kStreamK) {
+              *reinterpret_cast<float4*>(c_row + 16 * cb) = make_float4(v[4 * cb], v[4 * cb + 1], v[4 * cb + 2], v[4 * cb + 3]);
+            } else {
+              red_add_v4(c_row + 16 * cb, v[4 * cb], v[4 * cb + 1], v[4 * cb + 2], v[4 * cb + 3]);
+            }
           }
         }
-      }
+    }
   }
 }
 
 template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, bool kStreamK, int kCtasPerSm>
-int launch_pipeline(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
+int launch_pipeline(const float* a, const float* b, float* c, const PeerOutputs& peers, int m, int n, int k,
+                    cudaStream_t stream) {
   using Layout = SmemLayout<BK, STAGES>;
   auto kernel = sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, kStreamK, kCtasPerSm>;
   // Function attributes are per device; setting them again is cheap and keeps
@@ -395,7 +403,9 @@ int launch_pipeline(const float* a, const float* b, float* c, int m, int n, int 
       !make_tensor_map_2d(&p.map_b, b, k, n, n, BK, kTile, Swizzle::kNone)) {
     return B200_ERR_MISALIGNED_OPERAND;
   }
+  if (kStreamK && peers.count > 0) return B200_ERR_NOT_SUPPORTED;   // partial sums need a cleared output
   p.c = c;
+  p.peers = peers;
   p.n = n;
   p.tiles_m = m / kTile;
   p.tiles_n = n / kTile;
@@ -416,19 +426,19 @@ int launch_pipeline(const float* a, const float* b, float* c, int m, int n, int 
 
 }  // namespace
 
-int sgemm_pipeline_launch(int impl, const float* a, const float* b, float* c, int m, int n, int k,
-                          cudaStream_t stream) {
+int sgemm_pipeline_launch(int impl, const float* a, const float* b, float* c, const PeerOutputs& peers, int m, int n,
+                          int k, cudaStream_t stream) {
   // Ring shapes come from a sweep on B200 at 4096^3: deeper stages amortise the
   // per-stage barrier traffic (58 -> 62 -> 63 TFLOP/s for 16 -> 32 -> 64 floats
   // of K per stage with 8 x 8 thread tiles); 8 x 16 thread tiles with an inline
   // producer measured slower (50 TFLOP/s) and are kept out of the dispatch.
   switch (impl) {
     case B200_SGEMM_PREFETCH_SMEM:
-      return launch_pipeline<WarpGrid<2, 2>, 64, 3, false, true, false, 1>(a, b, c, m, n, k, stream);
+      return launch_pipeline<WarpGrid<2, 2>, 64, 3, false, true, false, 1>(a, b, c, peers, m, n, k, stream);
     case B200_SGEMM_PREFETCH_REG:
-      return launch_pipeline<WarpGrid<2, 2>, 64, 3, true, true, false, 1>(a, b, c, m, n, k, stream);
+      return launch_pipeline<WarpGrid<2, 2>, 64, 3, true, true, false, 1>(a, b, c, peers, m, n, k, stream);
     case B200_SGEMM_SPLIT_K:
-      return launch_pipeline<WarpGrid<2, 2>, 64, 3, true, true, true, 1>(a, b, c, m, n, k, stream);
+      return launch_pipeline<WarpGrid<2, 2>, 64, 3, true, true, true, 1>(a, b, c, peers, m, n, k, stream);
     default:
       return B200_ERR_INVALID_ARGUMENT;
   }

@@ -185,7 +185,8 @@ int launch_act(const SkinnyParams& p, int ranks, cudaStream_t stream) {
 
 }  // namespace
 
-int launch_skinny(const b200_gemm_problem& q, cudaStream_t stream) {
+int launch_skinny(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  if (peers.count > 0) return B200_ERR_NOT_SUPPORTED;
   if (q.m > kSkinnyMaxRows || q.n % 4 != 0) return B200_ERR_INVALID_PROBLEM;
   const int sms = sm_count();
   if (sms <= 0) return B200_ERR_INTERNAL;

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include "b200_kernels.h"
+#include "host_common.h"
 
 namespace b200 {
 
@@ -14,6 +15,7 @@ constexpr int kSkinnyMaxRows = 16;
 // D = act(alpha * A @ B + beta * C + bias) for M <= kSkinnyMaxRows, N % 4 == 0,
 // B 16-byte aligned with ldb % 4 == 0; FP32 FMA arithmetic, B streamed once.
 // Returns B200_ERR_INVALID_PROBLEM for shapes outside that range.
-int launch_skinny(const b200_gemm_problem& q, cudaStream_t stream);
+// Cannot store to peer outputs: B200_ERR_NOT_SUPPORTED when `peers` is not empty.
+int launch_skinny(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream);
 
 }  // namespace b200

@@ -83,6 +83,7 @@ struct UmmaParams {
   int m, n, k;
   float alpha, beta;
   int vector_io;       // C/D rows allow 128-bit accesses
+  PeerOutputs peers;   // further destinations of every finished element (fused all-gather), usually none
 #ifdef B200_PROBE_TIMING
   uint64_t* probe;     // [grid][8] time stamps, or null
 #endif
@@ -100,10 +101,19 @@ struct EpilogueArgs {
   int m, n;
   float alpha, beta;
   int vector_io;
+  PeerOutputs peers;
 };
 
 __device__ __forceinline__ EpilogueArgs epilogue_args(const UmmaParams& p) {
-  return EpilogueArgs{p.c, p.bias, p.d, p.ldc, p.ldd, p.m, p.n, p.alpha, p.beta, p.vector_io};
+  return EpilogueArgs{p.c, p.bias, p.d, p.ldc, p.ldd, p.m, p.n, p.alpha, p.beta, p.vector_io, p.peers};
+}
+
+// The same element(s) of every peer's copy of the output (fused all-gather).
+__device__ __forceinline__ void store_peers(const EpilogueArgs& p, int64_t offset, float4 v) {
+  for (int i = 0; i < p.peers.count; ++i) *reinterpret_cast<float4*>(p.peers.ptr[i] + offset) = v;
+}
+__device__ __forceinline__ void store_peers(const EpilogueArgs& p, int64_t offset, float v) {
+  for (int i = 0; i < p.peers.count; ++i) p.peers.ptr[i][offset] = v;
 }
 
 template <int BN>
@@ -111,9 +121,18 @@ __host__ __device__ constexpr uint32_t stage_bytes() {
   return kASlabBytes + (BN / 32) * kBBoxBytes;
 }
 
+// Staging of the fused all-gather: an epilogue warp turns its 32 x 32 chunk (one row per lane in
+// registers) by way of shared memory so that peer copies are written in 128-byte row segments, four
+// rows per instruction, instead of 32 scattered 16-byte pieces (NVLink moves those poorly). The
+// pitch of 36 floats keeps both the row-per-lane writes and the row-wise reads free of conflicts.
+constexpr int kPeerStagePitch = 36;
+constexpr size_t kPeerStageBytesPerWarp = 32 * kPeerStagePitch * sizeof(float);
+constexpr size_t kPeerStageBytes = 4 * kPeerStageBytesPerWarp;   // four epilogue warps
+
 template <int BN, int STAGES>
 __host__ __device__ constexpr size_t smem_bytes() {
-  return static_cast<size_t>(STAGES) * stage_bytes<BN>() + 1024 /*alignment slack*/ + 256 /*barriers + tmem ptr*/;
+  return static_cast<size_t>(STAGES) * stage_bytes<BN>() + 1024 /*alignment slack*/ + 256 /*barriers + tmem ptr*/ +
+         kPeerStageBytes;
 }
 
 template <int BN>
@@ -163,8 +182,9 @@ __device__ __forceinline__ float activate(float v) {
 // chunks of 32 columns.
 template <int BN, int kAct>
 __device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tmem_acc, int quarter, int lane, int m0,
-                                              int n0) {
+                                              int n0, float* stage) {
   const int row = m0 + quarter * 32 + lane;
+  const bool stage_peers = p.peers.count > 0 && p.vector_io;   // `stage`: this warp's kPeerStageBytesPerWarp
   const bool row_ok = row < p.m;
   const bool use_c = p.beta != 0.f;
   const bool use_bias = p.bias != nullptr;
@@ -177,7 +197,48 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tm
     uint32_t raw[32];
     tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 32, raw);
     tmem_ld_wait();
-    if (!row_ok) continue;
+    if (!row_ok && !stage_peers) continue;
+    if (stage_peers) {
+      // Local copy straight from registers; peer copies row-wise from the staged chunk.
+      if (row_ok) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const int col = col0 + 4 * g;
+          if (col < p.n) {
+            float4 v = make_float4(p.alpha * __uint_as_float(raw[4 * g + 0]), p.alpha * __uint_as_float(raw[4 * g + 1]),
+                                   p.alpha * __uint_as_float(raw[4 * g + 2]), p.alpha * __uint_as_float(raw[4 * g + 3]));
+            if (use_c) {
+              const float4 s = __ldg(reinterpret_cast<const float4*>(c_row + col));
+              v.x = fmaf(p.beta, s.x, v.x), v.y = fmaf(p.beta, s.y, v.y);
+              v.z = fmaf(p.beta, s.z, v.z), v.w = fmaf(p.beta, s.w, v.w);
+            }
+            if (use_bias) {
+              const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+              v.x += bv.x, v.y += bv.y, v.z += bv.z, v.w += bv.w;
+            }
+            v = make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
+            *reinterpret_cast<float4*>(d_row + col) = v;
+            *reinterpret_cast<float4*>(stage + lane * kPeerStagePitch + 4 * g) = v;
+          }
+        }
+      }
+      __syncwarp();
+      // Lane l takes column quad l % 8 of rows 4 j + l / 8.
+      const int quad_col = col0 + 4 * (lane & 7);
+      if (quad_col < p.n) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int r = 4 * j + (lane >> 3);
+          const int out_row = m0 + quarter * 32 + r;
+          if (out_row < p.m) {
+            const float4 v = *reinterpret_cast<const float4*>(stage + r * kPeerStagePitch + 4 * (lane & 7));
+            store_peers(p, static_cast<int64_t>(out_row) * p.ldd + quad_col, v);
+          }
+        }
+      }
+      __syncwarp();   // the chunk is reused by the next iteration
+      continue;
+    }
     if (p.vector_io) {
       // n % 4 == 0 here, so a 4-wide group is entirely inside or outside.
 #pragma unroll
@@ -209,6 +270,7 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tm
           if (use_bias) v += __ldg(p.bias + col);
           v = activate<kAct>(v);
           d_row[col] = v;
+          store_peers(p, static_cast<int64_t>(row) * p.ldd + col, v);
         }
       }
     }
@@ -222,6 +284,7 @@ struct SmemCarve {
   uint64_t* acc_full;
   uint64_t* acc_empty;
   uint32_t* tmem_ptr;
+  float* peer_stage;   // kPeerStageBytes, 16-byte aligned
 };
 
 template <int BN, int STAGES>
@@ -233,6 +296,7 @@ __device__ __forceinline__ SmemCarve carve(uint8_t* raw) {
   s.acc_full = s.empty + STAGES;
   s.acc_empty = s.acc_full + 2;
   s.tmem_ptr = reinterpret_cast<uint32_t*>(s.acc_empty + 2);
+  s.peer_stage = reinterpret_cast<float*>(s.tmem_ptr + 4);
   return s;
 }
 
@@ -278,7 +342,8 @@ __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCar
     tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
     if (!mbar_wait(&sm.acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
     tcgen05_fence_after_sync();
-    epilogue_tile<BN, kAct>(ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN);
+    epilogue_tile<BN, kAct>(ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN,
+                            sm.peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float)));
     tcgen05_fence_before_sync();
     __syncwarp();
     if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
@@ -378,7 +443,7 @@ constexpr uint32_t kPairStageBytes = kASlabBytes + (kPairN / 2 / 32) * kBBoxByte
 
 template <int STAGES>
 __host__ __device__ constexpr size_t pair_smem_bytes() {
-  return static_cast<size_t>(STAGES) * kPairStageBytes + 1024 + 256;
+  return static_cast<size_t>(STAGES) * kPairStageBytes + 1024 + 256 + kPeerStageBytes;
 }
 
 template <int STAGES, int kAct>
@@ -392,6 +457,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
   uint64_t* acc_full = empty + STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  float* peer_stage = reinterpret_cast<float*>(tmem_ptr + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();  // 0: issues the MMAs, 1: peer
@@ -503,7 +569,8 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
       if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
       epilogue_tile<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane,
-                                   tm * 2 * kTileM + static_cast<int>(rank) * kTileM, tn * kPairN);
+                                   tm * 2 * kTileM + static_cast<int>(rank) * kTileM, tn * kPairN,
+                                   peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float)));
       tcgen05_fence_before_sync();
       __syncwarp();
       // The MMA issuer (CTA 0) waits for the epilogues of both CTAs.
@@ -554,8 +621,9 @@ __device__ __forceinline__ void finish_quad(const EpilogueArgs& p, int row, int 
       const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
       v[0] += bv.x, v[1] += bv.y, v[2] += bv.z, v[3] += bv.w;
     }
-    *reinterpret_cast<float4*>(d_row + col) =
-        make_float4(activate<kAct>(v[0]), activate<kAct>(v[1]), activate<kAct>(v[2]), activate<kAct>(v[3]));
+    const float4 out = make_float4(activate<kAct>(v[0]), activate<kAct>(v[1]), activate<kAct>(v[2]), activate<kAct>(v[3]));
+    *reinterpret_cast<float4*>(d_row + col) = out;
+    store_peers(p, static_cast<int64_t>(row) * p.ldd + col, out);
   } else {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -563,7 +631,9 @@ __device__ __forceinline__ void finish_quad(const EpilogueArgs& p, int row, int 
         float out = v[e];
         if (p.beta != 0.f) out = fmaf(p.beta, __ldg(c_row + col + e), out);
         if (p.bias != nullptr) out += __ldg(p.bias + col + e);
-        d_row[col + e] = activate<kAct>(out);
+        out = activate<kAct>(out);
+        d_row[col + e] = out;
+        store_peers(p, static_cast<int64_t>(row) * p.ldd + col + e, out);
       }
     }
   }
@@ -941,8 +1011,9 @@ __global__ void __launch_bounds__(kGenericThreads, 1) umma_generic_kernel(const 
 
 bool aligned16(const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; }
 
-void fill_common(UmmaParams* p, const b200_gemm_problem& q) {
+void fill_common(UmmaParams* p, const b200_gemm_problem& q, const PeerOutputs& peers) {
   std::memset(p, 0, sizeof(*p));
+  p->peers = peers;
   p->a = q.a, p->b = q.b, p->d = q.d;
   p->c = q.beta != 0.f ? q.c : nullptr;
   p->bias = q.bias;
@@ -951,18 +1022,20 @@ void fill_common(UmmaParams* p, const b200_gemm_problem& q) {
   p->alpha = q.alpha, p->beta = q.beta;
   const bool c_ok = q.beta == 0.f || (aligned16(q.c) && q.ldc % 4 == 0);
   const bool bias_ok = q.bias == nullptr || aligned16(q.bias);
-  p->vector_io = (q.n % 4 == 0 && aligned16(q.d) && q.ldd % 4 == 0 && c_ok && bias_ok) ? 1 : 0;
+  bool peers_ok = true;   // peer copies share the row pitch of D, only their bases can differ in alignment
+  for (int i = 0; i < peers.count; ++i) peers_ok = peers_ok && aligned16(peers.ptr[i]);
+  p->vector_io = (q.n % 4 == 0 && aligned16(q.d) && q.ldd % 4 == 0 && c_ok && bias_ok && peers_ok) ? 1 : 0;
 }
 
 template <int BN, int STAGES, int kAct>
-int launch_tma(const b200_gemm_problem& q, cudaStream_t stream) {
+int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   auto kernel = umma_tma_kernel<BN, STAGES, kAct>;
   constexpr size_t smem = smem_bytes<BN, STAGES>();
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
   }
   UmmaParams p;
-  fill_common(&p, q);
+  fill_common(&p, q, peers);
   if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
       !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
     return B200_ERR_MISALIGNED_OPERAND;
@@ -981,14 +1054,14 @@ int launch_tma(const b200_gemm_problem& q, cudaStream_t stream) {
 }
 
 template <int STAGES, int kAct>
-int launch_pair(const b200_gemm_problem& q, cudaStream_t stream) {
+int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   auto kernel = umma_pair_kernel<STAGES, kAct>;
   constexpr size_t smem = pair_smem_bytes<STAGES>();
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
   }
   UmmaParams p;
-  fill_common(&p, q);
+  fill_common(&p, q, peers);
   if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
       !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
     return B200_ERR_MISALIGNED_OPERAND;
@@ -1026,7 +1099,7 @@ int splitk_max_clusters(int cluster_size) {
   const int slot = cluster_size == 1 ? 0 : cluster_size == 2 ? 1 : cluster_size == 4 ? 2 : 3;
   if (cache[device][slot] != 0) return cache[device][slot];
   auto kernel = umma_splitk_kernel<3, B200_EPILOGUE_LINEAR>;   // the activation does not change the footprint
-  constexpr size_t smem = smem_bytes<kSplitN, 3>();
+  constexpr size_t smem = smem_bytes<kSplitN, 3>() - kPeerStageBytes;   // no staging: two CTAs fit an SM
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(cluster_size) * 64);
@@ -1072,14 +1145,14 @@ int splitk_ranks(const b200_gemm_problem& q, int sms, float* estimate_us = nullp
 }
 
 template <int STAGES, int kAct>
-int launch_splitk(const b200_gemm_problem& q, cudaStream_t stream) {
+int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   auto kernel = umma_splitk_kernel<STAGES, kAct>;
-  constexpr size_t smem = smem_bytes<kSplitN, STAGES>();
+  constexpr size_t smem = smem_bytes<kSplitN, STAGES>() - kPeerStageBytes;   // its finishing pass needs no staging
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
   }
   UmmaParams p;
-  fill_common(&p, q);
+  fill_common(&p, q, peers);
   if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
       !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
     return B200_ERR_MISALIGNED_OPERAND;
@@ -1110,14 +1183,14 @@ int launch_splitk(const b200_gemm_problem& q, cudaStream_t stream) {
 }
 
 template <int BN, int STAGES, int kAct>
-int launch_generic(const b200_gemm_problem& q, cudaStream_t stream) {
+int launch_generic(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   auto kernel = umma_generic_kernel<BN, STAGES, kAct>;
   constexpr size_t smem = smem_bytes<BN, STAGES>();
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
   }
   UmmaParams p;
-  fill_common(&p, q);
+  fill_common(&p, q, peers);
   const int sms = sm_count();
   if (sms <= 0) return B200_ERR_INTERNAL;
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + BN - 1) / BN);
@@ -1128,7 +1201,7 @@ int launch_generic(const b200_gemm_problem& q, cudaStream_t stream) {
 
 // ------------------------------------------------------------------- registry
 
-using LaunchFn = int (*)(const b200_gemm_problem&, cudaStream_t);
+using LaunchFn = int (*)(const b200_gemm_problem&, const PeerOutputs&, cudaStream_t);
 // Shape heuristic consulted only by automatic dispatch; a forced kernel runs
 // whatever the shape.
 using AutoGateFn = bool (*)(const b200_gemm_problem&, int sms);
@@ -1305,18 +1378,24 @@ int b200_tf32_can_implement(int kernel_id, const b200_gemm_problem* q) {
 int b200_tf32_gemm_launch(int kernel_id, const b200_gemm_problem* q, b200_stream_t stream) {
   const int status = b200_tf32_can_implement(kernel_id, q);
   if (status != B200_OK) return status;
-  return b200::find_entry(kernel_id)->launch(*q, static_cast<cudaStream_t>(stream));
+  b200::PeerOutputs none;
+  b200::make_peer_outputs(&none, nullptr, 0);
+  return b200::find_entry(kernel_id)->launch(*q, none, static_cast<cudaStream_t>(stream));
 }
 
-int b200_tf32_gemm_dispatch(int requested, const b200_gemm_problem* q, int* chosen, b200_stream_t stream) {
+int b200_tf32_gemm_dispatch_gather(int requested, const b200_gemm_problem* q, float* const* peer_d, int n_peers,
+                                   int* chosen, b200_stream_t stream) {
   const int basic = b200::check_problem(q);
   if (basic != B200_OK) return basic;
+  b200::PeerOutputs peers;
+  if (!b200::make_peer_outputs(&peers, peer_d, n_peers)) return B200_ERR_INVALID_ARGUMENT;
   if (requested == B200_TF32_KERNEL_CUBLAS) return B200_ERR_INVALID_ARGUMENT;  // library baseline lives in the caller
   const int sms = requested == B200_TF32_KERNEL_AUTO ? b200::sm_count() : 0;
   for (const b200::RegistryEntry& e : b200::kRegistry) {
     if (requested != B200_TF32_KERNEL_AUTO && e.meta.id != requested) continue;
     if (requested == B200_TF32_KERNEL_AUTO && !e.auto_gate(*q, sms)) continue;
-    const int status = b200_tf32_gemm_launch(e.meta.id, q, stream);
+    int status = b200_tf32_can_implement(e.meta.id, q);
+    if (status == B200_OK) status = e.launch(*q, peers, static_cast<cudaStream_t>(stream));
     if (status == B200_OK) {
       if (chosen != nullptr) *chosen = e.meta.id;
       return B200_OK;
@@ -1330,6 +1409,10 @@ int b200_tf32_gemm_dispatch(int requested, const b200_gemm_problem* q, int* chos
     }
   }
   return B200_ERR_NOT_SUPPORTED;
+}
+
+int b200_tf32_gemm_dispatch(int requested, const b200_gemm_problem* q, int* chosen, b200_stream_t stream) {
+  return b200_tf32_gemm_dispatch_gather(requested, q, nullptr, 0, chosen, stream);
 }
 
 }  // extern "C"

@@ -7,7 +7,9 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <cublas_v2.h>
 
+#include <cstdint>
 #include <limits>
+#include <vector>
 
 #include "op_common.h"
 #include "ops.h"
@@ -97,9 +99,15 @@ const char* registry_name(int id) {
 
 std::string adaptive_gemm_last_kernel() { return g_last_kernel; }
 
-torch::Tensor adaptive_gemm(const torch::Tensor& a, const torch::Tensor& b, const c10::optional<at::Tensor>& c,
-                            const c10::optional<at::Tensor>& bias, double alpha, double beta,
-                            const std::string& epilogue, const std::string& kernel) {
+namespace {
+
+// Shared body of adaptive_gemm and adaptive_gemm_gather. Without `out` the
+// result is a fresh tensor; with it the result is written there and fanned out
+// to `peer_ptrs` by the kernel's epilogue.
+torch::Tensor run_adaptive(const torch::Tensor& a, const torch::Tensor& b, const c10::optional<at::Tensor>& c,
+                           const c10::optional<at::Tensor>& bias, double alpha, double beta,
+                           const std::string& epilogue, const std::string& kernel, const c10::optional<at::Tensor>& out,
+                           const std::vector<int64_t>& peer_ptrs) {
   check_ab(a, b);
   const ParsedEpilogue parsed = parse_epilogue(epilogue);
   const int requested = parse_kernel(kernel);
@@ -123,7 +131,18 @@ torch::Tensor adaptive_gemm(const torch::Tensor& a, const torch::Tensor& b, cons
   }
 
   const c10::cuda::CUDAGuard guard(a.device());
-  auto d = torch::empty({m, n}, a.options());
+  if (out.has_value()) {
+    B200_CHECK_CUDA((*out));
+    B200_CHECK_FLOAT32((*out));
+    TORCH_CHECK(out->device() == a.device(), "out must be on the same CUDA device as A");
+    TORCH_CHECK(out->dim() == 2 && out->size(0) == m && out->size(1) == n, "out must have shape [", m, ", ", n,
+                "] but got ", out->sizes());
+    TORCH_CHECK(out->stride(1) == 1 && out->stride(0) >= n, "out must be row-major");
+    TORCH_CHECK(requested != B200_TF32_KERNEL_CUBLAS, "adaptive_gemm_gather has no cuBLAS arm");
+    TORCH_CHECK(peer_ptrs.size() <= B200_MAX_PEERS, "at most ", B200_MAX_PEERS, " peer destinations");
+    for (const int64_t ptr : peer_ptrs) TORCH_CHECK(ptr != 0, "peer destination pointers must not be null");
+  }
+  auto d = out.has_value() ? *out : torch::empty({m, n}, a.options());
 
   b200_gemm_problem q{};
   q.m = static_cast<int>(m), q.n = static_cast<int>(n), q.k = static_cast<int>(a.size(1));
@@ -146,9 +165,27 @@ torch::Tensor adaptive_gemm(const torch::Tensor& a, const torch::Tensor& b, cons
     return d;
   }
 
+  float* peers[B200_MAX_PEERS] = {};
+  for (size_t i = 0; i < peer_ptrs.size(); ++i) peers[i] = reinterpret_cast<float*>(static_cast<std::uintptr_t>(peer_ptrs[i]));
   int chosen = -1;
-  const int status = b200_tf32_gemm_dispatch(requested, &q, &chosen, current_stream(a));
+  const int status = b200_tf32_gemm_dispatch_gather(requested, &q, peers, static_cast<int>(peer_ptrs.size()), &chosen,
+                                                    current_stream(a));
   TORCH_CHECK(status == B200_OK, "adaptive GEMM dispatch failed: ", b200_status_string(status));
   g_last_kernel = registry_name(chosen);
   return d;
+}
+
+}  // namespace
+
+torch::Tensor adaptive_gemm(const torch::Tensor& a, const torch::Tensor& b, const c10::optional<at::Tensor>& c,
+                            const c10::optional<at::Tensor>& bias, double alpha, double beta,
+                            const std::string& epilogue, const std::string& kernel) {
+  return run_adaptive(a, b, c, bias, alpha, beta, epilogue, kernel, c10::nullopt, {});
+}
+
+torch::Tensor adaptive_gemm_gather(const torch::Tensor& a, const torch::Tensor& b, const c10::optional<at::Tensor>& c,
+                                   const c10::optional<at::Tensor>& bias, double alpha, double beta,
+                                   const std::string& epilogue, const std::string& kernel, torch::Tensor out,
+                                   std::vector<int64_t> peer_ptrs) {
+  return run_adaptive(a, b, c, bias, alpha, beta, epilogue, kernel, out, peer_ptrs);
 }

@@ -1,6 +1,7 @@
 // pybind11 module `cuda_ai_kernels._C`: the 23 functions of the reference
 // module (csrc/bindings.cpp:10-45) with identical names, positional order,
-// keyword names and defaults, plus one introspection helper.
+// keyword names and defaults, plus one introspection helper and the two fused all-gather entries of the
+// multi-GPU path.
 #include <torch/extension.h>
 
 #include "ops.h"
@@ -33,6 +34,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adaptive_gemm", &adaptive_gemm, "TF32 GEMM with fused epilogue behind a compatibility registry",
         py::arg("a"), py::arg("b"), py::arg("c") = py::none(), py::arg("bias") = py::none(), py::arg("alpha") = 1.0,
         py::arg("beta") = 0.0, py::arg("epilogue") = "linear", py::arg("kernel") = "auto");
+  m.def("gemm_gather", &gemm_gather, "FP32 SIMT GEMM whose epilogue also stores every tile to peer GPUs (fused all-gather)",
+        py::arg("a"), py::arg("b"), py::arg("out"), py::arg("peer_ptrs"), py::arg("impl") = "prefetch_reg");
+  m.def("adaptive_gemm_gather", &adaptive_gemm_gather,
+        "TF32 GEMM + fused epilogue whose stores also go to peer GPUs (fused all-gather)", py::arg("a"), py::arg("b"),
+        py::arg("c") = py::none(), py::arg("bias") = py::none(), py::arg("alpha") = 1.0, py::arg("beta") = 0.0,
+        py::arg("epilogue") = "linear", py::arg("kernel") = "auto", py::arg("out"), py::arg("peer_ptrs"));
   m.def("adaptive_gemm_last_kernel", &adaptive_gemm_last_kernel,
         "Registry name chosen by this thread's last adaptive_gemm call");
 }

@@ -111,6 +111,20 @@ torch::Tensor run_named(int impl, const torch::Tensor& a, const torch::Tensor& b
   return launch_ladder(impl, a, b);
 }
 
+// Destination checks shared by the fused all-gather entries: `out` is where
+// this rank's rows live inside its copy of the gathered matrix.
+void check_gather_output(const torch::Tensor& out, const torch::Tensor& a, int64_t m, int64_t n,
+                         const std::vector<int64_t>& peer_ptrs) {
+  B200_CHECK_CUDA(out);
+  B200_CHECK_FLOAT32(out);
+  TORCH_CHECK(out.device() == a.device(), "out must be on the same CUDA device as A");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == m && out.size(1) == n, "out must have shape [", m, ", ", n, "] but got ",
+              out.sizes());
+  TORCH_CHECK(out.stride(1) == 1 && out.stride(0) == n, "out must be a dense row-major block of rows");
+  TORCH_CHECK(peer_ptrs.size() <= B200_MAX_PEERS, "at most ", B200_MAX_PEERS, " peer destinations");
+  for (const int64_t ptr : peer_ptrs) TORCH_CHECK(ptr != 0, "peer destination pointers must not be null");
+}
+
 // alpha = 1, beta = 0 TF32 product of two row-major matrices through the
 // tcgen05 registry. Degenerate sizes never reach a kernel.
 torch::Tensor run_tf32_row_major(const torch::Tensor& a, const torch::Tensor& b, const char* what) {
@@ -160,6 +174,27 @@ torch::Tensor gemm_warp_tile(torch::Tensor a, torch::Tensor b) { return run_regu
 torch::Tensor gemm_prefetch_smem(torch::Tensor a, torch::Tensor b) { return run_named(B200_SGEMM_PREFETCH_SMEM, a, b); }
 torch::Tensor gemm_prefetch_reg(torch::Tensor a, torch::Tensor b) { return run_named(B200_SGEMM_PREFETCH_REG, a, b); }
 torch::Tensor gemm_split_k(torch::Tensor a, torch::Tensor b) { return run_named(B200_SGEMM_SPLIT_K, a, b); }
+
+torch::Tensor gemm_gather(torch::Tensor a, torch::Tensor b, torch::Tensor out, std::vector<int64_t> peer_ptrs,
+                          const std::string& impl) {
+  const int id = b200_sgemm_impl_from_name(impl.c_str());
+  TORCH_CHECK(id == B200_SGEMM_PREFETCH_SMEM || id == B200_SGEMM_PREFETCH_REG,
+              "gemm_gather supports impl='prefetch_smem' or 'prefetch_reg', got '", impl, "'");
+  const char* label = b200_sgemm_impl_name(id);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm expects 2D tensors");
+  TORCH_CHECK(a.size(0) > 0 && a.size(1) > 0 && b.size(1) > 0, label, " requires positive M, N and K");
+  check_ladder_layout(a, b);
+  check_ladder_sizes(id, label, true, a, b);
+  const int m = static_cast<int>(a.size(0)), k = static_cast<int>(a.size(1)), n = static_cast<int>(b.size(1));
+  check_gather_output(out, a, m, n, peer_ptrs);
+  const c10::cuda::CUDAGuard guard(a.device());
+  float* peers[B200_MAX_PEERS] = {};
+  for (size_t i = 0; i < peer_ptrs.size(); ++i) peers[i] = reinterpret_cast<float*>(static_cast<std::uintptr_t>(peer_ptrs[i]));
+  const int status = b200_sgemm_gather(id, a.data_ptr<float>(), b.data_ptr<float>(), out.data_ptr<float>(), peers,
+                                       static_cast<int>(peer_ptrs.size()), m, n, k, current_stream(a));
+  check_status(status, label);
+  return out;
+}
 
 // Library baseline: strict FP32 cuBLAS irrespective of the process-wide TF32
 // switches, on PyTorch's handle for the current device and stream. Accepts the

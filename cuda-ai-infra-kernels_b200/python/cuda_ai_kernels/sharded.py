@@ -3,8 +3,12 @@
 C[r0:r1, :] = A[r0:r1, :] @ B needs nothing from other rows, so the rows of A
 are dealt out to the ranks (one process per GPU), B is replicated, and C stays
 sharded: there is no collective on the data path. Gathering the shards of C on
-every rank is optional and separate (`all_gather_rows`, NCCL over NVLink on
-GPUs, gloo on CPU for tests). The reference is single-GPU; this module is new.
+every rank is optional: either as a separate collective (`all_gather_rows`,
+NCCL over NVLink on GPUs, gloo on CPU for tests) or fused into the GEMM
+(`GatheredOutput` + `sharded_gemm_gather` / `sharded_adaptive_gemm_gather`:
+the kernel's epilogue stores every finished tile into every rank's copy of C
+with plain stores over NVLink, so the transfer overlaps the remaining tiles).
+The reference is single-GPU; this module is new.
 
 The row plan comes from the C ABI (`b200_shard_rows`), so that a C++ host that
 drives the kernels directly partitions exactly like this module does.
@@ -83,3 +87,85 @@ def all_gather_rows(c_shard: torch.Tensor, row_counts: Sequence[int], group=None
     out = torch.empty(world * tallest, n, dtype=c_shard.dtype, device=c_shard.device)
     dist.all_gather_into_tensor(out, padded, group=group)
     return torch.cat([out[r * tallest:r * tallest + rows] for r, rows in enumerate(row_counts)], dim=0)
+
+
+# ------------------------------------------------- GEMM fused with the all-gather
+
+
+def peer_row_pointers(base_ptrs: Sequence[int], rank: int, first_row: int, n: int, itemsize: int = 4) -> list[int]:
+    """Addresses of row `first_row` in every OTHER rank's copy of a gathered [M, n] matrix.
+
+    `base_ptrs[r]` is the address, valid in this process, of rank r's copy.
+    These are the `peer_ptrs` the fused kernels store to (at most 7: 8 GPUs).
+    """
+    if not 0 <= rank < len(base_ptrs):
+        raise ValueError("rank outside the pointer table")
+    if len(base_ptrs) - 1 > 7:
+        raise ValueError("at most 8 ranks can be gathered by the fused kernels")
+    if first_row < 0 or n <= 0:
+        raise ValueError("invalid row offset or width")
+    offset = first_row * n * itemsize
+    return [int(ptr) + offset for r, ptr in enumerate(base_ptrs) if r != rank]
+
+
+class GatheredOutput:
+    """Every rank's copy of the gathered C[M, N] (FP32), mapped into every process.
+
+    Built on torch symmetric memory (CUDA virtual-memory handles exchanged
+    through the process group's store), which is plumbing only: the kernels see
+    raw device addresses. Multicast (NVLS) bindings are switched off before the
+    first allocation; the fused kernels use plain peer stores. Collective: every
+    rank of `group` must construct it with the same shape.
+    """
+
+    def __init__(self, m: int, n: int, plan: Sequence[tuple[int, int]], group=None, device=None):
+        import os
+
+        import torch.distributed as dist
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        if len(plan) != self.world or sum(count for _, count in plan) != m:
+            raise ValueError("the row plan must cover M with one entry per rank")
+        self.m, self.n, self.plan = m, n, list(plan)
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.full = symm_mem.empty((m, n), dtype=torch.float32, device=device)
+        self._handle = symm_mem.rendezvous(self.full, self.group)
+        self.base_ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        first, rows = self.plan[self.rank]
+        self.local_rows = self.full[first:first + rows]
+        self.peer_ptrs = peer_row_pointers(self.base_ptrs, self.rank, first, n)
+
+    def barrier(self) -> None:
+        """All ranks' launches so far have completed: every copy of C is whole.
+
+        A device-side barrier on the current stream (signal pads of the
+        symmetric allocation), so no host synchronisation is needed between the
+        GEMM and a consumer kernel on the same stream.
+        """
+        self._handle.barrier()
+
+
+def sharded_gemm_gather(a_shard: torch.Tensor, b: torch.Tensor, out: GatheredOutput, impl: str = "prefetch_reg") -> torch.Tensor:
+    """FP32 SIMT: this rank's rows of C, written into every rank's copy. Returns the local copy.
+
+    The copy is complete only after `out.barrier()`.
+    """
+    from cuda_ai_kernels import _C
+
+    _C.gemm_gather(a_shard, b, out.local_rows, out.peer_ptrs, impl)
+    return out.full
+
+
+def sharded_adaptive_gemm_gather(a_rows: torch.Tensor, b: torch.Tensor, out: GatheredOutput, c: Optional[torch.Tensor] = None,
+                                 bias: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0,
+                                 epilogue: str = "linear", kernel: str = "auto") -> torch.Tensor:
+    """TF32 + fused epilogue: this rank's rows of D, written into every rank's copy. Returns the local copy."""
+    from cuda_ai_kernels import _C
+
+    _C.adaptive_gemm_gather(a_rows, b, c, bias, alpha, beta, epilogue, kernel, out=out.local_rows, peer_ptrs=out.peer_ptrs)
+    return out.full

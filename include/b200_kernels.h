@@ -251,6 +251,34 @@ int b200_softmax(int impl, const float* x, float* y,
 int b200_shard_rows(int64_t m, int parts, int granule,
                     int64_t* row_begin, int64_t* row_count);
 
+/*
+ * Sharded GEMM fused with the all-gather of its output. Each device computes
+ * its row block and the kernel's epilogue stores every finished tile not only
+ * to the local output but also, with plain global stores over NVLink, to the
+ * same position of up to B200_MAX_PEERS other buffers: `peer_c[i]` /
+ * `peer_d[i]` is the address, in peer i's copy of the full output, where this
+ * device's element (0, 0) belongs (same row pitch as the local output; the
+ * caller maps the peers' buffers into this process, e.g. CUDA IPC or symmetric
+ * memory, and owns the synchronisation: a peer may read its buffer once every
+ * device's call has completed). Peer buffers are only ever stored to: no loads,
+ * no TMA, no multicast. With n_peers == 0 the calls equal b200_sgemm and
+ * b200_tf32_gemm_dispatch. The reference is single-GPU (README.md:34) and has
+ * no counterpart; the partition and the optional all-gather of C are the
+ * multi-GPU configuration of the benchmark.
+ *   b200_sgemm_gather: impl must be B200_SGEMM_PREFETCH_SMEM or _PREFETCH_REG
+ *     (B200_ERR_NOT_SUPPORTED otherwise); peer addresses 16-byte aligned.
+ *   b200_tf32_gemm_dispatch_gather: registry entries that cannot fan out
+ *     (the skinny FP32 entries) are skipped by automatic dispatch and refuse
+ *     a forced call with B200_ERR_NOT_SUPPORTED.
+ */
+#define B200_MAX_PEERS 7
+int b200_sgemm_gather(int impl, const float* a_colmajor, const float* b, float* c,
+                      float* const* peer_c, int n_peers,
+                      int m, int n, int k, b200_stream_t stream);
+int b200_tf32_gemm_dispatch_gather(int requested, const b200_gemm_problem* problem,
+                                   float* const* peer_d, int n_peers,
+                                   int* chosen, b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

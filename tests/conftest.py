@@ -81,6 +81,10 @@ def load_abi() -> ctypes.CDLL:
     lib.b200_rmsnorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, ctypes.c_double, c_void_p]
     lib.b200_softmax.argtypes = [c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p]
     lib.b200_shard_rows.argtypes = [c_int64, c_int, c_int, ctypes.POINTER(c_int64), ctypes.POINTER(c_int64)]
+    lib.b200_sgemm_gather.argtypes = [c_int, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p), c_int, c_int, c_int,
+                                      c_int, c_void_p]
+    lib.b200_tf32_gemm_dispatch_gather.argtypes = [c_int, ctypes.POINTER(GemmProblem), ctypes.POINTER(c_void_p), c_int,
+                                                   int_p, c_void_p]
     return lib
 
 

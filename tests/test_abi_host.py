@@ -221,3 +221,28 @@ def test_device_launch_entry_points_reject_null_and_bad_ids_without_a_gpu(abi):
     assert abi.b200_tf32_gemm_dispatch(2, ctypes.byref(mismatched), None, None) == NOT_SUPPORTED
     misaligned = problem(33, 65, 20)
     assert abi.b200_tf32_gemm_dispatch(2, ctypes.byref(misaligned), None, None) == NOT_SUPPORTED
+
+
+def test_gather_entry_points_validate_on_the_host(abi):
+    """Argument checks of the fused all-gather entries that return before any CUDA call."""
+    from conftest import GemmProblem
+
+    peers = (ctypes.c_void_p * 8)(*[0x1000 * (i + 1) for i in range(8)])
+    a = b = c = ctypes.c_void_p(0x10000)
+    # Null operands, too many peers, a null peer, a negative count.
+    assert abi.b200_sgemm_gather(11, None, b, c, peers, 1, 128, 128, 16, None) == INVALID_ARGUMENT
+    assert abi.b200_sgemm_gather(11, a, b, c, peers, 8, 128, 128, 16, None) == INVALID_ARGUMENT
+    assert abi.b200_sgemm_gather(11, a, b, c, None, 1, 128, 128, 16, None) == INVALID_ARGUMENT
+    assert abi.b200_sgemm_gather(11, a, b, c, peers, -1, 128, 128, 16, None) == INVALID_ARGUMENT
+    holes = (ctypes.c_void_p * 2)(0x1000, None)
+    assert abi.b200_sgemm_gather(11, a, b, c, holes, 2, 128, 128, 16, None) == INVALID_ARGUMENT
+    # Shape rules are the ladder's; entries that cannot fan out are refused; peers must allow 128-bit stores.
+    assert abi.b200_sgemm_gather(11, a, b, c, peers, 1, 100, 128, 16, None) == 2
+    assert abi.b200_sgemm_gather(12, a, b, c, peers, 1, 128, 128, 16, None) == 3      # split_k
+    assert abi.b200_sgemm_gather(5, a, b, c, peers, 1, 128, 128, 16, None) == 3       # a ladder stage
+    odd = (ctypes.c_void_p * 1)(0x1004)
+    assert abi.b200_sgemm_gather(11, a, b, c, odd, 1, 128, 128, 16, None) == 1
+    q = GemmProblem(128, 128, 32, 0x10000, 0x20000, None, 0x30000, 32, 128, 128, 128, 1.0, 0.0, 0, None)
+    assert abi.b200_tf32_gemm_dispatch_gather(0, ctypes.byref(q), peers, 8, None, None) == INVALID_ARGUMENT
+    assert abi.b200_tf32_gemm_dispatch_gather(0, ctypes.byref(q), None, 2, None, None) == INVALID_ARGUMENT
+    assert abi.b200_tf32_gemm_dispatch_gather(1, ctypes.byref(q), peers, 1, None, None) == INVALID_ARGUMENT  # cuBLAS id

@@ -73,3 +73,22 @@ def test_shard_rows_python_wrapper():
     assert sharded.shard_rows(384, 2) == [(0, 256), (256, 128)]
     with pytest.raises(ValueError):
         sharded.shard_rows(128, 0)
+
+
+def test_peer_row_pointers_of_the_fused_all_gather():
+    from cuda_ai_kernels import sharded
+
+    bases = [0x1000_0000, 0x2000_0000, 0x3000_0000, 0x4000_0000]
+    plan = sharded.shard_rows(1024, 4)
+    for rank, (first, _) in enumerate(plan):
+        ptrs = sharded.peer_row_pointers(bases, rank, first, n=512)
+        assert len(ptrs) == 3 and bases[rank] + first * 512 * 4 not in ptrs
+        assert ptrs == [b + first * 512 * 4 for r, b in enumerate(bases) if r != rank]
+        assert all(p % 16 == 0 for p in ptrs)
+    assert sharded.peer_row_pointers([0x1000], 0, 0, 128) == []      # one rank: nothing to fan out to
+    with pytest.raises(ValueError):
+        sharded.peer_row_pointers(bases, 4, 0, 512)
+    with pytest.raises(ValueError):
+        sharded.peer_row_pointers(list(range(1, 10)), 0, 0, 512)       # nine ranks exceed the kernels' seven peers
+    with pytest.raises(ValueError):
+        sharded.peer_row_pointers(bases, 0, -128, 512)
