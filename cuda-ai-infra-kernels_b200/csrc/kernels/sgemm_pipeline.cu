@@ -233,7 +233,7 @@ __device__ __forceinline__ bool produce_stage(const PipelineParams& p, ProducerC
   return true;
 }
 
-template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, bool kStreamK, int kCtasPerSm>
+template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, bool kStreamK, int kCtasPerSm, bool kGather>
 __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_kernel(const __grid_constant__ PipelineParams p) {
   using Layout = SmemLayout<BK, STAGES>;
   constexpr int RM = Grid::RM, RN = Grid::RN;
@@ -360,7 +360,8 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
     const int64_t tile_offset = static_cast<int64_t>(tm * kTile + row0) * p.n + tn * kTile + col0;
     // Destination 0 is this GPU's output; the others (fused all-gather) are the
     // same tile in peer GPUs' buffers, written with the same plain stores.
-    const int destinations = kStreamK ? 1 : 1 + p.peers.count;
+    // (kGather is a template flag so that the plain GEMM keeps a straight-line epilogue.)
+    const int destinations = kGather ? 1 + p.peers.count : 1;
     for (int dest = 0; dest < destinations; ++dest) {
       float* c_tile = (dest == 0 ? p.c : p.peers.ptr[dest - 1]) + tile_offset;
 #pragma unroll
@@ -386,7 +387,10 @@ template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, bool 
 int launch_pipeline(const float* a, const float* b, float* c, const PeerOutputs& peers, int m, int n, int k,
                     cudaStream_t stream) {
   using Layout = SmemLayout<BK, STAGES>;
-  auto kernel = sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, kStreamK, kCtasPerSm>;
+  if (kStreamK && peers.count > 0) return B200_ERR_NOT_SUPPORTED;   // partial sums need a cleared output
+  auto kernel = (!kStreamK && peers.count > 0)
+                    ? sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, kStreamK, kCtasPerSm, !kStreamK>
+                    : sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, kStreamK, kCtasPerSm, false>;
   // Function attributes are per device; setting them again is cheap and keeps
   // the launcher free of per-device state.
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Layout::kBytes)) !=
@@ -403,7 +407,6 @@ int launch_pipeline(const float* a, const float* b, float* c, const PeerOutputs&
       !make_tensor_map_2d(&p.map_b, b, k, n, n, BK, kTile, Swizzle::kNone)) {
     return B200_ERR_MISALIGNED_OPERAND;
   }
-  if (kStreamK && peers.count > 0) return B200_ERR_NOT_SUPPORTED;   // partial sums need a cleared output
   p.c = c;
   p.peers = peers;
   p.n = n;

@@ -1034,6 +1034,9 @@ int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
   }
+  // The staging area of the fused all-gather is only asked for when there are peers: a plain GEMM
+  // keeps the larger L1 for its epilogue's source reads.
+  const size_t launch_smem = smem - (peers.count > 0 ? 0 : kPeerStageBytes);
   UmmaParams p;
   fill_common(&p, q, peers);
   if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
@@ -1049,7 +1052,7 @@ int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_
   if (sms <= 0) return B200_ERR_INTERNAL;
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + BN - 1) / BN);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  kernel<<<grid, kTmaThreads, smem, stream>>>(p);
+  kernel<<<grid, kTmaThreads, launch_smem, stream>>>(p);
   return launch_status();
 }
 
@@ -1060,6 +1063,7 @@ int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
   }
+  const size_t launch_smem = smem - (peers.count > 0 ? 0 : kPeerStageBytes);
   UmmaParams p;
   fill_common(&p, q, peers);
   if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
@@ -1077,7 +1081,7 @@ int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
   cfg.blockDim = dim3(kTmaThreads);
-  cfg.dynamicSmemBytes = smem;
+  cfg.dynamicSmemBytes = launch_smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -1189,13 +1193,14 @@ int launch_generic(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStr
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
   }
+  const size_t launch_smem = smem - (peers.count > 0 ? 0 : kPeerStageBytes);
   UmmaParams p;
   fill_common(&p, q, peers);
   const int sms = sm_count();
   if (sms <= 0) return B200_ERR_INTERNAL;
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + BN - 1) / BN);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  kernel<<<grid, kGenericThreads, smem, stream>>>(p);
+  kernel<<<grid, kGenericThreads, launch_smem, stream>>>(p);
   return launch_status();
 }
 
