@@ -241,6 +241,23 @@ def measure_extras(pkg, peaks: dict, steps: int, warmup: int) -> dict:
                             "peak_source": f"{peaks['source']} bf16 burst / 2",
                             "traffic": NCU_TRAFFIC_BYTES["tf32_4096"]}
 
+    # TF32 registry entries for the shapes the tile kernels fit badly, each beside cuBLAS TF32
+    # (microseconds per call, alpha = 1, beta = 0): 1024^3 (benchmark configuration), decode-like
+    # rows (FP32 stream / split-K cluster), misaligned operands (warp-specialised loader).
+    from cuda_ai_kernels import _C
+
+    for label, (m_, n_, k_) in (("1024", (1024, 1024, 1024)), ("1x4096x4096", (1, 4096, 4096)),
+                                ("16x4096x4096", (16, 4096, 4096)), ("1024x1024x8192", (1024, 1024, 8192)),
+                                ("4095x4093x4091", (4095, 4093, 4091))):
+        a = [torch.randn(m_, k_, device=dev) for _ in range(2)]
+        b = [torch.randn(k_, n_, device=dev) for _ in range(2)]
+        ms = timed(lambda i: pkg.adaptive_gemm(a[i & 1], b[i & 1]))
+        out[f"tf32_{label}_us"] = ms * 1e3
+        out[f"tf32_{label}_kernel"] = _C.adaptive_gemm_last_kernel()
+        ms = timed(lambda i: pkg.adaptive_gemm(a[i & 1], b[i & 1], kernel="cublas"))
+        out[f"tf32_{label}_cublas_us"] = ms * 1e3
+        del a, b
+
     # Row operators: bytes = one read of x + one write of y (+ weight once).
     rows, hidden = 16384, 4096
     xs = [torch.randn(rows, hidden, device=dev) for _ in range(2)]

@@ -1,6 +1,6 @@
 """Launches each hot-path kernel a few times at its benchmark shape, for ncu.
 
-    python cuda-ai-infra-kernels_b200/benchmarks/profile_kernels.py [sgemm] [tf32] [rows] [--small]
+    python cuda-ai-infra-kernels_b200/benchmarks/profile_kernels.py [sgemm] [tf32] [rows] [tf32_other] [--small]
 
 Meant to be wrapped by Nsight Compute, one kernel family per capture, e.g.
 
@@ -9,7 +9,10 @@ Meant to be wrapped by Nsight Compute, one kernel family per capture, e.g.
 
 The role of the reference's profiling/profile_*.sh wrappers. `--small` halves
 the GEMM edge (2048) so that a multi-pass capture stays short; the row-operator
-shapes (256 MiB and 128 MiB per tensor) are already small enough.
+shapes (256 MiB and 128 MiB per tensor) are already small enough. `tf32_other`
+runs the registry entries for awkward shapes: the warp-specialised loader on
+misaligned operands (2047 x 2049 x 2051), the split-K cluster kernel
+(16 x 4096 x 4096) and the FP32 stream kernel (4 x 4096 x 16384, B = 268 MB).
 """
 import sys
 from pathlib import Path
@@ -36,6 +39,12 @@ def main(argv):
         c = torch.randn(edge, edge, device=dev)
         for _ in range(2):
             pkg.adaptive_gemm(a, b, c=c, alpha=1.0, beta=0.5, epilogue="relu")
+    if "tf32_other" in which:
+        for (m, n, k) in ((2047, 2049, 2051), (16, 4096, 4096), (4, 4096, 16384)):
+            a = torch.randn(m, k, device=dev)
+            b = torch.randn(k, n, device=dev)
+            for _ in range(2):
+                pkg.adaptive_gemm(a, b)
     if "rows" in which:
         x = torch.randn(16384, 4096, device=dev)
         w = torch.rand(4096, device=dev) + 0.5

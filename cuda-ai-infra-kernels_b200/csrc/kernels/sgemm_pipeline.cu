@@ -433,8 +433,11 @@ int sgemm_pipeline_launch(int impl, const float* a, const float* b, float* c, co
                           int k, cudaStream_t stream) {
   // Ring shapes come from a sweep on B200 at 4096^3: deeper stages amortise the
   // per-stage barrier traffic (58 -> 62 -> 63 TFLOP/s for 16 -> 32 -> 64 floats
-  // of K per stage with 8 x 8 thread tiles); 8 x 16 thread tiles with an inline
-  // producer measured slower (50 TFLOP/s) and are kept out of the dispatch.
+  // of K per stage with 8 x 8 thread tiles). Larger thread tiles (a quarter
+  // fewer shared-memory bytes per FMA) measured slower and are kept out of the
+  // dispatch: 8 x 16 with an inline producer at two CTAs per SM 50 TFLOP/s;
+  // 8 x 16 or 16 x 8 with four consumer warps + producer at 255 registers
+  // 40-45 TFLOP/s (one warp per scheduler cannot keep the FMA pipe fed).
   switch (impl) {
     case B200_SGEMM_PREFETCH_SMEM:
       return launch_pipeline<WarpGrid<2, 2>, 64, 3, false, true, false, 1>(a, b, c, peers, m, n, k, stream);
