@@ -109,11 +109,18 @@ __device__ __forceinline__ EpilogueArgs epilogue_args(const UmmaParams& p) {
 }
 
 // The same element(s) of every peer's copy of the output (fused all-gather).
+// (Unrolled with constant indices: a run-time index would put the whole argument block in local memory.)
 __device__ __forceinline__ void store_peers(const EpilogueArgs& p, int64_t offset, float4 v) {
-  for (int i = 0; i < p.peers.count; ++i) *reinterpret_cast<float4*>(p.peers.ptr[i] + offset) = v;
+#pragma unroll
+  for (int i = 0; i < B200_MAX_PEERS; ++i) {
+    if (i < p.peers.count) *reinterpret_cast<float4*>(p.peers.ptr[i] + offset) = v;
+  }
 }
 __device__ __forceinline__ void store_peers(const EpilogueArgs& p, int64_t offset, float v) {
-  for (int i = 0; i < p.peers.count; ++i) p.peers.ptr[i][offset] = v;
+#pragma unroll
+  for (int i = 0; i < B200_MAX_PEERS; ++i) {
+    if (i < p.peers.count) p.peers.ptr[i][offset] = v;
+  }
 }
 
 template <int BN>
@@ -649,40 +656,52 @@ constexpr int kExchangePitch = kTileM + 1;
 // TMEM at `tmem_row`): the columns of share s go to the CTA with cluster rank
 // s * rank_stride + rank_offset, into that CTA's buffer for source `my_slice`. The next 32 columns
 // are fetched from TMEM while the current ones are being sent; a share is at least 16 columns
-// wide, so each half chunk (four quads) has a single destination.
+// wide, so each half chunk (four quads) has a single destination. `send_chunk` sends one chunk.
+__device__ __forceinline__ void send_chunk(cg::cluster_group& cluster, const uint32_t (&cur)[32], int chunk, float4* exchange,
+                                           int my_slice, int quads_log2, int rank_stride, int rank_offset,
+                                           int row_in_tile) {
+  const int quads = 1 << quads_log2;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int quad0 = chunk * 8 + half * 4;
+    const int dest_slice = quad0 >> quads_log2, local_quad0 = quad0 & (quads - 1);
+    float4* dst = cluster.map_shared_rank(exchange, dest_slice * rank_stride + rank_offset) +
+                  (my_slice * quads + local_quad0) * kExchangePitch + row_in_tile;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = half * 16 + j * 4;
+      dst[j * kExchangePitch] = make_float4(__uint_as_float(cur[e + 0]), __uint_as_float(cur[e + 1]),
+                                            __uint_as_float(cur[e + 2]), __uint_as_float(cur[e + 3]));
+    }
+  }
+}
+
 template <int kCols>
 __device__ __forceinline__ void send_partial_row(cg::cluster_group& cluster, uint32_t tmem_row, bool have_acc,
                                                  float4* exchange, int my_slice, int quads_log2, int rank_stride,
                                                  int rank_offset, int row_in_tile) {
   constexpr int kChunks = kCols / 32;
-  const int quads = 1 << quads_log2;
-  uint32_t raw[2][32];
+  static_assert(kChunks % 2 == 0, "chunks are handled in pairs");
+  // Two register sets, named rather than indexed so that both stay in registers.
+  uint32_t even[32], odd[32];
   if (have_acc) {
-    tmem_ld_32x32(tmem_row, raw[0]);
+    tmem_ld_32x32(tmem_row, even);
   } else {
 #pragma unroll
-    for (int e = 0; e < 32; ++e) raw[0][e] = raw[1][e] = 0u;   // an empty K range contributes zeros
+    for (int e = 0; e < 32; ++e) even[e] = odd[e] = 0u;   // an empty K range contributes zeros
   }
 #pragma unroll
-  for (int chunk = 0; chunk < kChunks; ++chunk) {
+  for (int chunk = 0; chunk < kChunks; chunk += 2) {
     if (have_acc) {
       tmem_ld_wait();
-      if (chunk + 1 < kChunks) tmem_ld_32x32(tmem_row + (chunk + 1) * 32, raw[(chunk + 1) & 1]);
+      tmem_ld_32x32(tmem_row + (chunk + 1) * 32, odd);
     }
-    const uint32_t(&cur)[32] = raw[chunk & 1];
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int quad0 = chunk * 8 + half * 4;
-      const int dest_slice = quad0 >> quads_log2, local_quad0 = quad0 & (quads - 1);
-      float4* dst = cluster.map_shared_rank(exchange, dest_slice * rank_stride + rank_offset) +
-                    (my_slice * quads + local_quad0) * kExchangePitch + row_in_tile;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int e = half * 16 + j * 4;
-        dst[j * kExchangePitch] = make_float4(__uint_as_float(cur[e + 0]), __uint_as_float(cur[e + 1]),
-                                              __uint_as_float(cur[e + 2]), __uint_as_float(cur[e + 3]));
-      }
+    send_chunk(cluster, even, chunk, exchange, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
+    if (have_acc) {
+      tmem_ld_wait();
+      if (chunk + 2 < kChunks) tmem_ld_32x32(tmem_row + (chunk + 2) * 32, even);
     }
+    send_chunk(cluster, odd, chunk + 1, exchange, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
   }
 }
 
@@ -1270,7 +1289,7 @@ bool gate_splitk(const b200_gemm_problem& q, int sms) {
   if (splitk_ranks(q, sms, &split_us) < 2) return false;
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
   const float unsplit_us = static_cast<float>(k_blocks) * (tiles_of(q, 64) <= sms ? 0.23f : 0.34f) + 3.5f;
-  return split_us < unsplit_us;
+  return split_us + 1.0f < unsplit_us;   // ties go to the simpler kernel (1024^3 with a source: 17.6 vs 16.6 us)
 }
 bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) * 2 <= sms && q.n > 64; }
 
