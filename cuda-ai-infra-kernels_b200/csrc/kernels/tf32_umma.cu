@@ -184,6 +184,81 @@ __device__ __forceinline__ float activate(float v) {
   return v;
 }
 
+// Source values of one 32-column chunk of a thread's row (zeros when there is no source).
+struct SourceChunk {
+  float4 v[8];
+};
+
+// C of chunk `chunk` for the row of this thread. Issued well before the values are needed:
+// for the first chunk of a tile even before the accumulator is ready.
+__device__ __forceinline__ void fetch_source(const EpilogueArgs& p, SourceChunk& out, int row, int col0) {
+  const bool want = p.beta != 0.f && row < p.m;
+  const float* c_row = p.c + static_cast<int64_t>(row) * p.ldc;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const int col = col0 + 4 * g;
+    out.v[g] = (want && col < p.n) ? __ldg(reinterpret_cast<const float4*>(c_row + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+// One chunk of the vectorised epilogue: alpha * acc + beta * C + bias, activation, 128-bit stores.
+template <int kAct>
+__device__ __forceinline__ void finish_chunk(const EpilogueArgs& p, const uint32_t (&raw)[32], const SourceChunk& src, int row,
+                                             int col0) {
+  if (row >= p.m) return;
+  const bool use_bias = p.bias != nullptr;
+  float* d_row = p.d + static_cast<int64_t>(row) * p.ldd;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const int col = col0 + 4 * g;
+    if (col < p.n) {   // n % 4 == 0 on this path: a quad is inside or outside as a whole
+      // Same operation order as every other epilogue path (alpha * acc rounded, then one FMA with
+      // the source), so that all paths give identical bits. Without a source src is zero and beta finite.
+      float4 v = make_float4(fmaf(p.beta, src.v[g].x, p.alpha * __uint_as_float(raw[4 * g + 0])),
+                             fmaf(p.beta, src.v[g].y, p.alpha * __uint_as_float(raw[4 * g + 1])),
+                             fmaf(p.beta, src.v[g].z, p.alpha * __uint_as_float(raw[4 * g + 2])),
+                             fmaf(p.beta, src.v[g].w, p.alpha * __uint_as_float(raw[4 * g + 3])));
+      if (use_bias) {
+        const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+        v.x += bv.x, v.y += bv.y, v.z += bv.z, v.w += bv.w;
+      }
+      *reinterpret_cast<float4*>(d_row + col) =
+          make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
+    }
+  }
+}
+
+// Vectorised epilogue of one 128 x BN tile for one warp, software-pipelined: while a chunk is
+// scaled and stored, the next chunk's accumulators are on their way from TMEM and its source
+// values from memory. `first` holds the source of chunk 0 (fetched by the caller before it waited
+// for the accumulator). Two named register sets alternate so that both stay in registers.
+template <int BN, int kAct>
+__device__ __forceinline__ void epilogue_tile_pipelined(const EpilogueArgs& p, uint32_t tmem_acc, int quarter, int lane,
+                                                        int m0, int n0, const SourceChunk& first) {
+  constexpr int kChunks = BN / 32;
+  static_assert(kChunks % 2 == 0, "chunks are handled in pairs");
+  const int row = m0 + quarter * 32 + lane;
+  const uint32_t tmem_row = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
+  uint32_t raw_even[32], raw_odd[32];
+  SourceChunk src_even = first, src_odd;
+  tmem_ld_32x32(tmem_row, raw_even);
+#pragma unroll
+  for (int chunk = 0; chunk < kChunks; chunk += 2) {
+    if (n0 + chunk * 32 >= p.n) break;   // uniform across the warp
+    tmem_ld_wait();
+    tmem_ld_32x32(tmem_row + (chunk + 1) * 32, raw_odd);
+    fetch_source(p, src_odd, row, n0 + (chunk + 1) * 32);
+    finish_chunk<kAct>(p, raw_even, src_even, row, n0 + chunk * 32);
+    tmem_ld_wait();
+    if (chunk + 2 < kChunks) {
+      tmem_ld_32x32(tmem_row + (chunk + 2) * 32, raw_even);
+      fetch_source(p, src_even, row, n0 + (chunk + 2) * 32);
+    }
+    finish_chunk<kAct>(p, raw_odd, src_odd, row, n0 + (chunk + 1) * 32);
+  }
+  tmem_ld_wait();   // nothing from TMEM is in flight when the accumulator is handed back
+}
+
 // Epilogue of one 128 x BN tile for one warp: TMEM lanes [32 * quarter, +32)
 // are rows m0 + 32 * quarter + lane. Each thread owns one row and walks it in
 // chunks of 32 columns.
@@ -336,7 +411,7 @@ __device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base
 }
 
 // One of the four epilogue warps of the persistent single-CTA kernels.
-template <int BN, int kAct>
+template <int BN, int kAct, bool kPipelinedEpilogue>
 __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCarve& sm, uint32_t tmem_base, int quarter,
                                               int lane, int tiles, int tiles_m, int tiles_n) {
   const EpilogueArgs ep = epilogue_args(p);
@@ -347,10 +422,17 @@ __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCar
     const uint32_t use_parity = (local >> 1) & 1u;
     int tm, tn;
     tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+    const bool pipelined = kPipelinedEpilogue && ep.vector_io && ep.peers.count == 0;
+    SourceChunk first;
+    if (pipelined) fetch_source(ep, first, tm * kTileM + quarter * 32 + lane, tn * BN);   // before the wait
     if (!mbar_wait(&sm.acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
     tcgen05_fence_after_sync();
-    epilogue_tile<BN, kAct>(ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN,
-                            sm.peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float)));
+    if (pipelined) {
+      epilogue_tile_pipelined<BN, kAct>(ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN, first);
+    } else {
+      epilogue_tile<BN, kAct>(ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN,
+                              sm.peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float)));
+    }
     tcgen05_fence_before_sync();
     __syncwarp();
     if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
@@ -425,7 +507,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_c
   } else if (warp == 1) {
     if (lane == 0) mma_role<BN, STAGES>(sm, tmem_base, tiles, k_blocks);
   } else {
-    epilogue_role<BN, kAct>(p, sm, tmem_base, warp & 3, lane, tiles, tiles_m, tiles_n);
+    epilogue_role<BN, kAct, true>(p, sm, tmem_base, warp & 3, lane, tiles, tiles_m, tiles_n);
   }
 
   tcgen05_fence_before_sync();
@@ -573,11 +655,18 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
       const uint32_t use_parity = (local >> 1) & 1u;
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      const int m0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
+      const bool pipelined = ep.vector_io && ep.peers.count == 0;
+      SourceChunk first;
+      if (pipelined) fetch_source(ep, first, m0 + quarter * 32 + lane, tn * kPairN);   // before the wait
       if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
-      epilogue_tile<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane,
-                                   tm * 2 * kTileM + static_cast<int>(rank) * kTileM, tn * kPairN,
-                                   peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float)));
+      if (pipelined) {
+        epilogue_tile_pipelined<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, tn * kPairN, first);
+      } else {
+        epilogue_tile<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, tn * kPairN,
+                                     peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float)));
+      }
       tcgen05_fence_before_sync();
       __syncwarp();
       // The MMA issuer (CTA 0) waits for the epilogues of both CTAs.
@@ -980,7 +1069,7 @@ __global__ void __launch_bounds__(kGenericThreads, 1) umma_generic_kernel(const 
   if (warp == 0) {
     if (lane == 0) mma_role<BN, STAGES>(sm, tmem_base, tiles, k_blocks);
   } else if (warp <= 4) {
-    epilogue_role<BN, kAct>(p, sm, tmem_base, warp & 3, lane, tiles, tiles_m, tiles_n);
+    epilogue_role<BN, kAct, false>(p, sm, tmem_base, warp & 3, lane, tiles, tiles_m, tiles_n);   // 416 threads: no room for two register sets
   } else {
     const int lw = warp - 5;
     LoaderCursor cursor{static_cast<int>(blockIdx.x), 0, 0, 0};  // the next stage to load
