@@ -442,6 +442,46 @@ def main() -> None:
         also["allgather_c_ms"] = float(t.item())
         also["allgather_c_recv_gbs_per_rank"] = recv_bytes / float(t.item()) / 1e6
         del gathered, c_shard
+        # The same gather fused into the GEMM: the kernel's epilogue stores every tile into every
+        # rank's copy of C (peer stores over NVLink), one device-side barrier per step. Reported
+        # beside "GEMM, then the collective"; never part of `value`. A box where the symmetric
+        # allocation cannot be set up reports why instead of a number.
+        from cuda_ai_kernels import sharded
+
+        out, setup_error = None, ""
+        try:
+            out = sharded.GatheredOutput(world * M, N, [(r * M, M) for r in range(world)])
+        except Exception as exc:  # noqa: BLE001
+            setup_error = f"{type(exc).__name__}: {exc}"[:200]
+        # Every rank goes on only if every rank has its buffer: no rank may wait alone in a collective.
+        ready = torch.tensor([int(out is not None)], device=dev)
+        dist.all_reduce(ready, op=dist.ReduceOp.MIN)
+        if not bool(ready.item()):
+            also["gemm_fused_allgather_error"] = setup_error or "symmetric allocation failed on another rank"
+        else:
+
+            def fused(i):
+                sharded.sharded_gemm_gather(a_sets[i & 1], b_sets[i & 1], out, impl=impl)
+                out.barrier()
+
+            def sequential(i):
+                dist.all_gather_into_tensor(seq_out, step(i))
+
+            seq_out = torch.empty(world * M, N, device=dev)
+            for name, fn in (("gemm_then_allgather_ms", sequential), ("gemm_fused_allgather_ms", fused)):
+                for i in range(3):
+                    fn(i)
+                dist.barrier()
+                t = torch.tensor([event_time_ms(fn, 10) / 10], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                also[name] = float(t.item())
+            fused(0), sequential(0)
+            torch.cuda.synchronize()
+            same = torch.tensor([int(torch.equal(out.full, seq_out))], device=dev)
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            also["gemm_fused_allgather_bit_identical"] = bool(same.item())
+            out.barrier()
+            del seq_out, out
 
     cpu_baseline = None
     if rank == 0 and world == 1:
