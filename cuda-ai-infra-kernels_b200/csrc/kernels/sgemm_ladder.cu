@@ -4,11 +4,12 @@
 // [K,M] array), B and C row-major. Full tiles only; sizes are validated on the
 // host (b200_sgemm_check) and the kernels do no bounds checks.
 //
-// Stages 2-5 share one kernel template: a CTA stages a [BK][BM] slab of A and a
-// [BK][BN] slab of B in shared memory, and every thread accumulates RM x RN
-// register blocks of CM x CN outputs whose origins inside the CTA tile come
-// from a mapping policy. The policies reproduce the work decomposition of each
-// ladder step of the reference (csrc/gemm/gemm_block_tile.cu,
+// Stages 2-3 (one output per thread) have a small double-buffered kernel of
+// their own; stages 4-5 share one kernel template: a CTA stages a [BK][BM] slab
+// of A and a [BK][BN] slab of B in shared memory, and every thread accumulates
+// RM x RN register blocks of 4 x 4 outputs whose origins inside the CTA tile
+// come from a mapping policy. Tile sizes and work decomposition are those of
+// each ladder step of the reference (csrc/gemm/gemm_block_tile.cu,
 // gemm_block_tile_float4.cu, gemm_thread_tile.cu, gemm_warp_tile.cu).
 #include "sgemm.h"
 
@@ -31,17 +32,6 @@ __global__ void __launch_bounds__(256) sgemm_naive_kernel(const float* __restric
 }
 
 // ------------------------------------------------------------ stages 2-5
-
-// One output per thread on a BM x BN thread grid (stages 2 and 3).
-template <int BM, int BN>
-struct MapOnePerThread {
-  static constexpr int kThreads = BM * BN;
-  static constexpr int kRowBlocks = 1, kColBlocks = 1, kBlockRows = 1, kBlockCols = 1;
-  int ty, tx;
-  __device__ explicit MapOnePerThread(int tid) : ty(tid / BN), tx(tid % BN) {}
-  __device__ int row_origin(int) const { return ty; }
-  __device__ int col_origin(int) const { return tx; }
-};
 
 // One contiguous TM x TN rectangle per thread (stage 4). With kWarp4x8 the
 // threads of a warp form 4 rows x 8 columns of rectangles instead of one row.
@@ -174,6 +164,76 @@ __global__ void __launch_bounds__(Map::kThreads) sgemm_smem_kernel(const float* 
     }
 }
 
+// Stages 2 and 3 (one output per thread, BM x BN outputs per CTA, operands staged in shared
+// memory BK rows of K at a time): the two slabs are double-buffered and the next slab's elements
+// travel from global memory in registers while the current slab is multiplied, so an iteration
+// has one barrier instead of two and the global-load latency is off the critical path. The tile
+// sizes, the staging width (scalar or 128-bit) and therefore the shape rules are those of the
+// reference's stages (csrc/gemm/gemm_block_tile.cu:4-35, gemm_block_tile_float4.cu).
+template <int BM, int BN, int BK, bool kVectorStaging>
+__global__ void __launch_bounds__(BM* BN) sgemm_block_tile_kernel(const float* __restrict__ a,
+                                                                   const float* __restrict__ b,
+                                                                   float* __restrict__ c, int m, int n, int k) {
+  constexpr int kThreads = BM * BN;
+  constexpr int kWidth = kVectorStaging ? 4 : 1;                  // floats per staged item
+  constexpr int kItemsA = BK * BM / kWidth, kItemsB = BK * BN / kWidth;
+  static_assert(kItemsA <= kThreads && kItemsB <= kThreads, "at most one item of each slab per thread");
+  __shared__ __align__(16) float a_s[2][BK][BM];
+  __shared__ __align__(16) float b_s[2][BK][BN];
+
+  const int tid = threadIdx.x;
+  const int ty = tid / BN, tx = tid % BN;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const bool has_a = tid < kItemsA, has_b = tid < kItemsB;
+  const int a_kk = tid / (BM / kWidth), a_mm = (tid % (BM / kWidth)) * kWidth;
+  const int b_kk = tid / (BN / kWidth), b_nn = (tid % (BN / kWidth)) * kWidth;
+  const float* a_src = a + static_cast<int64_t>(a_kk) * m + m0 + a_mm;
+  const float* b_src = b + static_cast<int64_t>(b_kk) * n + n0 + b_nn;
+
+  float4 ra = make_float4(0.f, 0.f, 0.f, 0.f), rb = ra;
+  auto fetch = [&](int k0) {
+    if constexpr (kVectorStaging) {
+      if (has_a) ra = *reinterpret_cast<const float4*>(a_src + static_cast<int64_t>(k0) * m);
+      if (has_b) rb = *reinterpret_cast<const float4*>(b_src + static_cast<int64_t>(k0) * n);
+    } else {
+      if (has_a) ra.x = a_src[static_cast<int64_t>(k0) * m];
+      if (has_b) rb.x = b_src[static_cast<int64_t>(k0) * n];
+    }
+  };
+  auto stash = [&](int buf) {
+    if constexpr (kVectorStaging) {
+      if (has_a) *reinterpret_cast<float4*>(&a_s[buf][a_kk][a_mm]) = ra;
+      if (has_b) *reinterpret_cast<float4*>(&b_s[buf][b_kk][b_nn]) = rb;
+    } else {
+      if (has_a) a_s[buf][a_kk][a_mm] = ra.x;
+      if (has_b) b_s[buf][b_kk][b_nn] = rb.x;
+    }
+  };
+
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  float acc = 0.f;
+  int buf = 0;
+  for (int k0 = 0; k0 < k; k0 += BK) {
+    const bool more = k0 + BK < k;
+    if (more) fetch(k0 + BK);
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) acc = fmaf(a_s[buf][kk][ty], b_s[buf][kk][tx], acc);
+    if (more) stash(buf ^ 1);
+    // One barrier per iteration: buffer buf ^ 1 was last read before the previous barrier.
+    __syncthreads();
+    buf ^= 1;
+  }
+  c[static_cast<int64_t>(m0 + ty) * n + n0 + tx] = acc;
+}
+
+template <int BM, int BN, int BK, bool kVectorStaging>
+int launch_block_tile(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
+  sgemm_block_tile_kernel<BM, BN, BK, kVectorStaging><<<dim3(n / BN, m / BM), BM * BN, 0, stream>>>(a, b, c, m, n, k);
+  return launch_status();
+}
+
 template <int BM, int BN, int BK, bool kVectorStaging, class Map>
 int launch_smem(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
   sgemm_smem_kernel<BM, BN, BK, kVectorStaging, Map>
@@ -190,13 +250,13 @@ int sgemm_ladder_launch(int impl, const float* a, const float* b, float* c, int 
       sgemm_naive_kernel<<<dim3(n / 16, m / 16), dim3(16, 16), 0, stream>>>(a, b, c, m, n, k);
       return launch_status();
     case B200_SGEMM_BLOCK_TILE:
-      return launch_smem<16, 16, 8, false, MapOnePerThread<16, 16>>(a, b, c, m, n, k, stream);
+      return launch_block_tile<16, 16, 8, false>(a, b, c, m, n, k, stream);
     case B200_SGEMM_BLOCK_TILE_F4_16x16:
-      return launch_smem<16, 16, 8, true, MapOnePerThread<16, 16>>(a, b, c, m, n, k, stream);
+      return launch_block_tile<16, 16, 8, true>(a, b, c, m, n, k, stream);
     case B200_SGEMM_BLOCK_TILE_F4_16x32:
-      return launch_smem<16, 32, 8, true, MapOnePerThread<16, 32>>(a, b, c, m, n, k, stream);
+      return launch_block_tile<16, 32, 8, true>(a, b, c, m, n, k, stream);
     case B200_SGEMM_BLOCK_TILE_F4_32x32:
-      return launch_smem<32, 32, 8, true, MapOnePerThread<32, 32>>(a, b, c, m, n, k, stream);
+      return launch_block_tile<32, 32, 8, true>(a, b, c, m, n, k, stream);
     case B200_SGEMM_THREAD_TILE_4x4:
       return launch_smem<128, 128, 8, true, MapThreadTile<128, 128, 4, 4, false>>(a, b, c, m, n, k, stream);
     case B200_SGEMM_THREAD_TILE_4x8:

@@ -1,8 +1,9 @@
 // TF32 tensor-core GEMM with a fused epilogue, written for sm_100a:
 //   D = epilogue(alpha * A * B + beta * C),  A [M,K], B [K,N], C/D [M,N],
 // all row-major FP32; products in TF32 on tcgen05.mma, accumulation in FP32 in
-// tensor memory (TMEM); epilogue (scale, source add, optional ReLU) applied on
-// the TMEM -> register -> global path, so the accumulator never touches HBM.
+// tensor memory (TMEM); epilogue (scale, source add, bias, optional ReLU or
+// GELU) applied on the TMEM -> register -> global path, so the accumulator
+// never touches HBM.
 //
 // It stands in for the CUTLASS device::Gemm instantiations of the reference
 // (csrc/adaptive_gemm/kernel_sm80.h:4-171, launched through
@@ -29,10 +30,14 @@
 //             accumulator so the epilogue of one tile overlaps the main loop of
 //             the next. Two forms: one CTA per 128 x BN tile, and CTA pairs
 //             (cta_group::2) that share a 256 x 256 tile and halve the B bytes
-//             each CTA pulls through L2.
-//   generic - any pointers, any sizes; predicated scalar loads written into the
-//             same swizzled layout, one tile per CTA.
-// Neither uses cluster multicast.
+//             each CTA pulls through L2. A third form gives one 128 x 128 tile
+//             to a cluster whose CTAs split K and exchange their partial tiles
+//             through distributed shared memory (few tiles, long K).
+//   generic - any pointers, any sizes; eight loader warps of a persistent CTA
+//             write predicated scalar loads into the same swizzled layout.
+// Nothing here uses cluster multicast. Every kernel can also store its finished
+// output to peer GPUs' copies of D (PeerOutputs: a GEMM fused with the
+// all-gather of its result); peer memory is only ever stored to.
 #include <cooperative_groups.h>
 
 #include <cstring>

@@ -170,9 +170,12 @@ typedef struct b200_gemm_problem {
  * Registry record: KernelEntry + KernelMeta of
  * csrc/adaptive_gemm/kernel_entry.h:7-61. `id` values 2..9 are the reference's
  * KernelId enumerators in declaration order (0 = Auto, 1 = Cublas); ids >= 16
- * are configurations that exist only here (wider or narrower tiles); automatic
- * dispatch tries them first, each behind a shape gate, and then walks the
- * reference's eight entries in the reference's order.
+ * are configurations that exist only here: 16-19 wider / narrower tiles,
+ * 20-22 CTA pairs (256 x 256), 23-26 GELU forms, 27-29 "skinny" (up to 16 rows,
+ * FP32 FMA stream over B; inst_* = 1), 30-32 "splitk" (one 128 x 128 tile per
+ * cluster, K split over its CTAs; supports_split_k = 1). Automatic dispatch
+ * tries them first, each behind a shape gate, and then walks the reference's
+ * eight entries in the reference's order.
  */
 typedef struct b200_tf32_kernel_meta {
   int id;
