@@ -1238,51 +1238,37 @@ int splitk_max_clusters(int cluster_size) {
   return result;
 }
 
-// Plan of the split-K kernel: cluster size and ring depth, from a cost model fitted to in-kernel
-// phase timings on a B200 (microseconds). One K block moves (rows + 128) * 128 bytes into a CTA
-// (rows of the matrix inside a 128-row tile; rows past M are not fetched). A CTA alone on its SM
-// runs the six-stage ring and is bound by the SM's ingest of about 105 KB/us, never faster than
-// 0.15 us per block; two CTAs per SM run three stages each, which the load latency (three blocks
-// per 0.87 us) and the shared ingest bound. Barriers, exchange and the finishing pass cost
-// 4.5 / 6.0 / 7.2 us for clusters of 2 / 4 / 8, half as much again when two CTAs share an SM. A
-// candidate keeps two K blocks per range and fits the device in one wave (two CTAs per SM: twice
-// the cluster count the occupancy query reports for one).
-struct SplitPlan {
-  int ranks;        // CTAs per cluster = K ranges per tile
-  bool deep_ring;   // six stages, one CTA per SM; otherwise three stages, two CTAs per SM
-  float us;         // modelled duration
-};
-
-SplitPlan splitk_plan(const b200_gemm_problem& q, int sms) {
+// Cluster size of the split-K kernel, from a cost model fitted to phase timings of the kernel on a
+// B200 (microseconds): a K block costs 0.34 with one CTA per SM and 0.53 per CTA with two (the
+// four 128 x 128 x 8 MMAs of a block take that long however few bytes the block loads: with 16 of
+// 128 rows present it is still 0.29, and a six-stage ring instead of three changes nothing, so it
+// is the SM's MMA rate at this tile shape, not memory, that a second CTA has to share); barriers,
+// exchange and the finishing pass cost 4.5 / 6.0 / 7.2 for clusters of 2 / 4 / 8 (half as much again when
+// two CTAs share an SM). A candidate must keep
+// two K blocks per range and fit the device in one wave (two CTAs per SM: twice the cluster count the
+// occupancy query reports for one). `estimate_us` receives the modelled time of the choice.
+int splitk_ranks(const b200_gemm_problem& q, int sms, float* estimate_us = nullptr) {
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
-  const float block_kb = static_cast<float>((q.m < kTileM ? q.m : kTileM) + kSplitN) * 128.f / 1000.f;
   constexpr float kExchangeUs[4] = {4.7f, 4.5f, 6.0f, 7.2f};
-  SplitPlan best{1, false, 1e30f};
-  const float ingest = block_kb / 105.f;
+  int best = 1;
+  float best_us = 1e30f;
   for (int log2r = 0; log2r < 4; ++log2r) {
     const int ranks = 1 << log2r;
     const int64_t ctas = tiles * ranks;
     if (ctas > 2LL * sms) break;
-    if (ranks > 1 && k_blocks / ranks < 2) break;
-    const int64_t resident = ranks > 1 ? splitk_max_clusters(ranks) : sms;   // clusters at one CTA per SM
-    const float blocks = static_cast<float>((k_blocks + ranks - 1) / ranks);
-    if (ctas <= sms && tiles <= resident) {          // six stages, alone on the SM
-      const float us = blocks * (ingest > 0.15f ? ingest : 0.15f) + kExchangeUs[log2r];
-      if (us < best.us) best = SplitPlan{ranks, true, us};
-    }
-    if (tiles <= 2 * resident) {                     // three stages, room for a second CTA on the SM
-      const bool shared_sm = ctas > sms;
-      const float bound = shared_sm ? 2.f * block_kb / 120.f : ingest;
-      const float us = blocks * (bound > 0.29f ? bound : 0.29f) + kExchangeUs[log2r] * (shared_sm ? 1.5f : 1.0f);
-      if (us < best.us) best = SplitPlan{ranks, false, us};
-    }
+    if (ranks > 1 && (k_blocks / ranks < 2 || tiles > 2LL * splitk_max_clusters(ranks))) break;
+    const bool shared_sm = ctas > sms;   // two CTAs per SM also share its exchange and store bandwidth
+    const float us = static_cast<float>((k_blocks + ranks - 1) / ranks) * (shared_sm ? 0.53f : 0.34f) +
+                     kExchangeUs[log2r] * (shared_sm ? 1.5f : 1.0f);
+    if (us < best_us) best_us = us, best = ranks;
   }
+  if (estimate_us != nullptr) *estimate_us = best_us;
   return best;
 }
 
 template <int STAGES, int kAct>
-int run_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, int ranks, cudaStream_t stream) {
+int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   auto kernel = umma_splitk_kernel<STAGES, kAct>;
   constexpr size_t smem = smem_bytes<kSplitN, STAGES>() - kPeerStageBytes;   // its finishing pass needs no staging
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
@@ -1298,6 +1284,9 @@ int run_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, int ranks, 
                                                         Swizzle::k128BAtom32B))
                    ? kSplitN / 32
                    : 0;
+  const int sms = sm_count();
+  if (sms <= 0) return B200_ERR_INTERNAL;
+  const int ranks = splitk_ranks(q, sms);
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
   if (tiles * ranks > 0x7fffffffLL) return B200_ERR_INVALID_PROBLEM;
   cudaLaunchConfig_t cfg = {};
@@ -1314,15 +1303,6 @@ int run_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, int ranks, 
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
   return launch_status();
-}
-
-template <int kAct>
-int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
-  const int sms = sm_count();
-  if (sms <= 0) return B200_ERR_INTERNAL;
-  const SplitPlan plan = splitk_plan(q, sms);
-  return plan.deep_ring ? run_splitk<6, kAct>(q, peers, plan.ranks, stream)
-                        : run_splitk<3, kAct>(q, peers, plan.ranks, stream);
 }
 
 template <int BN, int STAGES, int kAct>
@@ -1405,11 +1385,11 @@ bool gate_skinny(const b200_gemm_problem& q, int) { return q.m <= 4; }
 // four ways against 73.0 us unsplit, 16 x 4096 x 4096 14.1 against 38.1, while 512^3 and 1024^3 stay
 // within 1 us of the 128 x 64 tile kernel either way.
 bool gate_splitk(const b200_gemm_problem& q, int sms) {
-  const SplitPlan plan = splitk_plan(q, sms);
-  if (plan.ranks < 2) return false;
+  float split_us = 0.f;
+  if (splitk_ranks(q, sms, &split_us) < 2) return false;
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
   const float unsplit_us = static_cast<float>(k_blocks) * (tiles_of(q, 64) <= sms ? 0.23f : 0.34f) + 3.5f;
-  return plan.us + 1.0f < unsplit_us;   // ties go to the simpler kernel (1024^3 with a source: 17.6 vs 16.6 us)
+  return split_us + 1.0f < unsplit_us;   // ties go to the simpler kernel (1024^3 with a source: 17.6 vs 16.6 us)
 }
 bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) * 2 <= sms && q.n > 64; }
 
@@ -1425,9 +1405,9 @@ const RegistryEntry kRegistry[] = {
     {meta_skinny(27, "simt16x128splitk", "skinny", B200_EPILOGUE_LINEAR), &launch_skinny, &gate_skinny},
     {meta_skinny(28, "simt16x128splitkRelu", "skinny_relu", B200_EPILOGUE_RELU), &launch_skinny, &gate_skinny},
     {meta_skinny(29, "simt16x128splitkGelu", "skinny_gelu", B200_EPILOGUE_GELU), &launch_skinny, &gate_skinny},
-    {meta_splitk(30, "umma128x128splitk", "splitk", B200_EPILOGUE_LINEAR, 3), &launch_splitk<B200_EPILOGUE_LINEAR>, &gate_splitk},
-    {meta_splitk(31, "umma128x128splitkRelu", "splitk_relu", B200_EPILOGUE_RELU, 3), &launch_splitk<B200_EPILOGUE_RELU>, &gate_splitk},
-    {meta_splitk(32, "umma128x128splitkGelu", "splitk_gelu", B200_EPILOGUE_GELU, 3), &launch_splitk<B200_EPILOGUE_GELU>, &gate_splitk},
+    {meta_splitk(30, "umma128x128stage3splitk", "splitk", B200_EPILOGUE_LINEAR, 3), &launch_splitk<3, B200_EPILOGUE_LINEAR>, &gate_splitk},
+    {meta_splitk(31, "umma128x128stage3splitkRelu", "splitk_relu", B200_EPILOGUE_RELU, 3), &launch_splitk<3, B200_EPILOGUE_RELU>, &gate_splitk},
+    {meta_splitk(32, "umma128x128stage3splitkGelu", "splitk_gelu", B200_EPILOGUE_GELU, 3), &launch_splitk<3, B200_EPILOGUE_GELU>, &gate_splitk},
     {meta_pair(20, "umma256x256stage6pair", "pair", B200_EPILOGUE_LINEAR, 6), &launch_pair<6, B200_EPILOGUE_LINEAR>, &gate_pair},
     {meta_pair(21, "umma256x256stage6pairRelu", "pair_relu", B200_EPILOGUE_RELU, 6), &launch_pair<6, B200_EPILOGUE_RELU>, &gate_pair},
     {meta(16, "umma128x256stage4tma", "wide", B200_EPILOGUE_LINEAR, 256, 4, 4), &launch_tma<256, 4, B200_EPILOGUE_LINEAR>, &gate_wide},
