@@ -30,10 +30,10 @@ from cuda_ai_kernels.benchmark import cuda_event_benchmark, cuda_graph_benchmark
 from cuda_ai_kernels.env import collect_env  # noqa: E402
 
 # "skinny*" runs only M <= 16 and is reported as skipped elsewhere.
-LINEAR_KERNELS = ["auto", "skinny", "splitk", "pair", "wide", "narrow", "fast", "fallback", "fast_mwarp", "fallback_mwarp",
+LINEAR_KERNELS = ["auto", "skinny", "swap", "splitk", "pair", "wide", "narrow", "fast", "fallback", "fast_mwarp", "fallback_mwarp",
                   "fast_stage3", "fast_stage2", "cublas"]
-RELU_KERNELS = ["auto", "skinny_relu", "splitk_relu", "pair_relu", "wide_relu", "narrow_relu", "fast_relu", "fallback_relu", "cublas"]
-GELU_KERNELS = ["auto", "skinny_gelu", "splitk_gelu", "pair_gelu", "wide_gelu", "narrow_gelu", "fast_gelu", "fallback_gelu"]
+RELU_KERNELS = ["auto", "skinny_relu", "swap_relu", "splitk_relu", "pair_relu", "wide_relu", "narrow_relu", "fast_relu", "fallback_relu", "cublas"]
+GELU_KERNELS = ["auto", "skinny_gelu", "swap_gelu", "splitk_gelu", "pair_gelu", "wide_gelu", "narrow_gelu", "fast_gelu", "fallback_gelu"]
 REL_FROBENIUS = 5e-3
 
 

@@ -958,6 +958,197 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
   }
 }
 
+// ---------------------------------------- TMA, operand-swapped kernel for few rows
+// Up to 64 rows (decode-like shapes): computing D^T = B^T * A^T puts the long
+// dimension N on the 128 rows of the MMA and the few rows of A on its N side, so
+// an instruction is 128 x NM x 8 with NM = 16 or 64 instead of 128 x 128 x 8 with
+// most rows zero. What the tensor pipe reads from shared memory per K block drops
+// from 32 KiB to 16 KiB + NM * 128 B, and that, not the arithmetic, is what the
+// K-block time of the 128 x 128 form consists of.
+//   MMA operand A = B^T: M-major, i.e. exactly the B slab of the other kernels
+//     (32-column boxes of 32 K rows, 128-byte swizzle in 32-byte granules).
+//   MMA operand B = A^T: K-major, i.e. the A slab of the other kernels with NM
+//     rows (8-row groups 1024 bytes apart, 128-byte swizzle).
+// The accumulator holds D^T: TMEM lane = column n of the tile, TMEM column = row
+// m, so an epilogue thread owns one output column and a warp writes 32 adjacent
+// floats of a row of D. A cluster of 1/2/4/8 CTAs splits K as in the split-K
+// kernel; CTA r finishes the 128 / cluster columns it owns.
+constexpr int kSwapTileN = 128;   // columns of D per CTA (the M side of the MMA)
+
+template <int NM>
+__host__ __device__ constexpr uint32_t swap_stage_bytes() {
+  return (kSwapTileN / 32) * kBBoxBytes + NM * kStageK * 4;
+}
+
+template <int NM, int STAGES>
+__host__ __device__ constexpr size_t swap_smem_bytes() {
+  return static_cast<size_t>(STAGES) * swap_stage_bytes<NM>() + 1024 + 256;
+}
+
+template <int NM, int STAGES, int kAct>
+__global__ void __launch_bounds__(kTmaThreads, 2) umma_swap_kernel(const __grid_constant__ UmmaParams p) {
+  static_assert(NM % 16 == 0 && NM >= 16 && NM <= 64, "rows of A per tile");
+  static_assert(static_cast<size_t>(STAGES) * swap_stage_bytes<NM>() >= sizeof(float) * NM * kSwapTileN,
+                "the idle operand ring must hold one exchanged tile");
+  constexpr uint32_t kTmemCols = NM < 32 ? 32 : NM;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int ranks = static_cast<int>(cluster.num_blocks());
+  const int rank = static_cast<int>(cluster.block_rank());
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(STAGES) * swap_stage_bytes<NM>());
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_full + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  B200_PROBE(p, 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&acc_full[0], 1);
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc<kTmemCols>(tmem_ptr);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr;
+  B200_PROBE(p, 1);
+
+  // Tiles: blocks of NM rows of A by 128 columns of B; row blocks innermost.
+  const int tiles_m = (p.m + NM - 1) / NM;
+  const int tile = static_cast<int>(blockIdx.x) / ranks;
+  const int m0 = (tile % tiles_m) * NM, n0 = (tile / tiles_m) * kSwapTileN;
+  const int k_blocks = (p.k + kStageK - 1) / kStageK;
+  const int per_rank = (k_blocks + ranks - 1) / ranks;
+  const int kb_begin = min(k_blocks, rank * per_rank);
+  const int kb_end = min(k_blocks, kb_begin + per_rank);
+  const bool has_work = kb_begin < kb_end;   // an empty K range contributes zeros
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&p.map_a);
+      prefetch_tensormap(p.b_strips == kSwapTileN / 32 ? &p.map_b_strips : &p.map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&empty[stage], phase ^ 1u, kSiteUmmaEmpty)) break;
+        uint8_t* b_dst = stages + static_cast<size_t>(stage) * swap_stage_bytes<NM>();   // B slab first
+        uint8_t* a_dst = b_dst + (kSwapTileN / 32) * kBBoxBytes;
+        mbar_expect_tx(&full[stage], swap_stage_bytes<NM>());
+        tma_load_2d(a_dst, &p.map_a, &full[stage], kb * kStageK, m0);   // NM rows x 32 floats of K
+        if (p.b_strips == kSwapTileN / 32) {
+          tma_load_3d(b_dst, &p.map_b_strips, &full[stage], 0, kb * kStageK, n0 / 32);
+        } else {
+#pragma unroll
+          for (int j = 0; j < kSwapTileN / 32; ++j) {
+            tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &full[stage], n0 + j * 32, kb * kStageK);
+          }
+        }
+        if (++stage == STAGES) stage = 0, phase ^= 1u;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && has_work) {
+      // M = 128 (columns of D), N = NM (rows of D); operand A M-major, operand B K-major.
+      constexpr uint32_t idesc = umma_idesc_tf32(kSwapTileN, NM, /*a_mn_major=*/true, /*b_mn_major=*/false);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool fed = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&full[stage], phase, kSiteUmmaFull)) { fed = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t b_addr = smem_u32(stages + static_cast<size_t>(stage) * swap_stage_bytes<NM>());
+        const uint32_t a_addr = b_addr + (kSwapTileN / 32) * kBBoxBytes;
+#pragma unroll
+        for (int j = 0; j < kStageK / kInstK; ++j) {
+          const uint64_t desc_mma_a = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
+          const uint64_t desc_mma_b = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
+          umma_tf32(tmem_base, desc_mma_a, desc_mma_b, idesc, (kb > kb_begin || j > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[stage]);
+        if (++stage == STAGES) stage = 0, phase ^= 1u;
+      }
+      if (fed) umma_commit(&acc_full[0]);
+    }
+  } else if (has_work) {
+    ok = mbar_wait(&acc_full[0], 0, kSiteUmmaAccFull);
+    tcgen05_fence_after_sync();
+  }
+
+  B200_PROBE(p, 2);
+  // 1. Every CTA of the cluster is past its main loop: the rings are idle.
+  tcgen05_fence_before_sync();
+  cluster.sync();
+  tcgen05_fence_after_sync();
+
+  B200_PROBE(p, 3);
+  // Exchange buffer of a CTA: floats [source rank][row m][column of its share]; a thread owns one
+  // column n of the tile, so all its values go to the one CTA that owns that column.
+  float* exchange = reinterpret_cast<float*>(stages);
+  const int width = kSwapTileN / ranks;                 // columns per CTA
+  if (warp >= 2) {
+    const int quarter = warp & 3;
+    const int n_local = quarter * 32 + lane;
+    float* remote = cluster.map_shared_rank(exchange, n_local / width) +
+                    static_cast<size_t>(rank) * NM * width + (n_local % width);
+#pragma unroll
+    for (int chunk = 0; chunk < kTmemCols / 32; ++chunk) {
+      uint32_t raw[32];
+      if (has_work && ok) {
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 32, raw);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) raw[e] = 0u;
+      }
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const int m = chunk * 32 + e;
+        if (m < NM) remote[m * width] = __uint_as_float(raw[e]);   // columns past NM were never accumulated
+      }
+    }
+  }
+  B200_PROBE(p, 4);
+  tcgen05_fence_before_sync();
+  cluster.sync();
+  B200_PROBE(p, 5);
+
+  // 3. Add the partials of this CTA's columns in rank order, apply the epilogue, lanes along a row of D.
+  {
+    const EpilogueArgs ep = epilogue_args(p);
+    const int col_base = n0 + rank * width;
+    for (int item = threadIdx.x; item < NM * width; item += kTmaThreads) {
+      const int m = item / width, nl = item % width;
+      const int row = m0 + m, col = col_base + nl;
+      if (row >= ep.m || col >= ep.n) continue;
+      float sum = 0.f;
+      for (int src = 0; src < ranks; ++src) sum += exchange[(src * NM + m) * width + nl];
+      float v = ep.alpha * sum;
+      if (ep.beta != 0.f) v = fmaf(ep.beta, __ldg(ep.c + static_cast<int64_t>(row) * ep.ldc + col), v);
+      if (ep.bias != nullptr) v += __ldg(ep.bias + col);
+      v = activate<kAct>(v);
+      const int64_t offset = static_cast<int64_t>(row) * ep.ldd + col;
+      ep.d[offset] = v;
+      store_peers(ep, offset, v);
+    }
+  }
+
+  B200_PROBE(p, 6);
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc<kTmemCols>(tmem_base);
+  }
+}
+
 // ------------------------------------------------------- generic loader kernel
 // For operands TMA cannot describe (base not 16-byte aligned, leading dimension
 // not a multiple of four floats). Persistent like the TMA kernel, same MMA and
@@ -1305,6 +1496,62 @@ int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStre
   return launch_status();
 }
 
+// Cluster size of the operand-swapped kernel: as many K ranges as keep every cluster resident at
+// once (two CTAs per SM) with at least four K blocks each.
+int swap_ranks(int64_t tiles, int k_blocks, int sms) {
+  int ranks = 1;
+  while (ranks < 8 && tiles * (ranks * 2) <= 2LL * sms && k_blocks / (ranks * 2) >= 4 &&
+         tiles <= 2LL * splitk_max_clusters(ranks * 2)) {
+    ranks *= 2;
+  }
+  return ranks;
+}
+
+template <int NM, int kAct>
+int run_swap(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  constexpr int STAGES = 4;
+  auto kernel = umma_swap_kernel<NM, STAGES, kAct>;
+  constexpr size_t smem = swap_smem_bytes<NM, STAGES>();
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+    return B200_ERR_LAUNCH_FAILED;
+  }
+  UmmaParams p;
+  fill_common(&p, q, peers);
+  // A: boxes of NM rows x 32 floats of K; B as in the other kernels.
+  if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, NM, kStageK, Swizzle::k128B) ||
+      !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
+    return B200_ERR_MISALIGNED_OPERAND;
+  }
+  p.b_strips = (q.n % 32 == 0 && make_tensor_map_strips(&p.map_b_strips, q.b, q.k, q.n, q.ldb, kStageK, kSwapTileN / 32,
+                                                        Swizzle::k128BAtom32B))
+                   ? kSwapTileN / 32
+                   : 0;
+  const int sms = sm_count();
+  if (sms <= 0) return B200_ERR_INTERNAL;
+  const int64_t tiles = static_cast<int64_t>((q.m + NM - 1) / NM) * ((q.n + kSwapTileN - 1) / kSwapTileN);
+  const int ranks = swap_ranks(tiles, (q.k + kStageK - 1) / kStageK, sms);
+  if (tiles * ranks > 0x7fffffffLL) return B200_ERR_INVALID_PROBLEM;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * ranks));
+  cfg.blockDim = dim3(kTmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(ranks);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  return launch_status();
+}
+
+template <int kAct>
+int launch_swap(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  return q.m <= 16 ? run_swap<16, kAct>(q, peers, stream) : run_swap<64, kAct>(q, peers, stream);
+}
+
 template <int BN, int STAGES, int kAct>
 int launch_generic(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   auto kernel = umma_generic_kernel<BN, STAGES, kAct>;
@@ -1353,6 +1600,11 @@ constexpr b200_tf32_kernel_meta meta_splitk(int id, const char* name, const char
   return b200_tf32_kernel_meta{id, name, alias, epilogue, kTileM, kSplitN, kStageK, kTileM, kSplitN, kInstK, stages, 4, 4, 4, 1};
 }
 
+// Few rows on the tensor cores: D^T = B^T A^T, 128 columns of D per CTA, K split over a cluster.
+constexpr b200_tf32_kernel_meta meta_swap(int id, const char* name, const char* alias, int epilogue) {
+  return b200_tf32_kernel_meta{id, name, alias, epilogue, 64, kSwapTileN, kStageK, kSwapTileN, 64, kInstK, 4, 4, 4, 4, 1};
+}
+
 // Skinny rows: FP32 FMA stream over B, 16 x 128 outputs per CTA, K split over warps and a cluster.
 constexpr b200_tf32_kernel_meta meta_skinny(int id, const char* name, const char* alias, int epilogue) {
   return b200_tf32_kernel_meta{id, name, alias, epilogue, kSkinnyMaxRows, 128, 64, kSkinnyMaxRows, 128, 1, 1, 1, 4, 1, 0};
@@ -1391,6 +1643,9 @@ bool gate_splitk(const b200_gemm_problem& q, int sms) {
   const float unsplit_us = static_cast<float>(k_blocks) * (tiles_of(q, 64) <= sms ? 0.23f : 0.34f) + 3.5f;
   return split_us + 1.0f < unsplit_us;   // ties go to the simpler kernel (1024^3 with a source: 17.6 vs 16.6 us)
 }
+// Measured against the split-K tile kernel: ahead up to 16 rows (16 x 8192 x 1024: 10.4 vs 16.2 us,
+// 16 x 4096 x 4096: 15.5 vs 16.5), behind from 32 rows on (64 x 4096 x 4096: 22.1 vs 17.6).
+bool gate_swap(const b200_gemm_problem& q, int) { return q.m <= 16; }
 bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) * 2 <= sms && q.n > 64; }
 
 // Dispatch order. Entries with ids >= 16 exist only here and are tried first by
@@ -1405,6 +1660,9 @@ const RegistryEntry kRegistry[] = {
     {meta_skinny(27, "simt16x128splitk", "skinny", B200_EPILOGUE_LINEAR), &launch_skinny, &gate_skinny},
     {meta_skinny(28, "simt16x128splitkRelu", "skinny_relu", B200_EPILOGUE_RELU), &launch_skinny, &gate_skinny},
     {meta_skinny(29, "simt16x128splitkGelu", "skinny_gelu", B200_EPILOGUE_GELU), &launch_skinny, &gate_skinny},
+    {meta_swap(36, "umma64x128swap", "swap", B200_EPILOGUE_LINEAR), &launch_swap<B200_EPILOGUE_LINEAR>, &gate_swap},
+    {meta_swap(37, "umma64x128swapRelu", "swap_relu", B200_EPILOGUE_RELU), &launch_swap<B200_EPILOGUE_RELU>, &gate_swap},
+    {meta_swap(38, "umma64x128swapGelu", "swap_gelu", B200_EPILOGUE_GELU), &launch_swap<B200_EPILOGUE_GELU>, &gate_swap},
     {meta_splitk(30, "umma128x128stage3splitk", "splitk", B200_EPILOGUE_LINEAR, 3), &launch_splitk<3, B200_EPILOGUE_LINEAR>, &gate_splitk},
     {meta_splitk(31, "umma128x128stage3splitkRelu", "splitk_relu", B200_EPILOGUE_RELU, 3), &launch_splitk<3, B200_EPILOGUE_RELU>, &gate_splitk},
     {meta_splitk(32, "umma128x128stage3splitkGelu", "splitk_gelu", B200_EPILOGUE_GELU, 3), &launch_splitk<3, B200_EPILOGUE_GELU>, &gate_splitk},

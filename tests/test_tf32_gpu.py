@@ -293,9 +293,11 @@ def test_skinny_dispatch_and_refusals(abi):
     for epilogue, expected_id in ((LINEAR, 27), (RELU, 28), (GELU, 29)):
         status, _, chosen = run(abi, 0, a.cuda(), b.cuda(), epilogue=epilogue, dispatch=True)
         assert status == 0 and chosen == expected_id
-    # From five rows on automatic dispatch prefers the tensor-core entries (here: split K).
+    # From five rows on automatic dispatch prefers the tensor-core entries: operands swapped up to 16 rows.
     a5, b5, _ = oracle.adaptive_inputs(16, 4096, 4096)
-    assert run(abi, 0, a5.cuda(), b5.cuda(), dispatch=True)[2] == 30
+    assert run(abi, 0, a5.cuda(), b5.cuda(), dispatch=True)[2] == 36
+    a6, b6, _ = oracle.adaptive_inputs(17, 4096, 4096)
+    assert run(abi, 0, a6.cuda(), b6.cuda(), dispatch=True)[2] == 30
     # More than 16 rows: a forced call is refused.
     a17, b17, _ = oracle.adaptive_inputs(17, 256, 64)
     assert run(abi, 27, a17.cuda(), b17.cuda())[0] == 2          # invalid problem
@@ -372,3 +374,34 @@ def test_split_k_auto_dispatch(abi):
     # Enough tiles for every SM: no split.
     a, b, _ = oracle.adaptive_inputs(128 * 8, 128 * ((sms + 7) // 8), 256)
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] not in (30, 31, 32)
+
+
+# --------------------------------------------------------- operands swapped
+# D^T = B^T A^T for few rows: the MMA's 128 rows run along N, its N side holds 16 or 64 rows of A.
+
+
+@pytest.mark.parametrize("entry", [e for e in entries() if e[1].startswith("swap")], ids=lambda e: e[1])
+@pytest.mark.parametrize("shape", [
+    (1, 4096, 4096), (16, 4096, 4096), (13, 260, 1000), (17, 132, 100), (64, 1024, 2048), (40, 8192, 320),
+    (5, 4, 8), (100, 200, 300),      # more than 64 rows: several row blocks
+])
+def test_swapped_operands_match_oracle(abi, entry, shape):
+    kernel_id, _, epilogue, _ = entry
+    a, b, c = oracle.adaptive_inputs(*shape, seed=shape[0])
+    bias = torch.linspace(-1.0, 1.0, shape[1])
+    status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c.cuda(), alpha=0.75, beta=0.25, epilogue=epilogue,
+                       bias=bias.cuda())
+    assert status == 0, abi.b200_status_string(status)
+    name = "bias" if epilogue == LINEAR else "bias_" + EPILOGUE_NAME[epilogue]
+    check(d, oracle.adaptive_gemm_fp64(a, b, c, 0.75, 0.25, name, bias=bias), k=shape[2])
+    assert_device_clean(abi)
+
+
+def test_swapped_operands_are_exact_on_integers_and_deterministic(abi):
+    g = torch.Generator().manual_seed(11)
+    for m in (3, 16, 33):
+        a = torch.randint(-4, 5, (m, 1024), generator=g).float()
+        b = torch.randint(-4, 5, (1024, 640), generator=g).float()
+        first = run(abi, 36, a.cuda(), b.cuda())[1]
+        torch.testing.assert_close(first.cpu(), oracle.adaptive_gemm_fp64(a, b), atol=0, rtol=0)
+        assert torch.equal(first, run(abi, 36, a.cuda(), b.cuda())[1])
