@@ -534,19 +534,23 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_c
 // Signals that both CTAs need (stage free, accumulator ready) are committed
 // twice, once per CTA; no multicast form is used anywhere.
 constexpr int kPairN = 256;
-constexpr uint32_t kPairStageBytes = kASlabBytes + (kPairN / 2 / 32) * kBBoxBytes;  // 32 KiB per CTA
+constexpr uint32_t kPairSubBytes = kASlabBytes + (kPairN / 2 / 32) * kBBoxBytes;  // 32 floats of K: 32 KiB per CTA
 
-template <int STAGES>
+// A pipeline stage holds KSUB such 32-wide K sub-blocks behind one pair of barriers: the MMA
+// thread's barrier wait, fence and commits are paid per stage, and they cost about as much as two
+// of the eight instructions of a two-sub-block stage.
+template <int STAGES, int KSUB>
 __host__ __device__ constexpr size_t pair_smem_bytes() {
-  return static_cast<size_t>(STAGES) * kPairStageBytes + 1024 + 256 + kPeerStageBytes;
+  return static_cast<size_t>(STAGES) * KSUB * kPairSubBytes + 1024 + 256 + kPeerStageBytes;
 }
 
-template <int STAGES, int kAct>
+template <int STAGES, int KSUB, int kAct>
 __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
   // Same carve-up in both CTAs: the MMA addresses the peer's shared memory by
   // the same offsets as its own.
   uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr uint32_t kPairStageBytes = KSUB * kPairSubBytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(STAGES) * kPairStageBytes);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;
@@ -581,7 +585,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
   const int tiles_m = (p.m + 2 * kTileM - 1) / (2 * kTileM);
   const int tiles_n = (p.n + kPairN - 1) / kPairN;
   const int tiles = tiles_m * tiles_n;
-  const int k_blocks = (p.k + kStageK - 1) / kStageK;
+  const int k_blocks = (p.k + KSUB * kStageK - 1) / (KSUB * kStageK);   // stages per tile; K past the end reads as zeros
   const int first_tile = blockIdx.x >> 1, tile_stride = gridDim.x >> 1;
 
   if (warp == 0) {
@@ -601,15 +605,19 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
           // Completion bytes of both CTAs are counted on CTA 0's barrier.
           const uint32_t full_addr = map_to_cta(smem_u32(&full[stage]), 0);
           if (rank == 0) mbar_expect_tx(&full[stage], 2 * kPairStageBytes);
-          uint8_t* a_dst = stages + static_cast<size_t>(stage) * kPairStageBytes;
-          uint8_t* b_dst = a_dst + kASlabBytes;
-          tma_load_2d_pair(a_dst, &p.map_a, full_addr, kb * kStageK, row0);
-          if (p.b_strips == kPairN / 2 / 32) {
-            tma_load_3d_pair(b_dst, &p.map_b_strips, full_addr, 0, kb * kStageK, col0 / 32);
-          } else {
 #pragma unroll
-            for (int j = 0; j < kPairN / 2 / 32; ++j) {
-              tma_load_2d_pair(b_dst + j * kBBoxBytes, &p.map_b, full_addr, col0 + j * 32, kb * kStageK);
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const int k0 = (kb * KSUB + sub) * kStageK;
+            uint8_t* a_dst = stages + static_cast<size_t>(stage) * kPairStageBytes + sub * kPairSubBytes;
+            uint8_t* b_dst = a_dst + kASlabBytes;
+            tma_load_2d_pair(a_dst, &p.map_a, full_addr, k0, row0);
+            if (p.b_strips == kPairN / 2 / 32) {
+              tma_load_3d_pair(b_dst, &p.map_b_strips, full_addr, 0, k0, col0 / 32);
+            } else {
+#pragma unroll
+              for (int j = 0; j < kPairN / 2 / 32; ++j) {
+                tma_load_2d_pair(b_dst + j * kBBoxBytes, &p.map_b, full_addr, col0 + j * 32, k0);
+              }
             }
           }
           if (++stage == STAGES) stage = 0, phase ^= 1u;
@@ -632,13 +640,16 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
           tcgen05_fence_after_sync();
-          const uint32_t a_addr = smem_u32(stages + static_cast<size_t>(stage) * kPairStageBytes);
-          const uint32_t b_addr = a_addr + kASlabBytes;
 #pragma unroll
-          for (int j = 0; j < kStageK / kInstK; ++j) {
-            const uint64_t desc_a = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
-            const uint64_t desc_b = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
-            umma_tf32_pair(tmem_acc, desc_a, desc_b, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const uint32_t a_addr = smem_u32(stages + static_cast<size_t>(stage) * kPairStageBytes + sub * kPairSubBytes);
+            const uint32_t b_addr = a_addr + kASlabBytes;
+#pragma unroll
+            for (int j = 0; j < kStageK / kInstK; ++j) {
+              const uint64_t desc_a = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
+              const uint64_t desc_b = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
+              umma_tf32_pair(tmem_acc, desc_a, desc_b, idesc, (kb > 0 || sub > 0 || j > 0) ? 1u : 0u);
+            }
           }
           // The stage is reusable in both CTAs once these MMAs have read it.
           umma_commit_pair(smem_u32(&empty[stage]));
@@ -1363,8 +1374,10 @@ int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_
 
 template <int STAGES, int kAct>
 int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
-  auto kernel = umma_pair_kernel<STAGES, kAct>;
-  constexpr size_t smem = pair_smem_bytes<STAGES>();
+  constexpr int KSUB = 2;                       // 64 floats of K per stage
+  static_assert(STAGES % KSUB == 0, "the registry states the ring depth in 32-wide K blocks");
+  auto kernel = umma_pair_kernel<STAGES / KSUB, KSUB, kAct>;
+  constexpr size_t smem = pair_smem_bytes<STAGES / KSUB, KSUB>();
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
   }
