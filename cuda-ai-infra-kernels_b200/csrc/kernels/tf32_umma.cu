@@ -391,8 +391,12 @@ __device__ __forceinline__ SmemCarve carve(uint8_t* raw) {
 // MMA issuer of the persistent single-CTA kernels (one thread): for every tile
 // of this CTA, waits until the epilogue has drained the accumulator buffer,
 // then consumes the operand ring stage by stage.
-template <int BN, int STAGES>
+// `KSUB` 32-wide K sub-blocks share one pipeline stage (one barrier wait, one commit): the ring has
+// STAGES / KSUB stages, and `k_blocks` counts stages.
+template <int BN, int STAGES, int KSUB = 1>
 __device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base, int tiles, int k_blocks) {
+  static_assert(STAGES % KSUB == 0, "whole stages");
+  constexpr int kRing = STAGES / KSUB;
   int stage = 0;
   uint32_t phase = 0;
   bool ok = true;
@@ -407,10 +411,13 @@ __device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base
     for (int kb = 0; kb < k_blocks; ++kb) {
       if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
-      const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>());
-      issue_stage_mmas<BN>(tmem_acc, a_addr, a_addr + kASlabBytes, kb > 0 ? 1u : 0u);
+#pragma unroll
+      for (int sub = 0; sub < KSUB; ++sub) {
+        const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage * KSUB + sub) * stage_bytes<BN>());
+        issue_stage_mmas<BN>(tmem_acc, a_addr, a_addr + kASlabBytes, (kb > 0 || sub > 0) ? 1u : 0u);
+      }
       umma_commit(&sm.empty[stage]);  // stage reusable once these MMAs have read it
-      if (++stage == STAGES) stage = 0, phase ^= 1u;
+      if (++stage == kRing) stage = 0, phase ^= 1u;
     }
     if (ok) umma_commit(&sm.acc_full[buf]);
   }
@@ -450,8 +457,12 @@ __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCar
 // warps 2-5: epilogue; warp w reads the TMEM lane quarter w % 4.
 constexpr int kTmaThreads = 6 * 32;
 
-template <int BN, int STAGES, int kAct>
+// STAGES counts 32-wide K blocks of shared memory; KSUB of them form one pipeline stage (the MMA
+// thread's barrier wait and commit cost about as much as four small MMAs, so narrow tiles, whose
+// MMAs are short, run two sub-blocks per stage).
+template <int BN, int STAGES, int kAct, int KSUB = 1>
 __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_constant__ UmmaParams p) {
+  constexpr int kRing = STAGES / KSUB;
   extern __shared__ uint8_t smem_raw[];
   const SmemCarve sm = carve<BN, STAGES>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -479,7 +490,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_c
   const int tiles_m = (p.m + kTileM - 1) / kTileM;
   const int tiles_n = (p.n + BN - 1) / BN;
   const int tiles = tiles_m * tiles_n;
-  const int k_blocks = (p.k + kStageK - 1) / kStageK;
+  const int k_blocks = (p.k + KSUB * kStageK - 1) / (KSUB * kStageK);   // stages per tile; K past the end reads as zeros
 
   if (warp == 0) {
     if (lane == 0) {
@@ -493,25 +504,29 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_c
         tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&sm.empty[stage], phase ^ 1u, kSiteUmmaEmpty)) { ok = false; break; }
-          uint8_t* a_dst = sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>();
-          uint8_t* b_dst = a_dst + kASlabBytes;
-          mbar_expect_tx(&sm.full[stage], stage_bytes<BN>());
-          tma_load_2d(a_dst, &p.map_a, &sm.full[stage], kb * kStageK, tm * kTileM);
-          if (p.b_strips == BN / 32) {
-            // The producer thread's issue rate matters: one copy instead of BN / 32.
-            tma_load_3d(b_dst, &p.map_b_strips, &sm.full[stage], 0, kb * kStageK, tn * (BN / 32));
-          } else {
+          mbar_expect_tx(&sm.full[stage], KSUB * stage_bytes<BN>());
 #pragma unroll
-            for (int j = 0; j < BN / 32; ++j) {
-              tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &sm.full[stage], tn * BN + j * 32, kb * kStageK);
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const int k0 = (kb * KSUB + sub) * kStageK;
+            uint8_t* a_dst = sm.stages + static_cast<size_t>(stage * KSUB + sub) * stage_bytes<BN>();
+            uint8_t* b_dst = a_dst + kASlabBytes;
+            tma_load_2d(a_dst, &p.map_a, &sm.full[stage], k0, tm * kTileM);
+            if (p.b_strips == BN / 32) {
+              // The producer thread's issue rate matters: one copy instead of BN / 32.
+              tma_load_3d(b_dst, &p.map_b_strips, &sm.full[stage], 0, k0, tn * (BN / 32));
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 32; ++j) {
+                tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &sm.full[stage], tn * BN + j * 32, k0);
+              }
             }
           }
-          if (++stage == STAGES) stage = 0, phase ^= 1u;
+          if (++stage == kRing) stage = 0, phase ^= 1u;
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) mma_role<BN, STAGES>(sm, tmem_base, tiles, k_blocks);
+    if (lane == 0) mma_role<BN, STAGES, KSUB>(sm, tmem_base, tiles, k_blocks);
   } else {
     epilogue_role<BN, kAct, true>(p, sm, tmem_base, warp & 3, lane, tiles, tiles_m, tiles_n);
   }
@@ -986,20 +1001,28 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
 // kernel; CTA r finishes the 128 / cluster columns it owns.
 constexpr int kSwapTileN = 128;   // columns of D per CTA (the M side of the MMA)
 
+// One 32-wide K sub-block: the B slab and NM rows of A.
 template <int NM>
-__host__ __device__ constexpr uint32_t swap_stage_bytes() {
+__host__ __device__ constexpr uint32_t swap_sub_bytes() {
   return (kSwapTileN / 32) * kBBoxBytes + NM * kStageK * 4;
 }
 
-template <int NM, int STAGES>
-__host__ __device__ constexpr size_t swap_smem_bytes() {
-  return static_cast<size_t>(STAGES) * swap_stage_bytes<NM>() + 1024 + 256;
+// A pipeline stage holds KSUB sub-blocks: the small MMAs of this kernel (54 cycles each in
+// isolation) are cheap next to the 380 cycles of a stage's barrier wait and commit.
+template <int NM, int KSUB>
+__host__ __device__ constexpr uint32_t swap_stage_bytes() {
+  return KSUB * swap_sub_bytes<NM>();
 }
 
-template <int NM, int STAGES, int kAct>
-__global__ void __launch_bounds__(kTmaThreads, 2) umma_swap_kernel(const __grid_constant__ UmmaParams p) {
+template <int NM, int STAGES, int KSUB>
+__host__ __device__ constexpr size_t swap_smem_bytes() {
+  return static_cast<size_t>(STAGES) * swap_stage_bytes<NM, KSUB>() + 1024 + 256;
+}
+
+template <int NM, int STAGES, int KSUB, int kAct>
+__global__ void __launch_bounds__(kTmaThreads, 1) umma_swap_kernel(const __grid_constant__ UmmaParams p) {
   static_assert(NM % 16 == 0 && NM >= 16 && NM <= 64, "rows of A per tile");
-  static_assert(static_cast<size_t>(STAGES) * swap_stage_bytes<NM>() >= sizeof(float) * NM * kSwapTileN,
+  static_assert(static_cast<size_t>(STAGES) * swap_stage_bytes<NM, KSUB>() >= sizeof(float) * NM * kSwapTileN,
                 "the idle operand ring must hold one exchanged tile");
   constexpr uint32_t kTmemCols = NM < 32 ? 32 : NM;
   cg::cluster_group cluster = cg::this_cluster();
@@ -1007,7 +1030,7 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_swap_kernel(const __grid_
   const int rank = static_cast<int>(cluster.block_rank());
   extern __shared__ uint8_t smem_raw[];
   uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(STAGES) * swap_stage_bytes<NM>());
+  uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(STAGES) * swap_stage_bytes<NM, KSUB>());
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_full + 2);
@@ -1036,7 +1059,7 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_swap_kernel(const __grid_
   const int tiles_m = (p.m + NM - 1) / NM;
   const int tile = static_cast<int>(blockIdx.x) / ranks;
   const int m0 = (tile % tiles_m) * NM, n0 = (tile / tiles_m) * kSwapTileN;
-  const int k_blocks = (p.k + kStageK - 1) / kStageK;
+  const int k_blocks = (p.k + KSUB * kStageK - 1) / (KSUB * kStageK);   // stages; K past the end reads as zeros
   const int per_rank = (k_blocks + ranks - 1) / ranks;
   const int kb_begin = min(k_blocks, rank * per_rank);
   const int kb_end = min(k_blocks, kb_begin + per_rank);
@@ -1051,16 +1074,20 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_swap_kernel(const __grid_
       uint32_t phase = 0;
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1u, kSiteUmmaEmpty)) break;
-        uint8_t* b_dst = stages + static_cast<size_t>(stage) * swap_stage_bytes<NM>();   // B slab first
-        uint8_t* a_dst = b_dst + (kSwapTileN / 32) * kBBoxBytes;
-        mbar_expect_tx(&full[stage], swap_stage_bytes<NM>());
-        tma_load_2d(a_dst, &p.map_a, &full[stage], kb * kStageK, m0);   // NM rows x 32 floats of K
-        if (p.b_strips == kSwapTileN / 32) {
-          tma_load_3d(b_dst, &p.map_b_strips, &full[stage], 0, kb * kStageK, n0 / 32);
-        } else {
+        mbar_expect_tx(&full[stage], swap_stage_bytes<NM, KSUB>());
 #pragma unroll
-          for (int j = 0; j < kSwapTileN / 32; ++j) {
-            tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &full[stage], n0 + j * 32, kb * kStageK);
+        for (int sub = 0; sub < KSUB; ++sub) {
+          const int k0 = (kb * KSUB + sub) * kStageK;
+          uint8_t* b_dst = stages + static_cast<size_t>(stage) * swap_stage_bytes<NM, KSUB>() + sub * swap_sub_bytes<NM>();
+          uint8_t* a_dst = b_dst + (kSwapTileN / 32) * kBBoxBytes;                // B slab first, then NM rows of A
+          tma_load_2d(a_dst, &p.map_a, &full[stage], k0, m0);
+          if (p.b_strips == kSwapTileN / 32) {
+            tma_load_3d(b_dst, &p.map_b_strips, &full[stage], 0, k0, n0 / 32);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kSwapTileN / 32; ++j) {
+              tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &full[stage], n0 + j * 32, k0);
+            }
           }
         }
         if (++stage == STAGES) stage = 0, phase ^= 1u;
@@ -1076,13 +1103,17 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_swap_kernel(const __grid_
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait(&full[stage], phase, kSiteUmmaFull)) { fed = false; break; }
         tcgen05_fence_after_sync();
-        const uint32_t b_addr = smem_u32(stages + static_cast<size_t>(stage) * swap_stage_bytes<NM>());
-        const uint32_t a_addr = b_addr + (kSwapTileN / 32) * kBBoxBytes;
 #pragma unroll
-        for (int j = 0; j < kStageK / kInstK; ++j) {
-          const uint64_t desc_mma_a = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
-          const uint64_t desc_mma_b = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
-          umma_tf32(tmem_base, desc_mma_a, desc_mma_b, idesc, (kb > kb_begin || j > 0) ? 1u : 0u);
+        for (int sub = 0; sub < KSUB; ++sub) {
+          const uint32_t b_addr =
+              smem_u32(stages + static_cast<size_t>(stage) * swap_stage_bytes<NM, KSUB>() + sub * swap_sub_bytes<NM>());
+          const uint32_t a_addr = b_addr + (kSwapTileN / 32) * kBBoxBytes;
+#pragma unroll
+          for (int j = 0; j < kStageK / kInstK; ++j) {
+            const uint64_t desc_mma_a = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
+            const uint64_t desc_mma_b = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
+            umma_tf32(tmem_base, desc_mma_a, desc_mma_b, idesc, (kb > kb_begin || sub > 0 || j > 0) ? 1u : 0u);
+          }
         }
         umma_commit(&empty[stage]);
         if (++stage == STAGES) stage = 0, phase ^= 1u;
@@ -1345,7 +1376,10 @@ void fill_common(UmmaParams* p, const b200_gemm_problem& q, const PeerOutputs& p
 
 template <int BN, int STAGES, int kAct>
 int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
-  auto kernel = umma_tma_kernel<BN, STAGES, kAct>;
+  // Two sub-blocks per stage where the ring has room for at least two such stages and the tile is
+  // not already bound by what an SM can pull from L2 (the 128 x 256 tile is).
+  constexpr int KSUB = (BN <= 128 && STAGES % 2 == 0 && STAGES >= 4) ? 2 : 1;
+  auto kernel = umma_tma_kernel<BN, STAGES, kAct, KSUB>;
   constexpr size_t smem = smem_bytes<BN, STAGES>();
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
@@ -1510,11 +1544,11 @@ int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStre
 }
 
 // Cluster size of the operand-swapped kernel: as many K ranges as keep every cluster resident at
-// once (two CTAs per SM) with at least four K blocks each.
-int swap_ranks(int64_t tiles, int k_blocks, int sms) {
+// once (one CTA per SM) with at least two pipeline stages each.
+int swap_ranks(int64_t tiles, int k_stages, int sms) {
   int ranks = 1;
-  while (ranks < 8 && tiles * (ranks * 2) <= 2LL * sms && k_blocks / (ranks * 2) >= 4 &&
-         tiles <= 2LL * splitk_max_clusters(ranks * 2)) {
+  while (ranks < 8 && tiles * (ranks * 2) <= sms && k_stages / (ranks * 2) >= 2 &&
+         tiles <= splitk_max_clusters(ranks * 2)) {
     ranks *= 2;
   }
   return ranks;
@@ -1522,9 +1556,10 @@ int swap_ranks(int64_t tiles, int k_blocks, int sms) {
 
 template <int NM, int kAct>
 int run_swap(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
-  constexpr int STAGES = 4;
-  auto kernel = umma_swap_kernel<NM, STAGES, kAct>;
-  constexpr size_t smem = swap_smem_bytes<NM, STAGES>();
+  // About 144 KiB of ring either way: 2 stages x 4 sub-blocks of 18 KiB, or 3 x 2 of 24 KiB.
+  constexpr int KSUB = NM <= 16 ? 4 : 2, STAGES = NM <= 16 ? 2 : 3;
+  auto kernel = umma_swap_kernel<NM, STAGES, KSUB, kAct>;
+  constexpr size_t smem = swap_smem_bytes<NM, STAGES, KSUB>();
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
   }
@@ -1542,7 +1577,7 @@ int run_swap(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t 
   const int sms = sm_count();
   if (sms <= 0) return B200_ERR_INTERNAL;
   const int64_t tiles = static_cast<int64_t>((q.m + NM - 1) / NM) * ((q.n + kSwapTileN - 1) / kSwapTileN);
-  const int ranks = swap_ranks(tiles, (q.k + kStageK - 1) / kStageK, sms);
+  const int ranks = swap_ranks(tiles, (q.k + KSUB * kStageK - 1) / (KSUB * kStageK), sms);
   if (tiles * ranks > 0x7fffffffLL) return B200_ERR_INVALID_PROBLEM;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(tiles * ranks));
@@ -1645,19 +1680,19 @@ bool gate_pair(const b200_gemm_problem& q, int sms) {
 // tensor-core split-K entry takes over (16 x 4096 x 4096: 22.1 vs 14.7 us).
 bool gate_skinny(const b200_gemm_problem& q, int) { return q.m <= 4; }
 // Split K when the model above predicts a shorter run than the unsplit tile kernels, which stream a
-// K block in about 0.23 us (128 x 64 tiles, when those fit the SMs in one round) or 0.34 us (128 x 128)
-// on top of 3.5 us of prologue and epilogue. Measured on a B200: 1024 x 1024 x 8192 39.8 us split
-// four ways against 73.0 us unsplit, 16 x 4096 x 4096 14.1 against 38.1, while 512^3 and 1024^3 stay
-// within 1 us of the 128 x 64 tile kernel either way.
+// 32-wide K block in about 0.18 us (128 x 64 tiles, two sub-blocks per stage, when those fit the
+// SMs in one round) or 0.29 us (128 x 128) on top of 3.5 us of prologue and epilogue. Measured on a
+// B200: 1024 x 1024 x 8192 40.7 us split four ways against 61.0 us unsplit, 64 x 4096 x 4096 17.8
+// against 31.7, while 512^3, 1024^3 and 512 x 2048 x 2048 are within 1 us either way.
 bool gate_splitk(const b200_gemm_problem& q, int sms) {
   float split_us = 0.f;
   if (splitk_ranks(q, sms, &split_us) < 2) return false;
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
-  const float unsplit_us = static_cast<float>(k_blocks) * (tiles_of(q, 64) <= sms ? 0.23f : 0.34f) + 3.5f;
+  const float unsplit_us = static_cast<float>(k_blocks) * (tiles_of(q, 64) <= sms ? 0.18f : 0.29f) + 3.5f;
   return split_us + 1.0f < unsplit_us;   // ties go to the simpler kernel (1024^3 with a source: 17.6 vs 16.6 us)
 }
-// Measured against the split-K tile kernel: ahead up to 16 rows (16 x 8192 x 1024: 10.4 vs 16.2 us,
-// 16 x 4096 x 4096: 15.5 vs 16.5), behind from 32 rows on (64 x 4096 x 4096: 22.1 vs 17.6).
+// Measured against the split-K tile kernel: ahead up to 16 rows (16 x 8192 x 1024: 11.7 vs 16.5 us,
+// 16 x 4096 x 4096: 12.7 vs 16.8, cuBLAS 12.9), level or behind from 32 rows on (64 x 4096 x 4096: 19.7 vs 18.2).
 bool gate_swap(const b200_gemm_problem& q, int) { return q.m <= 16; }
 bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) * 2 <= sms && q.n > 64; }
 
