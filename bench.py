@@ -61,7 +61,7 @@ PUBLISHED_A800_SPLIT_K_TFLOPS = 17.206
 # roofline objects can set traffic beside the algorithmic bytes.
 NCU_TRAFFIC_BYTES = {
     "sgemm_4096": 334.2e6 + 54.9e6,      # profiles/sgemm_pipeline_4096.md (algorithmic: 201 MB of operands + output)
-    "tf32_4096": 373.7e6 + 52.7e6,       # profiles/tf32_umma_4096.md (CTA-pair kernel)
+    "tf32_4096": 372.6e6 + 50.7e6,       # profiles/tf32_umma_4096.md (CTA-pair kernel)
     "rmsnorm_16384x4096": 268.5e6 + 213.0e6,   # profiles/rowops_c4.md (writes partly still in L2 at kernel end)
     "softmax_32768x1024": 134.2e6 + 78.2e6,
 }
