@@ -90,6 +90,8 @@ struct UmmaParams {
   float alpha, beta;
   int vector_io;       // C/D rows allow 128-bit accesses
   PeerOutputs peers;   // further destinations of every finished element (fused all-gather), usually none
+  int pair_full_tiles;  // CTA-pair kernel: work items [0, full) are whole 256 x 256 tiles, the rest
+                        // are the two 256 x 128 halves of the tiles after them (see launch_pair)
 #ifdef B200_PROBE_TIMING
   uint64_t* probe;     // [grid][8] time stamps, or null
 #endif
@@ -559,6 +561,18 @@ __host__ __device__ constexpr size_t pair_smem_bytes() {
   return static_cast<size_t>(STAGES) * KSUB * kPairSubBytes + 1024 + 256 + kPeerStageBytes;
 }
 
+// Work item of the CTA-pair kernel: a whole 256 x 256 tile, or (for the last, partial round of
+// tiles) one 256 x 128 half of one, so that twice as many pairs share the tail.
+struct PairItem {
+  int tile;
+  int half;   // -1: whole tile; 0 / 1: left / right 128 columns
+};
+__device__ __forceinline__ PairItem pair_item(int item, int full_tiles) {
+  if (item < full_tiles) return PairItem{item, -1};
+  const int h = item - full_tiles;
+  return PairItem{full_tiles + (h >> 1), h & 1};
+}
+
 template <int STAGES, int KSUB, int kAct>
 __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -600,6 +614,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
   const int tiles_m = (p.m + 2 * kTileM - 1) / (2 * kTileM);
   const int tiles_n = (p.n + kPairN - 1) / kPairN;
   const int tiles = tiles_m * tiles_n;
+  const int items = p.pair_full_tiles + 2 * (tiles - p.pair_full_tiles);   // whole tiles, then halves
   const int k_blocks = (p.k + KSUB * kStageK - 1) / (KSUB * kStageK);   // stages per tile; K past the end reads as zeros
   const int first_tile = blockIdx.x >> 1, tile_stride = gridDim.x >> 1;
 
@@ -610,27 +625,30 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = first_tile; tile < tiles && ok; tile += tile_stride) {
+      for (int item = first_tile; item < items && ok; item += tile_stride) {
+        const PairItem it = pair_item(item, p.pair_full_tiles);
         int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        tile_coords(it.tile, tiles_m, tiles_n, &tm, &tn);
         const int row0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
-        const int col0 = tn * kPairN + static_cast<int>(rank) * (kPairN / 2);
+        // This CTA's share of the B columns: 128 of a whole tile, 64 of a half tile.
+        const int cta_cols = it.half < 0 ? kPairN / 2 : kPairN / 4;
+        const int col0 = tn * kPairN + (it.half < 0 ? 0 : it.half * (kPairN / 2)) + static_cast<int>(rank) * cta_cols;
+        const uint32_t sub_tx = kASlabBytes + (cta_cols / 32) * kBBoxBytes;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, kSiteUmmaEmpty)) { ok = false; break; }
           // Completion bytes of both CTAs are counted on CTA 0's barrier.
           const uint32_t full_addr = map_to_cta(smem_u32(&full[stage]), 0);
-          if (rank == 0) mbar_expect_tx(&full[stage], 2 * kPairStageBytes);
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * KSUB * sub_tx);
 #pragma unroll
           for (int sub = 0; sub < KSUB; ++sub) {
             const int k0 = (kb * KSUB + sub) * kStageK;
             uint8_t* a_dst = stages + static_cast<size_t>(stage) * kPairStageBytes + sub * kPairSubBytes;
             uint8_t* b_dst = a_dst + kASlabBytes;
             tma_load_2d_pair(a_dst, &p.map_a, full_addr, k0, row0);
-            if (p.b_strips == kPairN / 2 / 32) {
+            if (it.half < 0 && p.b_strips == kPairN / 2 / 32) {
               tma_load_3d_pair(b_dst, &p.map_b_strips, full_addr, 0, k0, col0 / 32);
             } else {
-#pragma unroll
-              for (int j = 0; j < kPairN / 2 / 32; ++j) {
+              for (int j = 0; j < cta_cols / 32; ++j) {
                 tma_load_2d_pair(b_dst + j * kBBoxBytes, &p.map_b, full_addr, col0 + j * 32, k0);
               }
             }
@@ -641,12 +659,14 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = umma_idesc_tf32(2 * kTileM, kPairN, /*a_mn_major=*/false, /*b_mn_major=*/true);
+      constexpr uint32_t idesc_whole = umma_idesc_tf32(2 * kTileM, kPairN, /*a_mn_major=*/false, /*b_mn_major=*/true);
+      constexpr uint32_t idesc_half = umma_idesc_tf32(2 * kTileM, kPairN / 2, /*a_mn_major=*/false, /*b_mn_major=*/true);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int local = 0;
-      for (int tile = first_tile; tile < tiles && ok; tile += tile_stride, ++local) {
+      for (int item = first_tile; item < items && ok; item += tile_stride, ++local) {
+        const uint32_t idesc = item < p.pair_full_tiles ? idesc_whole : idesc_half;
         const int buf = local & 1;
         const uint32_t use_parity = (local >> 1) & 1u;
         if (!mbar_wait(&acc_empty[buf], use_parity ^ 1u, kSiteUmmaAccEmpty)) { ok = false; break; }
@@ -682,22 +702,30 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
     const int quarter = warp & 3;
     bool ok = true;
     int local = 0;
-    for (int tile = first_tile; tile < tiles && ok; tile += tile_stride, ++local) {
+    for (int item = first_tile; item < items && ok; item += tile_stride, ++local) {
+      const PairItem it = pair_item(item, p.pair_full_tiles);
       const int buf = local & 1;
       const uint32_t use_parity = (local >> 1) & 1u;
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      tile_coords(it.tile, tiles_m, tiles_n, &tm, &tn);
+      const int n0 = tn * kPairN + (it.half < 0 ? 0 : it.half * (kPairN / 2));
       const int m0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
       const bool pipelined = ep.vector_io && ep.peers.count == 0;
       SourceChunk first;
-      if (pipelined) fetch_source(ep, first, m0 + quarter * 32 + lane, tn * kPairN);   // before the wait
+      if (pipelined) fetch_source(ep, first, m0 + quarter * 32 + lane, n0);   // before the wait
       if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
-      if (pipelined) {
-        epilogue_tile_pipelined<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, tn * kPairN, first);
+      float* stage_area = peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float));
+      if (it.half < 0) {
+        if (pipelined) {
+          epilogue_tile_pipelined<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, first);
+        } else {
+          epilogue_tile<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, stage_area);
+        }
+      } else if (pipelined) {
+        epilogue_tile_pipelined<kPairN / 2, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, first);
       } else {
-        epilogue_tile<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, tn * kPairN,
-                                     peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float)));
+        epilogue_tile<kPairN / 2, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, stage_area);
       }
       tcgen05_fence_before_sync();
       __syncwarp();
@@ -1430,6 +1458,11 @@ int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream
   if (sms < 2) return B200_ERR_INTERNAL;
   const int64_t tiles = static_cast<int64_t>((q.m + 2 * kTileM - 1) / (2 * kTileM)) * ((q.n + kPairN - 1) / kPairN);
   const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+  // A last round that occupies at most half the pairs is run as 256 x 128 half tiles on twice as
+  // many pairs: a half tile streams 24 instead of 32 KiB per K block and CTA and takes about 0.6 of
+  // a whole tile's time (4096^3: 34 left-over tiles become 68 halves on 74 pairs).
+  const int64_t remainder = tiles % pairs;
+  p.pair_full_tiles = static_cast<int>((remainder != 0 && 2 * remainder <= pairs) ? tiles - remainder : tiles);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
   cfg.blockDim = dim3(kTmaThreads);

@@ -405,3 +405,26 @@ def test_swapped_operands_are_exact_on_integers_and_deterministic(abi):
         first = run(abi, 36, a.cuda(), b.cuda())[1]
         torch.testing.assert_close(first.cpu(), oracle.adaptive_gemm_fp64(a, b), atol=0, rtol=0)
         assert torch.equal(first, run(abi, 36, a.cuda(), b.cuda())[1])
+
+
+# ------------------------------------------------ CTA pairs: half tiles in the last round
+
+
+@pytest.mark.parametrize("kernel,epilogue", [(20, LINEAR), (21, RELU)])
+def test_pair_kernel_runs_a_short_last_round_as_half_tiles(abi, kernel, epilogue):
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    pairs = sms // 2
+    # pairs + 10 tiles of 256 x 256 (arranged 2 x ... would need a factorisation: use one tile row more than fits):
+    tiles_n = 7
+    tiles_m = (pairs + 10 + tiles_n - 1) // tiles_n        # 12 on 148 SMs: 84 tiles, 10 left over -> 20 half tiles
+    assert 0 < (tiles_m * tiles_n) % pairs <= pairs // 2
+    m, n, k = 256 * tiles_m, 256 * tiles_n - 36, 100        # ragged right edge: the last half tile is partly outside
+    g = torch.Generator().manual_seed(3)
+    a = torch.randint(-4, 5, (m, k), generator=g).float()
+    b = torch.randint(-4, 5, (k, n), generator=g).float()
+    c = torch.randint(-4, 5, (m, n), generator=g).float()
+    status, d, _ = run(abi, kernel, a.cuda(), b.cuda(), c.cuda(), alpha=1.0, beta=0.5, epilogue=epilogue)
+    assert status == 0, abi.b200_status_string(status)
+    expected = oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, EPILOGUE_NAME[epilogue])
+    torch.testing.assert_close(d.cpu(), expected, atol=0, rtol=0)      # integers: exact
+    assert_device_clean(abi)
