@@ -1,0 +1,666 @@
+// TF32 tensor-core GEMM, kernels whose cluster splits K and meets in distributed shared memory:
+// the 128 x 128 split-K tile kernel and the operand-swapped kernel for few rows, with their
+// planners. Layouts, the parameter block and the epilogue pieces are in tf32_umma.cuh.
+#include <atomic>
+
+#include "tf32_umma.cuh"
+
+namespace b200 {
+
+cudaError_t tf32_cluster_status_read_clear(uint32_t* word) { return status_word_read_clear(word); }
+
+namespace {
+
+// ------------------------------------------------ TMA, split-K cluster kernel
+// For problems with too few 128 x 128 output tiles to occupy the SMs (few rows,
+// or small M x N with a long K): the 1, 2, 4 or 8 CTAs of a cluster share one
+// output tile and each reduces a contiguous range of K blocks into its own TMEM
+// accumulator (same producer / MMA roles as above, one tile per CTA, up to
+// two CTAs per SM). The partial tiles then meet in shared memory across the cluster:
+//   1. cluster barrier: every main loop is finished, so every operand ring is
+//      idle and becomes the exchange buffer;
+//   2. each epilogue thread (one accumulator row) sends the columns
+//      [r * W, (r + 1) * W), W = 128 / cluster, of its partial row to CTA r
+//      (distributed-shared-memory stores), rows outside the matrix are skipped;
+//   3. cluster barrier; CTA r adds the partials of its W columns in rank order
+//      (a fixed order: results do not depend on timing) and applies the fused
+//      epilogue. No scratch buffer, no atomics, no second launch.
+namespace cg = cooperative_groups;
+
+constexpr int kSplitN = 128;
+
+// Scaling, source, bias and activation for four adjacent outputs of one row.
+template <int kAct>
+__device__ __forceinline__ void finish_quad(const EpilogueArgs& p, int row, int col, float4 acc) {
+  float v[4] = {p.alpha * acc.x, p.alpha * acc.y, p.alpha * acc.z, p.alpha * acc.w};
+  const float* c_row = p.c + static_cast<int64_t>(row) * p.ldc;
+  float* d_row = p.d + static_cast<int64_t>(row) * p.ldd;
+  if (p.vector_io) {  // n % 4 == 0: the quad is inside the matrix as a whole
+    if (p.beta != 0.f) {
+      const float4 s = __ldg(reinterpret_cast<const float4*>(c_row + col));
+      v[0] = fmaf(p.beta, s.x, v[0]), v[1] = fmaf(p.beta, s.y, v[1]);
+      v[2] = fmaf(p.beta, s.z, v[2]), v[3] = fmaf(p.beta, s.w, v[3]);
+    }
+    if (p.bias != nullptr) {
+      const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+      v[0] += bv.x, v[1] += bv.y, v[2] += bv.z, v[3] += bv.w;
+    }
+    const float4 out = make_float4(activate<kAct>(v[0]), activate<kAct>(v[1]), activate<kAct>(v[2]), activate<kAct>(v[3]));
+    *reinterpret_cast<float4*>(d_row + col) = out;
+    store_peers(p, static_cast<int64_t>(row) * p.ldd + col, out);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (col + e < p.n) {
+        float out = v[e];
+        if (p.beta != 0.f) out = fmaf(p.beta, __ldg(c_row + col + e), out);
+        if (p.bias != nullptr) out += __ldg(p.bias + col + e);
+        out = activate<kAct>(out);
+        d_row[col + e] = out;
+        store_peers(p, static_cast<int64_t>(row) * p.ldd + col + e, out);
+      }
+    }
+  }
+}
+
+// Exchange buffer of a CTA: float4 elements [source][column quad of its share][row], kExchangePitch
+// elements per (source, quad). Senders own a row each, so a warp writes 32 consecutive elements;
+// the finishing pass reads row-wise (lanes = adjacent quads of one row) and the odd pitch spreads
+// those reads over the banks.
+constexpr int kExchangePitch = kTileM + 1;
+
+// Step 2 of the split-K kernels for one epilogue thread (one accumulator row of kCols columns in
+// TMEM at `tmem_row`): the columns of share s go to the CTA with cluster rank
+// s * rank_stride + rank_offset, into that CTA's buffer for source `my_slice`. The next 32 columns
+// are fetched from TMEM while the current ones are being sent; a share is at least 16 columns
+// wide, so each half chunk (four quads) has a single destination. `send_chunk` sends one chunk.
+__device__ __forceinline__ void send_chunk(cg::cluster_group& cluster, const uint32_t (&cur)[32], int chunk, float4* exchange,
+                                           int my_slice, int quads_log2, int rank_stride, int rank_offset,
+                                           int row_in_tile) {
+  const int quads = 1 << quads_log2;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int quad0 = chunk * 8 + half * 4;
+    const int dest_slice = quad0 >> quads_log2, local_quad0 = quad0 & (quads - 1);
+    float4* dst = cluster.map_shared_rank(exchange, dest_slice * rank_stride + rank_offset) +
+                  (my_slice * quads + local_quad0) * kExchangePitch + row_in_tile;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = half * 16 + j * 4;
+      dst[j * kExchangePitch] = make_float4(__uint_as_float(cur[e + 0]), __uint_as_float(cur[e + 1]),
+                                            __uint_as_float(cur[e + 2]), __uint_as_float(cur[e + 3]));
+    }
+  }
+}
+
+template <int kCols>
+__device__ __forceinline__ void send_partial_row(cg::cluster_group& cluster, uint32_t tmem_row, bool have_acc,
+                                                 float4* exchange, int my_slice, int quads_log2, int rank_stride,
+                                                 int rank_offset, int row_in_tile) {
+  constexpr int kChunks = kCols / 32;
+  static_assert(kChunks % 2 == 0, "chunks are handled in pairs");
+  // Two register sets, named rather than indexed so that both stay in registers.
+  uint32_t even[32], odd[32];
+  if (have_acc) {
+    tmem_ld_32x32(tmem_row, even);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) even[e] = odd[e] = 0u;   // an empty K range contributes zeros
+  }
+#pragma unroll
+  for (int chunk = 0; chunk < kChunks; chunk += 2) {
+    if (have_acc) {
+      tmem_ld_wait();
+      tmem_ld_32x32(tmem_row + (chunk + 1) * 32, odd);
+    }
+    send_chunk(cluster, even, chunk, exchange, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
+    if (have_acc) {
+      tmem_ld_wait();
+      if (chunk + 2 < kChunks) tmem_ld_32x32(tmem_row + (chunk + 2) * 32, even);
+    }
+    send_chunk(cluster, odd, chunk + 1, exchange, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
+  }
+}
+
+// Step 3 of the split-K kernels for thread t of `threads`: adds the partials of this CTA's column
+// share in source order and writes finished rows with lanes along the row, so that C is read and
+// D is written in contiguous segments. Only a few warps run this, so four outputs per thread are
+// kept in flight to cover the latencies.
+template <int kAct>
+__device__ __forceinline__ void exchange_finish(const EpilogueArgs& p, const float4* exchange, int sources, int quads_log2,
+                                                int row0, int col_base, int t, int threads) {
+  constexpr int kBatch = 4;
+  const int quads = 1 << quads_log2;
+  const int items = kTileM << quads_log2;
+  for (int base = t; base < items; base += kBatch * threads) {
+    float4 sum[kBatch];
+    const float4* src_ptr[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int item = min(base + u * threads, items - 1);   // clamped: a duplicate read, no duplicate write below
+      src_ptr[u] = exchange + (item & (quads - 1)) * kExchangePitch + (item >> quads_log2);
+      sum[u] = *src_ptr[u];
+    }
+    for (int src = 1; src < sources; ++src) {
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const float4 v = src_ptr[u][src * quads * kExchangePitch];
+        sum[u].x += v.x, sum[u].y += v.y, sum[u].z += v.z, sum[u].w += v.w;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int item = base + u * threads;
+      const int row = row0 + (item >> quads_log2), col = col_base + 4 * (item & (quads - 1));
+      if (item < items && row < p.m && col < p.n) finish_quad<kAct>(p, row, col, sum[u]);
+    }
+  }
+}
+
+template <int STAGES, int kAct>
+__global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __grid_constant__ UmmaParams p) {
+  constexpr int BN = kSplitN;
+  static_assert(static_cast<size_t>(STAGES) * stage_bytes<BN>() >= sizeof(float4) * kExchangePitch * (BN / 4),
+                "the idle operand ring must hold one exchanged tile");
+  cg::cluster_group cluster = cg::this_cluster();
+  const int ranks = static_cast<int>(cluster.num_blocks());
+  const int rank = static_cast<int>(cluster.block_rank());
+  extern __shared__ uint8_t smem_raw[];
+  const SmemCarve sm = carve<BN, STAGES>(smem_raw);
+  B200_PROBE(p, 0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    mbar_init(&sm.acc_full[0], 1);
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc<BN>(sm.tmem_ptr);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_ptr;
+  B200_PROBE(p, 1);
+
+  const int tiles_m = (p.m + kTileM - 1) / kTileM;
+  const int tiles_n = (p.n + BN - 1) / BN;
+  int tm, tn;
+  tile_coords(static_cast<int>(blockIdx.x) / ranks, tiles_m, tiles_n, &tm, &tn);
+  const int k_blocks = (p.k + kStageK - 1) / kStageK;
+  const int per_rank = (k_blocks + ranks - 1) / ranks;
+  const int kb_begin = min(k_blocks, rank * per_rank);
+  const int kb_end = min(k_blocks, kb_begin + per_rank);
+  const bool has_work = kb_begin < kb_end;   // an empty range contributes zeros
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&p.map_a);
+      prefetch_tensormap(p.b_strips == BN / 32 ? &p.map_b_strips : &p.map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&sm.empty[stage], phase ^ 1u, kSiteUmmaEmpty)) break;
+        uint8_t* a_dst = sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>();
+        uint8_t* b_dst = a_dst + kASlabBytes;
+        mbar_expect_tx(&sm.full[stage], stage_bytes<BN>());
+        tma_load_2d(a_dst, &p.map_a, &sm.full[stage], kb * kStageK, tm * kTileM);
+        if (p.b_strips == BN / 32) {
+          tma_load_3d(b_dst, &p.map_b_strips, &sm.full[stage], 0, kb * kStageK, tn * (BN / 32));
+        } else {
+#pragma unroll
+          for (int j = 0; j < BN / 32; ++j) {
+            tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &sm.full[stage], tn * BN + j * 32, kb * kStageK);
+          }
+        }
+        if (++stage == STAGES) stage = 0, phase ^= 1u;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && has_work) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool fed = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { fed = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>());
+        issue_stage_mmas<BN>(tmem_base, a_addr, a_addr + kASlabBytes, kb > kb_begin ? 1u : 0u);
+        umma_commit(&sm.empty[stage]);
+        if (++stage == STAGES) stage = 0, phase ^= 1u;
+      }
+      if (fed) umma_commit(&sm.acc_full[0]);
+    }
+  } else if (has_work) {
+    ok = mbar_wait(&sm.acc_full[0], 0, kSiteUmmaAccFull);
+    tcgen05_fence_after_sync();
+  }
+
+  B200_PROBE(p, 2);
+  // 1. Every CTA of the cluster is past its main loop.
+  tcgen05_fence_before_sync();
+  cluster.sync();
+  tcgen05_fence_after_sync();
+
+  B200_PROBE(p, 3);
+  // Exchange buffer of a CTA: float4 elements [source rank][column quad of its W columns][row]. Rows are
+  // innermost so that the 32 lanes of a warp (32 rows) touch 512 contiguous bytes: no bank conflicts
+  // on either side.
+  float4* exchange = reinterpret_cast<float4*>(sm.stages);
+  const int width = BN / ranks;                            // W: 128, 64, 32 or 16 columns per CTA
+  const int quads = width / 4;
+  const int quarter = warp & 3;
+  const int row_in_tile = quarter * 32 + lane;
+  const bool warp_rows = tm * kTileM + quarter * 32 < p.m;   // any row of this warp inside the matrix
+  const int quads_log2 = 31 - __clz(quads);
+  if (warp >= 2 && warp_rows) {
+    // 2. Send this CTA's partial row, W columns to each CTA.
+    send_partial_row<BN>(cluster, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), has_work && ok, exchange,
+                         rank, quads_log2, 1, 0, row_in_tile);
+  }
+  B200_PROBE(p, 4);
+  tcgen05_fence_before_sync();
+  cluster.sync();
+  B200_PROBE(p, 5);
+
+  // 3. Add the partials of this CTA's columns in rank order and finish them.
+  exchange_finish<kAct>(epilogue_args(p), exchange, ranks, quads_log2, tm * kTileM, tn * BN + rank * width, threadIdx.x, kTmaThreads);
+
+  B200_PROBE(p, 6);
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc<BN>(tmem_base);
+  }
+}
+
+// ---------------------------------------- TMA, operand-swapped kernel for few rows
+// Up to 64 rows (decode-like shapes): computing D^T = B^T * A^T puts the long
+// dimension N on the 128 rows of the MMA and the few rows of A on its N side, so
+// an instruction is 128 x NM x 8 with NM = 16 or 64 instead of 128 x 128 x 8 with
+// most rows zero. What the tensor pipe reads from shared memory per K block drops
+// from 32 KiB to 16 KiB + NM * 128 B, and that, not the arithmetic, is what the
+// K-block time of the 128 x 128 form consists of.
+//   MMA operand A = B^T: M-major, i.e. exactly the B slab of the other kernels
+//     (32-column boxes of 32 K rows, 128-byte swizzle in 32-byte granules).
+//   MMA operand B = A^T: K-major, i.e. the A slab of the other kernels with NM
+//     rows (8-row groups 1024 bytes apart, 128-byte swizzle).
+// The accumulator holds D^T: TMEM lane = column n of the tile, TMEM column = row
+// m, so an epilogue thread owns one output column and a warp writes 32 adjacent
+// floats of a row of D. A cluster of 1/2/4/8 CTAs splits K as in the split-K
+// kernel; CTA r finishes the 128 / cluster columns it owns.
+constexpr int kSwapTileN = 128;   // columns of D per CTA (the M side of the MMA)
+
+// One 32-wide K sub-block: the B slab and NM rows of A.
+template <int NM>
+__host__ __device__ constexpr uint32_t swap_sub_bytes() {
+  return (kSwapTileN / 32) * kBBoxBytes + NM * kStageK * 4;
+}
+
+// A pipeline stage holds KSUB sub-blocks: the small MMAs of this kernel (54 cycles each in
+// isolation) are cheap next to the 380 cycles of a stage's barrier wait and commit.
+template <int NM, int KSUB>
+__host__ __device__ constexpr uint32_t swap_stage_bytes() {
+  return KSUB * swap_sub_bytes<NM>();
+}
+
+template <int NM, int STAGES, int KSUB>
+__host__ __device__ constexpr size_t swap_smem_bytes() {
+  return static_cast<size_t>(STAGES) * swap_stage_bytes<NM, KSUB>() + 1024 + 256;
+}
+
+template <int NM, int STAGES, int KSUB, int kAct>
+__global__ void __launch_bounds__(kTmaThreads, 1) umma_swap_kernel(const __grid_constant__ UmmaParams p) {
+  static_assert(NM % 16 == 0 && NM >= 16 && NM <= 64, "rows of A per tile");
+  static_assert(static_cast<size_t>(STAGES) * swap_stage_bytes<NM, KSUB>() >= sizeof(float) * NM * kSwapTileN,
+                "the idle operand ring must hold one exchanged tile");
+  constexpr uint32_t kTmemCols = NM < 32 ? 32 : NM;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int ranks = static_cast<int>(cluster.num_blocks());
+  const int rank = static_cast<int>(cluster.block_rank());
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(STAGES) * swap_stage_bytes<NM, KSUB>());
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_full + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  B200_PROBE(p, 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&acc_full[0], 1);
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc<kTmemCols>(tmem_ptr);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr;
+  B200_PROBE(p, 1);
+
+  // Tiles: blocks of NM rows of A by 128 columns of B; row blocks innermost.
+  const int tiles_m = (p.m + NM - 1) / NM;
+  const int tile = static_cast<int>(blockIdx.x) / ranks;
+  const int m0 = (tile % tiles_m) * NM, n0 = (tile / tiles_m) * kSwapTileN;
+  const int k_blocks = (p.k + KSUB * kStageK - 1) / (KSUB * kStageK);   // stages; K past the end reads as zeros
+  const int per_rank = (k_blocks + ranks - 1) / ranks;
+  const int kb_begin = min(k_blocks, rank * per_rank);
+  const int kb_end = min(k_blocks, kb_begin + per_rank);
+  const bool has_work = kb_begin < kb_end;   // an empty K range contributes zeros
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&p.map_a);
+      prefetch_tensormap(p.b_strips == kSwapTileN / 32 ? &p.map_b_strips : &p.map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&empty[stage], phase ^ 1u, kSiteUmmaEmpty)) break;
+        mbar_expect_tx(&full[stage], swap_stage_bytes<NM, KSUB>());
+#pragma unroll
+        for (int sub = 0; sub < KSUB; ++sub) {
+          const int k0 = (kb * KSUB + sub) * kStageK;
+          uint8_t* b_dst = stages + static_cast<size_t>(stage) * swap_stage_bytes<NM, KSUB>() + sub * swap_sub_bytes<NM>();
+          uint8_t* a_dst = b_dst + (kSwapTileN / 32) * kBBoxBytes;                // B slab first, then NM rows of A
+          tma_load_2d(a_dst, &p.map_a, &full[stage], k0, m0);
+          if (p.b_strips == kSwapTileN / 32) {
+            tma_load_3d(b_dst, &p.map_b_strips, &full[stage], 0, k0, n0 / 32);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kSwapTileN / 32; ++j) {
+              tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &full[stage], n0 + j * 32, k0);
+            }
+          }
+        }
+        if (++stage == STAGES) stage = 0, phase ^= 1u;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && has_work) {
+      // M = 128 (columns of D), N = NM (rows of D); operand A M-major, operand B K-major.
+      constexpr uint32_t idesc = umma_idesc_tf32(kSwapTileN, NM, /*a_mn_major=*/true, /*b_mn_major=*/false);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool fed = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&full[stage], phase, kSiteUmmaFull)) { fed = false; break; }
+        tcgen05_fence_after_sync();
+#pragma unroll
+        for (int sub = 0; sub < KSUB; ++sub) {
+          const uint32_t b_addr =
+              smem_u32(stages + static_cast<size_t>(stage) * swap_stage_bytes<NM, KSUB>() + sub * swap_sub_bytes<NM>());
+          const uint32_t a_addr = b_addr + (kSwapTileN / 32) * kBBoxBytes;
+#pragma unroll
+          for (int j = 0; j < kStageK / kInstK; ++j) {
+            const uint64_t desc_mma_a = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
+            const uint64_t desc_mma_b = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
+            umma_tf32(tmem_base, desc_mma_a, desc_mma_b, idesc, (kb > kb_begin || sub > 0 || j > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(&empty[stage]);
+        if (++stage == STAGES) stage = 0, phase ^= 1u;
+      }
+      if (fed) umma_commit(&acc_full[0]);
+    }
+  } else if (has_work) {
+    ok = mbar_wait(&acc_full[0], 0, kSiteUmmaAccFull);
+    tcgen05_fence_after_sync();
+  }
+
+  B200_PROBE(p, 2);
+  // 1. Every CTA of the cluster is past its main loop: the rings are idle.
+  tcgen05_fence_before_sync();
+  cluster.sync();
+  tcgen05_fence_after_sync();
+
+  B200_PROBE(p, 3);
+  // Exchange buffer of a CTA: floats [source rank][row m][column of its share]; a thread owns one
+  // column n of the tile, so all its values go to the one CTA that owns that column.
+  float* exchange = reinterpret_cast<float*>(stages);
+  const int width = kSwapTileN / ranks;                 // columns per CTA
+  if (warp >= 2) {
+    const int quarter = warp & 3;
+    const int n_local = quarter * 32 + lane;
+    float* remote = cluster.map_shared_rank(exchange, n_local / width) +
+                    static_cast<size_t>(rank) * NM * width + (n_local % width);
+#pragma unroll
+    for (int chunk = 0; chunk < kTmemCols / 32; ++chunk) {
+      uint32_t raw[32];
+      if (has_work && ok) {
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 32, raw);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) raw[e] = 0u;
+      }
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const int m = chunk * 32 + e;
+        if (m < NM) remote[m * width] = __uint_as_float(raw[e]);   // columns past NM were never accumulated
+      }
+    }
+  }
+  B200_PROBE(p, 4);
+  tcgen05_fence_before_sync();
+  cluster.sync();
+  B200_PROBE(p, 5);
+
+  // 3. Add the partials of this CTA's columns in rank order, apply the epilogue, lanes along a row of D.
+  {
+    const EpilogueArgs ep = epilogue_args(p);
+    const int col_base = n0 + rank * width;
+    for (int item = threadIdx.x; item < NM * width; item += kTmaThreads) {
+      const int m = item / width, nl = item % width;
+      const int row = m0 + m, col = col_base + nl;
+      if (row >= ep.m || col >= ep.n) continue;
+      float sum = 0.f;
+      for (int src = 0; src < ranks; ++src) sum += exchange[(src * NM + m) * width + nl];
+      float v = ep.alpha * sum;
+      if (ep.beta != 0.f) v = fmaf(ep.beta, __ldg(ep.c + static_cast<int64_t>(row) * ep.ldc + col), v);
+      if (ep.bias != nullptr) v += __ldg(ep.bias + col);
+      v = activate<kAct>(v);
+      const int64_t offset = static_cast<int64_t>(row) * ep.ldd + col;
+      ep.d[offset] = v;
+      store_peers(ep, offset, v);
+    }
+  }
+
+  B200_PROBE(p, 6);
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc<kTmemCols>(tmem_base);
+  }
+}
+// ------------------------------------------------------------------ launchers
+
+// Most clusters of `cluster_size` CTAs of the split-K kernel that the device keeps resident at once
+// (cached per device; clusters of eight fit far fewer CTAs than the SM count suggests).
+int splitk_max_clusters(int cluster_size) {
+  static std::atomic<int> cache[64][4];   // [device][log2 cluster size], 0 = not asked yet
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  const int slot = cluster_size == 1 ? 0 : cluster_size == 2 ? 1 : cluster_size == 4 ? 2 : 3;
+  const int cached = cache[device][slot].load(std::memory_order_relaxed);
+  if (cached != 0) return cached;
+  auto kernel = umma_splitk_kernel<3, B200_EPILOGUE_LINEAR>;   // the activation does not change the footprint
+  constexpr size_t smem = smem_bytes<kSplitN, 3>() - kPeerStageBytes;   // no staging: two CTAs fit an SM
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(cluster_size) * 64);
+  cfg.blockDim = dim3(kTmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(cluster_size);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) clusters = 0;
+  const int result = clusters > 0 ? clusters : -1;   // concurrent first calls compute the same value
+  cache[device][slot].store(result, std::memory_order_relaxed);
+  return result;
+}
+
+// Cluster size of the split-K kernel, from a cost model fitted to phase timings of the kernel on a
+// B200 (microseconds): a K block costs 0.34 with one CTA per SM and 0.53 per CTA with two (the
+// four 128 x 128 x 8 MMAs of a block take that long however few bytes the block loads: with 16 of
+// 128 rows present it is still 0.29, and a six-stage ring instead of three changes nothing, so it
+// is the SM's MMA rate at this tile shape, not memory, that a second CTA has to share); barriers,
+// exchange and the finishing pass cost 4.5 / 6.0 / 7.2 for clusters of 2 / 4 / 8 (half as much again when
+// two CTAs share an SM). A candidate must keep
+// two K blocks per range and fit the device in one wave (two CTAs per SM: twice the cluster count the
+// occupancy query reports for one). `estimate_us` receives the modelled time of the choice.
+int splitk_ranks(const b200_gemm_problem& q, int sms, float* estimate_us = nullptr) {
+  const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
+  const int k_blocks = (q.k + kStageK - 1) / kStageK;
+  constexpr float kExchangeUs[4] = {4.7f, 4.5f, 6.0f, 7.2f};
+  int best = 1;
+  float best_us = 1e30f;
+  for (int log2r = 0; log2r < 4; ++log2r) {
+    const int ranks = 1 << log2r;
+    const int64_t ctas = tiles * ranks;
+    if (ctas > 2LL * sms) break;
+    if (ranks > 1 && (k_blocks / ranks < 2 || tiles > 2LL * splitk_max_clusters(ranks))) break;
+    const bool shared_sm = ctas > sms;   // two CTAs per SM also share its exchange and store bandwidth
+    const float us = static_cast<float>((k_blocks + ranks - 1) / ranks) * (shared_sm ? 0.53f : 0.34f) +
+                     kExchangeUs[log2r] * (shared_sm ? 1.5f : 1.0f);
+    if (us < best_us) best_us = us, best = ranks;
+  }
+  if (estimate_us != nullptr) *estimate_us = best_us;
+  return best;
+}
+
+template <int STAGES, int kAct>
+int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  auto kernel = umma_splitk_kernel<STAGES, kAct>;
+  constexpr size_t smem = smem_bytes<kSplitN, STAGES>() - kPeerStageBytes;   // its finishing pass needs no staging
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+    return B200_ERR_LAUNCH_FAILED;
+  }
+  UmmaParams p;
+  fill_common(&p, q, peers);
+  if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
+      !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
+    return B200_ERR_MISALIGNED_OPERAND;
+  }
+  p.b_strips = (q.n % 32 == 0 && make_tensor_map_strips(&p.map_b_strips, q.b, q.k, q.n, q.ldb, kStageK, kSplitN / 32,
+                                                        Swizzle::k128BAtom32B))
+                   ? kSplitN / 32
+                   : 0;
+  const int sms = sm_count();
+  if (sms <= 0) return B200_ERR_INTERNAL;
+  const int ranks = splitk_ranks(q, sms);
+  const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
+  if (tiles * ranks > 0x7fffffffLL) return B200_ERR_INVALID_PROBLEM;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * ranks));
+  cfg.blockDim = dim3(kTmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(ranks);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  return launch_status();
+}
+
+// Cluster size of the operand-swapped kernel: as many K ranges as keep every cluster resident at
+// once (one CTA per SM) with at least two pipeline stages each.
+int swap_ranks(int64_t tiles, int k_stages, int sms) {
+  int ranks = 1;
+  while (ranks < 8 && tiles * (ranks * 2) <= sms && k_stages / (ranks * 2) >= 2 &&
+         tiles <= splitk_max_clusters(ranks * 2)) {
+    ranks *= 2;
+  }
+  return ranks;
+}
+
+template <int NM, int kAct>
+int run_swap(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  // About 144 KiB of ring either way: 2 stages x 4 sub-blocks of 18 KiB, or 3 x 2 of 24 KiB.
+  constexpr int KSUB = NM <= 16 ? 4 : 2, STAGES = NM <= 16 ? 2 : 3;
+  auto kernel = umma_swap_kernel<NM, STAGES, KSUB, kAct>;
+  constexpr size_t smem = swap_smem_bytes<NM, STAGES, KSUB>();
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+    return B200_ERR_LAUNCH_FAILED;
+  }
+  UmmaParams p;
+  fill_common(&p, q, peers);
+  // A: boxes of NM rows x 32 floats of K; B as in the other kernels.
+  if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, NM, kStageK, Swizzle::k128B) ||
+      !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
+    return B200_ERR_MISALIGNED_OPERAND;
+  }
+  p.b_strips = (q.n % 32 == 0 && make_tensor_map_strips(&p.map_b_strips, q.b, q.k, q.n, q.ldb, kStageK, kSwapTileN / 32,
+                                                        Swizzle::k128BAtom32B))
+                   ? kSwapTileN / 32
+                   : 0;
+  const int sms = sm_count();
+  if (sms <= 0) return B200_ERR_INTERNAL;
+  const int64_t tiles = static_cast<int64_t>((q.m + NM - 1) / NM) * ((q.n + kSwapTileN - 1) / kSwapTileN);
+  const int ranks = swap_ranks(tiles, (q.k + KSUB * kStageK - 1) / (KSUB * kStageK), sms);
+  if (tiles * ranks > 0x7fffffffLL) return B200_ERR_INVALID_PROBLEM;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * ranks));
+  cfg.blockDim = dim3(kTmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(ranks);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  return launch_status();
+}
+
+template <int kAct>
+int launch_swap(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  return q.m <= 16 ? run_swap<16, kAct>(q, peers, stream) : run_swap<64, kAct>(q, peers, stream);
+}
+}  // namespace
+
+int launch_tf32_splitk(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  switch (act) {
+    case B200_EPILOGUE_LINEAR: return launch_splitk<3, B200_EPILOGUE_LINEAR>(q, peers, stream);
+    case B200_EPILOGUE_RELU: return launch_splitk<3, B200_EPILOGUE_RELU>(q, peers, stream);
+    case B200_EPILOGUE_GELU: return launch_splitk<3, B200_EPILOGUE_GELU>(q, peers, stream);
+    default: return B200_ERR_INVALID_ARGUMENT;
+  }
+}
+
+int launch_tf32_swap(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  switch (act) {
+    case B200_EPILOGUE_LINEAR: return launch_swap<B200_EPILOGUE_LINEAR>(q, peers, stream);
+    case B200_EPILOGUE_RELU: return launch_swap<B200_EPILOGUE_RELU>(q, peers, stream);
+    case B200_EPILOGUE_GELU: return launch_swap<B200_EPILOGUE_GELU>(q, peers, stream);
+    default: return B200_ERR_INVALID_ARGUMENT;
+  }
+}
+
+int tf32_splitk_plan(const b200_gemm_problem& q, int sms, float* estimate_us) { return splitk_ranks(q, sms, estimate_us); }
+
+}  // namespace b200

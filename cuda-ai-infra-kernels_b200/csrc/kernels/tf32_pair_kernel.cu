@@ -1,0 +1,272 @@
+// TF32 tensor-core GEMM, CTA-pair kernel (tcgen05 cta_group::2, 256 x 256 tiles). Layouts, the
+// parameter block and the epilogues are in tf32_umma.cuh.
+#include "tf32_umma.cuh"
+
+namespace b200 {
+
+cudaError_t tf32_pair_status_read_clear(uint32_t* word) { return status_word_read_clear(word); }
+
+namespace {
+
+// ---------------------------------------------------- TMA, CTA-pair kernel
+// Two CTAs of a cluster share one 256 x 256 output tile through
+// tcgen05.mma.cta_group::2: CTA r of the pair holds rows [128 r, 128 r + 128) of
+// A, columns [128 r, 128 r + 128) of B and the accumulator rows [128 r, +128)
+// (all 256 columns). Per CTA a stage is 16 KiB of A + 16 KiB of B for a
+// 256 x 256 x 32 product, a third fewer operand bytes through L2 per flop than
+// the single-CTA 128 x 256 tile. The even CTA issues the MMAs for both.
+// Signals that both CTAs need (stage free, accumulator ready) are committed
+// twice, once per CTA; no multicast form is used anywhere.
+constexpr int kPairN = 256;
+constexpr uint32_t kPairSubBytes = kASlabBytes + (kPairN / 2 / 32) * kBBoxBytes;  // 32 floats of K: 32 KiB per CTA
+
+// A pipeline stage holds KSUB such 32-wide K sub-blocks behind one pair of barriers: the MMA
+// thread's barrier wait, fence and commits are paid per stage, and they cost about as much as two
+// of the eight instructions of a two-sub-block stage.
+template <int STAGES, int KSUB>
+__host__ __device__ constexpr size_t pair_smem_bytes() {
+  return static_cast<size_t>(STAGES) * KSUB * kPairSubBytes + 1024 + 256 + kPeerStageBytes;
+}
+
+// Work item of the CTA-pair kernel: a whole 256 x 256 tile, or (for the last, partial round of
+// tiles) one 256 x 128 half of one, so that twice as many pairs share the tail.
+struct PairItem {
+  int tile;
+  int half;   // -1: whole tile; 0 / 1: left / right 128 columns
+};
+__device__ __forceinline__ PairItem pair_item(int item, int full_tiles) {
+  if (item < full_tiles) return PairItem{item, -1};
+  const int h = item - full_tiles;
+  return PairItem{full_tiles + (h >> 1), h & 1};
+}
+
+template <int STAGES, int KSUB, int kAct>
+__global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_constant__ UmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // Same carve-up in both CTAs: the MMA addresses the peer's shared memory by
+  // the same offsets as its own.
+  uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr uint32_t kPairStageBytes = KSUB * kPairSubBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(STAGES) * kPairStageBytes);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  float* peer_stage = reinterpret_cast<float*>(tmem_ptr + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();  // 0: issues the MMAs, 1: peer
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);   // used in CTA 0 only: one expect_tx arrival, bytes of both CTAs
+      mbar_init(&empty[s], 1);  // one tcgen05.commit per use, sent to each CTA
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);  // used in CTA 0 only: four epilogue warps of each CTA
+    }
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair<512>(tmem_ptr);
+    tmem_relinquish_pair();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before any remote arrival
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  const int tiles_m = (p.m + 2 * kTileM - 1) / (2 * kTileM);
+  const int tiles_n = (p.n + kPairN - 1) / kPairN;
+  const int tiles = tiles_m * tiles_n;
+  const int items = p.pair_full_tiles + 2 * (tiles - p.pair_full_tiles);   // whole tiles, then halves
+  const int k_blocks = (p.k + KSUB * kStageK - 1) / (KSUB * kStageK);   // stages per tile; K past the end reads as zeros
+  const int first_tile = blockIdx.x >> 1, tile_stride = gridDim.x >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&p.map_a);
+      prefetch_tensormap(&p.map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = first_tile; item < items && ok; item += tile_stride) {
+        const PairItem it = pair_item(item, p.pair_full_tiles);
+        int tm, tn;
+        tile_coords(it.tile, tiles_m, tiles_n, &tm, &tn);
+        const int row0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
+        // This CTA's share of the B columns: 128 of a whole tile, 64 of a half tile.
+        const int cta_cols = it.half < 0 ? kPairN / 2 : kPairN / 4;
+        const int col0 = tn * kPairN + (it.half < 0 ? 0 : it.half * (kPairN / 2)) + static_cast<int>(rank) * cta_cols;
+        const uint32_t sub_tx = kASlabBytes + (cta_cols / 32) * kBBoxBytes;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, kSiteUmmaEmpty)) { ok = false; break; }
+          // Completion bytes of both CTAs are counted on CTA 0's barrier.
+          const uint32_t full_addr = map_to_cta(smem_u32(&full[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * KSUB * sub_tx);
+#pragma unroll
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const int k0 = (kb * KSUB + sub) * kStageK;
+            uint8_t* a_dst = stages + static_cast<size_t>(stage) * kPairStageBytes + sub * kPairSubBytes;
+            uint8_t* b_dst = a_dst + kASlabBytes;
+            tma_load_2d_pair(a_dst, &p.map_a, full_addr, k0, row0);
+            if (it.half < 0 && p.b_strips == kPairN / 2 / 32) {
+              tma_load_3d_pair(b_dst, &p.map_b_strips, full_addr, 0, k0, col0 / 32);
+            } else {
+              for (int j = 0; j < cta_cols / 32; ++j) {
+                tma_load_2d_pair(b_dst + j * kBBoxBytes, &p.map_b, full_addr, col0 + j * 32, k0);
+              }
+            }
+          }
+          if (++stage == STAGES) stage = 0, phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc_whole = umma_idesc_tf32(2 * kTileM, kPairN, /*a_mn_major=*/false, /*b_mn_major=*/true);
+      constexpr uint32_t idesc_half = umma_idesc_tf32(2 * kTileM, kPairN / 2, /*a_mn_major=*/false, /*b_mn_major=*/true);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int item = first_tile; item < items && ok; item += tile_stride, ++local) {
+        const uint32_t idesc = item < p.pair_full_tiles ? idesc_whole : idesc_half;
+        const int buf = local & 1;
+        const uint32_t use_parity = (local >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[buf], use_parity ^ 1u, kSiteUmmaAccEmpty)) { ok = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + buf * kPairN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
+          tcgen05_fence_after_sync();
+#pragma unroll
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const uint32_t a_addr = smem_u32(stages + static_cast<size_t>(stage) * kPairStageBytes + sub * kPairSubBytes);
+            const uint32_t b_addr = a_addr + kASlabBytes;
+#pragma unroll
+            for (int j = 0; j < kStageK / kInstK; ++j) {
+              const uint64_t desc_a = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
+              const uint64_t desc_b = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
+              umma_tf32_pair(tmem_acc, desc_a, desc_b, idesc, (kb > 0 || sub > 0 || j > 0) ? 1u : 0u);
+            }
+          }
+          // The stage is reusable in both CTAs once these MMAs have read it.
+          umma_commit_pair(smem_u32(&empty[stage]));
+          umma_commit_pair(map_to_cta(smem_u32(&empty[stage]), 1));
+          if (++stage == STAGES) stage = 0, phase ^= 1u;
+        }
+        if (ok) {
+          umma_commit_pair(smem_u32(&acc_full[buf]));
+          umma_commit_pair(map_to_cta(smem_u32(&acc_full[buf]), 1));
+        }
+      }
+    }
+  } else {
+    const EpilogueArgs ep = epilogue_args(p);
+    const int quarter = warp & 3;
+    bool ok = true;
+    int local = 0;
+    for (int item = first_tile; item < items && ok; item += tile_stride, ++local) {
+      const PairItem it = pair_item(item, p.pair_full_tiles);
+      const int buf = local & 1;
+      const uint32_t use_parity = (local >> 1) & 1u;
+      int tm, tn;
+      tile_coords(it.tile, tiles_m, tiles_n, &tm, &tn);
+      const int n0 = tn * kPairN + (it.half < 0 ? 0 : it.half * (kPairN / 2));
+      const int m0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
+      const bool pipelined = ep.vector_io && ep.peers.count == 0;
+      SourceChunk first;
+      if (pipelined) fetch_source(ep, first, m0 + quarter * 32 + lane, n0);   // before the wait
+      if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
+      tcgen05_fence_after_sync();
+      float* stage_area = peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float));
+      if (it.half < 0) {
+        if (pipelined) {
+          epilogue_tile_pipelined<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, first);
+        } else {
+          epilogue_tile<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, stage_area);
+        }
+      } else if (pipelined) {
+        epilogue_tile_pipelined<kPairN / 2, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, first);
+      } else {
+        epilogue_tile<kPairN / 2, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, stage_area);
+      }
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      // The MMA issuer (CTA 0) waits for the epilogues of both CTAs.
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+    }
+  }
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer may still be signalling this CTA's barriers or reading its operands
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc_pair<512>(tmem_base);
+  }
+}
+// ------------------------------------------------------------------- launcher
+
+template <int STAGES, int kAct>
+int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  constexpr int KSUB = 2;                       // 64 floats of K per stage
+  static_assert(STAGES % KSUB == 0, "the registry states the ring depth in 32-wide K blocks");
+  auto kernel = umma_pair_kernel<STAGES / KSUB, KSUB, kAct>;
+  constexpr size_t smem = pair_smem_bytes<STAGES / KSUB, KSUB>();
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+    return B200_ERR_LAUNCH_FAILED;
+  }
+  const size_t launch_smem = smem - (peers.count > 0 ? 0 : kPeerStageBytes);
+  UmmaParams p;
+  fill_common(&p, q, peers);
+  if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
+      !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
+    return B200_ERR_MISALIGNED_OPERAND;
+  }
+  p.b_strips = (q.n % 32 == 0 && make_tensor_map_strips(&p.map_b_strips, q.b, q.k, q.n, q.ldb, kStageK,
+                                                        kPairN / 2 / 32, Swizzle::k128BAtom32B))
+                   ? kPairN / 2 / 32
+                   : 0;
+  const int sms = sm_count();
+  if (sms < 2) return B200_ERR_INTERNAL;
+  const int64_t tiles = static_cast<int64_t>((q.m + 2 * kTileM - 1) / (2 * kTileM)) * ((q.n + kPairN - 1) / kPairN);
+  const int64_t all_pairs = sms / 2;
+  // A last round that occupies at most half the pairs is run as 256 x 128 half tiles on twice as
+  // many pairs: a half tile streams 24 instead of 32 KiB per K block and CTA and takes about 0.6 of
+  // a whole tile's time (4096^3: 34 left-over tiles become 68 halves on 74 pairs). A problem with
+  // no more tiles than half the pairs is such a last round from the start.
+  const int64_t remainder = tiles % all_pairs;
+  p.pair_full_tiles = static_cast<int>((remainder != 0 && 2 * remainder <= all_pairs) ? tiles - remainder : tiles);
+  const int64_t items = p.pair_full_tiles + 2 * (tiles - p.pair_full_tiles);
+  const int64_t pairs = items < all_pairs ? items : all_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  cfg.blockDim = dim3(kTmaThreads);
+  cfg.dynamicSmemBytes = launch_smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  return launch_status();
+}
+}  // namespace
+
+int launch_tf32_pair(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  switch (act) {
+    case B200_EPILOGUE_LINEAR: return launch_pair<6, B200_EPILOGUE_LINEAR>(q, peers, stream);
+    case B200_EPILOGUE_RELU: return launch_pair<6, B200_EPILOGUE_RELU>(q, peers, stream);
+    case B200_EPILOGUE_GELU: return launch_pair<6, B200_EPILOGUE_GELU>(q, peers, stream);
+    default: return B200_ERR_INVALID_ARGUMENT;
+  }
+}
+
+}  // namespace b200

@@ -1,0 +1,486 @@
+// Shared device code and launch helpers of the TF32 tensor-core GEMM kernels (tcgen05, sm_100a):
+// the operand layouts in shared memory, the kernel parameter block, the epilogues, and the
+// producer-independent roles (MMA issuer, epilogue warps) of the single-CTA persistent kernels.
+// Included by the kernel translation units only; everything here has internal linkage.
+//
+// TF32 tensor-core GEMM with a fused epilogue, written for sm_100a:
+//   D = epilogue(alpha * A * B + beta * C),  A [M,K], B [K,N], C/D [M,N],
+// all row-major FP32; products in TF32 on tcgen05.mma, accumulation in FP32 in
+// tensor memory (TMEM); epilogue (scale, source add, bias, optional ReLU or
+// GELU) applied on the TMEM -> register -> global path, so the accumulator
+// never touches HBM.
+//
+// It stands in for the CUTLASS device::Gemm instantiations of the reference
+// (csrc/adaptive_gemm/kernel_sm80.h:4-171, launched through
+// csrc/adaptive_gemm/kernel_launcher.h:7-29).
+//
+// Operand staging. One pipeline stage holds a 128 x 32 slab of A and a
+// 32 x BN slab of B in swizzled layouts that both TMA and the MMA unit
+// understand:
+//   A is K-major for the MMA (K contiguous in memory). The slab is one TMA box
+//     {32 (k), 128 (m)}: 128 rows of 128 bytes, 128-byte swizzle in 16-byte
+//     granules (period 8 rows), 8-row groups 1024 bytes apart.
+//   B is N-major for the MMA (N contiguous in memory). A 32-bit N-major operand
+//     must use the 128-byte swizzle with 32-byte granules (period 4 rows). The
+//     slab is BN/32 TMA boxes {32 (n), 32 (k)}: each 32 rows (k) of 128 bytes
+//     (32 n), boxes 4096 bytes apart; inside a box, 4-row k groups are 512
+//     bytes apart.
+// One tcgen05.mma consumes 8 floats of K: the A descriptor advances 32 bytes
+// inside the swizzled row, the B descriptor advances two 4-row groups.
+//
+// Two loaders feed that layout:
+//   TMA     - needs 16-byte aligned pointers and leading dimensions that are
+//             multiples of four floats; persistent, warp-specialised kernels
+//             (producer / MMA issuer / epilogue warps), double-buffered TMEM
+//             accumulator so the epilogue of one tile overlaps the main loop of
+//             the next. Two forms: one CTA per 128 x BN tile, and CTA pairs
+//             (cta_group::2) that share a 256 x 256 tile and halve the B bytes
+//             each CTA pulls through L2. A third form gives one 128 x 128 tile
+//             to a cluster whose CTAs split K and exchange their partial tiles
+//             through distributed shared memory (few tiles, long K).
+//   generic - any pointers, any sizes; eight loader warps of a persistent CTA
+//             write predicated scalar loads into the same swizzled layout.
+// Nothing here uses cluster multicast. Every kernel can also store its finished
+// output to peer GPUs' copies of D (PeerOutputs: a GEMM fused with the
+// all-gather of its result); peer memory is only ever stored to.
+#pragma once
+
+#include <cooperative_groups.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+
+#include "host_common.h"
+#include "ptx_sm100.cuh"
+#include "tf32_gemm.h"
+
+namespace b200 {
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kStageK = 32;                       // floats of K per stage (one 128-byte swizzle row)
+constexpr int kInstK = 8;                         // K of one tcgen05.mma kind::tf32
+constexpr uint32_t kASlabBytes = kTileM * kStageK * 4;  // 16 KiB
+constexpr uint32_t kBBoxBytes = 32 * kStageK * 4;       // 4 KiB: 32 (n) x 32 (k)
+
+// Build-time instrumentation (-DB200_PROBE_TIMING, never in the shipped library):
+// one thread per CTA stamps the global timer at the phase boundaries of a kernel.
+#ifdef B200_PROBE_TIMING
+#define B200_PROBE(params, slot)                                                              \
+  do {                                                                                        \
+    if ((params).probe != nullptr && threadIdx.x == 64) {                                     \
+      uint64_t t_;                                                                            \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
+      (params).probe[static_cast<size_t>(blockIdx.x) * 8 + (slot)] = t_;                      \
+      (params).probe[2048 + static_cast<size_t>(blockIdx.x) * 8 + (slot)] = clock64();        \
+    }                                                                                         \
+  } while (0)
+#else
+#define B200_PROBE(params, slot) do { } while (0)
+#endif
+
+struct UmmaParams {
+  CUtensorMap map_a;   // [M][K] boxes {32, 128}, 128-byte swizzle   (TMA loader only)
+  CUtensorMap map_b;   // [K][N] boxes {32, 32},  128-byte swizzle, 32-byte granules
+  CUtensorMap map_b_strips;  // [N/32][K][32] boxes {32, 32, strips}: a whole B slab in one copy (N % 32 == 0)
+  int b_strips;        // strips per map_b_strips box, 0 when that map is not usable
+  const float* a;      // generic loader only
+  const float* b;
+  const float* c;      // source, may be null when beta == 0
+  const float* bias;   // [N] added to every row before the activation, or null
+  float* d;
+  int64_t lda, ldb, ldc, ldd;
+  int m, n, k;
+  float alpha, beta;
+  int vector_io;       // C/D rows allow 128-bit accesses
+  PeerOutputs peers;   // further destinations of every finished element (fused all-gather), usually none
+  int pair_full_tiles;  // CTA-pair kernel: work items [0, full) are whole 256 x 256 tiles, the rest
+                        // are the two 256 x 128 halves of the tiles after them (see launch_pair)
+#ifdef B200_PROBE_TIMING
+  uint64_t* probe;     // [grid][8] time stamps, or null
+#endif
+};
+
+// The epilogue's view of the problem, copied into registers once per thread. The kernel parameter
+// block is memory as far as the compiler can tell, memory that the epilogue's own stores might
+// alias: reading it inside the store loops would reload every field after every store, a chain of
+// dependent loads that the few epilogue warps cannot hide.
+struct EpilogueArgs {
+  const float* c;      // null when beta == 0
+  const float* bias;   // or null
+  float* d;
+  int64_t ldc, ldd;
+  int m, n;
+  float alpha, beta;
+  int vector_io;
+  PeerOutputs peers;
+};
+
+__device__ __forceinline__ EpilogueArgs epilogue_args(const UmmaParams& p) {
+  return EpilogueArgs{p.c, p.bias, p.d, p.ldc, p.ldd, p.m, p.n, p.alpha, p.beta, p.vector_io, p.peers};
+}
+
+// The same element(s) of every peer's copy of the output (fused all-gather).
+// (Unrolled with constant indices: a run-time index would put the whole argument block in local memory.)
+__device__ __forceinline__ void store_peers(const EpilogueArgs& p, int64_t offset, float4 v) {
+#pragma unroll
+  for (int i = 0; i < B200_MAX_PEERS; ++i) {
+    if (i < p.peers.count) *reinterpret_cast<float4*>(p.peers.ptr[i] + offset) = v;
+  }
+}
+__device__ __forceinline__ void store_peers(const EpilogueArgs& p, int64_t offset, float v) {
+#pragma unroll
+  for (int i = 0; i < B200_MAX_PEERS; ++i) {
+    if (i < p.peers.count) p.peers.ptr[i][offset] = v;
+  }
+}
+
+template <int BN>
+__host__ __device__ constexpr uint32_t stage_bytes() {
+  return kASlabBytes + (BN / 32) * kBBoxBytes;
+}
+
+// Staging of the fused all-gather: an epilogue warp turns its 32 x 32 chunk (one row per lane in
+// registers) by way of shared memory so that peer copies are written in 128-byte row segments, four
+// rows per instruction, instead of 32 scattered 16-byte pieces (NVLink moves those poorly). The
+// pitch of 36 floats keeps both the row-per-lane writes and the row-wise reads free of conflicts.
+constexpr int kPeerStagePitch = 36;
+constexpr size_t kPeerStageBytesPerWarp = 32 * kPeerStagePitch * sizeof(float);
+constexpr size_t kPeerStageBytes = 4 * kPeerStageBytesPerWarp;   // four epilogue warps
+
+template <int BN, int STAGES>
+__host__ __device__ constexpr size_t smem_bytes() {
+  return static_cast<size_t>(STAGES) * stage_bytes<BN>() + 1024 /*alignment slack*/ + 256 /*barriers + tmem ptr*/ +
+         kPeerStageBytes;
+}
+
+template <int BN>
+__host__ __device__ constexpr uint32_t tmem_columns() {
+  return 2 * BN < 32 ? 32 : 2 * BN;  // two accumulator buffers; BN in {64,128,256} keeps this a power of two
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int* tm, int* tn) {
+  constexpr int kBand = 8;
+  const int per_band = kBand * tiles_n;
+  const int band = tile / per_band;
+  const int first_m = band * kBand;
+  const int band_rows = min(kBand, tiles_m - first_m);
+  const int in_band = tile - band * per_band;
+  *tm = first_m + in_band % band_rows;
+  *tn = in_band / band_rows;
+}
+
+// Issues the four MMAs of one stage. `accumulate_first` is 0 only for the very
+// first MMA of an output tile.
+template <int BN>
+__device__ __forceinline__ void issue_stage_mmas(uint32_t tmem_acc, uint32_t a_addr, uint32_t b_addr,
+                                                 uint32_t accumulate_first) {
+  constexpr uint32_t idesc = umma_idesc_tf32(kTileM, BN, /*a_mn_major=*/false, /*b_mn_major=*/true);
+#pragma unroll
+  for (int j = 0; j < kStageK / kInstK; ++j) {
+    // A: K-major, 8-row groups 1024 bytes apart (SBO); LBO is not used by the
+    //    swizzled K-major form and carries the customary 16 bytes.
+    // B: N-major, 32-column groups 4096 bytes apart (LBO), 4-row k groups
+    //    512 bytes apart (SBO); one MMA spans two of them.
+    const uint64_t desc_a = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
+    const uint64_t desc_b = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
+    umma_tf32(tmem_acc, desc_a, desc_b, idesc, j == 0 ? accumulate_first : 1u);
+  }
+}
+
+// Activation applied last: after scaling, source add and bias.
+template <int kAct>
+__device__ __forceinline__ float activate(float v) {
+  if constexpr (kAct == B200_EPILOGUE_RELU) return fmaxf(v, 0.f);
+  if constexpr (kAct == B200_EPILOGUE_GELU) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));  // exact (erf) GELU
+  return v;
+}
+
+// Source values of one 32-column chunk of a thread's row (zeros when there is no source).
+struct SourceChunk {
+  float4 v[8];
+};
+
+// C of chunk `chunk` for the row of this thread. Issued well before the values are needed:
+// for the first chunk of a tile even before the accumulator is ready.
+__device__ __forceinline__ void fetch_source(const EpilogueArgs& p, SourceChunk& out, int row, int col0) {
+  const bool want = p.beta != 0.f && row < p.m;
+  const float* c_row = p.c + static_cast<int64_t>(row) * p.ldc;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const int col = col0 + 4 * g;
+    out.v[g] = (want && col < p.n) ? __ldg(reinterpret_cast<const float4*>(c_row + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+// One chunk of the vectorised epilogue: alpha * acc + beta * C + bias, activation, 128-bit stores.
+template <int kAct>
+__device__ __forceinline__ void finish_chunk(const EpilogueArgs& p, const uint32_t (&raw)[32], const SourceChunk& src, int row,
+                                             int col0) {
+  if (row >= p.m) return;
+  const bool use_bias = p.bias != nullptr;
+  float* d_row = p.d + static_cast<int64_t>(row) * p.ldd;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const int col = col0 + 4 * g;
+    if (col < p.n) {   // n % 4 == 0 on this path: a quad is inside or outside as a whole
+      // Same operation order as every other epilogue path (alpha * acc rounded, then one FMA with
+      // the source), so that all paths give identical bits. Without a source src is zero and beta finite.
+      float4 v = make_float4(fmaf(p.beta, src.v[g].x, p.alpha * __uint_as_float(raw[4 * g + 0])),
+                             fmaf(p.beta, src.v[g].y, p.alpha * __uint_as_float(raw[4 * g + 1])),
+                             fmaf(p.beta, src.v[g].z, p.alpha * __uint_as_float(raw[4 * g + 2])),
+                             fmaf(p.beta, src.v[g].w, p.alpha * __uint_as_float(raw[4 * g + 3])));
+      if (use_bias) {
+        const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+        v.x += bv.x, v.y += bv.y, v.z += bv.z, v.w += bv.w;
+      }
+      *reinterpret_cast<float4*>(d_row + col) =
+          make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
+    }
+  }
+}
+
+// Vectorised epilogue of one 128 x BN tile for one warp, software-pipelined: while a chunk is
+// scaled and stored, the next chunk's accumulators are on their way from TMEM and its source
+// values from memory. `first` holds the source of chunk 0 (fetched by the caller before it waited
+// for the accumulator). Two named register sets alternate so that both stay in registers.
+template <int BN, int kAct>
+__device__ __forceinline__ void epilogue_tile_pipelined(const EpilogueArgs& p, uint32_t tmem_acc, int quarter, int lane,
+                                                        int m0, int n0, const SourceChunk& first) {
+  constexpr int kChunks = BN / 32;
+  static_assert(kChunks % 2 == 0, "chunks are handled in pairs");
+  const int row = m0 + quarter * 32 + lane;
+  const uint32_t tmem_row = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
+  uint32_t raw_even[32], raw_odd[32];
+  SourceChunk src_even = first, src_odd;
+  tmem_ld_32x32(tmem_row, raw_even);
+#pragma unroll
+  for (int chunk = 0; chunk < kChunks; chunk += 2) {
+    if (n0 + chunk * 32 >= p.n) break;   // uniform across the warp
+    tmem_ld_wait();
+    tmem_ld_32x32(tmem_row + (chunk + 1) * 32, raw_odd);
+    fetch_source(p, src_odd, row, n0 + (chunk + 1) * 32);
+    finish_chunk<kAct>(p, raw_even, src_even, row, n0 + chunk * 32);
+    tmem_ld_wait();
+    if (chunk + 2 < kChunks) {
+      tmem_ld_32x32(tmem_row + (chunk + 2) * 32, raw_even);
+      fetch_source(p, src_even, row, n0 + (chunk + 2) * 32);
+    }
+    finish_chunk<kAct>(p, raw_odd, src_odd, row, n0 + (chunk + 1) * 32);
+  }
+  tmem_ld_wait();   // nothing from TMEM is in flight when the accumulator is handed back
+}
+
+// Epilogue of one 128 x BN tile for one warp: TMEM lanes [32 * quarter, +32)
+// are rows m0 + 32 * quarter + lane. Each thread owns one row and walks it in
+// chunks of 32 columns.
+template <int BN, int kAct>
+__device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tmem_acc, int quarter, int lane, int m0,
+                                              int n0, float* stage) {
+  const int row = m0 + quarter * 32 + lane;
+  const bool stage_peers = p.peers.count > 0 && p.vector_io;   // `stage`: this warp's kPeerStageBytesPerWarp
+  const bool row_ok = row < p.m;
+  const bool use_c = p.beta != 0.f;
+  const bool use_bias = p.bias != nullptr;
+  const float* c_row = p.c + static_cast<int64_t>(row) * p.ldc;
+  float* d_row = p.d + static_cast<int64_t>(row) * p.ldd;
+#pragma unroll 1
+  for (int chunk = 0; chunk < BN / 32; ++chunk) {
+    const int col0 = n0 + chunk * 32;
+    if (col0 >= p.n) break;  // uniform across the warp
+    uint32_t raw[32];
+    tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 32, raw);
+    tmem_ld_wait();
+    if (!row_ok && !stage_peers) continue;
+    if (stage_peers) {
+      // Local copy straight from registers; peer copies row-wise from the staged chunk.
+      if (row_ok) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const int col = col0 + 4 * g;
+          if (col < p.n) {
+            float4 v = make_float4(p.alpha * __uint_as_float(raw[4 * g + 0]), p.alpha * __uint_as_float(raw[4 * g + 1]),
+                                   p.alpha * __uint_as_float(raw[4 * g + 2]), p.alpha * __uint_as_float(raw[4 * g + 3]));
+            if (use_c) {
+              const float4 s = __ldg(reinterpret_cast<const float4*>(c_row + col));
+              v.x = fmaf(p.beta, s.x, v.x), v.y = fmaf(p.beta, s.y, v.y);
+              v.z = fmaf(p.beta, s.z, v.z), v.w = fmaf(p.beta, s.w, v.w);
+            }
+            if (use_bias) {
+              const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+              v.x += bv.x, v.y += bv.y, v.z += bv.z, v.w += bv.w;
+            }
+            v = make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
+            *reinterpret_cast<float4*>(d_row + col) = v;
+            *reinterpret_cast<float4*>(stage + lane * kPeerStagePitch + 4 * g) = v;
+          }
+        }
+      }
+      __syncwarp();
+      // Lane l takes column quad l % 8 of rows 4 j + l / 8.
+      const int quad_col = col0 + 4 * (lane & 7);
+      if (quad_col < p.n) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int r = 4 * j + (lane >> 3);
+          const int out_row = m0 + quarter * 32 + r;
+          if (out_row < p.m) {
+            const float4 v = *reinterpret_cast<const float4*>(stage + r * kPeerStagePitch + 4 * (lane & 7));
+            store_peers(p, static_cast<int64_t>(out_row) * p.ldd + quad_col, v);
+          }
+        }
+      }
+      __syncwarp();   // the chunk is reused by the next iteration
+      continue;
+    }
+    if (p.vector_io) {
+      // n % 4 == 0 here, so a 4-wide group is entirely inside or outside.
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const int col = col0 + 4 * g;
+        if (col < p.n) {
+          float4 v = make_float4(p.alpha * __uint_as_float(raw[4 * g + 0]), p.alpha * __uint_as_float(raw[4 * g + 1]),
+                                 p.alpha * __uint_as_float(raw[4 * g + 2]), p.alpha * __uint_as_float(raw[4 * g + 3]));
+          if (use_c) {
+            const float4 s = __ldg(reinterpret_cast<const float4*>(c_row + col));
+            v.x = fmaf(p.beta, s.x, v.x), v.y = fmaf(p.beta, s.y, v.y);
+            v.z = fmaf(p.beta, s.z, v.z), v.w = fmaf(p.beta, s.w, v.w);
+          }
+          if (use_bias) {
+            const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+            v.x += bv.x, v.y += bv.y, v.z += bv.z, v.w += bv.w;
+          }
+          v = make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
+          *reinterpret_cast<float4*>(d_row + col) = v;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const int col = col0 + e;
+        if (col < p.n) {
+          float v = p.alpha * __uint_as_float(raw[e]);
+          if (use_c) v = fmaf(p.beta, __ldg(c_row + col), v);
+          if (use_bias) v += __ldg(p.bias + col);
+          v = activate<kAct>(v);
+          d_row[col] = v;
+          store_peers(p, static_cast<int64_t>(row) * p.ldd + col, v);
+        }
+      }
+    }
+  }
+}
+
+struct SmemCarve {
+  uint8_t* stages;
+  uint64_t* full;
+  uint64_t* empty;
+  uint64_t* acc_full;
+  uint64_t* acc_empty;
+  uint32_t* tmem_ptr;
+  float* peer_stage;   // kPeerStageBytes, 16-byte aligned
+};
+
+template <int BN, int STAGES>
+__device__ __forceinline__ SmemCarve carve(uint8_t* raw) {
+  SmemCarve s;
+  s.stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  s.full = reinterpret_cast<uint64_t*>(s.stages + static_cast<size_t>(STAGES) * stage_bytes<BN>());
+  s.empty = s.full + STAGES;
+  s.acc_full = s.empty + STAGES;
+  s.acc_empty = s.acc_full + 2;
+  s.tmem_ptr = reinterpret_cast<uint32_t*>(s.acc_empty + 2);
+  s.peer_stage = reinterpret_cast<float*>(s.tmem_ptr + 4);
+  return s;
+}
+
+// MMA issuer of the persistent single-CTA kernels (one thread): for every tile
+// of this CTA, waits until the epilogue has drained the accumulator buffer,
+// then consumes the operand ring stage by stage.
+// `KSUB` 32-wide K sub-blocks share one pipeline stage (one barrier wait, one commit): the ring has
+// STAGES / KSUB stages, and `k_blocks` counts stages.
+template <int BN, int STAGES, int KSUB = 1>
+__device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base, int tiles, int k_blocks) {
+  static_assert(STAGES % KSUB == 0, "whole stages");
+  constexpr int kRing = STAGES / KSUB;
+  int stage = 0;
+  uint32_t phase = 0;
+  bool ok = true;
+  int local = 0;
+  for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+    const int buf = local & 1;
+    const uint32_t use_parity = (local >> 1) & 1u;
+    // The epilogue must have drained this accumulator buffer.
+    if (!mbar_wait(&sm.acc_empty[buf], use_parity ^ 1u, kSiteUmmaAccEmpty)) { ok = false; break; }
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_acc = tmem_base + buf * BN;
+    for (int kb = 0; kb < k_blocks; ++kb) {
+      if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
+      tcgen05_fence_after_sync();
+#pragma unroll
+      for (int sub = 0; sub < KSUB; ++sub) {
+        const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage * KSUB + sub) * stage_bytes<BN>());
+        issue_stage_mmas<BN>(tmem_acc, a_addr, a_addr + kASlabBytes, (kb > 0 || sub > 0) ? 1u : 0u);
+      }
+      umma_commit(&sm.empty[stage]);  // stage reusable once these MMAs have read it
+      if (++stage == kRing) stage = 0, phase ^= 1u;
+    }
+    if (ok) umma_commit(&sm.acc_full[buf]);
+  }
+}
+
+// One of the four epilogue warps of the persistent single-CTA kernels.
+template <int BN, int kAct, bool kPipelinedEpilogue>
+__device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCarve& sm, uint32_t tmem_base, int quarter,
+                                              int lane, int tiles, int tiles_m, int tiles_n) {
+  const EpilogueArgs ep = epilogue_args(p);
+  bool ok = true;
+  int local = 0;
+  for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+    const int buf = local & 1;
+    const uint32_t use_parity = (local >> 1) & 1u;
+    int tm, tn;
+    tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+    const bool pipelined = kPipelinedEpilogue && ep.vector_io && ep.peers.count == 0;
+    SourceChunk first;
+    if (pipelined) fetch_source(ep, first, tm * kTileM + quarter * 32 + lane, tn * BN);   // before the wait
+    if (!mbar_wait(&sm.acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
+    tcgen05_fence_after_sync();
+    if (pipelined) {
+      epilogue_tile_pipelined<BN, kAct>(ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN, first);
+    } else {
+      epilogue_tile<BN, kAct>(ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN,
+                              sm.peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float)));
+    }
+    tcgen05_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
+  }
+}
+
+// Threads of every TMA-fed kernel: warp 0 producer, warp 1 TMEM owner + MMA issuer, warps 2-5 epilogue.
+constexpr int kTmaThreads = 6 * 32;
+
+// ------------------------------------------------------------- host-side helpers
+
+bool aligned16(const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; }
+
+void fill_common(UmmaParams* p, const b200_gemm_problem& q, const PeerOutputs& peers) {
+  std::memset(p, 0, sizeof(*p));
+  p->peers = peers;
+  p->a = q.a, p->b = q.b, p->d = q.d;
+  p->c = q.beta != 0.f ? q.c : nullptr;
+  p->bias = q.bias;
+  p->lda = q.lda, p->ldb = q.ldb, p->ldc = q.ldc, p->ldd = q.ldd;
+  p->m = q.m, p->n = q.n, p->k = q.k;
+  p->alpha = q.alpha, p->beta = q.beta;
+  const bool c_ok = q.beta == 0.f || (aligned16(q.c) && q.ldc % 4 == 0);
+  const bool bias_ok = q.bias == nullptr || aligned16(q.bias);
+  bool peers_ok = true;   // peer copies share the row pitch of D, only their bases can differ in alignment
+  for (int i = 0; i < peers.count; ++i) peers_ok = peers_ok && aligned16(peers.ptr[i]);
+  p->vector_io = (q.n % 4 == 0 && aligned16(q.d) && q.ldd % 4 == 0 && c_ok && bias_ok && peers_ok) ? 1 : 0;
+}
+
+}  // namespace
+}  // namespace b200
