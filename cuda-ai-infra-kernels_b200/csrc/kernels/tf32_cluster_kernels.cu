@@ -157,9 +157,13 @@ __device__ __forceinline__ void exchange_finish(const EpilogueArgs& p, const flo
   }
 }
 
-template <int STAGES, int kAct>
+// STAGES counts 32-wide K blocks of shared memory; KSUB of them form one pipeline stage (two when
+// the CTA has its SM to itself and the ring can be twice as large: one barrier round trip per 64 of K).
+template <int STAGES, int kAct, int KSUB = 1>
 __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __grid_constant__ UmmaParams p) {
   constexpr int BN = kSplitN;
+  static_assert(STAGES % KSUB == 0, "whole stages");
+  constexpr int kRing = STAGES / KSUB;
   static_assert(static_cast<size_t>(STAGES) * stage_bytes<BN>() >= sizeof(float4) * kExchangePitch * (BN / 4),
                 "the idle operand ring must hold one exchanged tile");
   cg::cluster_group cluster = cg::this_cluster();
@@ -192,7 +196,7 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
   const int tiles_n = (p.n + BN - 1) / BN;
   int tm, tn;
   tile_coords(static_cast<int>(blockIdx.x) / ranks, tiles_m, tiles_n, &tm, &tn);
-  const int k_blocks = (p.k + kStageK - 1) / kStageK;
+  const int k_blocks = (p.k + KSUB * kStageK - 1) / (KSUB * kStageK);   // stages; K past the end reads as zeros
   const int per_rank = (k_blocks + ranks - 1) / ranks;
   const int kb_begin = min(k_blocks, rank * per_rank);
   const int kb_end = min(k_blocks, kb_begin + per_rank);
@@ -207,19 +211,23 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
       uint32_t phase = 0;
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait(&sm.empty[stage], phase ^ 1u, kSiteUmmaEmpty)) break;
-        uint8_t* a_dst = sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>();
-        uint8_t* b_dst = a_dst + kASlabBytes;
-        mbar_expect_tx(&sm.full[stage], stage_bytes<BN>());
-        tma_load_2d(a_dst, &p.map_a, &sm.full[stage], kb * kStageK, tm * kTileM);
-        if (p.b_strips == BN / 32) {
-          tma_load_3d(b_dst, &p.map_b_strips, &sm.full[stage], 0, kb * kStageK, tn * (BN / 32));
-        } else {
+        mbar_expect_tx(&sm.full[stage], KSUB * stage_bytes<BN>());
 #pragma unroll
-          for (int j = 0; j < BN / 32; ++j) {
-            tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &sm.full[stage], tn * BN + j * 32, kb * kStageK);
+        for (int sub = 0; sub < KSUB; ++sub) {
+          const int k0 = (kb * KSUB + sub) * kStageK;
+          uint8_t* a_dst = sm.stages + static_cast<size_t>(stage * KSUB + sub) * stage_bytes<BN>();
+          uint8_t* b_dst = a_dst + kASlabBytes;
+          tma_load_2d(a_dst, &p.map_a, &sm.full[stage], k0, tm * kTileM);
+          if (p.b_strips == BN / 32) {
+            tma_load_3d(b_dst, &p.map_b_strips, &sm.full[stage], 0, k0, tn * (BN / 32));
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 32; ++j) {
+              tma_load_2d(b_dst + j * kBBoxBytes, &p.map_b, &sm.full[stage], tn * BN + j * 32, k0);
+            }
           }
         }
-        if (++stage == STAGES) stage = 0, phase ^= 1u;
+        if (++stage == kRing) stage = 0, phase ^= 1u;
       }
     }
   } else if (warp == 1) {
@@ -230,10 +238,13 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { fed = false; break; }
         tcgen05_fence_after_sync();
-        const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage) * stage_bytes<BN>());
-        issue_stage_mmas<BN>(tmem_base, a_addr, a_addr + kASlabBytes, kb > kb_begin ? 1u : 0u);
+#pragma unroll
+        for (int sub = 0; sub < KSUB; ++sub) {
+          const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage * KSUB + sub) * stage_bytes<BN>());
+          issue_stage_mmas<BN>(tmem_base, a_addr, a_addr + kASlabBytes, (kb > kb_begin || sub > 0) ? 1u : 0u);
+        }
         umma_commit(&sm.empty[stage]);
-        if (++stage == STAGES) stage = 0, phase ^= 1u;
+        if (++stage == kRing) stage = 0, phase ^= 1u;
       }
       if (fed) umma_commit(&sm.acc_full[0]);
     }
@@ -518,19 +529,23 @@ int splitk_max_clusters(int cluster_size) {
   return result;
 }
 
-// Cluster size of the split-K kernel, from a cost model fitted to phase timings of the kernel on a
-// B200 (microseconds): a K block costs 0.34 with one CTA per SM and 0.53 per CTA with two (the
-// four 128 x 128 x 8 MMAs of a block take that long however few bytes the block loads: with 16 of
-// 128 rows present it is still 0.29, and a six-stage ring instead of three changes nothing, so it
-// is the SM's MMA rate at this tile shape, not memory, that a second CTA has to share); barriers,
-// exchange and the finishing pass cost 4.5 / 6.0 / 7.2 for clusters of 2 / 4 / 8 (half as much again when
-// two CTAs share an SM). A candidate must keep
-// two K blocks per range and fit the device in one wave (two CTAs per SM: twice the cluster count the
-// occupancy query reports for one). `estimate_us` receives the modelled time of the choice.
+// Cluster size of the split-K kernel, from a cost model fitted to timings of the kernel on a B200
+// (microseconds). With f the fraction of the tile's 128 rows that exist, a 32-wide K block costs
+// 0.22 + 0.13 f when the CTA has its SM to itself and runs two sub-blocks per stage, 0.29 + 0.05 f
+// when the grid fits one CTA per SM but its clusters only fit the device at two (single-block
+// stages), and 0.43 + 0.10 f per CTA when two share an SM. Most of it is the MMA thread's
+// instruction stream and barrier round trips; a deeper ring changes nothing. Barriers, exchange
+// and the finishing pass cost 4.5 / 6.0 / 7.2 for
+// clusters of 2 / 4 / 8 when few rows exist and 7 / 8 / 9 when all 128 do (interpolated by the row
+// count), half as much again when two CTAs share an SM. A candidate must keep two K blocks per
+// range and fit the device in one wave (two CTAs per SM: twice the cluster count the occupancy
+// query reports for one). `estimate_us` receives the modelled time of the choice.
 int splitk_ranks(const b200_gemm_problem& q, int sms, float* estimate_us = nullptr) {
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
-  constexpr float kExchangeUs[4] = {4.7f, 4.5f, 6.0f, 7.2f};
+  constexpr float kExchangeFewRows[4] = {4.7f, 4.5f, 6.0f, 7.2f};
+  constexpr float kExchangeAllRows[4] = {4.7f, 7.0f, 8.0f, 9.0f};
+  const float row_fraction = static_cast<float>(q.m < kTileM ? q.m : kTileM) / kTileM;
   int best = 1;
   float best_us = 1e30f;
   for (int log2r = 0; log2r < 4; ++log2r) {
@@ -538,18 +553,22 @@ int splitk_ranks(const b200_gemm_problem& q, int sms, float* estimate_us = nullp
     const int64_t ctas = tiles * ranks;
     if (ctas > 2LL * sms) break;
     if (ranks > 1 && (k_blocks / ranks < 2 || tiles > 2LL * splitk_max_clusters(ranks))) break;
-    const bool shared_sm = ctas > sms;   // two CTAs per SM also share its exchange and store bandwidth
-    const float us = static_cast<float>((k_blocks + ranks - 1) / ranks) * (shared_sm ? 0.53f : 0.34f) +
-                     kExchangeUs[log2r] * (shared_sm ? 1.5f : 1.0f);
+    const bool shared_sm = ctas > sms;
+    const bool deep = !shared_sm && (ranks == 1 || tiles <= splitk_max_clusters(ranks));   // as launch_splitk_for decides
+    const float exchange = kExchangeFewRows[log2r] + row_fraction * (kExchangeAllRows[log2r] - kExchangeFewRows[log2r]);
+    const float per_block = shared_sm ? 0.43f + 0.10f * row_fraction
+                                      : (deep ? 0.22f + 0.13f * row_fraction : 0.29f + 0.05f * row_fraction);
+    const float us = static_cast<float>((k_blocks + ranks - 1) / ranks) * per_block +
+                     exchange * (shared_sm ? 1.5f : (deep ? 1.0f : 1.1f));
     if (us < best_us) best_us = us, best = ranks;
   }
   if (estimate_us != nullptr) *estimate_us = best_us;
   return best;
 }
 
-template <int STAGES, int kAct>
+template <int STAGES, int kAct, int KSUB = 1>
 int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
-  auto kernel = umma_splitk_kernel<STAGES, kAct>;
+  auto kernel = umma_splitk_kernel<STAGES, kAct, KSUB>;
   constexpr size_t smem = smem_bytes<kSplitN, STAGES>() - kPeerStageBytes;   // its finishing pass needs no staging
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     return B200_ERR_LAUNCH_FAILED;
@@ -643,11 +662,28 @@ int launch_swap(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream
 }
 }  // namespace
 
+namespace {
+
+// A CTA that has its SM to itself (and whose cluster count fits the device at one CTA per SM) runs
+// the ring of four K blocks as two stages of two; otherwise three single-block stages leave room
+// for a second CTA on the SM.
+template <int kAct>
+int launch_splitk_for(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  const int sms = sm_count();
+  if (sms <= 0) return B200_ERR_INTERNAL;
+  const int ranks = splitk_ranks(q, sms);
+  const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
+  const bool alone = tiles * ranks <= sms && (ranks == 1 || tiles <= splitk_max_clusters(ranks));
+  return alone ? launch_splitk<4, kAct, 2>(q, peers, stream) : launch_splitk<3, kAct, 1>(q, peers, stream);
+}
+
+}  // namespace
+
 int launch_tf32_splitk(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   switch (act) {
-    case B200_EPILOGUE_LINEAR: return launch_splitk<3, B200_EPILOGUE_LINEAR>(q, peers, stream);
-    case B200_EPILOGUE_RELU: return launch_splitk<3, B200_EPILOGUE_RELU>(q, peers, stream);
-    case B200_EPILOGUE_GELU: return launch_splitk<3, B200_EPILOGUE_GELU>(q, peers, stream);
+    case B200_EPILOGUE_LINEAR: return launch_splitk_for<B200_EPILOGUE_LINEAR>(q, peers, stream);
+    case B200_EPILOGUE_RELU: return launch_splitk_for<B200_EPILOGUE_RELU>(q, peers, stream);
+    case B200_EPILOGUE_GELU: return launch_splitk_for<B200_EPILOGUE_GELU>(q, peers, stream);
     default: return B200_ERR_INVALID_ARGUMENT;
   }
 }

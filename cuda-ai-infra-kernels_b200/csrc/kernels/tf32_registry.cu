@@ -116,15 +116,15 @@ bool gate_pair(const b200_gemm_problem& q, int sms) {
 // tensor-core split-K entry takes over (16 x 4096 x 4096: 22.1 vs 14.7 us).
 bool gate_skinny(const b200_gemm_problem& q, int) { return q.m <= 4; }
 // Split K when the model above predicts a shorter run than the unsplit tile kernels, which stream a
-// 32-wide K block in about 0.18 us (128 x 64 tiles, two sub-blocks per stage, when those fit the
-// SMs in one round) or 0.29 us (128 x 128) on top of 3.5 us of prologue and epilogue. Measured on a
-// B200: 1024 x 1024 x 8192 40.7 us split four ways against 61.0 us unsplit, 64 x 4096 x 4096 17.8
-// against 31.7, while 512^3, 1024^3 and 512 x 2048 x 2048 are within 1 us either way.
+// 32-wide K block in about 0.23 us (128 x 64 tiles, when those fit the SMs in one round) or 0.29 us
+// (128 x 128) on top of 3.5 us of prologue and epilogue. Measured on a B200: 1024 x 1024 x 8192
+// 41.0 us split against 61.5 us unsplit, 64 x 4096 x 4096 16.1 against 31.7, 256 x 4096 x 4096 26.8
+// against 32.7, while 512^3, 1024^3 and 512 x 2048 x 2048 are within 1 us either way.
 bool gate_splitk(const b200_gemm_problem& q, int sms) {
   float split_us = 0.f;
   if (tf32_splitk_plan(q, sms, &split_us) < 2) return false;
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
-  const float unsplit_us = static_cast<float>(k_blocks) * (tiles_of(q, 64) <= sms ? 0.18f : 0.29f) + 3.5f;
+  const float unsplit_us = static_cast<float>(k_blocks) * (tiles_of(q, 64) <= sms ? 0.23f : 0.29f) + 3.5f;
   return split_us + 1.0f < unsplit_us;   // ties go to the simpler kernel (1024^3 with a source: 17.6 vs 16.6 us)
 }
 // Measured against the split-K tile kernel: ahead up to 16 rows (16 x 8192 x 1024: 11.7 vs 16.5 us,
