@@ -11,8 +11,9 @@ The role of the reference's profiling/profile_*.sh wrappers. `--small` halves
 the GEMM edge (2048) so that a multi-pass capture stays short; the row-operator
 shapes (256 MiB and 128 MiB per tensor) are already small enough. `tf32_other`
 runs the registry entries for awkward shapes: the warp-specialised loader on
-misaligned operands (2047 x 2049 x 2051), the split-K cluster kernel
-(16 x 4096 x 4096) and the FP32 stream kernel (4 x 4096 x 16384, B = 268 MB).
+misaligned operands (2047 x 2049 x 2051), the operand-swapped kernel
+(16 x 4096 x 4096), the split-K cluster kernel (64 x 4096 x 4096) and the FP32
+stream kernel (4 x 4096 x 16384, B = 268 MB).
 """
 import sys
 from pathlib import Path
@@ -40,7 +41,7 @@ def main(argv):
         for _ in range(2):
             pkg.adaptive_gemm(a, b, c=c, alpha=1.0, beta=0.5, epilogue="relu")
     if "tf32_other" in which:
-        for (m, n, k) in ((2047, 2049, 2051), (16, 4096, 4096), (4, 4096, 16384)):
+        for (m, n, k) in ((2047, 2049, 2051), (16, 4096, 4096), (64, 4096, 4096), (4, 4096, 16384)):
             a = torch.randn(m, k, device=dev)
             b = torch.randn(k, n, device=dev)
             for _ in range(2):
