@@ -428,3 +428,24 @@ def test_pair_kernel_runs_a_short_last_round_as_half_tiles(abi, kernel, epilogue
     expected = oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, EPILOGUE_NAME[epilogue])
     torch.testing.assert_close(d.cpu(), expected, atol=0, rtol=0)      # integers: exact
     assert_device_clean(abi)
+
+
+# ------------------------------------------------ K that ends inside a pipeline stage
+# Stages hold two or four 32-wide K sub-blocks; a K that ends inside the first sub-block, between
+# sub-blocks or inside the last one must read the missing part as zeros.
+
+
+@pytest.mark.parametrize("entry", entries(align=4), ids=lambda e: e[1])
+@pytest.mark.parametrize("k", [4, 36, 64, 68, 100, 132])
+def test_k_tail_inside_a_stage(abi, entry, k):
+    kernel_id, alias, epilogue, _ = entry
+    m, n = (16, 256) if alias.startswith("swap") else (256, 384)
+    g = torch.Generator().manual_seed(k)
+    a = torch.randint(-4, 5, (m, k), generator=g).float()
+    b = torch.randint(-4, 5, (k, n), generator=g).float()
+    status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), epilogue=epilogue)
+    assert status == 0, abi.b200_status_string(status)
+    expected = oracle.adaptive_gemm_fp64(a, b, epilogue=EPILOGUE_NAME[epilogue])
+    tol = 1e-5 if epilogue == GELU else 0
+    torch.testing.assert_close(d.cpu(), expected, atol=tol, rtol=tol)
+    assert_device_clean(abi)
