@@ -220,6 +220,15 @@ def measure_extras(pkg, peaks: dict, steps: int, warmup: int) -> dict:
         ms = timed(lambda i, name=name: pkg.gemm(a_sets[i & 1], b_sets[i & 1], impl=name))
         out[f"sgemm_{name}_tflops"] = flops / ms / 1e9
     del a_sets, b_sets
+    # The other two FP32 benchmark shapes: 1024^3 and 1024 x 4096 x 4096, where tiles do not fill
+    # whole rounds of SMs and the stream-K entry (output cleared inside the timed call) matters.
+    for (m_, n_, k_) in ((1024, 1024, 1024), (1024, 4096, 4096)):
+        a_small = [torch.randn(k_, m_, device=dev).t() for _ in range(2)]
+        b_small = [torch.randn(k_, n_, device=dev) for _ in range(2)]
+        for name in ("cublas", "prefetch_reg", "split_k"):
+            ms = timed(lambda i, name=name: pkg.gemm(a_small[i & 1], b_small[i & 1], impl=name))
+            out[f"sgemm_{name}_{m_}x{n_}x{k_}_tflops"] = 2.0 * m_ * n_ * k_ / ms / 1e9
+        del a_small, b_small
 
     # TF32 tcgen05 GEMM with fused epilogue, D = relu(A@B + 0.5*C), and cuBLAS TF32.
     tf32_peak = peaks["bf16_tflops"] / 2.0
