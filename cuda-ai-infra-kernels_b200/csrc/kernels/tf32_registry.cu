@@ -116,15 +116,17 @@ bool gate_pair(const b200_gemm_problem& q, int sms) {
 // tensor-core split-K entry takes over (16 x 4096 x 4096: 22.1 vs 14.7 us).
 bool gate_skinny(const b200_gemm_problem& q, int) { return q.m <= 4; }
 // Split K when the model above predicts a shorter run than the unsplit tile kernels, which stream a
-// 32-wide K block in about 0.23 us (128 x 64 tiles, when those fit the SMs in one round) or 0.29 us
-// (128 x 128) on top of 3.5 us of prologue and epilogue. Measured on a B200: 1024 x 1024 x 8192
-// 41.0 us split against 61.5 us unsplit, 64 x 4096 x 4096 16.1 against 31.7, 256 x 4096 x 4096 26.8
-// against 32.7, while 512^3, 1024^3 and 512 x 2048 x 2048 are within 1 us either way.
+// 32-wide K block in about 0.185 us (128 x 64 tiles, when those fit the SMs in one round) or 0.235 us
+// (128 x 128) on top of 3.5 us of prologue and epilogue. Measured on a B200 with a source and ReLU:
+// 1024 x 1024 x 8192 45.4 us split against 56.7 us unsplit, 64 x 4096 x 4096 16.7 against 28.7,
+// 768 x 768 x 4096 23.7 against 29.8, while 256 x 4096 x 4096 (30.5 / 32.2), 1024 x 1024 x 4096
+// (28.1 / 29.5) and 1280 x 1280 x 8192 (68.4 / 71.4) are close and 512^3, 1024^3 and
+// 512 x 2048 x 2048 are 1 to 4 us faster unsplit.
 bool gate_splitk(const b200_gemm_problem& q, int sms) {
   float split_us = 0.f;
   if (tf32_splitk_plan(q, sms, &split_us) < 2) return false;
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
-  const float unsplit_us = static_cast<float>(k_blocks) * (tiles_of(q, 64) <= sms ? 0.23f : 0.29f) + 3.5f;
+  const float unsplit_us = static_cast<float>(k_blocks) * (tiles_of(q, 64) <= sms ? 0.185f : 0.235f) + 3.5f;
   return split_us + 1.0f < unsplit_us;   // ties go to the simpler kernel (1024^3 with a source: 17.6 vs 16.6 us)
 }
 // Measured against the split-K tile kernel: ahead up to 16 rows (16 x 8192 x 1024: 11.7 vs 16.5 us,
@@ -154,21 +156,21 @@ const RegistryEntry kRegistry[] = {
     {meta_pair(21, "umma256x256stage6pairRelu", "pair_relu", B200_EPILOGUE_RELU, 6), &pair_entry<B200_EPILOGUE_RELU>, &gate_pair},
     {meta(16, "umma128x256stage4tma", "wide", B200_EPILOGUE_LINEAR, 256, 4, 4), &tile_entry<256, 4, B200_EPILOGUE_LINEAR>, &gate_wide},
     {meta(17, "umma128x256stage4tmaRelu", "wide_relu", B200_EPILOGUE_RELU, 256, 4, 4), &tile_entry<256, 4, B200_EPILOGUE_RELU>, &gate_wide},
-    {meta(18, "umma128x64stage6tma", "narrow", B200_EPILOGUE_LINEAR, 64, 6, 4), &tile_entry<64, 6, B200_EPILOGUE_LINEAR>, &gate_narrow},
-    {meta(19, "umma128x64stage6tmaRelu", "narrow_relu", B200_EPILOGUE_RELU, 64, 6, 4), &tile_entry<64, 6, B200_EPILOGUE_RELU>, &gate_narrow},
+    {meta(18, "umma128x64stage8tma", "narrow", B200_EPILOGUE_LINEAR, 64, 8, 4), &tile_entry<64, 8, B200_EPILOGUE_LINEAR>, &gate_narrow},
+    {meta(19, "umma128x64stage8tmaRelu", "narrow_relu", B200_EPILOGUE_RELU, 64, 8, 4), &tile_entry<64, 8, B200_EPILOGUE_RELU>, &gate_narrow},
     {meta_pair(22, "umma256x256stage6pairGelu", "pair_gelu", B200_EPILOGUE_GELU, 6), &pair_entry<B200_EPILOGUE_GELU>, &gate_pair},
     {meta(23, "umma128x256stage4tmaGelu", "wide_gelu", B200_EPILOGUE_GELU, 256, 4, 4), &tile_entry<256, 4, B200_EPILOGUE_GELU>, &gate_wide},
-    {meta(24, "umma128x64stage6tmaGelu", "narrow_gelu", B200_EPILOGUE_GELU, 64, 6, 4), &tile_entry<64, 6, B200_EPILOGUE_GELU>, &gate_narrow},
-    {meta(2, "umma128x128stage4tma", "fast", B200_EPILOGUE_LINEAR, 128, 4, 4), &tile_entry<128, 4, B200_EPILOGUE_LINEAR>, &gate_always},
+    {meta(24, "umma128x64stage8tmaGelu", "narrow_gelu", B200_EPILOGUE_GELU, 64, 8, 4), &tile_entry<64, 8, B200_EPILOGUE_GELU>, &gate_narrow},
+    {meta(2, "umma128x128stage6tma", "fast", B200_EPILOGUE_LINEAR, 128, 6, 4), &tile_entry<128, 6, B200_EPILOGUE_LINEAR>, &gate_always},
     {meta(3, "umma128x128stage4generic", "fallback", B200_EPILOGUE_LINEAR, 128, 4, 1), &generic_entry<128, B200_EPILOGUE_LINEAR>, &gate_always},
     {meta(4, "umma128x64stage4tma", "fast_mwarp", B200_EPILOGUE_LINEAR, 64, 4, 4), &tile_entry<64, 4, B200_EPILOGUE_LINEAR>, &gate_always},
     {meta(5, "umma128x64stage4generic", "fallback_mwarp", B200_EPILOGUE_LINEAR, 64, 4, 1), &generic_entry<64, B200_EPILOGUE_LINEAR>, &gate_always},
     {meta(6, "umma128x128stage3tma", "fast_stage3", B200_EPILOGUE_LINEAR, 128, 3, 4), &tile_entry<128, 3, B200_EPILOGUE_LINEAR>, &gate_always},
     {meta(7, "umma128x128stage2tma", "fast_stage2", B200_EPILOGUE_LINEAR, 128, 2, 4), &tile_entry<128, 2, B200_EPILOGUE_LINEAR>, &gate_always},
-    {meta(8, "umma128x128stage4tmaRelu", "fast_relu", B200_EPILOGUE_RELU, 128, 4, 4), &tile_entry<128, 4, B200_EPILOGUE_RELU>, &gate_always},
+    {meta(8, "umma128x128stage6tmaRelu", "fast_relu", B200_EPILOGUE_RELU, 128, 6, 4), &tile_entry<128, 6, B200_EPILOGUE_RELU>, &gate_always},
     {meta(9, "umma128x128stage4genericRelu", "fallback_relu", B200_EPILOGUE_RELU, 128, 4, 1), &generic_entry<128, B200_EPILOGUE_RELU>, &gate_always},
     // GELU has no entry in the reference registry (the epilogue is parsed but refused there).
-    {meta(25, "umma128x128stage4tmaGelu", "fast_gelu", B200_EPILOGUE_GELU, 128, 4, 4), &tile_entry<128, 4, B200_EPILOGUE_GELU>, &gate_always},
+    {meta(25, "umma128x128stage6tmaGelu", "fast_gelu", B200_EPILOGUE_GELU, 128, 6, 4), &tile_entry<128, 6, B200_EPILOGUE_GELU>, &gate_always},
     {meta(26, "umma128x128stage4genericGelu", "fallback_gelu", B200_EPILOGUE_GELU, 128, 4, 1), &generic_entry<128, B200_EPILOGUE_GELU>, &gate_always},
 };
 constexpr int kRegistrySize = sizeof(kRegistry) / sizeof(kRegistry[0]);

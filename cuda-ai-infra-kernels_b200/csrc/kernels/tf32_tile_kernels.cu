@@ -261,9 +261,16 @@ __global__ void __launch_bounds__(kGenericThreads, 1) umma_generic_kernel(const 
 
 template <int BN, int STAGES, int kAct>
 int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
-  // Two sub-blocks per stage where the ring has room for at least two such stages and the tile is
-  // not already bound by what an SM can pull from L2 (the 128 x 256 tile is).
-  constexpr int KSUB = (BN <= 128 && STAGES % 2 == 0 && STAGES >= 4) ? 2 : 1;
+  // K sub-blocks per pipeline stage. The MMA thread pays about 380 cycles per stage (barrier wait,
+  // fence, commit) next to 54 per instruction, so a 128 x 64 tile (54 cycles of tensor pipe per
+  // instruction) wants four sub-blocks per stage and a 128 x 128 tile (71 cycles) two; the ring must
+  // still hold two or three such stages to cover the load latency. Measured on a B200, unsplit, with
+  // a source: 128 x 128 at 1280 x 1280 x 8192 takes 97 us with 2 stages of 2, 72 us with 3 of 2, 81 us
+  // with 2 of 3, 84 us with 6 of 1; 128 x 64 at 1024 x 1024 x 4096 takes 35.4 us with 3 stages of 2 or
+  // 4 of 2 and 29.4 us with 2 of 4. The 128 x 256 tile (134 cycles per instruction) is slower with two
+  // sub-blocks per stage (2048 x 2048 x 8192: 129-140 against 107-122 us): only two stages fit.
+  constexpr int KSUB = (BN == 64 && STAGES % 4 == 0 && STAGES >= 8) ? 4
+                       : (BN <= 128 && STAGES % 2 == 0 && STAGES >= 4) ? 2 : 1;
   auto kernel = umma_tma_kernel<BN, STAGES, kAct, KSUB>;
   constexpr size_t smem = smem_bytes<BN, STAGES>();
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
@@ -322,8 +329,8 @@ int launch_tf32_tile(int tile_n, int stages, int act, const b200_gemm_problem& q
     }                                                                                              \
   }
   B200_TILE_CASE(256, 4)
-  B200_TILE_CASE(128, 4)
-  B200_TILE_CASE(64, 6)
+  B200_TILE_CASE(128, 6)
+  B200_TILE_CASE(64, 8)
 #undef B200_TILE_CASE
   // Configurations that exist with the linear epilogue only (the reference's stage and warp-shape variants).
   if (act != B200_EPILOGUE_LINEAR) return B200_ERR_INVALID_ARGUMENT;
