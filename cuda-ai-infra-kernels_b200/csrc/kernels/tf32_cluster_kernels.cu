@@ -534,8 +534,8 @@ int splitk_max_clusters(int cluster_size) {
 // 0.22 + 0.13 f when the CTA has its SM to itself and runs two sub-blocks per stage, 0.29 + 0.05 f
 // when the grid fits one CTA per SM but its clusters only fit the device at two (single-block
 // stages), and 0.43 + 0.10 f per CTA when two share an SM. Most of it is the MMA thread's
-// instruction stream and barrier round trips; a deeper ring changes nothing. Barriers, exchange
-// and the finishing pass cost 4.5 / 6.0 / 7.2 for
+// instruction stream and barrier round trips; with single-block stages a deeper ring changes
+// nothing. Barriers, exchange and the finishing pass cost 4.5 / 6.0 / 7.2 for
 // clusters of 2 / 4 / 8 when few rows exist and 7 / 8 / 9 when all 128 do (interpolated by the row
 // count), half as much again when two CTAs share an SM. A candidate must keep two K blocks per
 // range and fit the device in one wave (two CTAs per SM: twice the cluster count the occupancy
@@ -665,8 +665,9 @@ int launch_swap(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream
 namespace {
 
 // A CTA that has its SM to itself (and whose cluster count fits the device at one CTA per SM) runs
-// the ring of four K blocks as two stages of two; otherwise three single-block stages leave room
-// for a second CTA on the SM.
+// a ring of six K blocks as three stages of two (against two stages of two: 512 x 1024 x 16384
+// 57.5 -> 46.5 us, 256 x 4096 x 4096 30.5 -> 29.5, 1024 x 1024 x 8192 45.4 -> 44.4); otherwise three
+// single-block stages leave room for a second CTA on the SM.
 template <int kAct>
 int launch_splitk_for(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   const int sms = sm_count();
@@ -674,7 +675,7 @@ int launch_splitk_for(const b200_gemm_problem& q, const PeerOutputs& peers, cuda
   const int ranks = splitk_ranks(q, sms);
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
   const bool alone = tiles * ranks <= sms && (ranks == 1 || tiles <= splitk_max_clusters(ranks));
-  return alone ? launch_splitk<4, kAct, 2>(q, peers, stream) : launch_splitk<3, kAct, 1>(q, peers, stream);
+  return alone ? launch_splitk<6, kAct, 2>(q, peers, stream) : launch_splitk<3, kAct, 1>(q, peers, stream);
 }
 
 }  // namespace
