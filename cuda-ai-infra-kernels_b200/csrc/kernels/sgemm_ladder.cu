@@ -164,49 +164,75 @@ __global__ void __launch_bounds__(Map::kThreads) sgemm_smem_kernel(const float* 
     }
 }
 
-// Stages 2 and 3 (one output per thread, BM x BN outputs per CTA, operands staged in shared
-// memory BK rows of K at a time): the two slabs are double-buffered and the next slab's elements
-// travel from global memory in registers while the current slab is multiplied, so an iteration
-// has one barrier instead of two and the global-load latency is off the critical path. The tile
-// sizes, the staging width (scalar or 128-bit) and therefore the shape rules are those of the
-// reference's stages (csrc/gemm/gemm_block_tile.cu:4-35, gemm_block_tile_float4.cu).
-template <int BM, int BN, int BK, bool kVectorStaging>
+// Stages 2 to 5 (one output per thread, BM x BN outputs per CTA, operands staged in shared memory).
+// With one output per thread every FMA needs one element of A and one of B from shared memory, so
+// the kernel runs at the rate of the shared-memory pipe: the layout decides the speed. Slabs of
+// kSlabK = 32 values of K are therefore stored K-innermost (a_s[row][k], b_s[column][k], row pitch
+// 36 floats): a thread reads four consecutive K values of its row and of its column with two
+// 128-bit loads, which cost 1 (A: the lanes of a warp share one or two rows) + 4 (B: 32 columns,
+// conflict-free at this pitch) wavefronts for four FMAs where k-outermost slabs cost 8. The two
+// slabs are double-buffered and the next slab travels from global memory in registers while the
+// current one is multiplied (one barrier per slab). The accumulation order is k = 0, 1, 2, ... in
+// one FMA chain, as in the reference's stages. Tile sizes, the staging width (scalar or 128-bit
+// global loads) and therefore the shape rules (K a multiple of 8) are those of the reference's
+// stages (csrc/gemm/gemm_block_tile.cu:4-35, gemm_block_tile_float4.cu); a last slab may hold 8,
+// 16 or 24 values of K.
+template <int BM, int BN, bool kVectorStaging>
 __global__ void __launch_bounds__(BM* BN) sgemm_block_tile_kernel(const float* __restrict__ a,
                                                                    const float* __restrict__ b,
                                                                    float* __restrict__ c, int m, int n, int k) {
+  constexpr int kSlabK = 32, kPitch = kSlabK + 4;
   constexpr int kThreads = BM * BN;
   constexpr int kWidth = kVectorStaging ? 4 : 1;                  // floats per staged item
-  constexpr int kItemsA = BK * BM / kWidth, kItemsB = BK * BN / kWidth;
-  static_assert(kItemsA <= kThreads && kItemsB <= kThreads, "at most one item of each slab per thread");
-  __shared__ __align__(16) float a_s[2][BK][BM];
-  __shared__ __align__(16) float b_s[2][BK][BN];
+  constexpr int kItemsA = kSlabK * BM / kWidth, kItemsB = kSlabK * BN / kWidth;
+  constexpr int kPerThreadA = (kItemsA + kThreads - 1) / kThreads, kPerThreadB = (kItemsB + kThreads - 1) / kThreads;
+  __shared__ __align__(16) float a_s[2][BM][kPitch];
+  __shared__ __align__(16) float b_s[2][BN][kPitch];
 
   const int tid = threadIdx.x;
   const int ty = tid / BN, tx = tid % BN;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  const bool has_a = tid < kItemsA, has_b = tid < kItemsB;
-  const int a_kk = tid / (BM / kWidth), a_mm = (tid % (BM / kWidth)) * kWidth;
-  const int b_kk = tid / (BN / kWidth), b_nn = (tid % (BN / kWidth)) * kWidth;
-  const float* a_src = a + static_cast<int64_t>(a_kk) * m + m0 + a_mm;
-  const float* b_src = b + static_cast<int64_t>(b_kk) * n + n0 + b_nn;
 
-  float4 ra = make_float4(0.f, 0.f, 0.f, 0.f), rb = ra;
+  float4 ra[kPerThreadA], rb[kPerThreadB];
+  // Item i of a slab: K row i / (B / kWidth), kWidth consecutive rows (A) or columns (B) of the tile.
   auto fetch = [&](int k0) {
-    if constexpr (kVectorStaging) {
-      if (has_a) ra = *reinterpret_cast<const float4*>(a_src + static_cast<int64_t>(k0) * m);
-      if (has_b) rb = *reinterpret_cast<const float4*>(b_src + static_cast<int64_t>(k0) * n);
-    } else {
-      if (has_a) ra.x = a_src[static_cast<int64_t>(k0) * m];
-      if (has_b) rb.x = b_src[static_cast<int64_t>(k0) * n];
+#pragma unroll
+    for (int i = 0; i < kPerThreadA; ++i) {
+      const int item = tid + i * kThreads, kk = item / (BM / kWidth), mm = (item % (BM / kWidth)) * kWidth;
+      ra[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (item < kItemsA && k0 + kk < k) {
+        const float* src = a + static_cast<int64_t>(k0 + kk) * m + m0 + mm;
+        if constexpr (kVectorStaging) ra[i] = *reinterpret_cast<const float4*>(src);
+        else ra[i].x = *src;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kPerThreadB; ++i) {
+      const int item = tid + i * kThreads, kk = item / (BN / kWidth), nn = (item % (BN / kWidth)) * kWidth;
+      rb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (item < kItemsB && k0 + kk < k) {
+        const float* src = b + static_cast<int64_t>(k0 + kk) * n + n0 + nn;
+        if constexpr (kVectorStaging) rb[i] = *reinterpret_cast<const float4*>(src);
+        else rb[i].x = *src;
+      }
     }
   };
   auto stash = [&](int buf) {
-    if constexpr (kVectorStaging) {
-      if (has_a) *reinterpret_cast<float4*>(&a_s[buf][a_kk][a_mm]) = ra;
-      if (has_b) *reinterpret_cast<float4*>(&b_s[buf][b_kk][b_nn]) = rb;
-    } else {
-      if (has_a) a_s[buf][a_kk][a_mm] = ra.x;
-      if (has_b) b_s[buf][b_kk][b_nn] = rb.x;
+#pragma unroll
+    for (int i = 0; i < kPerThreadA; ++i) {
+      const int item = tid + i * kThreads, kk = item / (BM / kWidth), mm = (item % (BM / kWidth)) * kWidth;
+      if (item < kItemsA) {
+        a_s[buf][mm][kk] = ra[i].x;
+        if constexpr (kVectorStaging) a_s[buf][mm + 1][kk] = ra[i].y, a_s[buf][mm + 2][kk] = ra[i].z, a_s[buf][mm + 3][kk] = ra[i].w;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kPerThreadB; ++i) {
+      const int item = tid + i * kThreads, kk = item / (BN / kWidth), nn = (item % (BN / kWidth)) * kWidth;
+      if (item < kItemsB) {
+        b_s[buf][nn][kk] = rb[i].x;
+        if constexpr (kVectorStaging) b_s[buf][nn + 1][kk] = rb[i].y, b_s[buf][nn + 2][kk] = rb[i].z, b_s[buf][nn + 3][kk] = rb[i].w;
+      }
     }
   };
 
@@ -215,11 +241,30 @@ __global__ void __launch_bounds__(BM* BN) sgemm_block_tile_kernel(const float* _
   __syncthreads();
   float acc = 0.f;
   int buf = 0;
-  for (int k0 = 0; k0 < k; k0 += BK) {
-    const bool more = k0 + BK < k;
-    if (more) fetch(k0 + BK);
+  for (int k0 = 0; k0 < k; k0 += kSlabK) {
+    const bool more = k0 + kSlabK < k;
+    if (more) fetch(k0 + kSlabK);
+    const float4* a_row = reinterpret_cast<const float4*>(&a_s[buf][ty][0]);
+    const float4* b_row = reinterpret_cast<const float4*>(&b_s[buf][tx][0]);
+    if (k - k0 >= kSlabK) {
 #pragma unroll
-    for (int kk = 0; kk < BK; ++kk) acc = fmaf(a_s[buf][kk][ty], b_s[buf][kk][tx], acc);
+      for (int q = 0; q < kSlabK / 4; ++q) {
+        const float4 av = a_row[q], bv = b_row[q];
+        acc = fmaf(av.x, bv.x, acc);
+        acc = fmaf(av.y, bv.y, acc);
+        acc = fmaf(av.z, bv.z, acc);
+        acc = fmaf(av.w, bv.w, acc);
+      }
+    } else {
+      const int quads = (k - k0) / 4;   // 2, 4 or 6
+      for (int q = 0; q < quads; ++q) {
+        const float4 av = a_row[q], bv = b_row[q];
+        acc = fmaf(av.x, bv.x, acc);
+        acc = fmaf(av.y, bv.y, acc);
+        acc = fmaf(av.z, bv.z, acc);
+        acc = fmaf(av.w, bv.w, acc);
+      }
+    }
     if (more) stash(buf ^ 1);
     // One barrier per iteration: buffer buf ^ 1 was last read before the previous barrier.
     __syncthreads();
@@ -228,9 +273,9 @@ __global__ void __launch_bounds__(BM* BN) sgemm_block_tile_kernel(const float* _
   c[static_cast<int64_t>(m0 + ty) * n + n0 + tx] = acc;
 }
 
-template <int BM, int BN, int BK, bool kVectorStaging>
+template <int BM, int BN, bool kVectorStaging>
 int launch_block_tile(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
-  sgemm_block_tile_kernel<BM, BN, BK, kVectorStaging><<<dim3(n / BN, m / BM), BM * BN, 0, stream>>>(a, b, c, m, n, k);
+  sgemm_block_tile_kernel<BM, BN, kVectorStaging><<<dim3(n / BN, m / BM), BM * BN, 0, stream>>>(a, b, c, m, n, k);
   return launch_status();
 }
 
@@ -250,13 +295,13 @@ int sgemm_ladder_launch(int impl, const float* a, const float* b, float* c, int 
       sgemm_naive_kernel<<<dim3(n / 16, m / 16), dim3(16, 16), 0, stream>>>(a, b, c, m, n, k);
       return launch_status();
     case B200_SGEMM_BLOCK_TILE:
-      return launch_block_tile<16, 16, 8, false>(a, b, c, m, n, k, stream);
+      return launch_block_tile<16, 16, false>(a, b, c, m, n, k, stream);
     case B200_SGEMM_BLOCK_TILE_F4_16x16:
-      return launch_block_tile<16, 16, 8, true>(a, b, c, m, n, k, stream);
+      return launch_block_tile<16, 16, true>(a, b, c, m, n, k, stream);
     case B200_SGEMM_BLOCK_TILE_F4_16x32:
-      return launch_block_tile<16, 32, 8, true>(a, b, c, m, n, k, stream);
+      return launch_block_tile<16, 32, true>(a, b, c, m, n, k, stream);
     case B200_SGEMM_BLOCK_TILE_F4_32x32:
-      return launch_block_tile<32, 32, 8, true>(a, b, c, m, n, k, stream);
+      return launch_block_tile<32, 32, true>(a, b, c, m, n, k, stream);
     case B200_SGEMM_THREAD_TILE_4x4:
       return launch_smem<128, 128, 8, true, MapThreadTile<128, 128, 4, 4, false>>(a, b, c, m, n, k, stream);
     case B200_SGEMM_THREAD_TILE_4x8:
