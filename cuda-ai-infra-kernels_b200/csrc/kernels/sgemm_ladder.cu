@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(256) sgemm_naive_kernel(const float* __restric
   c[static_cast<int64_t>(row) * n + col] = acc;
 }
 
-// ------------------------------------------------------------ stages 2-5
+// ------------------------------------------------- register-tiled stages
 
 // One contiguous TM x TN rectangle per thread (stage 4). With kWarp4x8 the
 // threads of a warp form 4 rows x 8 columns of rectangles instead of one row.
@@ -72,14 +72,20 @@ struct MapWarpTile {
   __device__ int col_origin(int c) const { return col0 + 16 * c; }
 };
 
-template <int BM, int BN, int BK, bool kVectorStaging, class Map>
+// Register-tiled stages: BM x BN outputs per CTA, `[BK][BM]` / `[BK][BN]` slabs in shared memory,
+// staged with 128-bit loads. The slabs are double-buffered and the next one travels from global
+// memory in registers while the current one is multiplied: one barrier per slab, global-load
+// latency off the critical path.
+template <int BM, int BN, int BK, class Map>
 __global__ void __launch_bounds__(Map::kThreads) sgemm_smem_kernel(const float* __restrict__ a,
                                                                      const float* __restrict__ b,
                                                                      float* __restrict__ c, int m, int n, int k) {
   constexpr int kThreads = Map::kThreads;
   constexpr int RM = Map::kRowBlocks, RN = Map::kColBlocks, CM = Map::kBlockRows, CN = Map::kBlockCols;
-  __shared__ __align__(16) float a_s[BK][BM];
-  __shared__ __align__(16) float b_s[BK][BN];
+  constexpr int kItemsA = BK * BM / 4, kItemsB = BK * BN / 4;   // 128-bit items per slab
+  constexpr int kPerThreadA = (kItemsA + kThreads - 1) / kThreads, kPerThreadB = (kItemsB + kThreads - 1) / kThreads;
+  __shared__ __align__(16) float a_s2[2][BK][BM];
+  __shared__ __align__(16) float b_s2[2][BK][BN];
 
   const int tid = threadIdx.x;
   const Map map(tid);
@@ -92,30 +98,42 @@ __global__ void __launch_bounds__(Map::kThreads) sgemm_smem_kernel(const float* 
 #pragma unroll
     for (int j = 0; j < RN * CN; ++j) acc[i][j] = 0.f;
 
-  for (int k0 = 0; k0 < k; k0 += BK) {
-    // Stage the two slabs. Row kk of either slab is contiguous in global memory.
-    if constexpr (kVectorStaging) {
-      for (int v = tid; v < BK * BM / 4; v += kThreads) {
-        const int kk = v / (BM / 4), mm = (v % (BM / 4)) * 4;
-        *reinterpret_cast<float4*>(&a_s[kk][mm]) =
-            *reinterpret_cast<const float4*>(a + static_cast<int64_t>(k0 + kk) * m + m0 + mm);
-      }
-      for (int v = tid; v < BK * BN / 4; v += kThreads) {
-        const int kk = v / (BN / 4), nn = (v % (BN / 4)) * 4;
-        *reinterpret_cast<float4*>(&b_s[kk][nn]) =
-            *reinterpret_cast<const float4*>(b + static_cast<int64_t>(k0 + kk) * n + n0 + nn);
-      }
-    } else {
-      for (int e = tid; e < BK * BM; e += kThreads) {
-        const int kk = e / BM, mm = e % BM;
-        a_s[kk][mm] = a[static_cast<int64_t>(k0 + kk) * m + m0 + mm];
-      }
-      for (int e = tid; e < BK * BN; e += kThreads) {
-        const int kk = e / BN, nn = e % BN;
-        b_s[kk][nn] = b[static_cast<int64_t>(k0 + kk) * n + n0 + nn];
-      }
+  // Row kk of either slab is contiguous in global memory.
+  float4 ra[kPerThreadA], rb[kPerThreadB];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < kPerThreadA; ++i) {
+      const int v = tid + i * kThreads, kk = v / (BM / 4), mm = (v % (BM / 4)) * 4;
+      if (v < kItemsA) ra[i] = *reinterpret_cast<const float4*>(a + static_cast<int64_t>(k0 + kk) * m + m0 + mm);
     }
-    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kPerThreadB; ++i) {
+      const int v = tid + i * kThreads, kk = v / (BN / 4), nn = (v % (BN / 4)) * 4;
+      if (v < kItemsB) rb[i] = *reinterpret_cast<const float4*>(b + static_cast<int64_t>(k0 + kk) * n + n0 + nn);
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < kPerThreadA; ++i) {
+      const int v = tid + i * kThreads, kk = v / (BM / 4), mm = (v % (BM / 4)) * 4;
+      if (v < kItemsA) *reinterpret_cast<float4*>(&a_s2[buf][kk][mm]) = ra[i];
+    }
+#pragma unroll
+    for (int i = 0; i < kPerThreadB; ++i) {
+      const int v = tid + i * kThreads, kk = v / (BN / 4), nn = (v % (BN / 4)) * 4;
+      if (v < kItemsB) *reinterpret_cast<float4*>(&b_s2[buf][kk][nn]) = rb[i];
+    }
+  };
+
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < k; k0 += BK) {
+    const bool more = k0 + BK < k;
+    if (more) fetch(k0 + BK);
+    const float (*a_s)[BM] = a_s2[buf];
+    const float (*b_s)[BN] = b_s2[buf];
 
 #pragma unroll
     for (int kk = 0; kk < BK; ++kk) {
@@ -143,7 +161,10 @@ __global__ void __launch_bounds__(Map::kThreads) sgemm_smem_kernel(const float* 
 #pragma unroll
         for (int j = 0; j < RN * CN; ++j) acc[i][j] = fmaf(a_frag[i], b_frag[j], acc[i][j]);
     }
+    if (more) stash(buf ^ 1);
+    // One barrier per slab: buffer buf ^ 1 was last read before the previous barrier.
     __syncthreads();
+    buf ^= 1;
   }
 
 #pragma unroll
@@ -279,9 +300,9 @@ int launch_block_tile(const float* a, const float* b, float* c, int m, int n, in
   return launch_status();
 }
 
-template <int BM, int BN, int BK, bool kVectorStaging, class Map>
+template <int BM, int BN, int BK, class Map>
 int launch_smem(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
-  sgemm_smem_kernel<BM, BN, BK, kVectorStaging, Map>
+  sgemm_smem_kernel<BM, BN, BK, Map>
       <<<dim3(n / BN, m / BM), Map::kThreads, 0, stream>>>(a, b, c, m, n, k);
   return launch_status();
 }
@@ -303,15 +324,15 @@ int sgemm_ladder_launch(int impl, const float* a, const float* b, float* c, int 
     case B200_SGEMM_BLOCK_TILE_F4_32x32:
       return launch_block_tile<32, 32, true>(a, b, c, m, n, k, stream);
     case B200_SGEMM_THREAD_TILE_4x4:
-      return launch_smem<128, 128, 8, true, MapThreadTile<128, 128, 4, 4, false>>(a, b, c, m, n, k, stream);
+      return launch_smem<128, 128, 8, MapThreadTile<128, 128, 4, 4, false>>(a, b, c, m, n, k, stream);
     case B200_SGEMM_THREAD_TILE_4x8:
-      return launch_smem<128, 128, 8, true, MapThreadTile<128, 128, 4, 8, false>>(a, b, c, m, n, k, stream);
+      return launch_smem<128, 128, 8, MapThreadTile<128, 128, 4, 8, false>>(a, b, c, m, n, k, stream);
     case B200_SGEMM_THREAD_TILE_8x8:
-      return launch_smem<128, 128, 8, true, MapThreadTile<128, 128, 8, 8, false>>(a, b, c, m, n, k, stream);
+      return launch_smem<128, 128, 8, MapThreadTile<128, 128, 8, 8, false>>(a, b, c, m, n, k, stream);
     case B200_SGEMM_THREAD_TILE_8x8_WARP4x8:
-      return launch_smem<128, 128, 8, true, MapThreadTile<128, 128, 8, 8, true>>(a, b, c, m, n, k, stream);
+      return launch_smem<128, 128, 8, MapThreadTile<128, 128, 8, 8, true>>(a, b, c, m, n, k, stream);
     case B200_SGEMM_WARP_TILE:
-      return launch_smem<128, 128, 8, true, MapWarpTile>(a, b, c, m, n, k, stream);
+      return launch_smem<128, 128, 8, MapWarpTile>(a, b, c, m, n, k, stream);
     default:
       return B200_ERR_INVALID_ARGUMENT;
   }
