@@ -92,6 +92,20 @@ def test_every_k_row_is_used_exactly_once(abi, impl, k):
     torch.testing.assert_close(abi_sgemm(abi, impl, a, b), expected, atol=0, rtol=0)
 
 
+@pytest.mark.parametrize("impl", LADDER[1:10])
+@pytest.mark.parametrize("k", [8, 24, 32, 40, 56, 72, 264])
+def test_staged_ladder_uses_every_k_row_once(abi, impl, k):
+    # The shared-memory stages hold 8 (register tiles) or 32 (one output per thread) rows of K per
+    # slab, double-buffered; K ends inside a slab for most of these. Same construction as above:
+    # exact on small integers, wrong if a slab is dropped, repeated or read past K.
+    values = torch.arange(1, k + 1, device="cuda", dtype=torch.float32) % 13 + 1
+    a = values.unsqueeze(1).expand(k, 128).contiguous().t()
+    b = values.unsqueeze(1).expand(k, 256).contiguous()
+    expected = torch.full((128, 256), float((values.double() ** 2).sum()), device="cuda")
+    torch.testing.assert_close(abi_sgemm(abi, impl, a, b), expected, atol=0, rtol=0)
+    assert_device_clean(abi)
+
+
 @pytest.mark.parametrize("impl", ["prefetch_smem", "prefetch_reg"])
 @pytest.mark.parametrize("k", [8, 24, 40])
 def test_k_tails_shorter_than_a_stage(abi, impl, k):
