@@ -115,19 +115,22 @@ bool gate_pair(const b200_gemm_problem& q, int sms) {
 // its FMA work per byte of B exceeds what hides behind the memory stream and the
 // tensor-core split-K entry takes over (16 x 4096 x 4096: 22.1 vs 14.7 us).
 bool gate_skinny(const b200_gemm_problem& q, int) { return q.m <= 4; }
-// Split K when the model above predicts a shorter run than the unsplit tile kernels, which stream a
-// 32-wide K block in about 0.185 us (128 x 64 tiles, when those fit the SMs in one round) or 0.235 us
-// (128 x 128) on top of 3.5 us of prologue and epilogue. Measured on a B200 with a source and ReLU:
-// 1024 x 1024 x 8192 45.4 us split against 56.7 us unsplit, 64 x 4096 x 4096 16.7 against 28.7,
-// 768 x 768 x 4096 23.7 against 29.8, while 256 x 4096 x 4096 (30.5 / 32.2), 1024 x 1024 x 4096
-// (28.1 / 29.5) and 1280 x 1280 x 8192 (68.4 / 71.4) are close and 512^3, 1024^3 and
-// 512 x 2048 x 2048 are 1 to 4 us faster unsplit.
+// Split K when the model above predicts a shorter run than the unsplit tile kernels. Those take, with
+// a source operand, about 0.19 us per 32-wide K block on top of 5.7 us (128 x 64 tiles, when they fit
+// the SMs in one round: 1024^3 11.8 us, 1024 x 1024 x 4096 29.4, 512 x 2048 x 2048 17.7) or 0.24 us on
+// top of 8.5 us (128 x 128: 1536^3 21.0, 1536 x 1536 x 4096 40.5, 1280 x 1280 x 8192 71.5). Measured on
+// a B200 with a source and ReLU, split against unsplit: 1024 x 1024 x 8192 45.6 / 57.5 us,
+// 64 x 4096 x 4096 15.9 / 28.6, 768 x 768 x 4096 23.7 / 29.7, 256 x 4096 x 4096 30.6 / 32.2,
+// 1024 x 1024 x 4096 28.2 / 29.2, 512 x 512 x 2048 15.4 / 17.2; 512^3, 1024^3, 1024 x 1024 x 2048,
+// 512 x 2048 x 2048 and 128 x 8192 x 1024 are 1 to 5 us faster unsplit. In a sweep of 15 such shapes
+// the gate picked the faster side everywhere but 1280 x 1280 x 8192 (71.5 us unsplit, 68.8 split).
 bool gate_splitk(const b200_gemm_problem& q, int sms) {
   float split_us = 0.f;
   if (tf32_splitk_plan(q, sms, &split_us) < 2) return false;
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
-  const float unsplit_us = static_cast<float>(k_blocks) * (tiles_of(q, 64) <= sms ? 0.185f : 0.235f) + 3.5f;
-  return split_us + 1.0f < unsplit_us;   // ties go to the simpler kernel (1024^3 with a source: 17.6 vs 16.6 us)
+  const bool narrow = tiles_of(q, 64) <= sms;
+  const float unsplit_us = static_cast<float>(k_blocks) * (narrow ? 0.19f : 0.24f) + (narrow ? 5.7f : 8.5f);
+  return split_us + 0.5f < unsplit_us;   // ties go to the simpler kernel
 }
 // Measured against the split-K tile kernel: ahead up to 16 rows (16 x 8192 x 1024: 11.7 vs 16.5 us,
 // 16 x 4096 x 4096: 12.7 vs 16.8, cuBLAS 12.9), level or behind from 32 rows on (64 x 4096 x 4096: 19.7 vs 18.2).
