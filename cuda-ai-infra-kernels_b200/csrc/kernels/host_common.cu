@@ -32,6 +32,39 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Encoded tensor maps, remembered per host thread. A map is a pure function of (base address,
+// extents, pitch, box, swizzle, rank): encoding it through the driver costs a few microseconds,
+// which a 10-microsecond GEMM launched over and over on the same buffers (a serving loop, a
+// benchmark) notices. Direct-mapped, thread-local: no locks, no invalidation needed (a stale entry
+// can only be returned for an identical key, for which the encoding is identical).
+struct MapKey {
+  const void* base;
+  uint64_t rows, cols, ld;
+  uint32_t box_a, box_b;
+  int32_t swizzle, kind;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_a == o.box_a && box_b == o.box_b &&
+           swizzle == o.swizzle && kind == o.kind;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kMapSlots = 64;
+
+MapSlot* map_slot(const MapKey& key) {
+  thread_local MapSlot slots[kMapSlots] = {};
+  uint64_t h = reinterpret_cast<uintptr_t>(key.base) >> 4;
+  h ^= key.rows * 0x9E3779B97F4A7C15ull;
+  h ^= (key.cols + (static_cast<uint64_t>(key.box_a) << 32)) * 0xC2B2AE3D27D4EB4Full;
+  h ^= (key.ld + (static_cast<uint64_t>(key.box_b) << 40) + (static_cast<uint64_t>(key.kind) << 20) +
+        static_cast<uint64_t>(key.swizzle)) * 0x165667B19E3779F9ull;
+  h ^= h >> 29;
+  return &slots[h % kMapSlots];
+}
+
 }  // namespace
 
 int sm_count() {
@@ -53,6 +86,12 @@ bool make_tensor_map_2d(CUtensorMap* out, const float* base, uint64_t rows, uint
   if ((ld * sizeof(float)) % 16 != 0 || (box_cols * sizeof(float)) % 16 != 0) return false;
   if (box_rows == 0 || box_cols == 0 || box_rows > 256 || box_cols > 256) return false;
   if (swizzle != Swizzle::kNone && box_cols * sizeof(float) > 128) return false;
+  const MapKey key{base, rows, cols, ld, box_rows, box_cols, static_cast<int32_t>(swizzle), 2};
+  MapSlot* slot = map_slot(key);
+  if (slot->used && slot->key == key) {
+    *out = slot->map;
+    return true;
+  }
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {ld * sizeof(float)};
   const cuuint32_t box[2] = {box_cols, box_rows};
@@ -63,7 +102,9 @@ bool make_tensor_map_2d(CUtensorMap* out, const float* base, uint64_t rows, uint
                              : swizzle == Swizzle::k128BAtom32B ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
                                                                 : CU_TENSOR_MAP_SWIZZLE_NONE,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return rc == CUDA_SUCCESS;
+  if (rc != CUDA_SUCCESS) return false;
+  slot->key = key, slot->map = *out, slot->used = true;
+  return true;
 }
 
 bool make_tensor_map_strips(CUtensorMap* out, const float* base, uint64_t rows, uint64_t cols, uint64_t ld,
@@ -72,6 +113,12 @@ bool make_tensor_map_strips(CUtensorMap* out, const float* base, uint64_t rows, 
   if (encode == nullptr) return false;
   if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || (ld * sizeof(float)) % 16 != 0) return false;
   if (cols == 0 || cols % 32 != 0 || box_rows == 0 || box_rows > 256 || box_groups == 0 || box_groups > 256) return false;
+  const MapKey key{base, rows, cols, ld, box_rows, box_groups, static_cast<int32_t>(swizzle), 3};
+  MapSlot* slot = map_slot(key);
+  if (slot->used && slot->key == key) {
+    *out = slot->map;
+    return true;
+  }
   const cuuint64_t dims[3] = {32, rows, cols / 32};
   const cuuint64_t strides[2] = {ld * sizeof(float), 32 * sizeof(float)};
   const cuuint32_t box[3] = {32, box_rows, box_groups};
@@ -82,7 +129,9 @@ bool make_tensor_map_strips(CUtensorMap* out, const float* base, uint64_t rows, 
                              : swizzle == Swizzle::k128BAtom32B ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
                                                                 : CU_TENSOR_MAP_SWIZZLE_NONE,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return rc == CUDA_SUCCESS;
+  if (rc != CUDA_SUCCESS) return false;
+  slot->key = key, slot->map = *out, slot->used = true;
+  return true;
 }
 
 }  // namespace b200
@@ -111,10 +160,13 @@ int b200_device_status_read(uint32_t* host_word, b200_stream_t stream) {
   if (host_word == nullptr) return B200_ERR_INVALID_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (cudaStreamSynchronize(s) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
-  uint32_t sgemm_word = 0, umma_word = 0;
+  uint32_t sgemm_word = 0, umma_word = 0, selftest_word = 0;
   if (b200::sgemm_status_read_clear(&sgemm_word) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
   if (b200::umma_status_read_clear(&umma_word) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
-  *host_word = sgemm_word | umma_word;
+  if (b200::selftest_status_read_clear(&selftest_word) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  uint32_t peer_word = 0;
+  if (b200::peer_sync_status_read_clear(&peer_word) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  *host_word = sgemm_word | umma_word | selftest_word | peer_word;
   return *host_word == 0 ? B200_OK : B200_ERR_DEVICE_TIMEOUT;
 }
 

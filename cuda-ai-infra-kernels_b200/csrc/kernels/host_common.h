@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "b200_kernels.h"
 
 namespace b200 {
@@ -34,14 +36,43 @@ inline bool make_peer_outputs(PeerOutputs* out, float* const* peers, int n_peers
 // Number of SMs of the current device (cached per device ordinal).
 int sm_count();
 
-// Maps the last launch error (cudaPeekAtLastError) to a status code.
+// Status of the launch just made. cudaGetLastError reads AND clears the runtime's per-thread error
+// slot: this library links its own (static) CUDA runtime, so nobody else would ever clear it, and a
+// single refused launch (a non-sticky error such as an invalid configuration) would otherwise make
+// every later call on the thread report failure.
 inline int launch_status() {
-  return cudaPeekAtLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH_FAILED;
+  return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH_FAILED;
+}
+
+// For runtime calls that returned their own error code (cudaLaunchKernelEx, cudaFuncSetAttribute):
+// the same code also sits in the per-thread slot; clear it and report the failure.
+inline int launch_failed() {
+  (void)cudaGetLastError();
+  return B200_ERR_LAUNCH_FAILED;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize for kernel `kKernel`, set once per device and process
+// (the attribute is per device; the call costs a few microseconds, which small problems notice).
+template <auto kKernel, size_t kBytes>
+inline bool ensure_dynamic_smem() {
+  static std::atomic<uint64_t> done{0};   // bit d: set on device ordinal d
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return false;
+  const uint64_t bit = (device >= 0 && device < 64) ? (uint64_t{1} << device) : 0;
+  if (bit != 0 && (done.load(std::memory_order_acquire) & bit) != 0) return true;
+  if (cudaFuncSetAttribute(kKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kBytes)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  if (bit != 0) done.fetch_or(bit, std::memory_order_release);
+  return true;
 }
 
 // Device status words of the translation units that contain bounded waits.
 cudaError_t sgemm_status_read_clear(uint32_t* word);
 cudaError_t umma_status_read_clear(uint32_t* word);
+cudaError_t selftest_status_read_clear(uint32_t* word);
+cudaError_t peer_sync_status_read_clear(uint32_t* word);
 
 // k128BAtom32B: 128-byte span swizzled in 32-byte granules (what an MN-major
 // 32-bit tcgen05 operand needs); k128B: the usual 16-byte granules.

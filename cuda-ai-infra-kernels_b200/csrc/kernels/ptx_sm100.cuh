@@ -36,6 +36,8 @@ enum WaitSite : uint32_t {
   kSiteUmmaAccFull = 1u << 4,
   kSiteUmmaAccEmpty = 1u << 5,
   kSiteUmmaStore = 1u << 6,
+  kSiteSelfTest = 1u << 7,
+  kSitePeerBarrier = 1u << 8,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -92,9 +94,10 @@ constexpr uint32_t kMaxWaitPolls = 1u << 22;
 // Waits for the phase with the given parity. Returns false (after recording
 // `site`) when the cap was reached; callers must then stop issuing work and
 // fall through to their teardown.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t site) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t site,
+                                          uint32_t max_polls = kMaxWaitPolls) {
   if (mbar_try_wait(bar, parity)) return true;
-  for (uint32_t i = 0; i < kMaxWaitPolls; ++i) {
+  for (uint32_t i = 0; i < max_polls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   atomicOr(&g_device_status, site);

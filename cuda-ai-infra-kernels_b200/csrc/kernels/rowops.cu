@@ -316,7 +316,7 @@ int launch_cluster(const RowArgs& a, int ranks, cudaStream_t s) {
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, row_cluster_kernel<kOp, VPT, kThreads>, a) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  if (cudaLaunchKernelEx(&cfg, row_cluster_kernel<kOp, VPT, kThreads>, a) != cudaSuccess) return launch_failed();
   return launch_status();
 }
 

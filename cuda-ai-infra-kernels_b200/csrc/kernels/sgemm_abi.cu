@@ -32,6 +32,13 @@ constexpr LadderEntry kLadder[B200_SGEMM_IMPL_COUNT] = {
 
 bool valid_impl(int impl) { return impl >= 0 && impl < B200_SGEMM_IMPL_COUNT; }
 
+// Every vectorised entry stores C with 128-bit accesses (split_k reduces into it with
+// red.global.add.v4.f32). The reference never meets a misaligned C because its launchers allocate
+// the output themselves; a caller of this ABI can pass one, so it is refused before any launch.
+bool output_misaligned(int impl, const float* c) {
+  return kLadder[impl].vectorized && reinterpret_cast<uintptr_t>(c) % 16 != 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -77,6 +84,7 @@ int b200_sgemm(int impl, const float* a_colmajor, const float* b, float* c, int 
   if (a_colmajor == nullptr || b == nullptr || c == nullptr) return B200_ERR_INVALID_ARGUMENT;
   const int check = b200_sgemm_check(impl, a_colmajor, b, m, n, k);
   if (check != B200_OK) return check;
+  if (output_misaligned(impl, c)) return B200_ERR_MISALIGNED_OPERAND;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (impl <= B200_SGEMM_WARP_TILE) return b200::sgemm_ladder_launch(impl, a_colmajor, b, c, m, n, k, s);
   b200::PeerOutputs none;
@@ -91,6 +99,7 @@ int b200_sgemm_gather(int impl, const float* a_colmajor, const float* b, float* 
   if (!b200::make_peer_outputs(&peers, peer_c, n_peers)) return B200_ERR_INVALID_ARGUMENT;
   const int check = b200_sgemm_check(impl, a_colmajor, b, m, n, k);
   if (check != B200_OK) return check;
+  if (output_misaligned(impl, c)) return B200_ERR_MISALIGNED_OPERAND;
   // Only the persistent pipeline kernels that store finished tiles once can fan them out.
   if (impl != B200_SGEMM_PREFETCH_SMEM && impl != B200_SGEMM_PREFETCH_REG) return B200_ERR_NOT_SUPPORTED;
   for (int i = 0; i < n_peers; ++i) {

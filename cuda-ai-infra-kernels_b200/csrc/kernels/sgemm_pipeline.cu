@@ -388,13 +388,11 @@ int launch_pipeline(const float* a, const float* b, float* c, const PeerOutputs&
                     cudaStream_t stream) {
   using Layout = SmemLayout<BK, STAGES>;
   if (kStreamK && peers.count > 0) return B200_ERR_NOT_SUPPORTED;   // partial sums need a cleared output
-  auto kernel = (!kStreamK && peers.count > 0)
-                    ? sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, kStreamK, kCtasPerSm, !kStreamK>
-                    : sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, kStreamK, kCtasPerSm, false>;
-  // Function attributes are per device; setting them again is cheap and keeps
-  // the launcher free of per-device state.
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Layout::kBytes)) !=
-      cudaSuccess) {
+  constexpr auto kFanOut = sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, kStreamK, kCtasPerSm, !kStreamK>;
+  constexpr auto kLocal = sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, kStreamK, kCtasPerSm, false>;
+  const bool fan_out = !kStreamK && peers.count > 0;
+  auto kernel = fan_out ? kFanOut : kLocal;
+  if (!(fan_out ? ensure_dynamic_smem<kFanOut, Layout::kBytes>() : ensure_dynamic_smem<kLocal, Layout::kBytes>())) {
     return B200_ERR_LAUNCH_FAILED;
   }
   const int sms = sm_count();

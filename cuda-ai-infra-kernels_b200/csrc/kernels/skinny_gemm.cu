@@ -154,9 +154,7 @@ template <int MR, int kAct>
 int launch_rows(const SkinnyParams& p, int ranks, cudaStream_t stream) {
   auto kernel = skinny_gemm_kernel<MR, kAct>;
   constexpr size_t smem = skinny_smem_bytes<MR>();
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
-    return B200_ERR_LAUNCH_FAILED;
-  }
+  if (!ensure_dynamic_smem<skinny_gemm_kernel<MR, kAct>, smem>()) return B200_ERR_LAUNCH_FAILED;
   const int64_t column_blocks = (p.n + kCols - 1) / kCols;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(column_blocks * ranks));
@@ -170,7 +168,7 @@ int launch_rows(const SkinnyParams& p, int ranks, cudaStream_t stream) {
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
 

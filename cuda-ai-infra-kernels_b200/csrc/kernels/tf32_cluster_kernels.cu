@@ -510,7 +510,7 @@ int splitk_max_clusters(int cluster_size) {
   if (cached != 0) return cached;
   auto kernel = umma_splitk_kernel<3, B200_EPILOGUE_LINEAR>;   // the activation does not change the footprint
   constexpr size_t smem = smem_bytes<kSplitN, 3>() - kPeerStageBytes;   // no staging: two CTAs fit an SM
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return 0;
+  if (!ensure_dynamic_smem<umma_splitk_kernel<3, B200_EPILOGUE_LINEAR>, smem>()) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(cluster_size) * 64);
   cfg.blockDim = dim3(kTmaThreads);
@@ -570,9 +570,7 @@ template <int STAGES, int kAct, int KSUB = 1>
 int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   auto kernel = umma_splitk_kernel<STAGES, kAct, KSUB>;
   constexpr size_t smem = smem_bytes<kSplitN, STAGES>() - kPeerStageBytes;   // its finishing pass needs no staging
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
-    return B200_ERR_LAUNCH_FAILED;
-  }
+  if (!ensure_dynamic_smem<umma_splitk_kernel<STAGES, kAct, KSUB>, smem>()) return B200_ERR_LAUNCH_FAILED;
   UmmaParams p;
   fill_common(&p, q, peers);
   if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
@@ -600,7 +598,7 @@ int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStre
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
 
@@ -621,9 +619,7 @@ int run_swap(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t 
   constexpr int KSUB = NM <= 16 ? 4 : 2, STAGES = NM <= 16 ? 2 : 3;
   auto kernel = umma_swap_kernel<NM, STAGES, KSUB, kAct>;
   constexpr size_t smem = swap_smem_bytes<NM, STAGES, KSUB>();
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
-    return B200_ERR_LAUNCH_FAILED;
-  }
+  if (!ensure_dynamic_smem<umma_swap_kernel<NM, STAGES, KSUB, kAct>, smem>()) return B200_ERR_LAUNCH_FAILED;
   UmmaParams p;
   fill_common(&p, q, peers);
   // A: boxes of NM rows x 32 floats of K; B as in the other kernels.
@@ -652,7 +648,7 @@ int run_swap(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t 
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
 

@@ -217,9 +217,7 @@ int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream
   static_assert(STAGES % KSUB == 0, "the registry states the ring depth in 32-wide K blocks");
   auto kernel = umma_pair_kernel<STAGES / KSUB, KSUB, kAct>;
   constexpr size_t smem = pair_smem_bytes<STAGES / KSUB, KSUB>();
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
-    return B200_ERR_LAUNCH_FAILED;
-  }
+  if (!ensure_dynamic_smem<umma_pair_kernel<STAGES / KSUB, KSUB, kAct>, smem>()) return B200_ERR_LAUNCH_FAILED;
   const size_t launch_smem = smem - (peers.count > 0 ? 0 : kPeerStageBytes);
   UmmaParams p;
   fill_common(&p, q, peers);
@@ -255,7 +253,7 @@ int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
 }  // namespace

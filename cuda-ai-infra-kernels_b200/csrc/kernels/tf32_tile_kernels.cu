@@ -273,9 +273,7 @@ int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_
                        : (BN <= 128 && STAGES % 2 == 0 && STAGES >= 4) ? 2 : 1;
   auto kernel = umma_tma_kernel<BN, STAGES, kAct, KSUB>;
   constexpr size_t smem = smem_bytes<BN, STAGES>();
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
-    return B200_ERR_LAUNCH_FAILED;
-  }
+  if (!ensure_dynamic_smem<umma_tma_kernel<BN, STAGES, kAct, KSUB>, smem>()) return B200_ERR_LAUNCH_FAILED;
   // The staging area of the fused all-gather is only asked for when there are peers: a plain GEMM
   // keeps the larger L1 for its epilogue's source reads.
   const size_t launch_smem = smem - (peers.count > 0 ? 0 : kPeerStageBytes);
@@ -302,9 +300,7 @@ template <int BN, int STAGES, int kAct>
 int launch_generic(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   auto kernel = umma_generic_kernel<BN, STAGES, kAct>;
   constexpr size_t smem = smem_bytes<BN, STAGES>();
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
-    return B200_ERR_LAUNCH_FAILED;
-  }
+  if (!ensure_dynamic_smem<umma_generic_kernel<BN, STAGES, kAct>, smem>()) return B200_ERR_LAUNCH_FAILED;
   const size_t launch_smem = smem - (peers.count > 0 ? 0 : kPeerStageBytes);
   UmmaParams p;
   fill_common(&p, q, peers);

@@ -31,8 +31,34 @@ def _abi() -> ctypes.CDLL:
         lib = ctypes.CDLL(str(path))
         lib.b200_shard_rows.argtypes = [ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int64),
                                         ctypes.POINTER(ctypes.c_int64)]
+        lib.b200_peer_barrier.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_uint32,
+                                          ctypes.c_uint32, ctypes.c_void_p]
+        lib.b200_device_status_read.argtypes = [ctypes.POINTER(ctypes.c_uint32), ctypes.c_void_p]
         _LIB = lib
     return _LIB
+
+
+def init_distributed(backend: str = "nccl", timeout_s: float = 120.0, device: Optional[torch.device] = None, **kwargs):
+    """`torch.distributed.init_process_group` with every wait bounded.
+
+    Rendezvous and communicator set-up give up after `timeout_s` instead of
+    waiting for a rank that never joins, and so does every later collective of
+    the group: gloo raises on the calling rank; with NCCL the process group's
+    watchdog thread polls the communicator's asynchronous error state
+    (`ncclCommGetAsyncError`) and, once a collective has been pending for
+    `timeout_s`, aborts the communicator and ends the process with an error
+    instead of leaving a kernel waiting on the GPU (PyTorch's default handling,
+    `TORCH_NCCL_ASYNC_ERROR_HANDLING`, left as the caller set it).
+    Rank, world size and master address come from the environment or `kwargs`.
+    """
+    import datetime
+
+    import torch.distributed as dist
+
+    if backend == "nccl" and device is not None:
+        kwargs.setdefault("device_id", device)
+    dist.init_process_group(backend, timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+    return dist.group.WORLD
 
 
 def shard_rows(m: int, parts: int, granule: int = 128) -> list[tuple[int, int]]:
@@ -108,6 +134,26 @@ def peer_row_pointers(base_ptrs: Sequence[int], rank: int, first_row: int, n: in
     return [int(ptr) + offset for r, ptr in enumerate(base_ptrs) if r != rank]
 
 
+WAIT_PEER_BARRIER = 1 << 8   # bit of the device status word set by a barrier that gave up
+
+
+def all_ranks_ok(ok: bool, group=None) -> bool:
+    """Host-side agreement: True only if every rank of `group` passed True.
+
+    Call it (on a CPU/gloo group, or any group) with the outcome of the work
+    done since the last barrier, before enqueuing the next device-side barrier:
+    if a rank failed, every rank skips the barrier instead of waiting for a
+    partner that will never arrive.
+    """
+    import torch.distributed as dist
+
+    backend = dist.get_backend(group)
+    device = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    return bool(flag.item())
+
+
 class GatheredOutput:
     """Every rank's copy of the gathered C[M, N] (FP32), mapped into every process.
 
@@ -116,6 +162,10 @@ class GatheredOutput:
     raw device addresses. Multicast (NVLS) bindings are switched off before the
     first allocation; the fused kernels use plain peer stores. Collective: every
     rank of `group` must construct it with the same shape.
+
+    The barrier between steps is this library's own kernel (`b200_peer_barrier`):
+    flag stores to the peers, bounded local waits, and a status bit instead of a
+    spin when a partner never arrives.
     """
 
     def __init__(self, m: int, n: int, plan: Sequence[tuple[int, int]], group=None, device=None):
@@ -139,15 +189,39 @@ class GatheredOutput:
         first, rows = self.plan[self.rank]
         self.local_rows = self.full[first:first + rows]
         self.peer_ptrs = peer_row_pointers(self.base_ptrs, self.rank, first, n)
+        # Barrier flags: one 32-bit slot per source rank, zeroed before any peer can reach them
+        # (the rendezvous below is a host-side collective that follows this rank's synchronize).
+        self.flags = symm_mem.empty((8,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        self._flag_handle = symm_mem.rendezvous(self.flags, self.group)
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self._flag_handle.buffer_ptrs])
+        self._epoch = 0
 
-    def barrier(self) -> None:
+    def barrier(self, max_polls: int = 1 << 21) -> None:
         """All ranks' launches so far have completed: every copy of C is whole.
 
-        A device-side barrier on the current stream (signal pads of the
-        symmetric allocation), so no host synchronisation is needed between the
-        GEMM and a consumer kernel on the same stream.
+        A device-side barrier on the current stream, so no host synchronisation
+        is needed between the GEMM and a consumer kernel on the same stream.
+        Every rank must call it the same number of times. The wait is bounded
+        (`max_polls` polls per peer, of the order of a second by default); when
+        it runs out the kernel returns and `check()` reports it.
         """
-        self._handle.barrier()
+        self._epoch = (self._epoch + 1) & 0xFFFFFFFF
+        stream = torch.cuda.current_stream(self.full.device).cuda_stream
+        status = _abi().b200_peer_barrier(self._flag_ptrs, self.world, self.rank, self._epoch, max_polls,
+                                          ctypes.c_void_p(stream))
+        if status != 0:
+            raise RuntimeError(f"b200_peer_barrier failed with status {status}")
+
+    def check(self) -> None:
+        """Synchronises the current stream and raises if a device-side wait gave up since the last check."""
+        word = ctypes.c_uint32(0)
+        stream = torch.cuda.current_stream(self.full.device).cuda_stream
+        status = _abi().b200_device_status_read(ctypes.byref(word), ctypes.c_void_p(stream))
+        if status != 0 or word.value != 0:
+            what = "a peer never reached the barrier" if word.value & WAIT_PEER_BARRIER else "a device-side wait gave up"
+            raise RuntimeError(f"{what} (status {status}, wait sites {word.value:#x})")
 
 
 def sharded_gemm_gather(a_shard: torch.Tensor, b: torch.Tensor, out: GatheredOutput, impl: str = "prefetch_reg") -> torch.Tensor:

@@ -70,6 +70,37 @@ const char* b200_build_info(void);
  */
 int b200_device_status_read(uint32_t* host_word, b200_stream_t stream);
 
+/*
+ * Bits of the status word: which wait gave up.
+ */
+enum {
+  B200_WAIT_SGEMM_FULL = 1 << 0,    /* FP32 pipeline: consumer waiting for a TMA stage */
+  B200_WAIT_SGEMM_EMPTY = 1 << 1,   /* FP32 pipeline: producer waiting for a free stage */
+  B200_WAIT_UMMA_FULL = 1 << 2,     /* TF32: MMA issuer waiting for operands */
+  B200_WAIT_UMMA_EMPTY = 1 << 3,    /* TF32: producer waiting for a free stage */
+  B200_WAIT_UMMA_ACC_FULL = 1 << 4, /* TF32: epilogue waiting for an accumulator */
+  B200_WAIT_UMMA_ACC_EMPTY = 1 << 5,/* TF32: MMA issuer waiting for a drained accumulator */
+  B200_WAIT_UMMA_STORE = 1 << 6,
+  B200_WAIT_SELFTEST = 1 << 7,      /* b200_selftest_wait_gives_up */
+  B200_WAIT_PEER_BARRIER = 1 << 8   /* b200_peer_barrier: a peer never signalled the step */
+};
+
+/*
+ * Self tests of the safety plumbing; no reference counterpart. Neither faults,
+ * traps or hangs anything.
+ *   b200_selftest_wait_gives_up: one thread waits, with the library's bounded
+ *     wait capped at `max_polls` (1 .. 2^20) polls, on a barrier that nothing
+ *     completes. The kernel returns normally; *outcome (device memory, may be
+ *     NULL) receives 2 ("gave up") and the next b200_device_status_read returns
+ *     B200_ERR_DEVICE_TIMEOUT with B200_WAIT_SELFTEST set, the one after that
+ *     B200_OK.
+ *   b200_selftest_refused_launch: asks for a launch configuration the CUDA
+ *     runtime refuses on the host; returns B200_ERR_LAUNCH_FAILED. The refusal
+ *     must not outlive the call: the next valid launch returns B200_OK.
+ */
+int b200_selftest_wait_gives_up(uint32_t max_polls, uint32_t* outcome, b200_stream_t stream);
+int b200_selftest_refused_launch(b200_stream_t stream);
+
 /* ----------------------------------------------------- FP32 SIMT GEMM ladder */
 
 /*
@@ -281,6 +312,25 @@ int b200_sgemm_gather(int impl, const float* a_colmajor, const float* b, float* 
 int b200_tf32_gemm_dispatch_gather(int requested, const b200_gemm_problem* problem,
                                    float* const* peer_d, int n_peers,
                                    int* chosen, b200_stream_t stream);
+
+/*
+ * Device-side barrier between the ranks of a fused step: "every rank's launches
+ * enqueued before its barrier have completed, and their stores to the peers'
+ * copies are visible". flags_by_rank[r] (host array of `world` device
+ * pointers, world <= B200_MAX_PEERS + 1) is rank r's array of `world` 32-bit
+ * flags, mapped into this process and zeroed once before first use;
+ * flags_by_rank[rank] is this device's own. `epoch` is the step number: every
+ * rank passes the same value, larger at every call (wrap-around is fine).
+ * The kernel stores `epoch` into slot `rank` of every other array and waits,
+ * at most `max_polls` polls (1 .. 2^24, about a third of a microsecond each)
+ * per peer, for its own slots to reach it. A wait that runs out sets
+ * B200_WAIT_PEER_BARRIER in the status word and the kernel returns: a rank
+ * whose partner died or skipped the step does not spin on the GPU. Peer memory
+ * is only stored to. One launch, capturable. No reference counterpart (the
+ * reference is single-GPU, README.md:34).
+ */
+int b200_peer_barrier(uint32_t* const* flags_by_rank, int world, int rank,
+                      uint32_t epoch, uint32_t max_polls, b200_stream_t stream);
 
 #ifdef __cplusplus
 }

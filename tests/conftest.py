@@ -67,6 +67,9 @@ def load_abi() -> ctypes.CDLL:
     lib.b200_status_string.argtypes = [c_int]
     lib.b200_build_info.restype = c_char_p
     lib.b200_device_status_read.argtypes = [ctypes.POINTER(ctypes.c_uint32), c_void_p]
+    lib.b200_selftest_wait_gives_up.argtypes = [ctypes.c_uint32, c_void_p, c_void_p]
+    lib.b200_selftest_refused_launch.argtypes = [c_void_p]
+    lib.b200_peer_barrier.argtypes = [ctypes.POINTER(c_void_p), c_int, c_int, ctypes.c_uint32, ctypes.c_uint32, c_void_p]
     lib.b200_sgemm_impl_name.restype = c_char_p
     lib.b200_sgemm_impl_name.argtypes = [c_int]
     lib.b200_sgemm_impl_from_name.argtypes = [c_char_p]

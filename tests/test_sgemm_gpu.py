@@ -166,3 +166,15 @@ def test_abi_rejects_without_launching(abi):
     assert abi.b200_sgemm(impl, *args, 127, 128, 16, current_stream_ptr()) == 2
     assert abi.b200_sgemm(impl, *args, 128, 128, 0, current_stream_ptr()) == 4
     assert abi.b200_sgemm(impl, a.data_ptr() + 4, b.data_ptr(), c.data_ptr(), 128, 128, 8, current_stream_ptr()) == 1
+    # A misaligned output: every vectorised entry stores C with 128-bit accesses, so it is refused
+    # before any launch; the two scalar entries accept it.
+    big = torch.zeros(128 * 128 + 4, device="cuda")
+    shifted_c = big.data_ptr() + 4
+    for name in LADDER:
+        idx = abi.b200_sgemm_impl_from_name(name.encode())
+        status = abi.b200_sgemm(idx, a.data_ptr(), b.data_ptr(), shifted_c, 128, 128, 16, current_stream_ptr())
+        assert status == (0 if name in ("naive", "block_tile") else 1), name
+    peers = (ctypes.c_void_p * 1)(c.data_ptr())
+    assert abi.b200_sgemm_gather(impl, a.data_ptr(), b.data_ptr(), shifted_c, peers, 1, 128, 128, 16,
+                                 current_stream_ptr()) == 1
+    assert_device_clean(abi)

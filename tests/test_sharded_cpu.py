@@ -56,6 +56,127 @@ def test_two_rank_sharded_gemm_reassembles_the_full_product(m):
         assert shape_ok and err <= tol and shard_err <= tol, (rank, err, shard_err, tol)
 
 
+# ------------------------------------------------------------- failures, injected on the host
+# A rank that skips a collective, a rank that reports a failure, a rank that never joins: each is
+# simulated on the host with gloo ranks; the others must find out within their time-out.
+
+
+def _skipping_worker(rank: int, world: int, port: int, result_queue, done):
+    import time
+
+    from cuda_ai_kernels import sharded
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sharded.init_distributed("gloo", timeout_s=5.0)
+    try:
+        shard = torch.full((4, 8), float(rank))
+        # Step 1: everybody takes part.
+        full = sharded.all_gather_rows(shard, [4] * world)
+        assert full.shape == (4 * world, 8)
+        # Step 2: rank 1 "forgets" the collective. Rank 0 must get an error, not block for ever.
+        if rank == 1:
+            done.wait(timeout=60)                 # stay alive (a dead peer would be a different failure)
+            result_queue.put((rank, "skipped", 0.0))
+            return
+        t0 = time.monotonic()
+        try:
+            sharded.all_gather_rows(shard, [4] * world)
+            outcome = "returned"
+        except Exception as exc:  # noqa: BLE001
+            outcome = f"raised {type(exc).__name__}"
+        result_queue.put((rank, outcome, time.monotonic() - t0))
+        done.set()
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001 - the group is already broken on the rank that timed out
+            pass
+
+
+def test_a_rank_that_skips_the_all_gather_makes_the_others_raise_within_the_timeout():
+    ctx = mp.get_context("spawn")
+    queue, done = ctx.Queue(), ctx.Event()
+    port = _free_port()
+    procs = [ctx.Process(target=_skipping_worker, args=(r, 2, port, queue, done)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        results = dict((rank, (outcome, seconds)) for rank, outcome, seconds in (queue.get(timeout=90) for _ in procs))
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.terminate()
+    outcome, seconds = results[0]
+    assert outcome.startswith("raised"), results
+    assert seconds < 30.0, results                # the 5 s time-out, not an endless wait
+    assert results[1][0] == "skipped"
+
+
+def _agreeing_worker(rank: int, world: int, port: int, result_queue):
+    from cuda_ai_kernels import sharded
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sharded.init_distributed("gloo", timeout_s=20.0)
+    try:
+        barriers = 0
+        verdicts = []
+        for step in range(3):
+            ok = not (rank == 1 and step == 1)    # rank 1's work fails in step 1
+            agreed = sharded.all_ranks_ok(ok)
+            verdicts.append(agreed)
+            if not agreed:
+                break                             # nobody enqueues the device-side barrier of this step
+            barriers += 1
+        result_queue.put((rank, verdicts, barriers))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_agree_on_the_host_before_a_device_barrier():
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_agreeing_worker, args=(r, 2, port, queue)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [queue.get(timeout=90) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    for rank, verdicts, barriers in results:
+        assert verdicts == [True, False] and barriers == 1, (rank, verdicts, barriers)
+
+
+def _lonely_worker(port: int, result_queue):
+    import time
+
+    from cuda_ai_kernels import sharded
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK="0", WORLD_SIZE="2")
+    t0 = time.monotonic()
+    try:
+        sharded.init_distributed("gloo", timeout_s=3.0)
+        outcome = "joined"
+    except Exception as exc:  # noqa: BLE001
+        outcome = f"raised {type(exc).__name__}"
+    result_queue.put((outcome, time.monotonic() - t0))
+
+
+def test_set_up_gives_up_when_a_rank_never_joins():
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    proc = ctx.Process(target=_lonely_worker, args=(_free_port(), queue))
+    proc.start()
+    try:
+        outcome, seconds = queue.get(timeout=90)
+    finally:
+        proc.join(timeout=30)
+        if proc.is_alive():
+            proc.terminate()
+    assert outcome.startswith("raised") and seconds < 45.0, (outcome, seconds)
+
+
 def test_column_major_shard_rejects_views():
     from cuda_ai_kernels import sharded
 

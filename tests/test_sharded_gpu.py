@@ -21,59 +21,100 @@ def _free_port() -> int:
 
 
 def _worker(rank, world, port, m, n, k, queue):
+    """One rank. Work between two device-side barriers runs under try/except; before every barrier
+    the ranks agree on the host (gloo) that all of them got there, and skip it otherwise, so no
+    rank waits on the GPU for a partner that raised."""
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
                       TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    host_group = dist.new_group(backend="gloo")
+    failure = [None]
     try:
         import cuda_ai_kernels
         from cuda_ai_kernels import sharded
 
-        a, b = oracle.ladder_inputs(m, n, k, seed=0)
-        plan = sharded.shard_rows(m, world)
-        first, rows = plan[rank]
-        dev = torch.device("cuda", rank)
-        a_shard = sharded.column_major_shard(a.t().contiguous().to(dev), first, rows)
-        b_dev = b.to(dev)
-        expected = oracle.gemm_fp64(a, b)
-        tol = oracle.sgemm_abs_tolerance(a, b)
+        def phase(fn):
+            """Runs fn unless an earlier phase failed somewhere; True when every rank is still fine."""
+            if failure[0] is None:
+                try:
+                    fn()
+                except Exception as exc:  # noqa: BLE001 - reported to the parent below
+                    failure[0] = f"{type(exc).__name__}: {exc}"
+            return sharded.all_ranks_ok(failure[0] is None, host_group)
+
+        state = {}
         errors = {}
-        for impl in ("prefetch_reg", "split_k"):
-            c_shard = sharded.sharded_gemm(a_shard, b_dev, impl=impl)
-            full = sharded.all_gather_rows(c_shard, [count for _, count in plan])
-            errors[impl] = (full.cpu() - expected).abs().max().item()
-        # TF32 path: a row slab of row-major A is already contiguous.
-        a_rows = a[first:first + rows].contiguous().to(dev)
-        d_shard = cuda_ai_kernels.adaptive_gemm(a_rows, b_dev)
-        full = sharded.all_gather_rows(d_shard, [count for _, count in plan])
-        rel = oracle.rel_frobenius(full, expected)
-        # Fused all-gather: the kernels' epilogues store every tile into every rank's copy of C.
-        counts = [count for _, count in plan]
-        gathered = sharded.GatheredOutput(m, n, plan)
-        gathered.full.fill_(float("nan"))
-        gathered.barrier()
-        torch.cuda.synchronize()
-        reference = sharded.all_gather_rows(sharded.sharded_gemm(a_shard, b_dev, impl="prefetch_reg"), counts)
-        fused = sharded.sharded_gemm_gather(a_shard, b_dev, gathered, impl="prefetch_reg")
-        gathered.barrier()
-        torch.cuda.synchronize()
-        errors["fused_fp32_vs_collective"] = 0.0 if torch.equal(fused, reference) else float("inf")
-        errors["fused_fp32"] = (fused.cpu() - expected).abs().max().item()
-        gathered.barrier()                       # nobody overwrites a copy that a peer is still comparing
-        gathered.full.fill_(float("nan"))
-        gathered.barrier()
-        torch.cuda.synchronize()
-        fused = sharded.sharded_adaptive_gemm_gather(a_rows, b_dev, gathered, epilogue="relu")
-        gathered.barrier()
-        torch.cuda.synchronize()
-        rel_fused = oracle.rel_frobenius(fused, expected.relu())
-        reference = sharded.all_gather_rows(cuda_ai_kernels.adaptive_gemm(a_rows, b_dev, epilogue="relu"), counts)
-        errors["fused_tf32_vs_collective"] = 0.0 if torch.equal(fused, reference) else float("inf")
-        gathered.barrier()
-        queue.put((rank, errors, tol, max(rel, rel_fused)))
+
+        def setup():
+            a, b = oracle.ladder_inputs(m, n, k, seed=0)
+            plan = sharded.shard_rows(m, world)
+            first, rows = plan[rank]
+            dev = torch.device("cuda", rank)
+            state.update(a=a, b=b, plan=plan, counts=[count for _, count in plan], dev=dev,
+                         a_shard=sharded.column_major_shard(a.t().contiguous().to(dev), first, rows), b_dev=b.to(dev),
+                         a_rows=a[first:first + rows].contiguous().to(dev),   # TF32 path: a row slab is contiguous
+                         expected=oracle.gemm_fp64(a, b), tol=oracle.sgemm_abs_tolerance(a, b))
+
+        def unfused():
+            for impl in ("prefetch_reg", "split_k"):
+                c_shard = sharded.sharded_gemm(state["a_shard"], state["b_dev"], impl=impl)
+                full = sharded.all_gather_rows(c_shard, state["counts"])
+                errors[impl] = (full.cpu() - state["expected"]).abs().max().item()
+            d_shard = cuda_ai_kernels.adaptive_gemm(state["a_rows"], state["b_dev"])
+            full = sharded.all_gather_rows(d_shard, state["counts"])
+            state["rel"] = oracle.rel_frobenius(full, state["expected"])
+
+        def allocate():
+            # Fused all-gather: the kernels' epilogues store every tile into every rank's copy of C.
+            state["gathered"] = sharded.GatheredOutput(m, n, state["plan"])
+            state["gathered"].full.fill_(float("nan"))
+
+        def fused_fp32():
+            state["reference"] = sharded.all_gather_rows(
+                sharded.sharded_gemm(state["a_shard"], state["b_dev"], impl="prefetch_reg"), state["counts"])
+            state["fused"] = sharded.sharded_gemm_gather(state["a_shard"], state["b_dev"], state["gathered"],
+                                                         impl="prefetch_reg")
+
+        def compare_fp32():
+            state["gathered"].check()
+            fused = state["fused"]
+            errors["fused_fp32_vs_collective"] = 0.0 if torch.equal(fused, state["reference"]) else float("inf")
+            errors["fused_fp32"] = (fused.cpu() - state["expected"]).abs().max().item()
+
+        def refill():
+            torch.cuda.synchronize()
+            state["gathered"].full.fill_(float("nan"))
+
+        def fused_tf32():
+            state["fused"] = sharded.sharded_adaptive_gemm_gather(state["a_rows"], state["b_dev"], state["gathered"],
+                                                                  epilogue="relu")
+
+        def compare_tf32():
+            state["gathered"].check()
+            fused = state["fused"]
+            state["rel"] = max(state["rel"], oracle.rel_frobenius(fused, state["expected"].relu()))
+            reference = sharded.all_gather_rows(
+                cuda_ai_kernels.adaptive_gemm(state["a_rows"], state["b_dev"], epilogue="relu"), state["counts"])
+            errors["fused_tf32_vs_collective"] = 0.0 if torch.equal(fused, reference) else float("inf")
+
+        # Each entry: (work, barrier after it?). A barrier is enqueued only when every rank agreed.
+        for work, barrier_after in ((setup, False), (unfused, False), (allocate, True), (fused_fp32, True),
+                                    (compare_fp32, True),   # nobody overwrites a copy a peer is still comparing
+                                    (refill, True), (fused_tf32, True), (compare_tf32, True)):
+            if not phase(work):
+                break
+            if barrier_after:
+                state["gathered"].barrier()
+        if failure[0] is None and sharded.all_ranks_ok(True, host_group):
+            torch.cuda.synchronize()
+            queue.put((rank, errors, state["tol"], state["rel"], None))
+        else:
+            queue.put((rank, errors, 0.0, 0.0, failure[0] or "another rank failed"))
     finally:
+        torch.cuda.synchronize()
         dist.destroy_process_group()
 
 
@@ -88,13 +129,73 @@ def test_sharded_gemm_across_gpus():
     procs = [ctx.Process(target=_worker, args=(r, world, port, m, n, k, queue)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [queue.get(timeout=300) for _ in procs]
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
-    for rank, errors, tol, rel in results:
+    try:
+        results = [queue.get(timeout=300) for _ in procs]
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    finally:
+        # No child outlives the test, whatever happened above.
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+    for rank, errors, tol, rel, failure in results:
+        assert failure is None, (rank, failure)
         assert all(err <= tol for err in errors.values()), (rank, errors, tol)
         assert rel <= oracle.TF32_REL_FROBENIUS, (rank, rel)
+
+
+# ------------------------------------------------- the barrier kernel on a single GPU
+# Two flag arrays on one GPU stand in for two ranks. Only ONE barrier kernel runs per case (two
+# launches that wait for each other must never share a GPU): the partner's flag is either written
+# beforehand by the host or never written at all.
+
+
+def _barrier(abi, arrays, rank, epoch, polls):
+    import ctypes
+
+    from conftest import current_stream_ptr
+
+    ptrs = (ctypes.c_void_p * len(arrays))(*[t.data_ptr() for t in arrays])
+    return abi.b200_peer_barrier(ptrs, len(arrays), rank, epoch, polls, current_stream_ptr())
+
+
+def test_peer_barrier_signals_and_passes_when_the_partner_has_arrived(abi):
+    from conftest import assert_device_clean
+
+    arrays = [torch.zeros(8, dtype=torch.int32, device="cuda") for _ in range(3)]
+    arrays[0][1] = 5            # "rank 1 reached step 5"
+    arrays[0][2] = 6            # "rank 2 is already a step ahead"
+    torch.cuda.synchronize()
+    assert _barrier(abi, arrays, 0, 5, 1 << 16) == 0
+    torch.cuda.synchronize()
+    assert arrays[1][0].item() == 5 and arrays[2][0].item() == 5      # rank 0 told both partners
+    assert arrays[1][1].item() == 0 and arrays[0][0].item() == 0      # and touched nothing else
+    assert_device_clean(abi)
+    assert _barrier(abi, arrays[:1], 0, 1, 1) == 0                    # a world of one has nobody to wait for
+    assert_device_clean(abi)
+
+
+def test_peer_barrier_gives_up_when_the_partner_never_arrives(abi):
+    import ctypes
+
+    from conftest import current_stream_ptr
+
+    arrays = [torch.zeros(8, dtype=torch.int32, device="cuda") for _ in range(2)]
+    arrays[0][1] = 3            # the partner stopped at step 3
+    torch.cuda.synchronize()
+    assert _barrier(abi, arrays, 0, 4, 2048) == 0                     # 2048 polls: about a millisecond
+    torch.cuda.synchronize()                                          # returns: the kernel ended by itself
+    word = ctypes.c_uint32(0)
+    assert abi.b200_device_status_read(ctypes.byref(word), ctypes.c_void_p(current_stream_ptr())) == 6
+    assert word.value == 1 << 8
+    assert abi.b200_device_status_read(ctypes.byref(word), ctypes.c_void_p(current_stream_ptr())) == 0
+    assert arrays[1][0].item() == 4                                   # it did signal before waiting
+    for bad in ((arrays, 2, 1, 16), (arrays, 0, 1, 0), ([], 0, 1, 16)):
+        assert _barrier(abi, *bad) == 4
 
 
 # ---------------------------------------------------- fan-out on a single GPU
