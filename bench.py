@@ -4,7 +4,7 @@
                     [--sgemm-impl NAME] [--no-extras]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Headline workload (N = 1): FP32 SIMT GEMM, M = N = K = 4096, A column-major,
+Headline workload: FP32 SIMT GEMM, M = N = K = 4096 per GPU, A column-major,
 B and C row-major, N(0,1) inputs from seed 0 - the configuration the reference
 publishes its numbers on. One step is one `cuda_ai_kernels.gemm` call.
 
@@ -12,29 +12,37 @@ publishes its numbers on. One step is one `cuda_ai_kernels.gemm` call.
             events around exactly K steps on the launching stream; two input
             sets are rotated so that a step never finds its operands in L2.
   e2e       the same metric through the operator API from pinned HOST buffers:
-            host->device copies of A and B and the device->host read of C are
-            inside the timed region of every step; upload, GEMM and download of
-            neighbouring steps overlap on three streams.
+            host->device copies of the operands and the device->host read of C
+            are inside the timed region of every step; upload, GEMM and download
+            of neighbouring steps overlap on separate streams. With N > 1 every
+            rank uploads its rows of A and 1/N of B; B is completed on every GPU
+            by an all-gather over NVLink, so each byte of B crosses PCIe once.
   roofline  the dominant kernel against the FP32 FMA peak; `also` carries the
             TF32 tensor-core GEMM (tensor roofline) and the two row operators
-            (HBM roofline) measured in the same run, next to cuBLAS.
-  cpu_baseline  the reference's CPU-capable path - its FP64 torch matmul oracle -
-            timed on this host's cores (rank 0, N = 1).
+            (HBM roofline) measured in the same run, next to cuBLAS, cuBLASLt
+            with its fused epilogue and - when its build is present - the
+            upstream project's own kernels rebuilt for this GPU.
+  cpu_baseline  the reference's CPU-capable path - its FP64 torch matmul oracle,
+            with the FP32 product beside it - timed on this host's cores.
 
 N > 1 (one rank per GPU under torchrun): the GEMM is sharded along M - every
 rank owns 4096 rows of A and a full B, C stays sharded, no data-path collective
-(weak scaling). An all-gather of C over NCCL is timed separately and reported
-under `also`.
+(weak scaling). `also.c5` times the large sharded configuration (M = 32768
+split over the ranks, N = K = 8192; strong scaling) on the FP32 and the TF32
+path at every N, with the all-gather of C as a separate collective and fused
+into the kernels' epilogues.
 
 `--impl reference` times the reference's own CPU implementation of the path
-(the FP64 oracle expression) on the host cores, one full 4096^3 product per step.
+(the FP64 oracle expression) on all host cores, one full 4096^3 product per step.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
+import subprocess
 import sys
 import threading
 import time
@@ -49,20 +57,23 @@ for _p in (str(PACKAGE / "python"), str(REPO)):
         sys.path.insert(0, _p)
 
 M = N = K = 4096
+C5_M, C5_N, C5_K = 32768, 8192, 8192
 METRIC = "fp32_simt_gemm_4096_tflops"
 UNIT = "TFLOP/s"
 FP32_LANES_PER_SM = 128
 # The reference's published figure for this metric: split_k at 4096^3 on an
 # A800 80GB PCIe, 17.206 TFLOP/s (its README.md:17). Other hardware; per GPU.
 PUBLISHED_A800_SPLIT_K_TFLOPS = 17.206
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the
-# committed Nsight Compute captures of exactly these workloads (profiles/*.md).
-# bench.py cannot run ncu on itself; the figures are carried here so that the
-# roofline objects can set traffic beside the algorithmic bytes.
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels.
+# A benchmark cannot run Nsight Compute on itself, so the figures are carried here: each comes from
+# one `ncu` capture of one launch of that kernel (FP32 and TF32: at 2048^3, scaled by the tile count
+# to 4096^3 - operand traffic per tile does not depend on the problem size once it exceeds L2; row
+# operators: at the benchmark shape itself, 256 / 128 MiB per array). Beside them stand the
+# algorithmic bytes: 201 MB (FP32 and TF32 at 4096^3: A + B + C), 537 MB, 268 MB.
 NCU_TRAFFIC_BYTES = {
-    "sgemm_4096": 334.2e6 + 54.9e6,      # profiles/sgemm_pipeline_4096.md (algorithmic: 201 MB of operands + output)
-    "tf32_4096": 372.6e6 + 50.7e6,       # profiles/tf32_umma_4096.md (CTA-pair kernel)
-    "rmsnorm_16384x4096": 268.5e6 + 213.0e6,   # profiles/rowops_c4.md (writes partly still in L2 at kernel end)
+    "sgemm_4096": 334.2e6 + 54.9e6,
+    "tf32_4096": 372.6e6 + 50.7e6,
+    "rmsnorm_16384x4096": 268.5e6 + 213.0e6,   # writes partly still in L2 at kernel end
     "softmax_32768x1024": 134.2e6 + 78.2e6,
 }
 
@@ -75,6 +86,22 @@ def load_peaks() -> dict:
         return peaks
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "sm_max_mhz": 1965.0,
             "source": "fallback"}
+
+
+def host_threads() -> int:
+    """Cores this process may run on (torchrun exports OMP_NUM_THREADS=1, which is not the machine)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def make_config(world: int, impl: str) -> dict:
+    """`config` of the JSON line; the same object in both arms (the reference arm times the same workload)."""
+    return {"workload": f"fp32_gemm_{M}x{N}x{K}_colmajorA", "impl": impl,
+            "sharding": "rows of A per rank, B replicated, C sharded" if world > 1 else "single GPU",
+            "rows_per_gpu": M, "global_m": M * world,
+            "l2": "two input sets alternate (A+B 256 MB > 126 MB L2), no flush kernel"}
 
 
 class ClockSampler:
@@ -116,6 +143,8 @@ class ClockSampler:
             time.sleep(self._period)
 
     def __enter__(self):
+        self.samples = []
+        self._stop.clear()
         if self._handle is not None:
             self._thread = threading.Thread(target=self._loop, daemon=True)
             self._thread.start()
@@ -125,6 +154,10 @@ class ClockSampler:
         self._stop.set()
         if self._thread is not None:
             self._thread.join()
+            self._thread = None
+
+    def median_mhz(self):
+        return statistics.median(s[0] for s in self.samples) if self.samples else None
 
     def summary(self) -> dict:
         if not self.samples:
@@ -149,7 +182,7 @@ class ClockSampler:
         }
 
 
-def event_time_ms(fn, steps: int, stream=None) -> float:
+def event_time_ms(fn, steps: int) -> float:
     """Device time of `steps` calls of fn(i), CUDA events on the current stream."""
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
@@ -161,24 +194,52 @@ def event_time_ms(fn, steps: int, stream=None) -> float:
     return begin.elapsed_time(end)
 
 
-def cpu_oracle_seconds(a_cpu, b_cpu, repeats: int) -> float:
-    from oracle import oracle
-
-    oracle.gemm_fp64(a_cpu, b_cpu)  # warm-up
+def best_seconds(fn, repeats: int) -> float:
+    fn()  # warm-up
     best = float("inf")
     for _ in range(repeats):
         t0 = time.perf_counter()
-        oracle.gemm_fp64(a_cpu, b_cpu)
+        fn()
         best = min(best, time.perf_counter() - t0)
     return best
 
 
-def run_reference(args, rank: int) -> None:
-    """The reference's CPU path (its FP64 torch oracle) on the host cores."""
+def cpu_baseline_block(a_cpu, b_cpu, repeats: int) -> dict:
+    """The reference's CPU-capable path on this host: FP64 oracle product, FP32 product beside it."""
+    from oracle import oracle
+
+    cores = torch.get_num_threads()
+    flop = 2.0 * M * N * K
+    fp64_s = best_seconds(lambda: oracle.gemm_fp64(a_cpu, b_cpu), repeats)
+    fp32_s = best_seconds(lambda: a_cpu @ b_cpu, repeats)
+    return {"value": flop / fp64_s / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+            "fp32_value": flop / fp32_s / 1e12,
+            "sample": f"full {M}x{N}x{K} product, best of {repeats} after 1 warm-up: FP64 torch matmul oracle "
+                      f"(A.double() @ B.double()).float() {fp64_s:.3f} s, FP32 A @ B (column-major A) {fp32_s:.3f} s; "
+                      f"{cores} threads, host has {os.cpu_count()} logical CPUs"}
+
+
+def cpu_rowop_seconds() -> dict:
+    """The reference's CPU oracle for the row operators at the benchmark shapes, one pass each after a warm-up."""
+    from oracle import oracle
+
+    x, w = oracle.rmsnorm_inputs(16384, 4096, seed=0)
+    logits = oracle.softmax_inputs(32768, 1024, seed=0)
+    out = {"threads": torch.get_num_threads()}
+    out["rmsnorm_fp32_s"] = best_seconds(lambda: x * torch.rsqrt(torch.mean(x * x, dim=-1, keepdim=True) + 1e-6) * w, 1)
+    out["rmsnorm_fp64_s"] = best_seconds(lambda: oracle.rmsnorm_fp64(x, w, 1e-6), 1)
+    out["softmax_fp32_s"] = best_seconds(lambda: torch.softmax(logits, dim=1), 1)
+    out["softmax_fp64_s"] = best_seconds(lambda: oracle.softmax_fp64(logits), 1)
+    return out
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    """The reference's CPU path (its FP64 torch oracle) on all host cores; rank 0 only."""
     if rank != 0:
         return
     from oracle import oracle
 
+    torch.set_num_threads(host_threads())
     a_cpu, b_cpu = oracle.ladder_inputs(M, N, K, seed=0)
     for _ in range(args.warmup):
         oracle.gemm_fp64(a_cpu, b_cpu)
@@ -187,63 +248,130 @@ def run_reference(args, rank: int) -> None:
         oracle.gemm_fp64(a_cpu, b_cpu)
     elapsed = time.perf_counter() - t0
     tflops = 2.0 * M * N * K * args.steps / elapsed / 1e12
+    fp32_s = best_seconds(lambda: a_cpu @ b_cpu, 3)
     cores = torch.get_num_threads()
-    sample = f"{args.steps} full {M}x{N}x{K} FP64 products, (A.double() @ B.double()).float(), column-major A"
+    sample = (f"{args.steps} full {M}x{N}x{K} FP64 products, (A.double() @ B.double()).float(), column-major A; "
+              f"FP32 A @ B best of 3: {fp32_s:.3f} s; {cores} threads of {os.cpu_count()} logical CPUs")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * elapsed / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": f"fp32_gemm_{M}x{N}x{K}_colmajorA", "host_cores": os.cpu_count()},
-        "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": make_config(world, args.sgemm_impl),
+        "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                         "fp32_value": 2.0 * M * N * K / fp32_s / 1e12},
         "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
 
 
-def measure_extras(pkg, peaks: dict, steps: int, warmup: int) -> dict:
+# ------------------------------------------------------------------ comparisons on one GPU
+
+
+class Comparator:
+    """Times competing implementations of one workload so that the ranking does not depend on the
+    order: the arms are interleaved (a, b, c, a, b, c, ...) over `rounds` rounds, every measurement
+    records the median SM clock seen while it ran, and the median over the rounds is reported with
+    the clock and the clock-normalised time (ms x MHz) beside it."""
+
+    def __init__(self, device_index: int, warmup: int, rounds: int = 3, target_ms: float = 30.0):
+        self.sampler = ClockSampler(device_index)
+        self.warmup, self.rounds, self.target_ms = warmup, rounds, target_ms
+
+    def run(self, arms: dict) -> dict:
+        steps = {}
+        for name, fn in arms.items():
+            for i in range(self.warmup):
+                fn(i)
+            probe = event_time_ms(fn, 3) / 3
+            steps[name] = int(min(2000, max(5, math.ceil(self.target_ms / max(probe, 1e-4)))))
+        samples = {name: [] for name in arms}
+        for _ in range(self.rounds):
+            for name, fn in arms.items():
+                fn(0)
+                with self.sampler:
+                    ms = event_time_ms(fn, steps[name]) / steps[name]
+                samples[name].append((ms, self.sampler.median_mhz()))
+        out = {}
+        for name, vals in samples.items():
+            ms = statistics.median(v[0] for v in vals)
+            clocks = [v[1] for v in vals if v[1] is not None]
+            mhz = statistics.median(clocks) if clocks else None
+            out[name] = {"ms": ms, "min_ms": min(v[0] for v in vals), "mhz": mhz,
+                         "ms_x_mhz": ms * mhz if mhz else None, "steps": steps[name], "rounds": self.rounds}
+        return out
+
+
+def graph_us(fn) -> dict:
+    """The reference's headline method (benchmarks/bench_gemm_all.py:46-77): 10 calls captured in a
+    CUDA graph, warm-up 10, 50 timed replays; microseconds per call."""
+    from cuda_ai_kernels.benchmark import cuda_graph_benchmark
+
+    t = cuda_graph_benchmark(fn, warmup=10, repeat=50, calls_per_graph=10)
+    return {"median_us": 1e3 * t["p50_ms"], "mean_us": 1e3 * t["mean_ms"], "min_us": 1e3 * t["min_ms"]}
+
+
+def eager_rmsnorm(x, w, eps: float = 1e-6):
+    """Eager PyTorch RMSNorm on the GPU, as the reference's benchmark times it (benchmarks/bench_rmsnorm.py:27-29)."""
+    return x * torch.rsqrt(torch.mean(x * x, dim=-1, keepdim=True) + eps) * w
+
+
+def measure_extras(pkg, peaks: dict, device_index: int, warmup: int) -> dict:
     """TF32 GEMM, row operators and library baselines, same process, same GPU."""
-    from oracle import oracle
-
     out: dict = {}
-    dev = "cuda"
+    dev = torch.device("cuda", device_index)
+    cmp = Comparator(device_index, warmup)
+    from cuda_ai_kernels import _C
 
-    def timed(fn, flush=None):
-        for i in range(warmup):
-            fn(i)
-        return event_time_ms(fn, steps) / steps
+    def put(prefix: str, result: dict, work: float, unit_scale: float, unit: str):
+        """`work / time` under `<prefix>_<unit>` with clock and clock-normalised time beside it."""
+        out[f"{prefix}_{unit}"] = work / result["ms"] / unit_scale
+        out[f"{prefix}_ms"] = result["ms"]
+        out[f"{prefix}_mhz"] = result["mhz"]
+        out[f"{prefix}_ms_x_mhz"] = result["ms_x_mhz"]
 
-    # cuBLAS strict-FP32 SGEMM through the operator API, same inputs as the headline.
+    # FP32 ladder and cuBLAS strict-FP32 SGEMM through the operator API, same inputs as the headline.
     a_sets = [torch.randn(K, M, device=dev).t() for _ in range(2)]
     b_sets = [torch.randn(K, N, device=dev) for _ in range(2)]
-    flops = 2.0 * M * N * K
-    for name in ("cublas", "prefetch_smem", "prefetch_reg", "split_k", "thread_tile_8x8", "warp_tile"):
-        ms = timed(lambda i, name=name: pkg.gemm(a_sets[i & 1], b_sets[i & 1], impl=name))
-        out[f"sgemm_{name}_tflops"] = flops / ms / 1e9
+    names = ("cublas", "prefetch_smem", "prefetch_reg", "split_k", "thread_tile_8x8", "warp_tile")
+    res = cmp.run({name: (lambda i, name=name: pkg.gemm(a_sets[i & 1], b_sets[i & 1], impl=name)) for name in names})
+    for name in names:
+        put(f"sgemm_{name}", res[name], 2.0 * M * N * K, 1e9, "tflops")
     del a_sets, b_sets
     # The other two FP32 benchmark shapes: 1024^3 and 1024 x 4096 x 4096, where tiles do not fill
     # whole rounds of SMs and the stream-K entry (output cleared inside the timed call) matters.
     for (m_, n_, k_) in ((1024, 1024, 1024), (1024, 4096, 4096)):
         a_small = [torch.randn(k_, m_, device=dev).t() for _ in range(2)]
         b_small = [torch.randn(k_, n_, device=dev) for _ in range(2)]
-        for name in ("cublas", "prefetch_reg", "split_k"):
-            ms = timed(lambda i, name=name: pkg.gemm(a_small[i & 1], b_small[i & 1], impl=name))
-            out[f"sgemm_{name}_{m_}x{n_}x{k_}_tflops"] = 2.0 * m_ * n_ * k_ / ms / 1e9
+        names = ("cublas", "prefetch_smem", "prefetch_reg", "split_k")
+        res = cmp.run({name: (lambda i, name=name: pkg.gemm(a_small[i & 1], b_small[i & 1], impl=name)) for name in names})
+        for name in names:
+            put(f"sgemm_{name}_{m_}x{n_}x{k_}", res[name], 2.0 * m_ * n_ * k_, 1e9, "tflops")
+            g = graph_us(lambda name=name: pkg.gemm(a_small[0], b_small[0], impl=name))
+            out[f"sgemm_{name}_{m_}x{n_}x{k_}_graph_us"] = g["median_us"]
+            out[f"sgemm_{name}_{m_}x{n_}x{k_}_graph_min_us"] = g["min_us"]
         del a_small, b_small
 
-    # TF32 tcgen05 GEMM with fused epilogue, D = relu(A@B + 0.5*C), and cuBLAS TF32.
+    # TF32 tcgen05 GEMM with fused epilogue, D = relu(A@B + 0.5*C) and the linear form, against
+    # cuBLAS TF32 + a separate ReLU pass (what the reference ships) and cuBLASLt with the ReLU fused
+    # by the library (the fair competitor), interleaved.
     tf32_peak = peaks["bf16_tflops"] / 2.0
     for size in (4096, 8192):
         a = [torch.randn(size, size, device=dev) for _ in range(2)]
         b = [torch.randn(size, size, device=dev) for _ in range(2)]
         c = torch.randn(size, size, device=dev)
-        f = 2.0 * size ** 3
-        ms = timed(lambda i: pkg.adaptive_gemm(a[i & 1], b[i & 1], c=c, alpha=1.0, beta=0.5, epilogue="relu"))
-        out[f"tf32_relu_{size}_tflops"] = f / ms / 1e9
-        ms = timed(lambda i: pkg.adaptive_gemm(a[i & 1], b[i & 1], c=c, alpha=1.0, beta=0.5, epilogue="linear"))
-        out[f"tf32_linear_{size}_tflops"] = f / ms / 1e9
-        ms = timed(lambda i: torch.relu_(pkg.adaptive_gemm(a[i & 1], b[i & 1], c=c, alpha=1.0, beta=0.5,
-                                                           kernel="cublas")))
-        out[f"tf32_cublas_unfused_relu_{size}_tflops"] = f / ms / 1e9
+        arms = {
+            "relu": lambda i: pkg.adaptive_gemm(a[i & 1], b[i & 1], c=c, alpha=1.0, beta=0.5, epilogue="relu"),
+            "cublaslt_fused_relu": lambda i: pkg.adaptive_gemm(a[i & 1], b[i & 1], c=c, alpha=1.0, beta=0.5,
+                                                               epilogue="relu", kernel="cublaslt"),
+            "linear": lambda i: pkg.adaptive_gemm(a[i & 1], b[i & 1], c=c, alpha=1.0, beta=0.5, epilogue="linear"),
+            "cublas_unfused_relu": lambda i: torch.relu_(pkg.adaptive_gemm(a[i & 1], b[i & 1], c=c, alpha=1.0, beta=0.5,
+                                                                           kernel="cublas")),
+        }
+        res = cmp.run(arms)
+        for name in arms:
+            put(f"tf32_{name}_{size}", res[name], 2.0 * size ** 3, 1e9, "tflops")
+        arms["relu"](0)
+        out[f"tf32_relu_{size}_kernel"] = _C.adaptive_gemm_last_kernel()
         del a, b, c
     out["tf32_roofline"] = {"bound": "tensor", "achieved": out["tf32_relu_4096_tflops"], "peak": tf32_peak,
                             "unit": "TFLOP/s", "frac": out["tf32_relu_4096_tflops"] / tf32_peak,
@@ -252,38 +380,46 @@ def measure_extras(pkg, peaks: dict, steps: int, warmup: int) -> dict:
 
     # TF32 registry entries for the shapes the tile kernels fit badly, each beside cuBLAS TF32
     # (microseconds per call, alpha = 1, beta = 0): 1024^3 (benchmark configuration), decode-like
-    # rows (FP32 stream / split-K cluster), misaligned operands (warp-specialised loader).
-    from cuda_ai_kernels import _C
-
+    # rows (FP32 stream / split-K cluster), misaligned operands (warp-specialised loader). Event
+    # timing through the API (includes the host's launch path) and graph timing (device time).
     for label, (m_, n_, k_) in (("1024", (1024, 1024, 1024)), ("1x4096x4096", (1, 4096, 4096)),
                                 ("16x4096x4096", (16, 4096, 4096)), ("1024x1024x8192", (1024, 1024, 8192)),
                                 ("4095x4093x4091", (4095, 4093, 4091))):
         a = [torch.randn(m_, k_, device=dev) for _ in range(2)]
         b = [torch.randn(k_, n_, device=dev) for _ in range(2)]
-        ms = timed(lambda i: pkg.adaptive_gemm(a[i & 1], b[i & 1]))
-        out[f"tf32_{label}_us"] = ms * 1e3
+        arms = {"ours": lambda i: pkg.adaptive_gemm(a[i & 1], b[i & 1]),
+                "cublas": lambda i: pkg.adaptive_gemm(a[i & 1], b[i & 1], kernel="cublas")}
+        res = cmp.run(arms)
+        out[f"tf32_{label}_us"] = 1e3 * res["ours"]["ms"]
+        out[f"tf32_{label}_cublas_us"] = 1e3 * res["cublas"]["ms"]
+        out[f"tf32_{label}_mhz"] = res["ours"]["mhz"]
+        out[f"tf32_{label}_cublas_mhz"] = res["cublas"]["mhz"]
+        arms["ours"](0)
         out[f"tf32_{label}_kernel"] = _C.adaptive_gemm_last_kernel()
-        ms = timed(lambda i: pkg.adaptive_gemm(a[i & 1], b[i & 1], kernel="cublas"))
-        out[f"tf32_{label}_cublas_us"] = ms * 1e3
+        if m_ * n_ * k_ <= 1024 * 1024 * 8192:
+            g = graph_us(lambda: pkg.adaptive_gemm(a[0], b[0]))
+            gc = graph_us(lambda: pkg.adaptive_gemm(a[0], b[0], kernel="cublas"))
+            out[f"tf32_{label}_graph_us"], out[f"tf32_{label}_graph_min_us"] = g["median_us"], g["min_us"]
+            out[f"tf32_{label}_cublas_graph_us"], out[f"tf32_{label}_cublas_graph_min_us"] = gc["median_us"], gc["min_us"]
         del a, b
 
     # Row operators: bytes = one read of x + one write of y (+ weight once).
     rows, hidden = 16384, 4096
     xs = [torch.randn(rows, hidden, device=dev) for _ in range(2)]
     w = torch.rand(hidden, device=dev) + 0.5
-    ms = timed(lambda i: pkg.rmsnorm(xs[i & 1], w, 1e-6))
     rms_bytes = 2.0 * rows * hidden * 4 + hidden * 4
-    out["rmsnorm_16384x4096_gbs"] = rms_bytes / ms / 1e6
-    ms = timed(lambda i: oracle_free_torch_rmsnorm(xs[i & 1], w))
-    out["rmsnorm_torch_gbs"] = rms_bytes / ms / 1e6
+    res = cmp.run({"ours": lambda i: pkg.rmsnorm(xs[i & 1], w, 1e-6), "torch": lambda i: eager_rmsnorm(xs[i & 1], w)})
+    out["rmsnorm_16384x4096_gbs"] = rms_bytes / res["ours"]["ms"] / 1e6
+    out["rmsnorm_torch_gbs"] = rms_bytes / res["torch"]["ms"] / 1e6
+    out["rmsnorm_16384x4096_mhz"] = res["ours"]["mhz"]
     del xs
     rows, cols = 32768, 1024
     ls = [2 * torch.randn(rows, cols, device=dev) for _ in range(3)]   # 3 x 128 MiB rotate through L2
-    ms = timed(lambda i: pkg.softmax(ls[i % 3]))
     sm_bytes = 2.0 * rows * cols * 4
-    out["softmax_32768x1024_gbs"] = sm_bytes / ms / 1e6
-    ms = timed(lambda i: torch.softmax(ls[i % 3], dim=1))
-    out["softmax_torch_gbs"] = sm_bytes / ms / 1e6
+    res = cmp.run({"ours": lambda i: pkg.softmax(ls[i % 3]), "torch": lambda i: torch.softmax(ls[i % 3], dim=1)})
+    out["softmax_32768x1024_gbs"] = sm_bytes / res["ours"]["ms"] / 1e6
+    out["softmax_torch_gbs"] = sm_bytes / res["torch"]["ms"] / 1e6
+    out["softmax_32768x1024_mhz"] = res["ours"]["mhz"]
     del ls
     for key in ("rmsnorm_16384x4096_gbs", "softmax_32768x1024_gbs"):
         out[key.replace("_gbs", "_roofline")] = {
@@ -293,10 +429,188 @@ def measure_extras(pkg, peaks: dict, steps: int, warmup: int) -> dict:
     return out
 
 
-def oracle_free_torch_rmsnorm(x, w, eps: float = 1e-6):
-    """Eager PyTorch RMSNorm on the GPU, as the reference's benchmark times it
-    (benchmarks/bench_rmsnorm.py:27-29)."""
-    return x * torch.rsqrt(torch.mean(x * x, dim=-1, keepdim=True) + eps) * w
+def rebuilt_reference_figures() -> dict:
+    """The upstream project's own kernels, rebuilt for this GPU, timed in a child process (both
+    packages are called `cuda_ai_kernels`). Present only where that build was staged beside the
+    repository; otherwise the reason is reported."""
+    ref_pkg = REPO / "baseline" / "_ref" / "cuda_ai_kernels"
+    if not ref_pkg.is_dir() or not list(ref_pkg.glob("_C*.so")):
+        return {"unavailable": "no rebuilt upstream extension under baseline/_ref"}
+    script = PACKAGE / "benchmarks" / "compare_reference.py"
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT")}
+    try:
+        proc = subprocess.run([sys.executable, str(script), "--arm", "reference", "--quick"], capture_output=True,
+                              text=True, timeout=600, env=env)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "child process exceeded 600 s"}
+    line = next((l for l in proc.stdout.splitlines() if l.startswith("RESULT ")), None)
+    if line is None:
+        return {"unavailable": (proc.stderr or proc.stdout)[-300:]}
+    data = json.loads(line[7:])
+    out = {"method": "CUDA-graph replay, median", "module": data.get("module")}
+    for item in data.get("gemm", []):
+        out[f"sgemm_{item['impl']}_{'x'.join(map(str, item['shape']))}_tflops"] = item["tflops_median"]
+    for item in data.get("adaptive", []):
+        out[f"tf32_{item['case']}_{item['size']}_tflops"] = item["tflops_median"]
+    for item in data.get("rows", []):
+        out[f"{item['case']}_gbs"] = item["gbs_median"]
+    return out
+
+
+# ------------------------------------------------------------------------ host link
+
+
+def measure_host_link(dev, world: int, dist) -> dict:
+    """Plain pinned cudaMemcpyAsync bandwidth of this rank's host link, all ranks copying at once."""
+    nbytes = 256 << 20
+    host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    device = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    device.copy_(host, non_blocking=True)
+    torch.cuda.synchronize()
+    out = {}
+    for name, fn in (("h2d", lambda i: device.copy_(host, non_blocking=True)),
+                     ("d2h", lambda i: host.copy_(device, non_blocking=True))):
+        if world > 1:
+            dist.barrier()
+        gbs = nbytes * 4 / event_time_ms(fn, 4) / 1e6
+        if world > 1:
+            t = torch.tensor([gbs], device=dev)
+            gathered = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(gathered, t)
+            vals = [float(g.item()) for g in gathered]
+        else:
+            vals = [gbs]
+        out[f"{name}_gbs_per_rank"] = round(statistics.fmean(vals), 2)
+        out[f"{name}_gbs_per_rank_min"] = round(min(vals), 2)
+        out[f"{name}_gbs_aggregate"] = round(sum(vals), 2)
+    return out
+
+
+# ---------------------------------------------------------------- the sharded configuration
+
+
+def measure_c5(pkg, dev, rank: int, world: int, dist, impl: str, device_index: int) -> dict:
+    """M = 32768 split over the ranks, N = K = 8192 (strong scaling): FP32 SIMT and TF32 paths,
+    all-gather of C as a separate collective and fused into the kernels' epilogues."""
+    from cuda_ai_kernels import _C, sharded
+
+    out: dict = {"m": C5_M, "n": C5_N, "k": C5_K, "n_gpus": world}
+    plan = sharded.shard_rows(C5_M, world)
+    first, rows = plan[rank]
+    out["rows_per_rank"] = rows
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    b = torch.randn(C5_K, C5_N, device=dev, generator=g)          # replicated: same seed on every rank
+    g.manual_seed(1000 + rank)
+    a_rows = torch.randn(rows, C5_K, device=dev, generator=g)     # TF32 path: contiguous row slab
+    a_col = a_rows.t().contiguous().t()                           # FP32 path: column-major shard, made once
+
+    # Parity gate on 48 sampled rows of this rank's shard (a row of C depends on that row of A only).
+    sample = torch.randperm(rows, device=dev, generator=g)[:48]
+    expected = (a_rows[sample].cpu().double() @ b.cpu().double()).float()
+    c = pkg.gemm(a_col, b, impl=impl)
+    tol = 1e-4 * C5_K ** 0.5 * float(a_rows.abs().max()) * float(b.abs().max())
+    err32 = (c[sample].cpu() - expected).abs().max().item()
+    d = pkg.adaptive_gemm(a_rows, b)
+    out["tf32_kernel"] = _C.adaptive_gemm_last_kernel()
+    rel = float((d[sample].cpu().double() - expected.double()).norm() / expected.double().norm())
+    del d
+    gate = torch.tensor([int(err32 <= tol and rel <= 5e-3)], device=dev)
+    if world > 1:
+        dist.all_reduce(gate, op=dist.ReduceOp.MIN)
+    out["parity"] = {"fp32_max_abs_error": err32, "fp32_tolerance": tol, "tf32_rel_frobenius": rel, "rows_sampled": 48,
+                     "passed_on_every_rank": bool(gate.item())}
+    if not bool(gate.item()):
+        out["error"] = "parity gate failed; nothing timed"
+        return out
+
+    def reduce_max(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    flop = 2.0 * C5_M * C5_N * C5_K
+    sampler = ClockSampler(device_index)
+
+    def timed(fn, warm: int, steps: int) -> tuple[float, object]:
+        for i in range(warm):
+            fn(i)
+        if world > 1:
+            dist.barrier()
+        with sampler:
+            ms = event_time_ms(fn, steps) / steps
+        return reduce_max(ms), sampler.median_mhz()
+
+    ms, mhz = timed(lambda i: pkg.gemm(a_col, b, impl=impl), 2, 3)
+    out.update(fp32_ms=ms, fp32_tflops_total=flop / ms / 1e9, fp32_mhz=mhz)
+    ms, mhz = timed(lambda i: pkg.adaptive_gemm(a_rows, b), 3, 10)
+    out.update(tf32_ms=ms, tf32_tflops_total=flop / ms / 1e9, tf32_mhz=mhz)
+    if world == 1:
+        return out
+
+    # All-gather of the 1 GiB C: as a collective on its own, after the GEMM, and fused into the GEMM.
+    counts = [count for _, count in plan]
+    full = torch.empty(C5_M, C5_N, device=dev)
+    ms, _ = timed(lambda i: dist.all_gather_into_tensor(full, c), 2, 5)
+    received = (C5_M - rows) * C5_N * 4
+    out.update(allgather_c_ms=ms, allgather_c_recv_gbs_per_rank=received / ms / 1e6)
+    ms, _ = timed(lambda i: dist.all_gather_into_tensor(full, pkg.gemm(a_col, b, impl=impl)), 1, 3)
+    out["fp32_then_allgather_ms"] = ms
+    ms, _ = timed(lambda i: dist.all_gather_into_tensor(full, pkg.adaptive_gemm(a_rows, b)), 2, 10)
+    out["tf32_then_allgather_ms"] = ms
+
+    fused_impl = impl if impl in ("prefetch_smem", "prefetch_reg") else "prefetch_reg"
+    gathered, why = None, ""
+    try:
+        gathered = sharded.GatheredOutput(C5_M, C5_N, plan)
+    except Exception as exc:  # noqa: BLE001
+        why = f"{type(exc).__name__}: {exc}"[:200]
+    if not sharded.all_ranks_ok(gathered is not None):
+        out["fused_error"] = why or "symmetric allocation failed on another rank"
+        return out
+    failure = [None]
+
+    def guarded(fn):
+        """A step of the fused path; after a failure nothing more is enqueued on this rank (the
+        others' bounded barriers give up and report instead of spinning)."""
+        def run(i):
+            if failure[0] is None:
+                try:
+                    fn(i)
+                    gathered.barrier()
+                except Exception as exc:  # noqa: BLE001
+                    failure[0] = f"{type(exc).__name__}: {exc}"[:200]
+        return run
+
+    fp32_fused = guarded(lambda i: sharded.sharded_gemm_gather(a_col, b, gathered, impl=fused_impl))
+    tf32_fused = guarded(lambda i: sharded.sharded_adaptive_gemm_gather(a_rows, b, gathered))
+    same = []
+    for fused_fn, collective in ((fp32_fused, lambda: pkg.gemm(a_col, b, impl=fused_impl)),
+                                 (tf32_fused, lambda: pkg.adaptive_gemm(a_rows, b))):
+        dist.all_gather_into_tensor(full, collective())
+        fused_fn(0)
+        torch.cuda.synchronize()
+        same.append(bool(torch.equal(gathered.full, full)))
+        if not sharded.all_ranks_ok(failure[0] is None):
+            break
+        gathered.barrier()      # nobody overwrites a copy that a peer is still comparing
+    ok = sharded.all_ranks_ok(failure[0] is None and all(same) and len(same) == 2)
+    out["fused_bit_identical"] = ok
+    if ok:
+        ms, _ = timed(fp32_fused, 1, 3)
+        out["fp32_fused_ms"] = ms
+        ms, _ = timed(tf32_fused, 2, 10)
+        out["tf32_fused_ms"] = ms
+        try:
+            gathered.check()
+        except RuntimeError as exc:
+            failure[0] = str(exc)[:200]
+    if failure[0] is not None:
+        out["fused_error"] = failure[0]
+    out["fused_impl"] = fused_impl
+    return out
 
 
 def main() -> None:
@@ -315,24 +629,28 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, world)
         return
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
     torch.cuda.set_device(local_rank)
+    torch.set_num_threads(max(1, host_threads() // max(1, world)))   # the parity gates run on the CPU
+    dev = torch.device("cuda", local_rank)
     distributed = world > 1
+    dist = None
     if distributed:
-        import torch.distributed as dist
+        import torch.distributed as dist  # noqa: F811
 
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        from cuda_ai_kernels import sharded
+
+        sharded.init_distributed("nccl", timeout_s=600.0, device=dev)
 
     import cuda_ai_kernels as pkg
     from cuda_ai_kernels import _C  # noqa: F401 - no extension, no benchmark
     from oracle import oracle
 
     peaks = load_peaks()
-    dev = torch.device("cuda", local_rank)
     impl = args.sgemm_impl
     launches_per_step = 2 if impl == "split_k" else 1  # split_k clears its output with a memset node first
 
@@ -371,17 +689,20 @@ def main() -> None:
     value = flops_per_step * args.steps / elapsed_ms / 1e9
     per_gpu_tflops = value / world
 
-    # End to end through the operator API from pinned host memory. Every step
-    # copies its A and B from the host and reads its C back. The three legs run
-    # on three streams with two device slots, so the upload of step i + 1 and
-    # the download of step i - 1 overlap the GEMM of step i (PCIe is full
-    # duplex); nothing is skipped, reused or left on the device.
+    # End to end through the operator API from pinned host memory. Every step copies its operands
+    # from the host and reads its C back; the legs run on separate streams with two device slots, so
+    # the upload of step i + 1 and the download of step i - 1 overlap the GEMM of step i (PCIe is
+    # full duplex); nothing is skipped, reused or left on the device. With several ranks a rank
+    # uploads its own rows of A and K / world rows of B; an all-gather over NVLink (NCCL) completes
+    # B on every GPU, so every byte of B crosses PCIe once instead of once per rank.
+    k_rows = K // world
     a_host = a_cpu.t().contiguous().pin_memory()   # storage [K, M]
-    b_host = b_cpu.contiguous().pin_memory()
+    b_host = b_cpu[rank * k_rows:(rank + 1) * k_rows].contiguous().pin_memory()   # this rank's rows of B (all of it alone)
     c_host = [torch.empty(M, N).pin_memory() for _ in range(2)]
     a_stage = [torch.empty(K, M, device=dev) for _ in range(2)]
-    b_stage = [torch.empty(K, N, device=dev) for _ in range(2)]
-    up, compute, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    b_part = [torch.empty(k_rows, N, device=dev) for _ in range(2)]
+    b_stage = [torch.empty(K, N, device=dev) for _ in range(2)] if distributed else b_part
+    up, gather, compute, down = (torch.cuda.Stream(dev) for _ in range(4))
     slot_free = [torch.cuda.Event() for _ in range(2)]     # GEMM that read the slot has finished
     host_free = [torch.cuda.Event() for _ in range(2)]     # download into the host slot has finished
 
@@ -390,10 +711,15 @@ def main() -> None:
         with torch.cuda.stream(up):
             up.wait_event(slot_free[slot])
             a_stage[slot].copy_(a_host, non_blocking=True)
-            b_stage[slot].copy_(b_host, non_blocking=True)
-            uploaded = up.record_event()
+            b_part[slot].copy_(b_host, non_blocking=True)
+            ready = up.record_event()
+        if distributed:
+            with torch.cuda.stream(gather):
+                gather.wait_event(ready)
+                dist.all_gather_into_tensor(b_stage[slot], b_part[slot])
+                ready = gather.record_event()
         with torch.cuda.stream(compute):
-            compute.wait_event(uploaded)
+            compute.wait_event(ready)
             c_dev = pkg.gemm(a_stage[slot].t(), b_stage[slot], impl=impl)
             slot_free[slot].record(compute)
             computed = compute.record_event()
@@ -404,24 +730,26 @@ def main() -> None:
             c_dev.record_stream(down)
             host_free[slot].record(down)
 
+    streams = (up, gather, compute, down)
+
     def e2e_run(steps: int) -> float:
         """Milliseconds from the first upload to the last download of `steps` steps."""
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        main = torch.cuda.current_stream()
-        begin.record(main)
-        for stream in (up, compute, down):
+        main_stream = torch.cuda.current_stream()
+        begin.record(main_stream)
+        for stream in streams:
             stream.wait_event(begin)
         for i in range(steps):
             e2e_step(i)
-        for stream in (up, compute, down):
-            main.wait_stream(stream)
-        end.record(main)
+        for stream in streams:
+            main_stream.wait_stream(stream)
+        end.record(main_stream)
         torch.cuda.synchronize()
         return begin.elapsed_time(end)
 
-    # Enough steps that filling and draining the three-stage pipeline (one upload, one GEMM and one
-    # download that overlap nothing) weigh little: 40 steps take about 0.1 s.
+    # Enough steps that filling and draining the pipeline (one upload, one GEMM and one download
+    # that overlap nothing) weigh little: 40 steps take about 0.1 s.
     e2e_steps = max(args.steps, 40)
     e2e_run(4)
     if distributed:
@@ -435,9 +763,17 @@ def main() -> None:
     e2e_err = max((c[:256] - expected).abs().max().item() for c in c_host)
     if not e2e_err <= tol:
         raise SystemExit(f"end-to-end result failed its parity gate: {e2e_err:.3e} > {tol:.3e}")
+    h2d_bytes = (world * M * K + K * N) * 4        # every rank its rows of A; B once in total
+    d2h_bytes = world * M * N * 4
 
     also: dict = {}
+    also.update(measure_host_link(dev, world, dist))
+    also["e2e_b_upload"] = "K/world rows of B per rank over PCIe, all-gather over NVLink" if distributed else "full B per step"
+    del a_stage, b_part, b_stage, c_host
+
     if distributed:
+        from cuda_ai_kernels import sharded
+
         # Optional collective, timed on its own: gather the row shards of C on every rank.
         c_shard = step(0)
         gathered = torch.empty(world * M, N, device=dev)
@@ -454,55 +790,76 @@ def main() -> None:
         # The same gather fused into the GEMM: the kernel's epilogue stores every tile into every
         # rank's copy of C (peer stores over NVLink), one device-side barrier per step. Reported
         # beside "GEMM, then the collective"; never part of `value`. A box where the symmetric
-        # allocation cannot be set up reports why instead of a number.
-        from cuda_ai_kernels import sharded
-
+        # allocation cannot be set up reports why instead of a number. Only the two pipeline
+        # entries that store each tile once can fan out; any other --sgemm-impl uses prefetch_reg here.
+        fused_impl = impl if impl in ("prefetch_smem", "prefetch_reg") else "prefetch_reg"
+        also["gemm_fused_allgather_impl"] = fused_impl
         out, setup_error = None, ""
         try:
             out = sharded.GatheredOutput(world * M, N, [(r * M, M) for r in range(world)])
         except Exception as exc:  # noqa: BLE001
             setup_error = f"{type(exc).__name__}: {exc}"[:200]
-        # Every rank goes on only if every rank has its buffer: no rank may wait alone in a collective.
-        ready = torch.tensor([int(out is not None)], device=dev)
-        dist.all_reduce(ready, op=dist.ReduceOp.MIN)
-        if not bool(ready.item()):
+        # Every rank goes on only if every rank has its buffer: no rank may wait alone.
+        if not sharded.all_ranks_ok(out is not None):
             also["gemm_fused_allgather_error"] = setup_error or "symmetric allocation failed on another rank"
         else:
+            failure = [None]
 
             def fused(i):
-                sharded.sharded_gemm_gather(a_sets[i & 1], b_sets[i & 1], out, impl=impl)
-                out.barrier()
+                # After a failure this rank enqueues nothing more; the other ranks' barriers are
+                # bounded, give up and report through the status word instead of spinning.
+                if failure[0] is None:
+                    try:
+                        sharded.sharded_gemm_gather(a_sets[i & 1], b_sets[i & 1], out, impl=fused_impl)
+                        out.barrier()
+                    except Exception as exc:  # noqa: BLE001
+                        failure[0] = f"{type(exc).__name__}: {exc}"[:200]
 
             def sequential(i):
-                dist.all_gather_into_tensor(seq_out, step(i))
+                dist.all_gather_into_tensor(seq_out, pkg.gemm(a_sets[i & 1], b_sets[i & 1], impl=fused_impl))
 
             seq_out = torch.empty(world * M, N, device=dev)
             for name, fn in (("gemm_then_allgather_ms", sequential), ("gemm_fused_allgather_ms", fused)):
                 for i in range(3):
                     fn(i)
+                if not sharded.all_ranks_ok(failure[0] is None):
+                    break
                 dist.barrier()
                 t = torch.tensor([event_time_ms(fn, 10) / 10], device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 also[name] = float(t.item())
-            fused(0), sequential(0)
-            torch.cuda.synchronize()
-            same = torch.tensor([int(torch.equal(out.full, seq_out))], device=dev)
-            dist.all_reduce(same, op=dist.ReduceOp.MIN)
-            also["gemm_fused_allgather_bit_identical"] = bool(same.item())
-            out.barrier()
+            if sharded.all_ranks_ok(failure[0] is None):
+                fused(0), sequential(0)
+                torch.cuda.synchronize()
+                same = torch.tensor([int(torch.equal(out.full, seq_out))], device=dev)
+                dist.all_reduce(same, op=dist.ReduceOp.MIN)
+                also["gemm_fused_allgather_bit_identical"] = bool(same.item())
+                try:
+                    out.check()
+                except RuntimeError as exc:
+                    failure[0] = str(exc)[:200]
+            if not sharded.all_ranks_ok(failure[0] is None):
+                also["gemm_fused_allgather_error"] = failure[0] or "another rank failed"
             del seq_out, out
+
+    del a_sets, b_sets
+    torch.cuda.empty_cache()
+    if not args.no_extras:
+        also["c5"] = measure_c5(pkg, dev, rank, world, dist, impl, local_rank)
+        for key in ("fp32_ms", "tf32_ms", "fp32_tflops_total", "tf32_tflops_total"):
+            if key in also["c5"]:
+                also[f"c5_{key}"] = also["c5"][key]
+        torch.cuda.empty_cache()
 
     cpu_baseline = None
     if rank == 0 and world == 1:
-        cores = torch.get_num_threads()
-        seconds = cpu_oracle_seconds(a_cpu, b_cpu, repeats=3)
-        cpu_baseline = {"value": 2.0 * M * N * K / seconds / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
-                        "sample": f"full {M}x{N}x{K} FP64 torch matmul oracle, best of 3 after 1 warm-up, "
-                                  f"{seconds:.3f} s; host has {os.cpu_count()} logical CPUs"}
+        torch.set_num_threads(host_threads())
+        cpu_baseline = cpu_baseline_block(a_cpu, b_cpu, repeats=3)
         if not args.no_extras:
-            del a_sets, b_sets, a_stage, b_stage, c_host
+            also["cpu_rowops"] = cpu_rowop_seconds()
+            also.update(measure_extras(pkg, peaks, local_rank, warmup=args.warmup))
             torch.cuda.empty_cache()
-            also.update(measure_extras(pkg, peaks, steps=max(5, min(args.steps, 20)), warmup=args.warmup))
+            also["upstream_kernels_rebuilt"] = rebuilt_reference_figures()
 
     if rank == 0:
         clk = clocks.summary()
@@ -520,14 +877,11 @@ def main() -> None:
             "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": per_gpu_tflops / PUBLISHED_A800_SPLIT_K_TFLOPS, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": f"fp32_gemm_{M}x{N}x{K}_colmajorA_per_gpu", "impl": impl,
-                       "sharding": "rows of A per rank, B replicated, C sharded" if distributed else "single GPU",
-                       "global_m": M * world,
-                       "l2": "two input sets alternate (A+B 256 MB > 126 MB L2), no flush kernel"},
+            "config": make_config(world, impl),
             "roofline": roofline,
             "cpu_baseline": cpu_baseline,
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": (M * K + K * N) * 4 * world,
-                    "d2h_bytes_per_step": M * N * 4 * world, "steps": e2e_steps},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clk,
             "also": also,

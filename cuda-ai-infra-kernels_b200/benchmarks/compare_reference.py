@@ -1,7 +1,12 @@
 """Side-by-side timing: this package's kernels vs the reference's own sm_80-era
 kernels recompiled for the box, cuBLAS, and PyTorch eager row ops.
 
-    python cuda-ai-infra-kernels_b200/benchmarks/compare_reference.py [--out FILE.json]
+    python cuda-ai-infra-kernels_b200/benchmarks/compare_reference.py [--out FILE.json] [--quick]
+
+`--quick` keeps the benchmark configurations only (split_k and prefetch_reg at
+4096^3, adaptive auto ReLU at 4096^3 and 8192^3, the two row operators);
+`--arm reference --quick` is what the repository's `bench.py` runs in a child
+process to put the rebuilt upstream kernels beside its own numbers.
 
 Both packages are called `cuda_ai_kernels`, so each arm runs in its own child
 process with its own `sys.path`:
@@ -79,7 +84,7 @@ def event_time_ms(torch, fn, warmup=10, repeat=50):
     return {"median_ms": statistics.median(samples), "mean_ms": statistics.fmean(samples), "min_ms": min(samples)}
 
 
-def run_arm(arm: str) -> dict:
+def run_arm(arm: str, quick: bool = False) -> dict:
     sys.path.insert(0, str(ARMS[arm]))
     import torch
     import cuda_ai_kernels as pkg
@@ -88,18 +93,23 @@ def run_arm(arm: str) -> dict:
     results = {"arm": arm, "module": _C.__file__, "gpu": torch.cuda.get_device_name(0), "gemm": [], "adaptive": [],
                "rows": []}
     torch.manual_seed(0)
-    for m, n, k in GEMM_SHAPES:
+    # Quick mode: 3 warm-up calls, 5 calls per graph, 10 replays (the full run: 10 / 10 / 50).
+    timing = dict(warmup=3, repeat=10, calls=5) if quick else {}
+    gemm_shapes = [(4096, 4096, 4096)] if quick else GEMM_SHAPES
+    ladder = ["prefetch_reg", "split_k", "cublas"] if quick else LADDER
+    adaptive_sizes = [4096, 8192] if quick else ADAPTIVE_SIZES
+    for m, n, k in gemm_shapes:
         a = torch.randn(k, m, device="cuda").t()
         b = torch.randn(k, n, device="cuda")
         expected = (a.double() @ b.double()).float()
-        for impl in LADDER:
+        for impl in ladder:
             out = pkg.gemm(a, b, impl=impl)
             err = (out - expected).abs().max().item()
-            t = graph_time_ms(torch, lambda: pkg.gemm(a, b, impl=impl))
+            t = graph_time_ms(torch, lambda: pkg.gemm(a, b, impl=impl), **timing)
             results["gemm"].append({"shape": [m, n, k], "impl": impl, "max_abs_error": err,
                                     "tflops_median": 2.0 * m * n * k / t["median_ms"] / 1e9, **t})
         del a, b, expected
-    for size in ADAPTIVE_SIZES:
+    for size in adaptive_sizes:
         a = torch.randn(size, size, device="cuda")
         b = torch.randn(size, size, device="cuda")
         c = torch.randn(size, size, device="cuda")
@@ -111,8 +121,10 @@ def run_arm(arm: str) -> dict:
                                                                            kernel="cublas")),
             "cublas_linear": lambda: pkg.adaptive_gemm(a, b, c=c, alpha=1.0, beta=0.5, kernel="cublas"),
         }
+        if quick:
+            cases = {"auto_relu": cases["auto_relu"]}
         for name, fn in cases.items():
-            t = graph_time_ms(torch, fn)
+            t = graph_time_ms(torch, fn, **timing)
             results["adaptive"].append({"size": size, "case": name, "tflops_median": flops / t["median_ms"] / 1e9, **t})
         del a, b, c
     x = torch.randn(16384, 4096, device="cuda")
@@ -127,7 +139,7 @@ def run_arm(arm: str) -> dict:
         "softmax_torch": (lambda: torch.softmax(logits, dim=1), 2.0 * logits.numel() * 4),
     }
     for name, (fn, nbytes) in row_cases.items():
-        t = event_time_ms(torch, fn)
+        t = event_time_ms(torch, fn, **({'warmup': 3, 'repeat': 10} if quick else {}))
         results["rows"].append({"case": name, "algorithmic_bytes": nbytes, "gbs_median": nbytes / t["median_ms"] / 1e6,
                                 **t})
     return results
@@ -137,16 +149,18 @@ def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--arm", choices=list(ARMS))
     parser.add_argument("--out")
+    parser.add_argument("--quick", action="store_true")
     args = parser.parse_args()
     if args.arm:
-        print("RESULT " + json.dumps(run_arm(args.arm)))
+        print("RESULT " + json.dumps(run_arm(args.arm, args.quick)))
         return
     merged = {}
     for arm, path in ARMS.items():
         if not (path / "cuda_ai_kernels").is_dir():
             merged[arm] = {"unavailable": f"{path} has no cuda_ai_kernels package"}
             continue
-        proc = subprocess.run([sys.executable, __file__, "--arm", arm], capture_output=True, text=True)
+        proc = subprocess.run([sys.executable, __file__, "--arm", arm, *(["--quick"] if args.quick else [])],
+                              capture_output=True, text=True)
         line = next((l for l in proc.stdout.splitlines() if l.startswith("RESULT ")), None)
         merged[arm] = json.loads(line[7:]) if line else {"unavailable": (proc.stderr or proc.stdout)[-800:]}
     if args.out:

@@ -120,7 +120,7 @@ def build_extension(force: bool = False, verbose: bool = False) -> Path:
                 f"-L{LIB_DIR}", "-lb200_kernels", "-Wl,-rpath,$ORIGIN/../../lib",
                 f"-L{torch_lib}", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
                 f"-Wl,-rpath,{torch_lib}",
-                f"-L{cublas_dir}", "-l:libcublas.so.12", f"-Wl,-rpath,{cublas_dir}",
+                f"-L{cublas_dir}", "-l:libcublas.so.12", "-l:libcublasLt.so.12", f"-Wl,-rpath,{cublas_dir}",
                 f"-L{cudart_dir}", "-l:libcudart.so.12", f"-Wl,-rpath,{cudart_dir}"]
         _run(link, verbose)
     return out

@@ -5,10 +5,13 @@
 // csrc/adaptive_gemm/adaptive_gemm.cu:14-174; the kernel choice is delegated to
 // the registry behind b200_tf32_gemm_dispatch (first compatible entry wins).
 #include <ATen/cuda/CUDAContext.h>
+#include <cublasLt.h>
 #include <cublas_v2.h>
 
 #include <cstdint>
 #include <limits>
+#include <map>
+#include <tuple>
 #include <vector>
 
 #include "op_common.h"
@@ -39,7 +42,11 @@ ParsedEpilogue parse_epilogue(const std::string& value) {
   TORCH_CHECK(false, "unsupported epilogue: ", value);
 }
 
+// kernel="cublaslt": library baseline with the epilogue fused by the library (no registry id).
+constexpr int kKernelCublasLt = -2;
+
 int parse_kernel(const std::string& value) {
+  if (value == "cublaslt") return kKernelCublasLt;
   const int id = b200_tf32_kernel_from_name(value.c_str());
   TORCH_CHECK(id >= 0, "unsupported adaptive_gemm kernel: ", value,
               "; expected one of: auto, cublas, fast, fallback, fast_mwarp, "
@@ -87,6 +94,63 @@ void launch_cublas_tf32(const b200_gemm_problem& q, cudaStream_t stream) {
   TORCH_CHECK(rc == CUBLAS_STATUS_SUCCESS, "cublasGemmEx failed with cuBLAS status ", static_cast<int>(rc));
 }
 
+// Library baseline with a FUSED epilogue: one cublasLtMatmul computes act(alpha * A @ B + beta * C
+// [+ bias]) with C as the library's own C operand and ReLU / bias as its epilogue, in TF32. This is
+// the fair competitor of the fused tcgen05 kernels (the reference ships only the unfused cuBLAS
+// baseline above and applies ReLU in a second pass, benchmarks/bench_adaptive_gemm.py:47-51).
+// Row-major D[M,N] is handed over as column-major D^T[N,M] = B^T[N,K] * A^T[K,M].
+struct LtPlan {
+  cublasLtMatmulDesc_t op = nullptr;
+  cublasLtMatrixLayout_t a = nullptr, b = nullptr, c = nullptr, d = nullptr;
+  cublasLtMatmulAlgo_t algo;
+};
+
+void lt_check(cublasStatus_t rc, const char* what) {
+  TORCH_CHECK(rc == CUBLAS_STATUS_SUCCESS, "cuBLASLt ", what, " failed with status ", static_cast<int>(rc));
+}
+
+void launch_cublaslt_tf32(const b200_gemm_problem& q, int device, cudaStream_t stream) {
+  using Key = std::tuple<int, int, int, int, int64_t, int64_t, int64_t, int64_t, int, bool>;
+  thread_local std::map<Key, LtPlan> plans;   // descriptors and the heuristic's choice, per shape
+  cublasLtHandle_t handle = at::cuda::getCurrentCUDABlasLtHandle();
+  const size_t workspace_bytes = at::cuda::getCUDABlasLtWorkspaceSize();
+  void* workspace = at::cuda::getCUDABlasLtWorkspace();
+  const Key key{device, q.m, q.n, q.k, q.lda, q.ldb, q.ldc, q.ldd, q.epilogue, q.bias != nullptr};
+  auto it = plans.find(key);
+  if (it == plans.end()) {
+    LtPlan plan;
+    lt_check(cublasLtMatmulDescCreate(&plan.op, CUBLAS_COMPUTE_32F_FAST_TF32, CUDA_R_32F), "descriptor creation");
+    cublasLtEpilogue_t epilogue = CUBLASLT_EPILOGUE_DEFAULT;
+    if (q.epilogue == B200_EPILOGUE_RELU) epilogue = q.bias ? CUBLASLT_EPILOGUE_RELU_BIAS : CUBLASLT_EPILOGUE_RELU;
+    else if (q.bias) epilogue = CUBLASLT_EPILOGUE_BIAS;
+    lt_check(cublasLtMatmulDescSetAttribute(plan.op, CUBLASLT_MATMUL_DESC_EPILOGUE, &epilogue, sizeof(epilogue)), "epilogue");
+    lt_check(cublasLtMatrixLayoutCreate(&plan.a, CUDA_R_32F, q.n, q.k, q.ldb), "layout");
+    lt_check(cublasLtMatrixLayoutCreate(&plan.b, CUDA_R_32F, q.k, q.m, q.lda), "layout");
+    lt_check(cublasLtMatrixLayoutCreate(&plan.c, CUDA_R_32F, q.n, q.m, q.ldc), "layout");
+    lt_check(cublasLtMatrixLayoutCreate(&plan.d, CUDA_R_32F, q.n, q.m, q.ldd), "layout");
+    cublasLtMatmulPreference_t pref = nullptr;
+    lt_check(cublasLtMatmulPreferenceCreate(&pref), "preference");
+    lt_check(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &workspace_bytes,
+                                                  sizeof(workspace_bytes)), "preference");
+    cublasLtMatmulHeuristicResult_t result;
+    int found = 0;
+    const cublasStatus_t rc = cublasLtMatmulAlgoGetHeuristic(handle, plan.op, plan.a, plan.b, plan.c, plan.d, pref, 1,
+                                                             &result, &found);
+    cublasLtMatmulPreferenceDestroy(pref);
+    TORCH_CHECK(rc == CUBLAS_STATUS_SUCCESS && found > 0, "cuBLASLt has no algorithm for this problem");
+    plan.algo = result.algo;
+    it = plans.emplace(key, plan).first;
+  }
+  const LtPlan& plan = it->second;
+  if (q.bias != nullptr) {
+    lt_check(cublasLtMatmulDescSetAttribute(plan.op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &q.bias, sizeof(q.bias)), "bias");
+  }
+  // With beta == 0 the library must still be given a valid C; D stands in and is never read.
+  const float* c_operand = q.beta != 0.f ? q.c : q.d;
+  lt_check(cublasLtMatmul(handle, plan.op, &q.alpha, q.b, plan.a, q.a, plan.b, &q.beta, c_operand, plan.c, q.d, plan.d,
+                          &plan.algo, workspace, workspace_bytes, stream), "matmul");
+}
+
 const char* registry_name(int id) {
   b200_tf32_kernel_meta meta;
   for (int i = 0; i < b200_tf32_registry_size(); ++i) {
@@ -115,6 +179,8 @@ torch::Tensor run_adaptive(const torch::Tensor& a, const torch::Tensor& b, const
   TORCH_CHECK(requested != B200_TF32_KERNEL_CUBLAS || (parsed.activation == B200_EPILOGUE_LINEAR && !parsed.wants_bias),
               "adaptive_gemm kernel='cublas' supports only the linear epilogue; "
               "apply torch.relu to its output for an unfused ReLU baseline");
+  TORCH_CHECK(requested != kKernelCublasLt || parsed.activation != B200_EPILOGUE_GELU,
+              "adaptive_gemm kernel='cublaslt' has linear, ReLU and bias epilogues (the library's GELU is the tanh form)");
   TORCH_CHECK(has_bias == parsed.wants_bias,
               parsed.wants_bias ? "bias is required by the '" : "a bias tensor needs a bias epilogue, not '", epilogue,
               "' epilogue");
@@ -138,7 +204,8 @@ torch::Tensor run_adaptive(const torch::Tensor& a, const torch::Tensor& b, const
     TORCH_CHECK(out->dim() == 2 && out->size(0) == m && out->size(1) == n, "out must have shape [", m, ", ", n,
                 "] but got ", out->sizes());
     TORCH_CHECK(out->stride(1) == 1 && out->stride(0) >= n, "out must be row-major");
-    TORCH_CHECK(requested != B200_TF32_KERNEL_CUBLAS, "adaptive_gemm_gather has no cuBLAS arm");
+    TORCH_CHECK(requested != B200_TF32_KERNEL_CUBLAS && requested != kKernelCublasLt,
+                "adaptive_gemm_gather has no cuBLAS arm");
     TORCH_CHECK(peer_ptrs.size() <= B200_MAX_PEERS, "at most ", B200_MAX_PEERS, " peer destinations");
     for (const int64_t ptr : peer_ptrs) TORCH_CHECK(ptr != 0, "peer destination pointers must not be null");
   }
@@ -162,6 +229,13 @@ torch::Tensor run_adaptive(const torch::Tensor& a, const torch::Tensor& b, const
   if (requested == B200_TF32_KERNEL_CUBLAS) {
     launch_cublas_tf32(q, static_cast<cudaStream_t>(current_stream(a)));
     g_last_kernel = "cublas";
+    return d;
+  }
+
+  if (requested == kKernelCublasLt) {
+    q.c = has_c ? c->data_ptr<float>() : d.data_ptr<float>();
+    launch_cublaslt_tf32(q, a.get_device(), static_cast<cudaStream_t>(current_stream(a)));
+    g_last_kernel = "cublaslt";
     return d;
   }
 

@@ -317,3 +317,19 @@ def test_rope_and_attention_decode_are_declared_but_refuse():
         cuda_ai_kernels.rope(x, x, x)
     with pytest.raises(RuntimeError, match="planned for v0.3"):
         cuda_ai_kernels.attention_decode(x, x, x)
+
+
+@pytest.mark.parametrize("epilogue", ["linear", "relu", "bias", "bias_relu"])
+def test_cublaslt_fused_baseline_matches_the_oracle(epilogue):
+    """kernel="cublaslt": the library's own fused epilogue, the baseline the fused kernels are timed against."""
+    a, b, c = oracle.adaptive_inputs(192, 320, 96, seed=5)
+    bias = torch.linspace(-1.0, 1.0, 320) if "bias" in epilogue else None
+    out = adaptive_gemm(a.cuda(), b.cuda(), c=c.cuda(), bias=None if bias is None else bias.cuda(), alpha=1.0, beta=0.5,
+                        epilogue=epilogue, kernel="cublaslt")
+    expected = oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, epilogue, bias=bias)
+    assert oracle.rel_frobenius(out, expected) <= oracle.TF32_REL_FROBENIUS
+    no_source = adaptive_gemm(a.cuda(), b.cuda(), epilogue="relu" if "relu" in epilogue else "linear", kernel="cublaslt")
+    expected = oracle.adaptive_gemm_fp64(a, b, None, 1.0, 0.0, "relu" if "relu" in epilogue else "linear")
+    assert oracle.rel_frobenius(no_source, expected) <= oracle.TF32_REL_FROBENIUS
+    with pytest.raises(RuntimeError, match="tanh form"):
+        adaptive_gemm(a.cuda(), b.cuda(), epilogue="gelu", kernel="cublaslt")
