@@ -127,7 +127,10 @@ void check_gather_output(const torch::Tensor& out, const torch::Tensor& a, int64
 
 // alpha = 1, beta = 0 TF32 product of two row-major matrices through the
 // tcgen05 registry. Degenerate sizes never reach a kernel.
-torch::Tensor run_tf32_row_major(const torch::Tensor& a, const torch::Tensor& b, const char* what) {
+// `compensated`: above 128 floats of K use the three-product form whose error is that of FP32
+// (b200_tf32x3_gemm); up to there one TF32 pass is well inside the entry's 3e-2 bound.
+torch::Tensor run_tf32_row_major(const torch::Tensor& a, const torch::Tensor& b, const char* what,
+                                 bool compensated = false) {
   check_row_major_inputs(a, b);
   const int64_t m = a.size(0), k = a.size(1), n = b.size(1);
   const c10::cuda::CUDAGuard guard(a.device());
@@ -139,6 +142,12 @@ torch::Tensor run_tf32_row_major(const torch::Tensor& a, const torch::Tensor& b,
   q.a = a.data_ptr<float>(), q.b = b.data_ptr<float>(), q.c = nullptr, q.d = d.data_ptr<float>();
   q.lda = a.stride(0), q.ldb = b.stride(0), q.ldc = d.stride(0), q.ldd = d.stride(0);
   q.alpha = 1.f, q.beta = 0.f, q.epilogue = B200_EPILOGUE_LINEAR;
+  if (compensated && k > 128) {
+    const size_t bytes = b200_tf32x3_scratch_bytes(q.m, q.n, q.k);
+    auto scratch = torch::empty({static_cast<int64_t>(bytes / sizeof(float))}, a.options());   // freed in stream order
+    check_status(b200_tf32x3_gemm(&q, scratch.data_ptr<float>(), bytes, current_stream(a)), what);
+    return d;
+  }
   check_status(b200_tf32_gemm_dispatch(B200_TF32_KERNEL_AUTO, &q, nullptr, current_stream(a)), what);
   return d;
 }
@@ -226,5 +235,7 @@ torch::Tensor gemm_cublas(torch::Tensor a, torch::Tensor b) {
 
 // Row-major TF32 side entries (csrc/gemm/gemm_tensor_core.cu:111-137,
 // csrc/gemm/gemm_cutlass.cu:76-126): any shape, tensor cores.
-torch::Tensor gemm_tensor_core(torch::Tensor a, torch::Tensor b) { return run_tf32_row_major(a, b, "gemm_tensor_core"); }
+torch::Tensor gemm_tensor_core(torch::Tensor a, torch::Tensor b) {
+  return run_tf32_row_major(a, b, "gemm_tensor_core", /*compensated=*/true);
+}
 torch::Tensor gemm_cutlass(torch::Tensor a, torch::Tensor b) { return run_tf32_row_major(a, b, "gemm_cutlass"); }

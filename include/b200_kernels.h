@@ -250,6 +250,23 @@ int b200_tf32_gemm_launch(int kernel_id, const b200_gemm_problem* problem,
 int b200_tf32_gemm_dispatch(int requested, const b200_gemm_problem* problem,
                             int* chosen, b200_stream_t stream);
 
+/*
+ * Error-compensated TF32 ("3xTF32"): the same D = act(alpha * A*B + beta * C
+ * [+ bias]) with FP32-class accuracy, as three TF32 tensor-core products
+ * A*B + A_lo*B + A*B_lo where x_lo = x - (x with its 13 low mantissa bits
+ * cleared, which is what the MMA unit reads). Stands in for the reference's
+ * row-major tensor-core entry gemm_tensor_core (csrc/gemm/gemm_tensor_core.cu:
+ * 111-137) where its element-wise bound of 3e-2 (tests/test_gemm.py:23-35) is
+ * out of reach of one TF32 pass (K above about 128).
+ * `scratch` is device memory of at least b200_tf32x3_scratch_bytes(m, n, k)
+ * bytes, 16-byte aligned, owned by the caller (it holds A_lo and B_lo for the
+ * duration of the call's work on `stream`). Four launches: one splitting pass,
+ * then three dispatches through the registry. C may not alias D unless it is D.
+ */
+size_t b200_tf32x3_scratch_bytes(int m, int n, int k);
+int b200_tf32x3_gemm(const b200_gemm_problem* problem, void* scratch,
+                     size_t scratch_bytes, b200_stream_t stream);
+
 /* ------------------------------------------------------------ row operators */
 
 typedef enum b200_rmsnorm_impl {

@@ -333,3 +333,16 @@ def test_cublaslt_fused_baseline_matches_the_oracle(epilogue):
     assert oracle.rel_frobenius(no_source, expected) <= oracle.TF32_REL_FROBENIUS
     with pytest.raises(RuntimeError, match="tanh form"):
         adaptive_gemm(a.cuda(), b.cuda(), epilogue="gelu", kernel="cublaslt")
+
+
+def test_tensor_core_entry_keeps_its_elementwise_bound_at_long_k():
+    """Upstream bounds gemm(impl="tensor_core") element-wise at 3e-2 for 1024^3 against an FP32 product
+    (tests/test_gemm.py:23-35); above 128 floats of K the entry runs the error-compensated form."""
+    torch.manual_seed(0)
+    a = torch.randn(1024, 1024, device="cuda")
+    b = torch.randn(1024, 1024, device="cuda")
+    expected = oracle.gemm_fp64(a, b)
+    torch.testing.assert_close(gemm(a, b, impl="tensor_core").cpu(), expected, atol=1e-3, rtol=1e-3)
+    torch.testing.assert_close(gemm(a, b, impl="cutlass").cpu(), expected, atol=0.1, rtol=3e-2)   # one TF32 pass
+    short = gemm(a[:, :128].contiguous(), b[:128], impl="tensor_core")                              # one pass as well
+    torch.testing.assert_close(short.cpu(), oracle.gemm_fp64(a[:, :128], b[:128]), atol=3e-2, rtol=3e-2)

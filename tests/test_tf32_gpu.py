@@ -449,3 +449,65 @@ def test_k_tail_inside_a_stage(abi, entry, k):
     tol = 1e-5 if epilogue == GELU else 0
     torch.testing.assert_close(d.cpu(), expected, atol=tol, rtol=tol)
     assert_device_clean(abi)
+
+
+# ------------------------------------------------------- error-compensated TF32 (three products)
+
+
+def run_x3(abi, a, b, c=None, alpha=1.0, beta=0.0, epilogue=LINEAR, bias=None, scratch_slack=0):
+    m, k = a.shape
+    n = b.shape[1]
+    d = torch.full((m, n), float("nan"), device=a.device)
+    q = GemmProblem(m, n, k, a.data_ptr(), b.data_ptr(), c.data_ptr() if c is not None else None, d.data_ptr(),
+                    a.stride(0), b.stride(0), c.stride(0) if c is not None else n, d.stride(0), alpha, beta, epilogue,
+                    bias.data_ptr() if bias is not None else None)
+    need = abi.b200_tf32x3_scratch_bytes(m, n, k)
+    scratch = torch.empty(need // 4 + scratch_slack, device=a.device)
+    status = abi.b200_tf32x3_gemm(ctypes.byref(q), scratch.data_ptr(), need, current_stream_ptr())
+    return status, d
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 1024), (130, 136, 300), (33, 65, 517), (1024, 1024, 1024)])
+def test_compensated_tf32_has_fp32_class_accuracy(abi, shape):
+    """Three TF32 products reach the accuracy bar of the FP32 SIMT ladder, which one pass misses by 100x."""
+    m, n, k = shape
+    a, b, c = oracle.adaptive_inputs(m, n, k, seed=11)
+    status, d = run_x3(abi, a.cuda(), b.cuda(), c.cuda(), alpha=1.0, beta=0.5, epilogue=RELU)
+    assert status == 0, abi.b200_status_string(status)
+    expected = oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, "relu")
+    err = (d.cpu() - expected).abs().max().item()
+    assert err <= oracle.sgemm_abs_tolerance(a, b), err            # 1e-4 * sqrt(K) * max|A| * max|B|
+    torch.testing.assert_close(d.cpu(), expected, atol=1e-3, rtol=1e-3)
+    assert oracle.rel_frobenius(d, expected) <= 2e-5
+    # One pass on the same inputs, for contrast: inside the TF32 bar, far outside the FP32 one.
+    _, single, _ = run(abi, 0, a.cuda(), b.cuda(), c.cuda(), 1.0, 0.5, RELU, dispatch=True)
+    assert oracle.rel_frobenius(single, expected) > 20 * oracle.rel_frobenius(d, expected)
+    assert_device_clean(abi)
+
+
+def test_compensated_tf32_bias_integers_and_refusals(abi):
+    g = torch.Generator().manual_seed(3)
+    a = torch.randint(-4, 5, (200, 96), generator=g).float()
+    b = torch.randint(-4, 5, (96, 264), generator=g).float()
+    bias = torch.arange(264).float() - 100
+    status, d = run_x3(abi, a.cuda(), b.cuda(), epilogue=LINEAR, bias=bias.cuda())
+    assert status == 0
+    torch.testing.assert_close(d.cpu(), oracle.adaptive_gemm_fp64(a, b, epilogue="bias", bias=bias), atol=0, rtol=0)
+    # Non-finite operands travel through the first product only.
+    a2 = a.clone()
+    a2[3, 5] = float("inf")
+    status, d = run_x3(abi, a2.cuda(), b.cuda())
+    expected = oracle.adaptive_gemm_fp64(a2, b)
+    assert status == 0 and torch.equal(torch.isnan(d.cpu()), torch.isnan(expected))
+    torch.testing.assert_close(d.cpu(), expected, atol=0, rtol=0, equal_nan=True)
+    # Scratch that is too small, missing or misaligned is refused before any launch.
+    q = GemmProblem(200, 264, 96, a.cuda().data_ptr(), b.cuda().data_ptr(), None, d.data_ptr(), 96, 264, 264, 264, 1.0, 0.0,
+                    LINEAR, None)
+    need = abi.b200_tf32x3_scratch_bytes(200, 264, 96)
+    assert need == (200 * 96 + 96 * 264) * 4
+    assert abi.b200_tf32x3_scratch_bytes(3, 5, 7) == (3 * 8 + 7 * 8) * 4          # rows padded to four floats
+    scratch = torch.empty(need // 4 + 4, device="cuda")
+    assert abi.b200_tf32x3_gemm(ctypes.byref(q), scratch.data_ptr(), need - 4, current_stream_ptr()) == 4
+    assert abi.b200_tf32x3_gemm(ctypes.byref(q), None, need, current_stream_ptr()) == 4
+    assert abi.b200_tf32x3_gemm(ctypes.byref(q), scratch.data_ptr() + 4, need, current_stream_ptr()) == 4
+    assert_device_clean(abi)
