@@ -26,7 +26,9 @@ __host__ __device__ inline int64_t padded4(int64_t cols) { return (cols + 3) / 4
 
 // lo[r][c] = x[r][c] - tf32_truncate(x[r][c]) for both operands in one launch; padding columns are
 // written as zeros (they are never multiplied with anything, K and N bound the products, but a
-// TMA box may read them). Non-finite inputs get lo = 0: the hi pass alone carries the inf / NaN.
+// TMA box may read them). Non-finite inputs get lo = 0 (inf - inf would be NaN); an infinite
+// operand still turns its whole row or column of D into NaN, because the correction products
+// multiply it with lo terms that are zero. A single pass would give +-inf there.
 __global__ void split_lo_kernel(const float* __restrict__ a, int64_t lda, int m, int k, float* __restrict__ a_lo,
                                 const float* __restrict__ b, int64_t ldb, int n, float* __restrict__ b_lo) {
   const int64_t ka = padded4(k), nb = padded4(n);
