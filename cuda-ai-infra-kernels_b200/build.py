@@ -11,7 +11,13 @@
 Both steps cross-compile on a machine without a GPU. Object files are cached in
 ``build/`` and rebuilt when a source or header is newer.
 
-Usage: ``python build.py [--force] [--kernels-only] [--verbose]``
+``--debug-bounds`` additionally builds ``lib/libb200_kernels_debug.so``: the same
+sources with ``-DB200_DEBUG_BOUNDS``, in which the kernels' stores and unpredicated
+loads are wrapped in index checks that record a bit in the device status word and
+skip the access (nothing traps). It stands in for a memory checker on shared GPUs;
+``tests/test_debug_bounds_gpu.py`` runs the exact small cases against it.
+
+Usage: ``python build.py [--force] [--kernels-only] [--debug-bounds] [--verbose]``
 """
 from __future__ import annotations
 
@@ -30,6 +36,7 @@ TORCH_DIR = PKG / "csrc" / "torch"
 OBJ_DIR = PKG / "build"
 LIB_DIR = PKG / "lib"
 KERNEL_LIB = LIB_DIR / "libb200_kernels.so"
+DEBUG_LIB = LIB_DIR / "libb200_kernels_debug.so"
 PY_PKG = PKG / "python" / "cuda_ai_kernels"
 
 CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
@@ -63,24 +70,27 @@ def extension_path() -> Path:
     return PY_PKG / f"_C{suffix}"
 
 
-def build_kernels(force: bool = False, verbose: bool = False) -> Path:
+def build_kernels(force: bool = False, verbose: bool = False, debug_bounds: bool = False) -> Path:
     OBJ_DIR.mkdir(exist_ok=True)
     LIB_DIR.mkdir(exist_ok=True)
+    target = DEBUG_LIB if debug_bounds else KERNEL_LIB
+    prefix = "dbg_" if debug_bounds else ""
+    extra = ["-DB200_DEBUG_BOUNDS"] if debug_bounds else []
     sources = sorted(KERNEL_DIR.glob("*.cu"))
     headers = list(KERNEL_DIR.glob("*.h")) + list(KERNEL_DIR.glob("*.cuh")) + [REPO / "include" / "b200_kernels.h"]
     header_time = _newest(headers)
     jobs = []
     objects = []
     for src in sources:
-        obj = OBJ_DIR / (src.stem + ".o")
+        obj = OBJ_DIR / (prefix + src.stem + ".o")
         objects.append(obj)
         if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, header_time):
-            jobs.append([NVCC, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)])
+            jobs.append([NVCC, *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)])
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
         list(pool.map(lambda c: _run(c, verbose), jobs))
-    if force or jobs or not KERNEL_LIB.exists():
-        _run([NVCC, "-shared", "-o", str(KERNEL_LIB), *map(str, objects), "-cudart", "static"], verbose)
-    return KERNEL_LIB
+    if force or jobs or not target.exists():
+        _run([NVCC, "-shared", "-o", str(target), *map(str, objects), "-cudart", "static"], verbose)
+    return target
 
 
 def build_extension(force: bool = False, verbose: bool = False) -> Path:
@@ -126,8 +136,10 @@ def build_extension(force: bool = False, verbose: bool = False) -> Path:
     return out
 
 
-def build_all(force: bool = False, verbose: bool = False, kernels_only: bool = False) -> None:
+def build_all(force: bool = False, verbose: bool = False, kernels_only: bool = False, debug_bounds: bool = False) -> None:
     build_kernels(force, verbose)
+    if debug_bounds:
+        build_kernels(force, verbose, debug_bounds=True)
     if not kernels_only:
         build_extension(force, verbose)
 
@@ -137,8 +149,9 @@ if __name__ == "__main__":
     parser.add_argument("--force", action="store_true")
     parser.add_argument("--kernels-only", action="store_true")
     parser.add_argument("--verbose", action="store_true")
+    parser.add_argument("--debug-bounds", action="store_true")
     args = parser.parse_args()
-    build_all(args.force, args.verbose, args.kernels_only)
+    build_all(args.force, args.verbose, args.kernels_only, args.debug_bounds)
     print(f"built {KERNEL_LIB}")
     if not args.kernels_only:
         print(f"built {extension_path()}")

@@ -38,7 +38,18 @@ enum WaitSite : uint32_t {
   kSiteUmmaStore = 1u << 6,
   kSiteSelfTest = 1u << 7,
   kSitePeerBarrier = 1u << 8,
+  kSiteBounds = 1u << 10,   // debug build only: an index check failed and the access was skipped
 };
+
+// Debug build (-DB200_DEBUG_BOUNDS, a separate library; never the shipped one): the stores and the
+// unpredicated loads of the kernels are wrapped in index checks against the extents the launcher
+// passed. A failing check records kSiteBounds in the status word and SKIPS the access; nothing
+// traps. The stand-in, on a shared GPU, for running the kernels under a memory checker.
+#ifdef B200_DEBUG_BOUNDS
+#define B200_IN_BOUNDS(cond) ((cond) ? true : (atomicOr(&::b200::g_device_status, ::b200::kSiteBounds), false))
+#else
+#define B200_IN_BOUNDS(cond) true
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

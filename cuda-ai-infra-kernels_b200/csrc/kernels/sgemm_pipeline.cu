@@ -17,6 +17,12 @@
 //                   space is cut into one equal range per CTA (stream-K), which
 //                   balances any shape.
 //
+// Few tiles, long K (fewer 128 x 128 tiles than SMs): prefetch_smem and prefetch_reg launch clusters
+// of 2 or 4 CTAs per tile, each CTA runs an equal share of the K blocks, and the partial tiles of
+// ranks 1.. travel through distributed shared memory into rank 0's idle operand ring, where they
+// are added in rank order before the one store of the tile. No atomics, no cleared output, the
+// same bits every run; 1024^3 runs on 128 SMs instead of 64.
+//
 // Layout in shared memory per stage: A slab [BK][128] (row kk = 128 consecutive
 // m of storage row k) and B slab [BK][128]; both arrive exactly as one TMA box.
 // K tails are handled by the tensor maps: rows past K read as zeros.
@@ -29,6 +35,8 @@
 // that configuration runs four consumer warps per CTA, two CTAs per SM, and no
 // separate producer warp (lane 0 of warp 0 issues the TMA loads a few stages
 // ahead of the warps that consume them).
+#include <atomic>
+
 #include "sgemm.h"
 #include "ptx_sm100.cuh"
 
@@ -156,14 +164,19 @@ struct Segment {
 //                 one tile, some whole tiles and the head of another, and every
 //                 segment is reduced into the output.
 // Producer and consumers walk identical copies.
-template <bool kStreamK>
+//   cluster split - (kSplit > 1) one tile per cluster of kSplit CTAs; CTA rank r owns the r-th of
+//                 kSplit equal shares of the K blocks; a single segment per CTA.
+template <bool kStreamK, int kSplit = 1>
 struct WorkIterator {
   int k_blocks;
   int tile, tile_end, tile_stride;  // whole tiles
   int64_t it, it_end;               // stream-K
 
   __device__ WorkIterator(int tiles, int k_blocks_) : k_blocks(k_blocks_) {
-    if constexpr (kStreamK) {
+    if constexpr (kSplit > 1) {
+      tile = blockIdx.x / kSplit, tile_end = tiles, tile_stride = 0;
+      it = it_end = 0;
+    } else if constexpr (kStreamK) {
       const int64_t total = static_cast<int64_t>(tiles) * k_blocks;
       it = total * blockIdx.x / gridDim.x;
       it_end = total * (blockIdx.x + 1) / gridDim.x;
@@ -175,7 +188,14 @@ struct WorkIterator {
   }
 
   __device__ bool next(Segment* s) {
-    if constexpr (kStreamK) {
+    if constexpr (kSplit > 1) {
+      if (tile >= tile_end) return false;
+      const int rank = static_cast<int>(cluster_cta_rank());
+      s->tile = tile;
+      s->kb_begin = k_blocks * rank / kSplit, s->kb_end = k_blocks * (rank + 1) / kSplit;
+      tile = tile_end;   // one segment only
+      return true;
+    } else if constexpr (kStreamK) {
       if (it >= it_end) return false;
       s->tile = static_cast<int>(it / k_blocks);
       s->kb_begin = static_cast<int>(it - static_cast<int64_t>(s->tile) * k_blocks);
@@ -194,9 +214,9 @@ struct WorkIterator {
 
 // Position of the TMA producer: its own copy of the work iterator plus the
 // ring slot it fills next.
-template <bool kStreamK>
+template <bool kStreamK, int kSplit = 1>
 struct ProducerCursor {
-  WorkIterator<kStreamK> work;
+  WorkIterator<kStreamK, kSplit> work;
   Segment seg{0, 0, 0};
   int kb = 0;
   int tm = 0, tn = 0;
@@ -217,8 +237,8 @@ struct ProducerCursor {
 
 // Issues the loads of the cursor's stage and advances it. Returns false only
 // when the bounded wait for a free stage expired.
-template <int BK, int STAGES, bool kStreamK>
-__device__ __forceinline__ bool produce_stage(const PipelineParams& p, ProducerCursor<kStreamK>& c, float* slabs,
+template <int BK, int STAGES, bool kStreamK, int kSplit>
+__device__ __forceinline__ bool produce_stage(const PipelineParams& p, ProducerCursor<kStreamK, kSplit>& c, float* slabs,
                                               uint64_t* full_bar, uint64_t* empty_bar) {
   using Layout = SmemLayout<BK, STAGES>;
   if (!c.active) return true;  // nothing left to fetch
@@ -233,9 +253,17 @@ __device__ __forceinline__ bool produce_stage(const PipelineParams& p, ProducerC
   return true;
 }
 
-template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, bool kStreamK, int kCtasPerSm, bool kGather>
+__device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, float x, float y, float z, float w) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+
+template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, bool kStreamK, int kCtasPerSm, bool kGather,
+          int kSplit = 1>
 __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_kernel(const __grid_constant__ PipelineParams p) {
   using Layout = SmemLayout<BK, STAGES>;
+  static_assert(kSplit == 1 || (!kStreamK && !kGather && Grid::kProducerWarp), "the cluster split stores each tile once, locally");
+  static_assert(kSplit == 1 || static_cast<size_t>(kSplit - 1) * kTile * kTile * sizeof(float) <= STAGES * Layout::kStageBytes,
+                "the partial tiles of ranks 1.. must fit rank 0's operand ring");
   constexpr int RM = Grid::RM, RN = Grid::RN;
   constexpr bool kInlineProducer = !Grid::kProducerWarp;
   // An inline producer runs this many stages ahead of warp 0. Two stages of
@@ -267,11 +295,11 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
     if (tid != Grid::kConsumerThreads) return;
     prefetch_tensormap(&p.map_a);
     prefetch_tensormap(&p.map_b);
-    ProducerCursor<kStreamK> cursor(p);
+    ProducerCursor<kStreamK, kSplit> cursor(p);
     while (cursor.active) {
       if (!produce_stage<BK, STAGES>(p, cursor, slabs, full_bar, empty_bar)) return;
     }
-    return;
+    return;   // (an exited thread does not take part in the cluster barriers below)
   }
 
   // ---------------------------------------------------------------- consumers
@@ -280,7 +308,7 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
   const int col0 = (warp % Grid::kWarpsN) * (16 * RN) + (lane & 3) * 4;
 
   const bool produces = kInlineProducer && tid == 0;
-  ProducerCursor<kStreamK> cursor(p);
+  ProducerCursor<kStreamK, kSplit> cursor(p);
   if (produces) {
     prefetch_tensormap(&p.map_a);
     prefetch_tensormap(&p.map_b);
@@ -292,7 +320,7 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
 
   int stage = 0;
   uint32_t phase = 0;
-  WorkIterator<kStreamK> work(p.tiles_m * p.tiles_n, p.k_blocks);
+  WorkIterator<kStreamK, kSplit> work(p.tiles_m * p.tiles_n, p.k_blocks);
   Segment seg;
   while (work.next(&seg)) {
     int tm, tn;
@@ -354,6 +382,42 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
       }
     }
 
+    if constexpr (kSplit > 1) {
+      // Cluster split: every CTA holds a partial tile. After the first cluster barrier nobody reads
+      // an operand ring any more (and every TMA write into one has been consumed), so ranks 1.. copy
+      // their accumulators into rank 0's ring, laid out [rank - 1][value quad][thread] so that a warp
+      // writes 512 contiguous bytes; after the second barrier rank 0 adds them in rank order.
+      // (A wait that ran out above has returned early: the barriers below are reached by all
+      // consumer threads or, after such a failure, the kernel ends on its bounded waits.)
+      constexpr int kQuads = RM * RN * 4;   // float4 values per thread
+      const uint32_t rank = cluster_cta_rank();
+      cluster_sync_all();
+      if (rank != 0) {
+        const uint32_t remote = map_to_cta(smem_u32(slabs), 0) +
+                                ((rank - 1) * kQuads * Grid::kConsumerThreads + tid) * static_cast<uint32_t>(sizeof(float4));
+#pragma unroll
+        for (int i = 0; i < 4 * RM; ++i)
+#pragma unroll
+          for (int cb = 0; cb < RN; ++cb) {
+            st_shared_cluster_v4(remote + (i * RN + cb) * Grid::kConsumerThreads * static_cast<uint32_t>(sizeof(float4)),
+                                 acc[i][4 * cb], acc[i][4 * cb + 1], acc[i][4 * cb + 2], acc[i][4 * cb + 3]);
+          }
+      }
+      cluster_sync_all();
+      if (rank != 0) return;
+      const float4* parts = reinterpret_cast<const float4*>(slabs) + tid;
+#pragma unroll 1
+      for (int r = 1; r < kSplit; ++r) {
+#pragma unroll
+        for (int i = 0; i < 4 * RM; ++i)
+#pragma unroll
+          for (int cb = 0; cb < RN; ++cb) {
+            const float4 v = parts[((r - 1) * kQuads + i * RN + cb) * Grid::kConsumerThreads];
+            acc[i][4 * cb] += v.x, acc[i][4 * cb + 1] += v.y, acc[i][4 * cb + 2] += v.z, acc[i][4 * cb + 3] += v.w;
+          }
+      }
+    }
+
     // Epilogue straight from registers: every store instruction of a warp
     // covers eight rows x 64 contiguous bytes. Stream-K segments are partial
     // sums and are reduced into the cleared output instead.
@@ -372,6 +436,10 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
           const float* v = acc[rb * 4 + i];
 #pragma unroll
           for (int cb = 0; cb < RN; ++cb) {
+            if (!B200_IN_BOUNDS(c_row + 16 * cb >= c_tile - tile_offset &&
+                                c_row + 16 * cb + 4 <= c_tile - tile_offset + static_cast<int64_t>(p.tiles_m) * kTile * p.n)) {
+              continue;
+            }
             if constexpr (!kStreamK) {
               *reinterpret_cast<float4*>(c_row + 16 * cb) = make_float4(v[4 * cb], v[4 * cb + 1], v[4 * cb + 2], v[4 * cb + 3]);
             } else {
@@ -381,6 +449,62 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
         }
     }
   }
+}
+
+// Clusters of `split` CTAs of the split kernel that the device keeps resident at once (cached per
+// device; 0 when the query fails).
+template <auto kKernel, size_t kSmem, int kThreads>
+int max_resident_clusters(int split) {
+  static std::atomic<int> cache[64][3];   // [device][log2 split], 0 = not asked yet
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  const int slot = split == 2 ? 1 : split == 4 ? 2 : 0;
+  const int cached = cache[device][slot].load(std::memory_order_relaxed);
+  if (cached != 0) return cached > 0 ? cached : 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(split) * 64);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(split);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kKernel, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    clusters = 0;
+  }
+  cache[device][slot].store(clusters > 0 ? clusters : -1, std::memory_order_relaxed);
+  return clusters;
+}
+
+// One tile per cluster of kSplit CTAs, K shared out over the ranks (see the kernel).
+template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, int kSplit>
+int launch_cluster_split(const PipelineParams& p, cudaStream_t stream, bool* fits) {
+  using Layout = SmemLayout<BK, STAGES>;
+  constexpr auto kernel = sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, false, 1, false, kSplit>;
+  *fits = false;
+  if (!ensure_dynamic_smem<kernel, Layout::kBytes>()) return B200_ERR_LAUNCH_FAILED;
+  const int tiles = p.tiles_m * p.tiles_n;
+  if (max_resident_clusters<kernel, Layout::kBytes, Grid::kThreads>(kSplit) < tiles) return B200_OK;   // would run in waves
+  *fits = true;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * kSplit));
+  cfg.blockDim = dim3(Grid::kThreads);
+  cfg.dynamicSmemBytes = Layout::kBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = kSplit;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
+  return launch_status();
 }
 
 template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, bool kStreamK, int kCtasPerSm>
@@ -414,10 +538,25 @@ int launch_pipeline(const float* a, const float* b, float* c, const PeerOutputs&
 
   if (kStreamK) {
     if (cudaMemsetAsync(c, 0, static_cast<size_t>(m) * n * sizeof(float), stream) != cudaSuccess) {
-      return B200_ERR_LAUNCH_FAILED;
+      return launch_failed();
     }
   }
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  if constexpr (!kStreamK && kCtasPerSm == 1 && Grid::kProducerWarp) {
+    // Fewer tiles than SMs: clusters of 4 or 2 CTAs share each tile's K range, as long as every
+    // rank keeps at least two K blocks and all clusters are resident at once.
+    if (!fan_out) {
+      bool fits = false;
+      if (tiles * 4 <= sms && p.k_blocks >= 8) {
+        const int status = launch_cluster_split<Grid, BK, STAGES, kRegPrefetch, kPacked, 4>(p, stream, &fits);
+        if (fits || status != B200_OK) return status;
+      }
+      if (tiles * 2 <= sms && p.k_blocks >= 4) {
+        const int status = launch_cluster_split<Grid, BK, STAGES, kRegPrefetch, kPacked, 2>(p, stream, &fits);
+        if (fits || status != B200_OK) return status;
+      }
+    }
+  }
   const int64_t units = kStreamK ? tiles * p.k_blocks : tiles;
   const int64_t slots = static_cast<int64_t>(sms) * kCtasPerSm;
   const int grid = static_cast<int>(units < slots ? units : slots);

@@ -509,7 +509,7 @@ int splitk_max_clusters(int cluster_size) {
   const int cached = cache[device][slot].load(std::memory_order_relaxed);
   if (cached != 0) return cached;
   auto kernel = umma_splitk_kernel<3, B200_EPILOGUE_LINEAR>;   // the activation does not change the footprint
-  constexpr size_t smem = smem_bytes<kSplitN, 3>() - kPeerStageBytes;   // no staging: two CTAs fit an SM
+  constexpr size_t smem = smem_bytes<kSplitN, 3>() - kStagingBytes;   // no staging: two CTAs fit an SM
   if (!ensure_dynamic_smem<umma_splitk_kernel<3, B200_EPILOGUE_LINEAR>, smem>()) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(cluster_size) * 64);
@@ -569,7 +569,7 @@ int splitk_ranks(const b200_gemm_problem& q, int sms, float* estimate_us = nullp
 template <int STAGES, int kAct, int KSUB = 1>
 int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   auto kernel = umma_splitk_kernel<STAGES, kAct, KSUB>;
-  constexpr size_t smem = smem_bytes<kSplitN, STAGES>() - kPeerStageBytes;   // its finishing pass needs no staging
+  constexpr size_t smem = smem_bytes<kSplitN, STAGES>() - kStagingBytes;   // its finishing pass needs no staging
   if (!ensure_dynamic_smem<umma_splitk_kernel<STAGES, kAct, KSUB>, smem>()) return B200_ERR_LAUNCH_FAILED;
   UmmaParams p;
   fill_common(&p, q, peers);

@@ -25,7 +25,7 @@ constexpr uint32_t kPairSubBytes = kASlabBytes + (kPairN / 2 / 32) * kBBoxBytes;
 // of the eight instructions of a two-sub-block stage.
 template <int STAGES, int KSUB>
 __host__ __device__ constexpr size_t pair_smem_bytes() {
-  return static_cast<size_t>(STAGES) * KSUB * kPairSubBytes + 1024 + 256 + kPeerStageBytes;
+  return static_cast<size_t>(STAGES) * KSUB * kPairSubBytes + 1024 + 1024 + kStagingBytes;   // ring | barriers | staging
 }
 
 // Work item of the CTA-pair kernel: a whole 256 x 256 tile, or (for the last, partial round of
@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
   uint64_t* acc_full = empty + STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_empty + 2);
-  float* peer_stage = reinterpret_cast<float*>(tmem_ptr + 4);
+  float* peer_stage = reinterpret_cast<float*>(stages + static_cast<size_t>(STAGES) * kPairStageBytes + 1024);   // kStagingBytes
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();  // 0: issues the MMAs, 1: peer
@@ -169,6 +169,9 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
     const int quarter = warp & 3;
     bool ok = true;
     int local = 0;
+    const bool boxed = p.tma_store != 0 && ep.vector_io && ep.peers.count == 0;
+    uint8_t* boxes = reinterpret_cast<uint8_t*>(peer_stage) + quarter * kOutStageBytesPerWarp;
+    uint32_t box_uses = 0;
     for (int item = first_tile; item < items && ok; item += tile_stride, ++local) {
       const PairItem it = pair_item(item, p.pair_full_tiles);
       const int buf = local & 1;
@@ -177,20 +180,19 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
       tile_coords(it.tile, tiles_m, tiles_n, &tm, &tn);
       const int n0 = tn * kPairN + (it.half < 0 ? 0 : it.half * (kPairN / 2));
       const int m0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
-      const bool pipelined = ep.vector_io && ep.peers.count == 0;
-      SourceChunk first;
-      if (pipelined) fetch_source(ep, first, m0 + quarter * 32 + lane, n0);   // before the wait
+      SourceQuads first;
+      if (boxed) fetch_source_coalesced(ep, first, m0 + quarter * 32, n0, lane);   // before the wait
       if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
       float* stage_area = peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float));
       if (it.half < 0) {
-        if (pipelined) {
-          epilogue_tile_pipelined<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, first);
+        if (boxed) {
+          epilogue_tile_boxed<kPairN, kAct>(p, ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, first, boxes, box_uses);
         } else {
           epilogue_tile<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, stage_area);
         }
-      } else if (pipelined) {
-        epilogue_tile_pipelined<kPairN / 2, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, first);
+      } else if (boxed) {
+        epilogue_tile_boxed<kPairN / 2, kAct>(p, ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, first, boxes, box_uses);
       } else {
         epilogue_tile<kPairN / 2, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, stage_area);
       }
@@ -199,6 +201,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
       // The MMA issuer (CTA 0) waits for the epilogues of both CTAs.
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
     }
+    if (boxed && lane == 0) tma_store_wait_all<0>();   // every store has left shared memory and landed
   }
 
   tcgen05_fence_before_sync();
@@ -218,13 +221,14 @@ int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream
   auto kernel = umma_pair_kernel<STAGES / KSUB, KSUB, kAct>;
   constexpr size_t smem = pair_smem_bytes<STAGES / KSUB, KSUB>();
   if (!ensure_dynamic_smem<umma_pair_kernel<STAGES / KSUB, KSUB, kAct>, smem>()) return B200_ERR_LAUNCH_FAILED;
-  const size_t launch_smem = smem - (peers.count > 0 ? 0 : kPeerStageBytes);
+  const size_t launch_smem = smem;
   UmmaParams p;
   fill_common(&p, q, peers);
   if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
       !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
     return B200_ERR_MISALIGNED_OPERAND;
   }
+  p.tma_store = (p.vector_io && make_tensor_map_2d(&p.map_d, q.d, q.m, q.n, q.ldd, 32, 32, Swizzle::k128B)) ? 1 : 0;
   p.b_strips = (q.n % 32 == 0 && make_tensor_map_strips(&p.map_b_strips, q.b, q.k, q.n, q.ldb, kStageK,
                                                         kPairN / 2 / 32, Swizzle::k128BAtom32B))
                    ? kPairN / 2 / 32

@@ -133,9 +133,15 @@ __device__ __forceinline__ void load_stage_regs(const UmmaParams& p, StageRegs<B
   const int64_t a_step = static_cast<int64_t>(kLoaderWarps) * p.lda, b_step = 4 * p.ldb;
   if (m0 + kTileM <= p.m && n0 + BN <= p.n && k0 + kStageK <= p.k) {  // interior stage: no predicates
 #pragma unroll
-    for (int i = 0; i < kGenericARows; ++i) r.a[i] = __ldg(a_ptr + i * a_step);
+    for (int i = 0; i < kGenericARows; ++i) {
+      r.a[i] = B200_IN_BOUNDS(a_ptr + i * a_step >= p.a && a_ptr + i * a_step < p.a + static_cast<int64_t>(p.m - 1) * p.lda + p.k)
+                   ? __ldg(a_ptr + i * a_step) : 0.f;
+    }
 #pragma unroll
-    for (int i = 0; i < StageRegs<BN>::kBRows; ++i) r.b[i] = __ldg(b_ptr + (i & 7) * b_step + (i >> 3) * 32);
+    for (int i = 0; i < StageRegs<BN>::kBRows; ++i) {
+      const float* src = b_ptr + (i & 7) * b_step + (i >> 3) * 32;
+      r.b[i] = B200_IN_BOUNDS(src >= p.b && src < p.b + static_cast<int64_t>(p.k - 1) * p.ldb + p.n) ? __ldg(src) : 0.f;
+    }
   } else {
     const bool k_ok = k0 + lane < p.k;
 #pragma unroll
@@ -274,15 +280,15 @@ int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_
   auto kernel = umma_tma_kernel<BN, STAGES, kAct, KSUB>;
   constexpr size_t smem = smem_bytes<BN, STAGES>();
   if (!ensure_dynamic_smem<umma_tma_kernel<BN, STAGES, kAct, KSUB>, smem>()) return B200_ERR_LAUNCH_FAILED;
-  // The staging area of the fused all-gather is only asked for when there are peers: a plain GEMM
-  // keeps the larger L1 for its epilogue's source reads.
-  const size_t launch_smem = smem - (peers.count > 0 ? 0 : kPeerStageBytes);
+  const size_t launch_smem = smem;
   UmmaParams p;
   fill_common(&p, q, peers);
   if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
       !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
     return B200_ERR_MISALIGNED_OPERAND;
   }
+  // The output leaves through TMA stores of 32 x 32 boxes whenever its rows allow 128-bit accesses.
+  p.tma_store = (p.vector_io && make_tensor_map_2d(&p.map_d, q.d, q.m, q.n, q.ldd, 32, 32, Swizzle::k128B)) ? 1 : 0;
   // One copy per B slab when the columns split into whole 32-wide strips.
   p.b_strips = (q.n % 32 == 0 && make_tensor_map_strips(&p.map_b_strips, q.b, q.k, q.n, q.ldb, kStageK, BN / 32,
                                                         Swizzle::k128BAtom32B))
@@ -301,7 +307,7 @@ int launch_generic(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStr
   auto kernel = umma_generic_kernel<BN, STAGES, kAct>;
   constexpr size_t smem = smem_bytes<BN, STAGES>();
   if (!ensure_dynamic_smem<umma_generic_kernel<BN, STAGES, kAct>, smem>()) return B200_ERR_LAUNCH_FAILED;
-  const size_t launch_smem = smem - (peers.count > 0 ? 0 : kPeerStageBytes);
+  const size_t launch_smem = smem;
   UmmaParams p;
   fill_common(&p, q, peers);
   const int sms = sm_count();

@@ -85,6 +85,8 @@ struct UmmaParams {
   CUtensorMap map_b;   // [K][N] boxes {32, 32},  128-byte swizzle, 32-byte granules
   CUtensorMap map_b_strips;  // [N/32][K][32] boxes {32, 32, strips}: a whole B slab in one copy (N % 32 == 0)
   int b_strips;        // strips per map_b_strips box, 0 when that map is not usable
+  CUtensorMap map_d;   // [M][N] boxes {32, 32}, 128-byte swizzle: the output, written by TMA stores
+  int tma_store;       // map_d is usable (D 16-byte aligned, ldd a multiple of four floats)
   const float* a;      // generic loader only
   const float* b;
   const float* c;      // source, may be null when beta == 0
@@ -149,10 +151,19 @@ constexpr int kPeerStagePitch = 36;
 constexpr size_t kPeerStageBytesPerWarp = 32 * kPeerStagePitch * sizeof(float);
 constexpr size_t kPeerStageBytes = 4 * kPeerStageBytesPerWarp;   // four epilogue warps
 
+// Staging of the ordinary epilogue: per epilogue warp two 32 x 32 boxes (4 KiB each) in the 128-byte
+// swizzle, from which TMA stores write the output in whole 128-byte row segments. The fused
+// all-gather's staging (above) lives in the same region; a launch uses one or the other.
+constexpr uint32_t kOutBoxBytes = 32 * 32 * sizeof(float);
+constexpr size_t kOutStageBytesPerWarp = 2 * kOutBoxBytes;
+constexpr size_t kStagingBytes = 4 * kOutStageBytesPerWarp;   // 32 KiB, 1024-byte aligned
+static_assert(kStagingBytes >= kPeerStageBytes, "one region serves both");
+
+// ring | 1 KiB of barriers and the TMEM pointer | staging; the base is rounded up to 1 KiB.
 template <int BN, int STAGES>
 __host__ __device__ constexpr size_t smem_bytes() {
-  return static_cast<size_t>(STAGES) * stage_bytes<BN>() + 1024 /*alignment slack*/ + 256 /*barriers + tmem ptr*/ +
-         kPeerStageBytes;
+  return static_cast<size_t>(STAGES) * stage_bytes<BN>() + 1024 /*alignment slack*/ + 1024 /*barriers + tmem ptr*/ +
+         kStagingBytes;
 }
 
 template <int BN>
@@ -197,77 +208,105 @@ __device__ __forceinline__ float activate(float v) {
   return v;
 }
 
-// Source values of one 32-column chunk of a thread's row (zeros when there is no source).
-struct SourceChunk {
-  float4 v[8];
+// ------------------------------------------------- epilogue through shared memory and TMA stores
+// A thread owns one ROW of the accumulator (that is how tcgen05.ld hands it out), so storing
+// straight from registers makes every warp-wide 128-bit access touch 32 different 128-byte lines:
+// the load/store unit handles one line per cycle, and a 256-column tile cost about 16 000 of those
+// cycles in reads of C and writes of D - 15 us that nothing hides for a CTA's last tile (in-kernel
+// time stamps at 1024^3 .. 4096^3). Here the warp turns each 32 x 32 chunk through a swizzled box in
+// shared memory instead: C arrives with coalesced loads (a lane holds column quad l % 8 of rows
+// 4 j + l / 8, four whole 128-byte rows per instruction) and is turned into row ownership in the box;
+// the finished chunk is written into the box row by row and leaves as ONE TMA store, which also
+// clips the edges of the matrix. Arithmetic and its order are those of every other epilogue path
+// (alpha * acc rounded, then one FMA with the source, then the bias): all paths give the same bits.
+
+// Source values of a 32 x 32 chunk in coalesced ownership.
+struct SourceQuads {
+  float4 v[8];   // v[j]: row 4 j + lane / 8, columns 4 (lane % 8) .. + 3
 };
 
-// C of chunk `chunk` for the row of this thread. Issued well before the values are needed:
-// for the first chunk of a tile even before the accumulator is ready.
-__device__ __forceinline__ void fetch_source(const EpilogueArgs& p, SourceChunk& out, int row, int col0) {
-  const bool want = p.beta != 0.f && row < p.m;
-  const float* c_row = p.c + static_cast<int64_t>(row) * p.ldc;
+__device__ __forceinline__ void fetch_source_coalesced(const EpilogueArgs& p, SourceQuads& out, int row0, int col0, int lane) {
+  const bool want = p.beta != 0.f && col0 + 4 * (lane & 7) < p.n;
+  const float* c_ptr = p.c + static_cast<int64_t>(row0 + (lane >> 3)) * p.ldc + col0 + 4 * (lane & 7);
 #pragma unroll
-  for (int g = 0; g < 8; ++g) {
-    const int col = col0 + 4 * g;
-    out.v[g] = (want && col < p.n) ? __ldg(reinterpret_cast<const float4*>(c_row + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j = 0; j < 8; ++j) {
+    out.v[j] = (want && row0 + 4 * j + (lane >> 3) < p.m) ? __ldg(reinterpret_cast<const float4*>(c_ptr + static_cast<int64_t>(4 * j) * p.ldc))
+                                                          : make_float4(0.f, 0.f, 0.f, 0.f);
   }
 }
 
-// One chunk of the vectorised epilogue: alpha * acc + beta * C + bias, activation, 128-bit stores.
+// Byte offset of the 16-byte granule (row, quad) of a 32 x 32 FP32 box in the 128-byte swizzle.
+__device__ __forceinline__ uint32_t box_offset(int row, int quad) {
+  return static_cast<uint32_t>(row) * 128u + (static_cast<uint32_t>(quad ^ (row & 7)) << 4);
+}
+
+// One chunk: source into row ownership, alpha * acc + beta * C + bias, activation, box, TMA store.
+// `box` is one of the warp's two boxes (alternating); at most one earlier store may still be reading
+// the other one.
 template <int kAct>
-__device__ __forceinline__ void finish_chunk(const EpilogueArgs& p, const uint32_t (&raw)[32], const SourceChunk& src, int row,
-                                             int col0) {
-  if (row >= p.m) return;
-  const bool use_bias = p.bias != nullptr;
-  float* d_row = p.d + static_cast<int64_t>(row) * p.ldd;
+__device__ __forceinline__ void finish_chunk_boxed(const UmmaParams& p, const EpilogueArgs& ep, const uint32_t (&raw)[32],
+                                                   const SourceQuads& cq, int row0, int col0, int lane, uint8_t* box) {
+  if (lane == 0) tma_store_wait_read<1>();   // the store that used this box two chunks ago has read it
+  __syncwarp();
+  const bool use_source = ep.beta != 0.f;
+  if (use_source) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(box + box_offset(4 * j + (lane >> 3), lane & 7)) = cq.v[j];
+    __syncwarp();
+  }
+  // From here on a lane touches its own row of the box only: it reads a granule of C and puts the
+  // finished values in its place.
+  const bool use_bias = ep.bias != nullptr;
 #pragma unroll
   for (int g = 0; g < 8; ++g) {
-    const int col = col0 + 4 * g;
-    if (col < p.n) {   // n % 4 == 0 on this path: a quad is inside or outside as a whole
-      // Same operation order as every other epilogue path (alpha * acc rounded, then one FMA with
-      // the source), so that all paths give identical bits. Without a source src is zero and beta finite.
-      float4 v = make_float4(fmaf(p.beta, src.v[g].x, p.alpha * __uint_as_float(raw[4 * g + 0])),
-                             fmaf(p.beta, src.v[g].y, p.alpha * __uint_as_float(raw[4 * g + 1])),
-                             fmaf(p.beta, src.v[g].z, p.alpha * __uint_as_float(raw[4 * g + 2])),
-                             fmaf(p.beta, src.v[g].w, p.alpha * __uint_as_float(raw[4 * g + 3])));
-      if (use_bias) {
-        const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
-        v.x += bv.x, v.y += bv.y, v.z += bv.z, v.w += bv.w;
-      }
-      *reinterpret_cast<float4*>(d_row + col) =
-          make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
+    float4* slot = reinterpret_cast<float4*>(box + box_offset(lane, g));
+    const float4 src = use_source ? *slot : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 v = make_float4(fmaf(ep.beta, src.x, ep.alpha * __uint_as_float(raw[4 * g + 0])),
+                           fmaf(ep.beta, src.y, ep.alpha * __uint_as_float(raw[4 * g + 1])),
+                           fmaf(ep.beta, src.z, ep.alpha * __uint_as_float(raw[4 * g + 2])),
+                           fmaf(ep.beta, src.w, ep.alpha * __uint_as_float(raw[4 * g + 3])));
+    if (use_bias && col0 + 4 * g < ep.n) {
+      const float4 bv = __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + 4 * g));
+      v.x += bv.x, v.y += bv.y, v.z += bv.z, v.w += bv.w;
     }
+    *slot = make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
+  }
+  fence_proxy_async_smem();   // the box was written through the generic proxy, the store reads through the async one
+  __syncwarp();
+  if (lane == 0) {
+    if (row0 < ep.m && col0 < ep.n) tma_store_2d(&p.map_d, box, col0, row0);   // rows and columns past the matrix are clipped
+    tma_store_commit();   // one group per use of a box, stored or not: the wait above counts groups
   }
 }
 
-// Vectorised epilogue of one 128 x BN tile for one warp, software-pipelined: while a chunk is
-// scaled and stored, the next chunk's accumulators are on their way from TMEM and its source
-// values from memory. `first` holds the source of chunk 0 (fetched by the caller before it waited
-// for the accumulator). Two named register sets alternate so that both stay in registers.
+// Epilogue of one 128 x BN tile for one warp through the boxes, software-pipelined: two named
+// register sets alternate, so while a chunk is finished the next chunk's accumulators are on their
+// way from TMEM and its source values from memory. `first` holds the source of chunk 0 (fetched by the
+// caller before it waited for the accumulator); `uses` counts the warp's box uses across tiles.
 template <int BN, int kAct>
-__device__ __forceinline__ void epilogue_tile_pipelined(const EpilogueArgs& p, uint32_t tmem_acc, int quarter, int lane,
-                                                        int m0, int n0, const SourceChunk& first) {
+__device__ __forceinline__ void epilogue_tile_boxed(const UmmaParams& p, const EpilogueArgs& ep, uint32_t tmem_acc, int quarter,
+                                                    int lane, int m0, int n0, const SourceQuads& first, uint8_t* boxes,
+                                                    uint32_t& uses) {
   constexpr int kChunks = BN / 32;
   static_assert(kChunks % 2 == 0, "chunks are handled in pairs");
-  const int row = m0 + quarter * 32 + lane;
+  const int row0 = m0 + quarter * 32;
   const uint32_t tmem_row = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
   uint32_t raw_even[32], raw_odd[32];
-  SourceChunk src_even = first, src_odd;
+  SourceQuads src_even = first, src_odd;
   tmem_ld_32x32(tmem_row, raw_even);
 #pragma unroll
   for (int chunk = 0; chunk < kChunks; chunk += 2) {
-    if (n0 + chunk * 32 >= p.n) break;   // uniform across the warp
+    if (n0 + chunk * 32 >= ep.n) break;   // uniform across the warp
     tmem_ld_wait();
     tmem_ld_32x32(tmem_row + (chunk + 1) * 32, raw_odd);
-    fetch_source(p, src_odd, row, n0 + (chunk + 1) * 32);
-    finish_chunk<kAct>(p, raw_even, src_even, row, n0 + chunk * 32);
+    fetch_source_coalesced(ep, src_odd, row0, n0 + (chunk + 1) * 32, lane);
+    finish_chunk_boxed<kAct>(p, ep, raw_even, src_even, row0, n0 + chunk * 32, lane, boxes + (uses++ & 1u) * kOutBoxBytes);
     tmem_ld_wait();
     if (chunk + 2 < kChunks) {
       tmem_ld_32x32(tmem_row + (chunk + 2) * 32, raw_even);
-      fetch_source(p, src_even, row, n0 + (chunk + 2) * 32);
+      fetch_source_coalesced(ep, src_even, row0, n0 + (chunk + 2) * 32, lane);
     }
-    finish_chunk<kAct>(p, raw_odd, src_odd, row, n0 + (chunk + 1) * 32);
+    finish_chunk_boxed<kAct>(p, ep, raw_odd, src_odd, row0, n0 + (chunk + 1) * 32, lane, boxes + (uses++ & 1u) * kOutBoxBytes);
   }
   tmem_ld_wait();   // nothing from TMEM is in flight when the accumulator is handed back
 }
@@ -352,6 +391,7 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tm
             v.x += bv.x, v.y += bv.y, v.z += bv.z, v.w += bv.w;
           }
           v = make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
+          if (!B200_IN_BOUNDS(row >= 0 && row < p.m && col >= 0 && col + 4 <= p.n && p.ldd >= p.n)) continue;
           *reinterpret_cast<float4*>(d_row + col) = v;
         }
       }
@@ -364,6 +404,7 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tm
           if (use_c) v = fmaf(p.beta, __ldg(c_row + col), v);
           if (use_bias) v += __ldg(p.bias + col);
           v = activate<kAct>(v);
+          if (!B200_IN_BOUNDS(row >= 0 && row < p.m && col >= 0 && col < p.n)) continue;
           d_row[col] = v;
           store_peers(p, static_cast<int64_t>(row) * p.ldd + col, v);
         }
@@ -379,7 +420,7 @@ struct SmemCarve {
   uint64_t* acc_full;
   uint64_t* acc_empty;
   uint32_t* tmem_ptr;
-  float* peer_stage;   // kPeerStageBytes, 16-byte aligned
+  float* peer_stage;   // kStagingBytes, 1024-byte aligned: fused all-gather staging or output boxes
 };
 
 template <int BN, int STAGES>
@@ -391,7 +432,7 @@ __device__ __forceinline__ SmemCarve carve(uint8_t* raw) {
   s.acc_full = s.empty + STAGES;
   s.acc_empty = s.acc_full + 2;
   s.tmem_ptr = reinterpret_cast<uint32_t*>(s.acc_empty + 2);
-  s.peer_stage = reinterpret_cast<float*>(s.tmem_ptr + 4);
+  s.peer_stage = reinterpret_cast<float*>(s.stages + static_cast<size_t>(STAGES) * stage_bytes<BN>() + 1024);
   return s;
 }
 
@@ -437,18 +478,20 @@ __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCar
   const EpilogueArgs ep = epilogue_args(p);
   bool ok = true;
   int local = 0;
+  const bool boxed = kPipelinedEpilogue && p.tma_store != 0 && ep.vector_io && ep.peers.count == 0;
+  uint8_t* boxes = reinterpret_cast<uint8_t*>(sm.peer_stage) + quarter * kOutStageBytesPerWarp;
+  uint32_t box_uses = 0;
   for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
     const int buf = local & 1;
     const uint32_t use_parity = (local >> 1) & 1u;
     int tm, tn;
     tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
-    const bool pipelined = kPipelinedEpilogue && ep.vector_io && ep.peers.count == 0;
-    SourceChunk first;
-    if (pipelined) fetch_source(ep, first, tm * kTileM + quarter * 32 + lane, tn * BN);   // before the wait
+    SourceQuads first;
+    if (boxed) fetch_source_coalesced(ep, first, tm * kTileM + quarter * 32, tn * BN, lane);   // before the wait
     if (!mbar_wait(&sm.acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
     tcgen05_fence_after_sync();
-    if (pipelined) {
-      epilogue_tile_pipelined<BN, kAct>(ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN, first);
+    if (boxed) {
+      epilogue_tile_boxed<BN, kAct>(p, ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN, first, boxes, box_uses);
     } else {
       epilogue_tile<BN, kAct>(ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN,
                               sm.peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float)));
@@ -457,6 +500,7 @@ __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCar
     __syncwarp();
     if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
   }
+  if (boxed && lane == 0) tma_store_wait_all<0>();   // every store has left shared memory and landed
 }
 
 // Threads of every TMA-fed kernel: warp 0 producer, warp 1 TMEM owner + MMA issuer, warps 2-5 epilogue.

@@ -178,3 +178,28 @@ def test_abi_rejects_without_launching(abi):
     assert abi.b200_sgemm_gather(impl, a.data_ptr(), b.data_ptr(), shifted_c, peers, 1, 128, 128, 16,
                                  current_stream_ptr()) == 1
     assert_device_clean(abi)
+
+
+# Few tiles and a long K: prefetch_smem / prefetch_reg run clusters of 4 or 2 CTAs per tile that
+# share the K range and add their partial tiles through distributed shared memory.
+CLUSTER_SPLIT_SHAPES = [(256, 384, 1024),    # 6 tiles, 16 K blocks: clusters of 4
+                        (128, 128, 200),     # 1 tile, 4 K blocks with a ragged last one: clusters of 2
+                        (128, 128, 4096),    # 1 tile, 64 K blocks
+                        (1024, 1024, 512),   # 64 tiles, 8 K blocks: clusters of 2
+                        (640, 768, 1104)]    # 30 tiles, 18 K blocks (uneven shares, ragged K): clusters of 4
+
+
+@pytest.mark.parametrize("impl", ["prefetch_smem", "prefetch_reg"])
+@pytest.mark.parametrize("shape", CLUSTER_SPLIT_SHAPES)
+def test_cluster_split_is_exact_on_integers_and_matches_the_oracle(abi, impl, shape):
+    m, n, k = shape
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randint(-3, 4, (k, m), generator=g).float().cuda().t()      # column-major A
+    b = torch.randint(-3, 4, (k, n), generator=g).float().cuda()
+    out = abi_sgemm(abi, impl, a, b)
+    torch.testing.assert_close(out.cpu(), oracle.gemm_fp64(a, b), atol=0, rtol=0)
+    a_cpu, b_cpu, a_dev, b_dev = device_inputs(m, n, k, seed=k)
+    first = abi_sgemm(abi, impl, a_dev, b_dev)
+    check_against_oracle(first, a_cpu, b_cpu)
+    assert torch.equal(abi_sgemm(abi, impl, a_dev, b_dev), first)          # partial tiles are added in rank order
+    assert_device_clean(abi)

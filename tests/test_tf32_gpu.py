@@ -513,3 +513,4 @@ def test_compensated_tf32_bias_integers_and_refusals(abi):
     assert abi.b200_tf32x3_gemm(ctypes.byref(q), None, need, current_stream_ptr()) == 4
     assert abi.b200_tf32x3_gemm(ctypes.byref(q), scratch.data_ptr() + 4, need, current_stream_ptr()) == 4
     assert_device_clean(abi)
+
