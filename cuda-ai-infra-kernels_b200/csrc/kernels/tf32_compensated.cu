@@ -16,11 +16,21 @@
 //
 // Scratch: the two lo matrices, dense, rows padded to four floats (so that the TMA-fed kernels
 // can take them): the caller passes b200_tf32x3_scratch_bytes(m, n, k) bytes of device memory.
+#include <atomic>
+#include <mutex>
+
 #include "host_common.h"
 #include "tf32_gemm.h"
 
 namespace b200 {
 namespace {
+
+// Scratch for callers that cannot hand any over (b200_tf32x3_gemm_static): a fixed array that is part
+// of the library image, 8 MiB on every GPU that loads the library, for as long as the library stays
+// loaded. In host code this name is only a handle for the symbol, not a device address: the address
+// a kernel can use is asked for once per device with cudaGetSymbolAddress (static_scratch below).
+constexpr size_t kStaticScratchBytes = size_t{8} << 20;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
 
 __host__ __device__ inline int64_t padded4(int64_t cols) { return (cols + 3) / 4 * 4; }
 
@@ -48,6 +58,26 @@ __global__ void split_lo_kernel(const float* __restrict__ a, int64_t lda, int m,
     }
     (in_a ? a_lo : b_lo)[j] = lo;
   }
+}
+
+// Device address of g_static_scratch on the CURRENT device, looked up on the first call for that
+// device (with that device current) and remembered. nullptr when the look-up failed.
+float* static_scratch() {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mutex;
+  static float* address[kMaxDevices] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return nullptr;
+  const std::lock_guard<std::mutex> lock(mutex);
+  if (address[device] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    address[device] = static_cast<float*>(ptr);
+  }
+  return address[device];
 }
 
 }  // namespace
@@ -98,6 +128,19 @@ int b200_tf32x3_gemm(const b200_gemm_problem* q, void* scratch, size_t scratch_b
   pass.epilogue = q->epilogue;
   pass.bias = q->bias;
   return b200_tf32_gemm_dispatch(B200_TF32_KERNEL_AUTO, &pass, nullptr, stream);
+}
+
+size_t b200_tf32x3_static_scratch_bytes(void) { return b200::kStaticScratchBytes; }
+
+int b200_tf32x3_gemm_static(const b200_gemm_problem* q, b200_stream_t stream) {
+  if (q == nullptr || q->m <= 0 || q->n <= 0 || q->k <= 0) return B200_ERR_INVALID_ARGUMENT;
+  // Too large for the fixed array: refused before anything is launched or looked up.
+  if (b200_tf32x3_scratch_bytes(q->m, q->n, q->k) > b200::kStaticScratchBytes) return B200_ERR_NOT_SUPPORTED;
+  float* scratch = b200::static_scratch();   // the first call on a device resolves the symbol's address
+  if (scratch == nullptr) return B200_ERR_INTERNAL;
+  // The splitting pass rewrites every element of the scratch that the products read (padding columns
+  // included), so whatever an earlier call left in the array does not matter and nothing is cleared.
+  return b200_tf32x3_gemm(q, scratch, b200::kStaticScratchBytes, stream);
 }
 
 }  // extern "C"

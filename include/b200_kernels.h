@@ -267,6 +267,36 @@ size_t b200_tf32x3_scratch_bytes(int m, int n, int k);
 int b200_tf32x3_gemm(const b200_gemm_problem* problem, void* scratch,
                      size_t scratch_bytes, b200_stream_t stream);
 
+/*
+ * b200_tf32x3_gemm for callers that have no device memory to lend and may not
+ * allocate any. This entry point has no counterpart in the reference. It is
+ * meant for hosts whose memory is spoken for before they load this library: a
+ * serving process whose framework allocator has claimed the whole GPU (a direct
+ * cudaMalloc then fails or fights that allocator), a plugin that is given
+ * buffers for inputs and outputs and nothing else, a latency-bound loop in
+ * which the device-wide synchronisation of cudaMalloc / cudaFree is not
+ * acceptable. The two lo matrices live in a fixed array inside the library
+ * image instead: b200_tf32x3_static_scratch_bytes() = 8 MiB, held by every GPU
+ * that loads the library until the process exits.
+ *   - The caller still passes A, B, C, D as for b200_tf32x3_gemm; results are
+ *     bit-identical to it.
+ *   - A problem whose b200_tf32x3_scratch_bytes(m, n, k) exceeds the array
+ *     (e.g. anything beyond m = n = k = 1024) returns B200_ERR_NOT_SUPPORTED
+ *     and launches nothing.
+ *   - The call, and everything below it, calls no cudaMalloc, cudaFree or other
+ *     allocating routine.
+ *   - The FIRST call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and remembers it. Make
+ *     that first call during set-up, before any stream capture begins.
+ *   - All calls on a device share the one array, which keeps whatever the last
+ *     call wrote; nothing in it needs to start at zero (each call rewrites all
+ *     it reads). Two calls whose work overlaps on the GPU (different streams, or
+ *     different host threads' streams) race on it: serialise them, or use
+ *     b200_tf32x3_gemm with scratch of your own.
+ */
+size_t b200_tf32x3_static_scratch_bytes(void);
+int b200_tf32x3_gemm_static(const b200_gemm_problem* problem, b200_stream_t stream);
+
 /* ------------------------------------------------------------ row operators */
 
 typedef enum b200_rmsnorm_impl {

@@ -84,6 +84,8 @@ def load_abi() -> ctypes.CDLL:
     lib.b200_tf32x3_scratch_bytes.restype = ctypes.c_size_t
     lib.b200_tf32x3_scratch_bytes.argtypes = [c_int, c_int, c_int]
     lib.b200_tf32x3_gemm.argtypes = [ctypes.POINTER(GemmProblem), c_void_p, ctypes.c_size_t, c_void_p]
+    lib.b200_tf32x3_static_scratch_bytes.restype = ctypes.c_size_t
+    lib.b200_tf32x3_gemm_static.argtypes = [ctypes.POINTER(GemmProblem), c_void_p]
     lib.b200_rmsnorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, ctypes.c_double, c_void_p]
     lib.b200_softmax.argtypes = [c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p]
     lib.b200_shard_rows.argtypes = [c_int64, c_int, c_int, ctypes.POINTER(c_int64), ctypes.POINTER(c_int64)]
