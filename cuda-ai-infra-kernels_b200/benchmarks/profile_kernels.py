@@ -1,6 +1,6 @@
 """Launches each hot-path kernel a few times at its benchmark shape, for ncu.
 
-    python cuda-ai-infra-kernels_b200/benchmarks/profile_kernels.py [sgemm] [tf32] [rows] [tf32_other] [tf32_mid] [--small]
+    python cuda-ai-infra-kernels_b200/benchmarks/profile_kernels.py [sgemm] [tf32] [tf32_pair] [rows] [tf32_other] [tf32_mid] [--small]
 
 Meant to be wrapped by Nsight Compute: ONE kernel per capture, two or three
 launches, the small case, e.g.
@@ -13,7 +13,8 @@ anything beyond a plain launch list is taken with `--small`, one `-k` pattern
 and `-c 2` or `-c 3`). The role of the reference's profiling/profile_*.sh
 wrappers. `--small` halves the GEMM edge (2048: operands 3 x 16 MiB) so that a
 multi-pass capture stays short; the row-operator shapes (256 MiB and 128 MiB per
-tensor) are already small enough. `tf32_mid` runs the mid-sized shapes where one
+tensor) are already small enough. `tf32` goes through automatic dispatch (CTA pairs at
+4096, 128 x 256 tiles at 2048); `tf32_pair` forces the CTA-pair kernel at either size. `tf32_mid` runs the mid-sized shapes where one
 round of tiles decides (1536^3 through the 128 x 128 TMA tile kernel,
 1024 x 1024 x 8192 through automatic dispatch). `tf32_other`
 runs the registry entries for awkward shapes: the warp-specialised loader on
@@ -46,6 +47,12 @@ def main(argv):
         c = torch.randn(edge, edge, device=dev)
         for _ in range(2):
             pkg.adaptive_gemm(a, b, c=c, alpha=1.0, beta=0.5, epilogue="relu")
+    if "tf32_pair" in which:
+        a = torch.randn(edge, edge, device=dev)
+        b = torch.randn(edge, edge, device=dev)
+        c = torch.randn(edge, edge, device=dev)
+        for _ in range(3):
+            pkg.adaptive_gemm(a, b, c=c, alpha=1.0, beta=0.5, epilogue="relu", kernel="pair_relu")
     if "tf32_mid" in which:
         a = torch.randn(1536, 1536, device=dev)
         b = torch.randn(1536, 1536, device=dev)

@@ -483,14 +483,11 @@ int max_resident_clusters(int split) {
 
 // One tile per cluster of kSplit CTAs, K shared out over the ranks (see the kernel).
 template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, int kSplit>
-int launch_cluster_split(const PipelineParams& p, cudaStream_t stream, bool* fits) {
+int launch_cluster_split(const PipelineParams& p, cudaStream_t stream) {
   using Layout = SmemLayout<BK, STAGES>;
   constexpr auto kernel = sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, false, 1, false, kSplit>;
-  *fits = false;
   if (!ensure_dynamic_smem<kernel, Layout::kBytes>()) return B200_ERR_LAUNCH_FAILED;
-  const int tiles = p.tiles_m * p.tiles_n;
-  if (max_resident_clusters<kernel, Layout::kBytes, Grid::kThreads>(kSplit) < tiles) return B200_OK;   // would run in waves
-  *fits = true;
+  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(tiles * kSplit));
   cfg.blockDim = dim3(Grid::kThreads);
@@ -505,6 +502,26 @@ int launch_cluster_split(const PipelineParams& p, cudaStream_t stream, bool* fit
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
+}
+
+// How many CTAs should share a tile's K range: the split with the fewest K blocks per CTA (plus the
+// exchange, about 1.5 K blocks of 64) among those whose clusters are all resident at once. Splits
+// that need more than one wave of clusters were measured and lose: 1024 x 4096 x 4096 (256 tiles)
+// as 512 half-K CTAs took 655 us against 626 us for one persistent CTA per SM - every CTA of a
+// split launch pays its own prologue and pipeline fill, and a wave of clusters only starts when
+// whole clusters' worth of SMs are free. 1024^3 (64 tiles, 16 K blocks): two CTAs per tile on 128
+// SMs, 80.7 -> 46.5 us; 512 x 512 x 4096: four per tile.
+inline int choose_split(int64_t tiles, int k_blocks, int max_clusters2, int max_clusters4) {
+  constexpr double kExchange = 1.5;
+  double best = static_cast<double>(k_blocks);
+  int split = 1;
+  for (int s = 2; s <= 4; s *= 2) {
+    if (k_blocks / s < 2) break;                                  // every rank keeps at least two K blocks
+    if (tiles > (s == 2 ? max_clusters2 : max_clusters4)) break;  // all clusters resident at once
+    const double cost = static_cast<double>(k_blocks) / s + kExchange;
+    if (cost < best * 0.97) best = cost, split = s;               // a tie goes to the simpler launch
+  }
+  return split;
 }
 
 template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, bool kStreamK, int kCtasPerSm>
@@ -543,18 +560,18 @@ int launch_pipeline(const float* a, const float* b, float* c, const PeerOutputs&
   }
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   if constexpr (!kStreamK && kCtasPerSm == 1 && Grid::kProducerWarp) {
-    // Fewer tiles than SMs: clusters of 4 or 2 CTAs share each tile's K range, as long as every
-    // rank keeps at least two K blocks and all clusters are resident at once.
+    // Tiles that fill the SMs badly: clusters of 2 or 4 CTAs share each tile's K range.
     if (!fan_out) {
-      bool fits = false;
-      if (tiles * 4 <= sms && p.k_blocks >= 8) {
-        const int status = launch_cluster_split<Grid, BK, STAGES, kRegPrefetch, kPacked, 4>(p, stream, &fits);
-        if (fits || status != B200_OK) return status;
+      constexpr auto kSplit2 = sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, false, 1, false, 2>;
+      constexpr auto kSplit4 = sgemm_pipeline_kernel<Grid, BK, STAGES, kRegPrefetch, kPacked, false, 1, false, 4>;
+      if (!ensure_dynamic_smem<kSplit2, Layout::kBytes>() || !ensure_dynamic_smem<kSplit4, Layout::kBytes>()) {
+        return B200_ERR_LAUNCH_FAILED;
       }
-      if (tiles * 2 <= sms && p.k_blocks >= 4) {
-        const int status = launch_cluster_split<Grid, BK, STAGES, kRegPrefetch, kPacked, 2>(p, stream, &fits);
-        if (fits || status != B200_OK) return status;
-      }
+      const int split = tiles >= sms ? 1
+                                     : choose_split(tiles, p.k_blocks, max_resident_clusters<kSplit2, Layout::kBytes, Grid::kThreads>(2),
+                                                    max_resident_clusters<kSplit4, Layout::kBytes, Grid::kThreads>(4));
+      if (split == 4) return launch_cluster_split<Grid, BK, STAGES, kRegPrefetch, kPacked, 4>(p, stream);
+      if (split == 2) return launch_cluster_split<Grid, BK, STAGES, kRegPrefetch, kPacked, 2>(p, stream);
     }
   }
   const int64_t units = kStreamK ? tiles * p.k_blocks : tiles;
