@@ -65,16 +65,17 @@ FP32_LANES_PER_SM = 128
 # A800 80GB PCIe, 17.206 TFLOP/s (its README.md:17). Other hardware; per GPU.
 PUBLISHED_A800_SPLIT_K_TFLOPS = 17.206
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels.
-# A benchmark cannot run Nsight Compute on itself, so the figures are carried here: each comes from
-# one `ncu` capture of one launch of that kernel (FP32 and TF32: at 2048^3, scaled by the tile count
-# to 4096^3 - operand traffic per tile does not depend on the problem size once it exceeds L2; row
-# operators: at the benchmark shape itself, 256 / 128 MiB per array). Beside them stand the
-# algorithmic bytes: 201 MB (FP32 and TF32 at 4096^3: A + B + C), 537 MB, 268 MB.
+# A benchmark cannot run Nsight Compute on itself, so the figures are carried here. Each comes from
+# one `ncu` capture of that kernel alone at the benchmark size (a handful of counters, two to four
+# launches): the small cases used for the full counter sets keep their operands in L2 and say
+# nothing about DRAM, so traffic is not scaled up from them. Beside them stand the algorithmic
+# bytes: 201 MB (FP32 4096^3: A + B + C), 268 MB (TF32 4096^3 with a source: A + B + C + D),
+# 537 MB (RMSNorm), 268 MB (softmax).
 NCU_TRAFFIC_BYTES = {
-    "sgemm_4096": 334.2e6 + 54.9e6,
-    "tf32_4096": 372.6e6 + 50.7e6,
-    "rmsnorm_16384x4096": 268.5e6 + 213.0e6,   # writes partly still in L2 at kernel end
-    "softmax_32768x1024": 134.2e6 + 78.2e6,
+    "sgemm_4096": 336.2e6 + 53.9e6,
+    "tf32_4096": 376.7e6 + 54.4e6,
+    "rmsnorm_16384x4096": 481.0e6,   # below the algorithmic bytes: the last written lines are still in L2
+    "softmax_32768x1024": 212.0e6,
 }
 
 
