@@ -361,6 +361,14 @@ def measure_extras(pkg, peaks: dict, device_index: int, warmup: int) -> dict:
     res = cmp.run({name: (lambda i, name=name: pkg.gemm(a_sets[i & 1], b_sets[i & 1], impl=name)) for name in names})
     for name in names:
         put(f"sgemm_{name}", res[name], 2.0 * M * N * K, 1e9, "tflops")
+    # The headline kernel and cuBLAS once more by the reference's own method (graph of 10 calls, 50
+    # replays): median, mean and minimum per call.
+    for name in ("prefetch_reg", "cublas"):
+        g = graph_us(lambda name=name: pkg.gemm(a_sets[0], b_sets[0], impl=name))
+        out[f"sgemm_{name}_graph_ms"] = g["median_us"] / 1e3
+        out[f"sgemm_{name}_graph_mean_ms"] = g["mean_us"] / 1e3
+        out[f"sgemm_{name}_graph_min_ms"] = g["min_us"] / 1e3
+        out[f"sgemm_{name}_graph_tflops"] = 2.0 * M * N * K / g["median_us"] / 1e6
     del a_sets, b_sets
     # The other two FP32 benchmark shapes: 1024^3 and 1024 x 4096 x 4096, where tiles do not fill
     # whole rounds of SMs and the stream-K entry (output cleared inside the timed call) matters.
