@@ -166,7 +166,9 @@ int b200_device_status_read(uint32_t* host_word, b200_stream_t stream) {
   if (b200::selftest_status_read_clear(&selftest_word) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
   uint32_t peer_word = 0;
   if (b200::peer_sync_status_read_clear(&peer_word) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
-  *host_word = sgemm_word | umma_word | selftest_word | peer_word;
+  uint32_t row_word = 0;
+  if (b200::rowops_status_read_clear(&row_word) != cudaSuccess) return B200_ERR_LAUNCH_FAILED;
+  *host_word = sgemm_word | umma_word | selftest_word | peer_word | row_word;
   return *host_word == 0 ? B200_OK : B200_ERR_DEVICE_TIMEOUT;
 }
 

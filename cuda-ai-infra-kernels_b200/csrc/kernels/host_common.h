@@ -73,6 +73,7 @@ cudaError_t sgemm_status_read_clear(uint32_t* word);
 cudaError_t umma_status_read_clear(uint32_t* word);
 cudaError_t selftest_status_read_clear(uint32_t* word);
 cudaError_t peer_sync_status_read_clear(uint32_t* word);
+cudaError_t rowops_status_read_clear(uint32_t* word);
 
 // k128BAtom32B: 128-byte span swizzled in 32-byte granules (what an MN-major
 // 32-bit tcgen05 operand needs); k128B: the usual 16-byte granules.

@@ -38,6 +38,7 @@ enum WaitSite : uint32_t {
   kSiteUmmaStore = 1u << 6,
   kSiteSelfTest = 1u << 7,
   kSitePeerBarrier = 1u << 8,
+  kSiteRowStaged = 1u << 9,   // row operators: the staged row never arrived
   kSiteBounds = 1u << 10,   // debug build only: an index check failed and the access was skipped
 };
 

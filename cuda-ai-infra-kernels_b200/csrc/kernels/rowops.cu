@@ -1,8 +1,9 @@
 // RMSNorm and softmax over the last dimension of a row-major FP32 matrix.
 //
 // Both operators are HBM-bound: the algorithmic traffic is one read of x and
-// one write of y. Every fast path therefore keeps a whole row in registers
-// between the reduction and the scaling pass (the reference re-reads x from
+// one write of y. Every fast path therefore keeps a whole row on chip (in
+// registers, long rows in shared memory) between the reduction and the scaling
+// pass (the reference re-reads x from
 // global memory, csrc/rmsnorm/rmsnorm_naive.cu:70-89, or round-trips it through
 // shared memory, csrc/rmsnorm/rmsnorm_cache_x.cu; its softmax makes three
 // passes, csrc/softmax/softmax.cu:25-121). Paths, chosen by row length:
@@ -11,10 +12,17 @@
 //            (rows of <= 1024 floats); shuffle reductions only.
 //   block  : one CTA per row, up to 4 vectors per thread: 256 or 512 threads
 //            (<= 4096 / 8192 floats); shuffle + one shared-memory hop.
-//   cluster: 2/4/8 CTAs per row joined by a thread-block cluster; partial
-//            results are exchanged through distributed shared memory. 256
-//            threads and 4 vectors per thread up to 32768 floats, 8 vectors up
-//            to 65536, 1024 threads up to 262144.
+//   staged : rows of more than 8192 floats. The copy engine brings a row (up to
+//            24 576 floats: one CTA per row) or a CTA's share of it (beyond:
+//            clusters of 2/4/8 CTAs per row, partial statistics exchanged
+//            through distributed shared memory; up to 401 408 floats) into
+//            shared memory with one bulk copy, the threads take their
+//            statistics from there, overwrite the data in place with the
+//            result, and one bulk copy writes it out. The memory system is kept
+//            busy by the copy engine whatever phase the threads are in, and two
+//            or three CTAs per SM are in flight (a register-resident cluster
+//            path, tried first, ran such rows at 65-72 % of the copy bandwidth
+//            and 131 072-float rows at 32-39 %; this one 70-97 % and 61-69 %).
 //   stream : any length / any alignment; re-reads the row (normally from L2).
 //
 // All offsets are 64-bit. 128-bit accesses are used only when the row length
@@ -22,17 +30,22 @@
 #include <cooperative_groups.h>
 #include <float.h>
 
+#include <type_traits>
+
 #include "host_common.h"
+#include "ptx_sm100.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace b200 {
+
+cudaError_t rowops_status_read_clear(uint32_t* word) { return status_word_read_clear(word); }
+
 namespace {
 
 constexpr int kMaxVec = 8;        // 128-bit vectors held per thread
 constexpr int kBlockThreads = 256;
 constexpr int kWarpsPerBlock = kBlockThreads / 32;
-constexpr int kBigBlockThreads = 1024;  // rows longer than 8192 floats, and every CTA of a cluster
 
 __device__ __forceinline__ float4 load_stream(const float4* p) { return __ldcs(p); }
 __device__ __forceinline__ void store_stream(float4* p, float4 v) { __stcs(p, v); }
@@ -230,28 +243,124 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const RowArgs a) {
   }
 }
 
-// One cluster per row; CTA `rank` owns vectors [rank * per_cta, ...).
-template <RowOp kOp, int VPT, int kThreads>
-__global__ void __launch_bounds__(kThreads) row_cluster_kernel(const RowArgs a) {
-  __shared__ float scratch[2 * (kThreads / 32 + 1)];
-  cg::cluster_group cluster = cg::this_cluster();
-  const unsigned ranks = cluster.num_blocks();
-  const unsigned rank = cluster.block_rank();
-  const int64_t row = blockIdx.x / ranks;
-  const int nvec_row = static_cast<int>(a.cols / 4);
-  const int per_cta = (nvec_row + ranks - 1) / ranks;
-  const int begin = min(static_cast<int>(rank) * per_cta, nvec_row);
-  const int nvec = min(per_cta, nvec_row - begin);
-  const float4* x_row = reinterpret_cast<const float4*>(a.x + row * a.cols) + begin;
-  float4* y_row = reinterpret_cast<float4*>(a.y + row * a.cols) + begin;
-  ClusterScope<kThreads / 32> scope{scratch};
-  if constexpr (kOp == RowOp::kRmsNorm) {
-    rmsnorm_row<VPT>(x_row, reinterpret_cast<const float4*>(a.w) + begin, y_row, nvec, threadIdx.x, kThreads, a.cols,
-                     a.eps, scope);
-  } else {
-    softmax_row<VPT>(x_row, y_row, nvec, threadIdx.x, kThreads, scope);
+// A row (or, with kCluster, a CTA's share of a row whose CTAs form a cluster and exchange their
+// partial statistics through distributed shared memory) staged in shared memory by the copy
+// engine (see the file header).
+constexpr int kStagedThreads = 512;
+constexpr int64_t kStagedMaxFloats = 50176;   // 196 KiB of row + barrier and reduction scratch inside 227 KiB
+constexpr int64_t kStagedPartFloats = 24576;  // largest preferred share per CTA of a cluster: 96 KiB, two CTAs per SM
+
+template <RowOp kOp, bool kCluster>
+__global__ void __launch_bounds__(kStagedThreads) row_staged_kernel(const RowArgs a) {
+  extern __shared__ __align__(128) uint8_t staged_raw[];
+  // This CTA's vectors [begin, begin + nvec) of row r.
+  int64_t r = blockIdx.x;
+  int begin = 0;
+  int nvec = static_cast<int>(a.cols / 4);
+  if constexpr (kCluster) {
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned ranks = cluster.num_blocks();
+    r = blockIdx.x / ranks;
+    const int per_cta = (nvec + ranks - 1) / ranks;
+    begin = min(static_cast<int>(cluster.block_rank()) * per_cta, nvec);
+    nvec = min(per_cta, nvec - begin);
   }
-  scope.finish();
+  float4* row = reinterpret_cast<float4*>(staged_raw);
+  const uint32_t bytes = static_cast<uint32_t>(nvec) * 16u;
+  // Barrier and scratch sit behind the largest share any CTA of this launch can have.
+  const uint32_t share_bytes = kCluster ? static_cast<uint32_t>((a.cols / 4 + gridDim.x / a.rows - 1) / (gridDim.x / a.rows)) * 16u
+                                        : bytes;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(staged_raw + ((share_bytes + 127u) & ~127u));
+  float* scratch = reinterpret_cast<float*>(bar + 2);
+  const float* x_part = a.x + r * a.cols + 4 * static_cast<int64_t>(begin);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    mbar_init_fence();
+    if (bytes > 0) {
+      mbar_expect_tx(bar, bytes);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(smem_u32(row)), "l"(reinterpret_cast<uint64_t>(x_part)), "r"(bytes), "r"(smem_u32(bar))
+                   : "memory");
+    } else {
+      mbar_arrive(bar);
+    }
+  }
+  __syncthreads();   // the barrier exists before anybody polls it
+  const bool arrived = mbar_wait(bar, 0, kSiteRowStaged);   // on failure the statistics below are garbage, nothing is stored
+  using Scope = typename std::conditional<kCluster, ClusterScope<kStagedThreads / 32>, BlockScope<kStagedThreads / 32>>::type;
+  Scope scope{scratch};
+  if constexpr (kOp == RowOp::kRmsNorm) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += kStagedThreads) {
+      const float4 v = row[i];
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = scope.template reduce<SumOp>(ss);
+    const float inv_rms = rsqrtf(static_cast<float>(static_cast<double>(ss / static_cast<float>(a.cols)) + a.eps));
+    const float4* w = reinterpret_cast<const float4*>(a.w) + begin;
+    for (int i = threadIdx.x; i < nvec; i += kStagedThreads) {
+      const float4 v = row[i], g = __ldg(w + i);
+      row[i] = make_float4(v.x * g.x * inv_rms, v.y * g.y * inv_rms, v.z * g.z * inv_rms, v.w * g.w * inv_rms);
+    }
+  } else {
+    // Maximum and sum of exponentials of THIS CTA's share first (block-wide reductions only); a
+    // cluster then exchanges the (maximum, sum) pairs once and rescales: exp(x - m_i) is already in
+    // shared memory and only needs the factor exp(m_i - M) / S. One cluster barrier instead of two.
+    BlockScope<kStagedThreads / 32> local{scratch};
+    float mx = -FLT_MAX;
+    for (int i = threadIdx.x; i < nvec; i += kStagedThreads) {
+      const float4 v = row[i];
+      mx = fmaxf(mx, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+    }
+    mx = local.template reduce<MaxOp>(mx);
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += kStagedThreads) {   // a thread revisits only its own vectors
+      float4 v = row[i];
+      v.x = __expf(v.x - mx), v.y = __expf(v.y - mx), v.z = __expf(v.z - mx), v.w = __expf(v.w - mx);
+      sum += (v.x + v.y) + (v.z + v.w);
+      row[i] = v;
+    }
+    sum = local.template reduce<SumOp>(sum);
+    float factor;
+    if constexpr (kCluster) {
+      cg::cluster_group cluster = cg::this_cluster();
+      float* pair = scratch + 2 * (kStagedThreads / 32);   // behind the two reduction slots
+      if (threadIdx.x == 0) pair[0] = mx, pair[1] = sum;
+      cluster.sync();
+      float row_max = -FLT_MAX;
+      const unsigned ranks = cluster.num_blocks();
+      for (unsigned peer = 0; peer < ranks; ++peer) row_max = fmaxf(row_max, cluster.map_shared_rank(pair, peer)[0]);
+      float total = 0.f;
+      for (unsigned peer = 0; peer < ranks; ++peer) {
+        const float* remote = cluster.map_shared_rank(pair, peer);
+        total += remote[1] * __expf(remote[0] - row_max);   // an empty share contributes 0 * exp(-FLT_MAX - M) = 0
+      }
+      factor = __expf(mx - row_max) * __frcp_rn(total);
+    } else {
+      factor = __frcp_rn(sum);
+    }
+    for (int i = threadIdx.x; i < nvec; i += kStagedThreads) {
+      const float4 v = row[i];
+      row[i] = make_float4(v.x * factor, v.y * factor, v.z * factor, v.w * factor);
+    }
+  }
+  fence_proxy_async_smem();   // the row was rewritten through the generic proxy, the copy engine reads it
+  __syncthreads();
+  if (threadIdx.x == 0 && arrived && bytes > 0) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(reinterpret_cast<uint64_t>(a.y + r * a.cols + 4 * static_cast<int64_t>(begin))), "r"(smem_u32(row)),
+                 "r"(bytes)
+                 : "memory");
+    tma_store_commit();
+    tma_store_wait_read<0>();   // shared memory must outlive the copy's reads; the writes drain after the CTA has gone
+  }
+  if constexpr (kCluster) scope.finish();
+}
+
+// Shared memory of a staged launch whose largest share is `share_floats`.
+constexpr size_t staged_smem_bytes(int64_t share_floats) {
+  return ((static_cast<size_t>(share_floats) * sizeof(float) + 127) & ~size_t{127}) + 16 +
+         2 * (kStagedThreads / 32 + 1) * sizeof(float);
 }
 
 // Any length, any alignment: scalar accesses, the row is re-read.
@@ -302,24 +411,6 @@ int launch_block(const RowArgs& a, cudaStream_t s) {
   return launch_status();
 }
 
-template <RowOp kOp, int VPT, int kThreads>
-int launch_cluster(const RowArgs& a, int ranks, cudaStream_t s) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(a.rows * ranks));
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = s;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = ranks;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, row_cluster_kernel<kOp, VPT, kThreads>, a) != cudaSuccess) return launch_failed();
-  return launch_status();
-}
-
 template <RowOp kOp>
 int launch_by_vectors_warp(int vpt, const RowArgs& a, cudaStream_t s) {
   switch (vpt) {
@@ -355,19 +446,39 @@ int launch_rows(const RowArgs& a, cudaStream_t s) {
   }
   // Beyond one warp per row, many small CTAs work best: with at most four
   // vectors per thread 2048 threads stay resident per SM, and the load phase of
-  // one CTA overlaps the store phase of another. Longer rows therefore get more
-  // CTAs (a cluster of 256-thread CTAs exchanging partials through DSMEM)
-  // rather than fatter ones; only the longest rows use eight vectors per thread
-  // and 1024-thread CTAs.
+  // one CTA overlaps the store phase of another. Rows too long for that are
+  // staged in shared memory by the copy engine instead of being held in registers.
   constexpr int kLightVec = 4;
   if (vector_ok && nvec <= 256 * kLightVec) return launch_by_vectors_block<kOp, 256>(static_cast<int>((nvec + 255) / 256), a, s);
   if (vector_ok && nvec <= 512 * kLightVec) return launch_by_vectors_block<kOp, 512>(static_cast<int>((nvec + 511) / 512), a, s);
-  if (vector_ok && nvec <= 8 * 256 * kLightVec) {
-    const int needed = static_cast<int>((nvec + 256 * kLightVec - 1) / (256 * kLightVec));
-    return launch_cluster<kOp, kLightVec, 256>(a, needed <= 2 ? 2 : (needed <= 4 ? 4 : 8), s);
+  if (vector_ok && a.cols <= 8 * kStagedMaxFloats) {
+    // One CTA per row while two rows fit an SM side by side (24 576 floats); beyond that a cluster of
+    // 2, 4 or 8 CTAs per row, with shares of at most 16 384 floats where eight CTAs allow it.
+    constexpr size_t kMaxSmem = staged_smem_bytes(kStagedMaxFloats);
+    if (a.cols <= 24576) {
+      if (!ensure_dynamic_smem<row_staged_kernel<kOp, false>, kMaxSmem>()) return B200_ERR_LAUNCH_FAILED;
+      row_staged_kernel<kOp, false><<<static_cast<unsigned>(a.rows), kStagedThreads, staged_smem_bytes(a.cols), s>>>(a);
+      return launch_status();
+    }
+    int ranks = 2;
+    while (ranks < 8 && (a.cols + ranks - 1) / ranks > kStagedPartFloats) ranks *= 2;
+    const int64_t share_vectors = (nvec + ranks - 1) / ranks;
+    if (!ensure_dynamic_smem<row_staged_kernel<kOp, true>, kMaxSmem>()) return B200_ERR_LAUNCH_FAILED;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(a.rows * ranks));
+    cfg.blockDim = dim3(kStagedThreads);
+    cfg.dynamicSmemBytes = staged_smem_bytes(4 * share_vectors);
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = ranks;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, row_staged_kernel<kOp, true>, a) != cudaSuccess) return launch_failed();
+    return launch_status();
   }
-  if (vector_ok && nvec <= 8 * 256 * kMaxVec) return launch_cluster<kOp, kMaxVec, 256>(a, 8, s);
-  if (vector_ok && nvec <= 8 * kBigBlockThreads * kMaxVec) return launch_cluster<kOp, kMaxVec, kBigBlockThreads>(a, 8, s);
   row_stream_kernel<kOp><<<static_cast<unsigned>(a.rows), kBlockThreads, 0, s>>>(a);
   return launch_status();
 }

@@ -172,7 +172,7 @@ __host__ __device__ constexpr uint32_t tmem_columns() {
 }
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int* tm, int* tn) {
-  constexpr int kBand = 8;
+  constexpr int kBand = 8;   // bands of 1, 2, 4 and 16 tile rows measured within noise of this at 3072^3 .. 8192^3
   const int per_band = kBand * tiles_n;
   const int band = tile / per_band;
   const int first_m = band * kBand;

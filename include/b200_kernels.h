@@ -82,7 +82,8 @@ enum {
   B200_WAIT_UMMA_ACC_EMPTY = 1 << 5,/* TF32: MMA issuer waiting for a drained accumulator */
   B200_WAIT_UMMA_STORE = 1 << 6,
   B200_WAIT_SELFTEST = 1 << 7,      /* b200_selftest_wait_gives_up */
-  B200_WAIT_PEER_BARRIER = 1 << 8   /* b200_peer_barrier: a peer never signalled the step */
+  B200_WAIT_PEER_BARRIER = 1 << 8,  /* b200_peer_barrier: a peer never signalled the step */
+  B200_WAIT_ROW_STAGED = 1 << 9     /* row operators: a row staged by the copy engine never arrived */
 };
 
 /*

@@ -1,7 +1,7 @@
 """Parity of the RMSNorm and softmax kernels with the CPU oracle, through the
 C ABI. Tolerance: max|y - ref| / max|ref| <= 1e-5 (north star) plus the
 reference suite's atol = 1e-5; every row-length path is covered (warp, block,
-cluster / DSMEM, streaming, unaligned)."""
+staged through shared memory by the copy engine, cluster / DSMEM, streaming, unaligned)."""
 import pytest
 import torch
 
@@ -11,11 +11,12 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 # (rows, cols): warp path (<= 1024), block path (256 / 512 threads, <= 4096 /
-# 8192), cluster paths (2/4/8 CTAs, <= 32768 / 65536 / 262144), streaming path,
-# lengths that are not a multiple of four, single row / single column.
-SHAPES = [(16, 128), (16, 768), (32, 1024), (33, 516), (8, 2048), (8, 4096), (5, 8192), (4, 12288), (3, 16384),
-          (3, 32768), (3, 33000), (2, 65536), (2, 70000), (2, 140000), (1, 262144), (1, 300000), (5, 1001), (7, 3),
-          (1, 1), (300, 4), (0, 16)]
+# 8192), rows staged in shared memory (8196 .. 50176), cluster paths (8 CTAs,
+# <= 65536 / 262144), streaming path, lengths that are not a multiple of four,
+# single row / single column.
+SHAPES = [(16, 128), (16, 768), (32, 1024), (33, 516), (8, 2048), (8, 4096), (5, 8192), (7, 8196), (4, 12288), (3, 16384),
+          (3, 32768), (3, 33000), (300, 20000), (3, 50176), (2, 50180), (2, 65536), (2, 70000), (2, 140000), (1, 262144),
+          (1, 300000), (5, 1001), (7, 3), (1, 1), (300, 4), (0, 16)]
 
 
 def rmsnorm(abi, x, w, eps, impl=0):
