@@ -41,7 +41,7 @@ __device__ __forceinline__ PairItem pair_item(int item, int full_tiles) {
 }
 
 template <int STAGES, int KSUB, int kAct>
-__global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_constant__ UmmaParams p) {
+__global__ void __launch_bounds__(kTileThreads, 1) umma_pair_kernel(const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
   // Same carve-up in both CTAs: the MMA addresses the peer's shared memory by
   // the same offsets as its own.
@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 8);  // used in CTA 0 only: four epilogue warps of each CTA
+      mbar_init(&acc_empty[b], 8 * kTileEpilogueShare);  // used in CTA 0 only: the epilogue warps of both CTAs
     }
     mbar_init_fence();
   }
@@ -166,11 +166,12 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
     }
   } else {
     const EpilogueArgs ep = epilogue_args(p);
-    const int quarter = warp & 3;
+    constexpr int kShare = kTileEpilogueShare;
+    const int quarter = warp & 3, part = (warp - 2) >> 2;   // rows of the accumulator, place among the quarter's warps
     bool ok = true;
     int local = 0;
     const bool boxed = p.tma_store != 0 && ep.vector_io && ep.peers.count == 0;
-    uint8_t* boxes = reinterpret_cast<uint8_t*>(peer_stage) + quarter * kOutStageBytesPerWarp;
+    uint8_t* boxes = reinterpret_cast<uint8_t*>(peer_stage) + (part * 4 + quarter) * (kStagingBytes / (4 * kShare));
     uint32_t box_uses = 0;
     for (int item = first_tile; item < items && ok; item += tile_stride, ++local) {
       const PairItem it = pair_item(item, p.pair_full_tiles);
@@ -181,20 +182,21 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_pair_kernel(const __grid_
       const int n0 = tn * kPairN + (it.half < 0 ? 0 : it.half * (kPairN / 2));
       const int m0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
       SourceQuads first;
-      if (boxed) fetch_source_coalesced(ep, first, m0 + quarter * 32, n0, lane);   // before the wait
+      if (boxed) fetch_source_coalesced(ep, first, m0 + quarter * 32, n0 + part * 32, lane);   // before the wait
       if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
-      float* stage_area = peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float));
       if (it.half < 0) {
         if (boxed) {
-          epilogue_tile_boxed<kPairN, kAct>(p, ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, first, boxes, box_uses);
+          epilogue_tile_boxed<kPairN, kAct, kShare>(p, ep, tmem_base + buf * kPairN, quarter, part, lane, m0, n0, first, boxes,
+                                                    box_uses);
         } else {
-          epilogue_tile<kPairN, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, stage_area);
+          epilogue_tile<kPairN, kAct, kShare>(ep, tmem_base + buf * kPairN, quarter, part, lane, m0, n0, boxes);
         }
       } else if (boxed) {
-        epilogue_tile_boxed<kPairN / 2, kAct>(p, ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, first, boxes, box_uses);
+        epilogue_tile_boxed<kPairN / 2, kAct, kShare>(p, ep, tmem_base + buf * kPairN, quarter, part, lane, m0, n0, first, boxes,
+                                                      box_uses);
       } else {
-        epilogue_tile<kPairN / 2, kAct>(ep, tmem_base + buf * kPairN, quarter, lane, m0, n0, stage_area);
+        epilogue_tile<kPairN / 2, kAct, kShare>(ep, tmem_base + buf * kPairN, quarter, part, lane, m0, n0, boxes);
       }
       tcgen05_fence_before_sync();
       __syncwarp();
@@ -247,7 +249,7 @@ int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream
   const int64_t pairs = items < all_pairs ? items : all_pairs;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
-  cfg.blockDim = dim3(kTmaThreads);
+  cfg.blockDim = dim3(kTileThreads);
   cfg.dynamicSmemBytes = launch_smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr;

@@ -17,11 +17,12 @@ namespace {
 // thread's barrier wait and commit cost about as much as four small MMAs, so narrow tiles, whose
 // MMAs are short, run two sub-blocks per stage).
 template <int BN, int STAGES, int kAct, int KSUB = 1>
-__global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_constant__ UmmaParams p) {
+__global__ void __launch_bounds__(kTileThreads, 1) umma_tma_kernel(const __grid_constant__ UmmaParams p) {
   constexpr int kRing = STAGES / KSUB;
   extern __shared__ uint8_t smem_raw[];
   const SmemCarve sm = carve<BN, STAGES>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  B200_PROBE(p, 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -30,7 +31,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_c
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.acc_full[b], 1);
-      mbar_init(&sm.acc_empty[b], 4);  // one arrive per epilogue warp
+      mbar_init(&sm.acc_empty[b], 4 * kTileEpilogueShare);  // one arrive per epilogue warp
     }
     mbar_init_fence();
   }
@@ -42,6 +43,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_c
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *sm.tmem_ptr;
+  B200_PROBE(p, 1);
 
   const int tiles_m = (p.m + kTileM - 1) / kTileM;
   const int tiles_n = (p.n + BN - 1) / BN;
@@ -84,11 +86,12 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_tma_kernel(const __grid_c
   } else if (warp == 1) {
     if (lane == 0) mma_role<BN, STAGES, KSUB>(sm, tmem_base, tiles, k_blocks);
   } else {
-    epilogue_role<BN, kAct, true>(p, sm, tmem_base, warp & 3, lane, tiles, tiles_m, tiles_n);
+    epilogue_role<BN, kAct, true, kTileEpilogueShare>(p, sm, tmem_base, warp & 3, (warp - 2) >> 2, lane, tiles, tiles_m, tiles_n);
   }
 
   tcgen05_fence_before_sync();
   __syncthreads();
+  B200_PROBE(p, 6);
   if (warp == 1) {
     tcgen05_fence_after_sync();
     tmem_dealloc<tmem_columns<BN>()>(tmem_base);
@@ -218,7 +221,7 @@ __global__ void __launch_bounds__(kGenericThreads, 1) umma_generic_kernel(const 
   if (warp == 0) {
     if (lane == 0) mma_role<BN, STAGES>(sm, tmem_base, tiles, k_blocks);
   } else if (warp <= 4) {
-    epilogue_role<BN, kAct, false>(p, sm, tmem_base, warp & 3, lane, tiles, tiles_m, tiles_n);   // 416 threads: no room for two register sets
+    epilogue_role<BN, kAct, false, 1>(p, sm, tmem_base, warp & 3, 0, lane, tiles, tiles_m, tiles_n);   // 416 threads: no room for two register sets
   } else {
     const int lw = warp - 5;
     LoaderCursor cursor{static_cast<int>(blockIdx.x), 0, 0, 0};  // the next stage to load
@@ -298,7 +301,7 @@ int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_
   if (sms <= 0) return B200_ERR_INTERNAL;
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + BN - 1) / BN);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  kernel<<<grid, kTmaThreads, launch_smem, stream>>>(p);
+  kernel<<<grid, kTileThreads, launch_smem, stream>>>(p);
   return launch_status();
 }
 

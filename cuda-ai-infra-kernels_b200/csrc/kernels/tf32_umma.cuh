@@ -72,10 +72,11 @@ constexpr uint32_t kBBoxBytes = 32 * kStageK * 4;       // 4 KiB: 32 (n) x 32 (k
     if ((params).probe != nullptr && threadIdx.x == 64) {                                     \
       uint64_t t_;                                                                            \
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
-      (params).probe[static_cast<size_t>(blockIdx.x) * 8 + (slot)] = t_;                      \
-      (params).probe[2048 + static_cast<size_t>(blockIdx.x) * 8 + (slot)] = clock64();        \
+      (params).probe[static_cast<size_t>(blockIdx.x) * 16 + (slot)] = t_;                      \
+      (params).probe[4096 + static_cast<size_t>(blockIdx.x) * 16 + (slot)] = clock64();        \
     }                                                                                         \
   } while (0)
+extern "C" uint64_t* b200_probe_buffer;   // [2][256][16], defined and set by the instrumented build's driver
 #else
 #define B200_PROBE(params, slot) do { } while (0)
 #endif
@@ -100,7 +101,7 @@ struct UmmaParams {
   int pair_full_tiles;  // CTA-pair kernel: work items [0, full) are whole 256 x 256 tiles, the rest
                         // are the two 256 x 128 halves of the tiles after them (see launch_pair)
 #ifdef B200_PROBE_TIMING
-  uint64_t* probe;     // [grid][8] time stamps, or null
+  uint64_t* probe;     // [2][256][16] time stamps, or null
 #endif
 };
 
@@ -143,21 +144,16 @@ __host__ __device__ constexpr uint32_t stage_bytes() {
   return kASlabBytes + (BN / 32) * kBBoxBytes;
 }
 
-// Staging of the fused all-gather: an epilogue warp turns its 32 x 32 chunk (one row per lane in
-// registers) by way of shared memory so that peer copies are written in 128-byte row segments, four
-// rows per instruction, instead of 32 scattered 16-byte pieces (NVLink moves those poorly). The
-// pitch of 36 floats keeps both the row-per-lane writes and the row-wise reads free of conflicts.
-constexpr int kPeerStagePitch = 36;
-constexpr size_t kPeerStageBytesPerWarp = 32 * kPeerStagePitch * sizeof(float);
-constexpr size_t kPeerStageBytes = 4 * kPeerStageBytesPerWarp;   // four epilogue warps
-
-// Staging of the ordinary epilogue: per epilogue warp two 32 x 32 boxes (4 KiB each) in the 128-byte
-// swizzle, from which TMA stores write the output in whole 128-byte row segments. The fused
-// all-gather's staging (above) lives in the same region; a launch uses one or the other.
+// Staging of the epilogues: 32 KiB of 32 x 32 FP32 boxes (4 KiB each) in the 128-byte swizzle, shared
+// out evenly among the epilogue warps of a kernel (two boxes per warp with four warps, one with eight).
+//   - Ordinary epilogue: a warp turns each 32 x 32 chunk through a box, from which one TMA store
+//     writes the output in whole 128-byte row segments.
+//   - Fused all-gather: the finished chunk (one row per lane in registers) is turned through a box
+//     so that peer copies are written in 128-byte row segments, four rows per instruction, instead
+//     of 32 scattered 16-byte pieces (NVLink moves those poorly).
+// A launch uses one or the other.
 constexpr uint32_t kOutBoxBytes = 32 * 32 * sizeof(float);
-constexpr size_t kOutStageBytesPerWarp = 2 * kOutBoxBytes;
-constexpr size_t kStagingBytes = 4 * kOutStageBytesPerWarp;   // 32 KiB, 1024-byte aligned
-static_assert(kStagingBytes >= kPeerStageBytes, "one region serves both");
+constexpr size_t kStagingBytes = 8 * kOutBoxBytes;   // 32 KiB, 1024-byte aligned
 
 // ring | 1 KiB of barriers and the TMEM pointer | staging; the base is rounded up to 1 KiB.
 template <int BN, int STAGES>
@@ -240,36 +236,64 @@ __device__ __forceinline__ uint32_t box_offset(int row, int quad) {
   return static_cast<uint32_t>(row) * 128u + (static_cast<uint32_t>(quad ^ (row & 7)) << 4);
 }
 
-// One chunk: source into row ownership, alpha * acc + beta * C + bias, activation, box, TMA store.
-// `box` is one of the warp's two boxes (alternating); at most one earlier store may still be reading
-// the other one.
-template <int kAct>
-__device__ __forceinline__ void finish_chunk_boxed(const UmmaParams& p, const EpilogueArgs& ep, const uint32_t (&raw)[32],
-                                                   const SourceQuads& cq, int row0, int col0, int lane, uint8_t* box) {
-  if (lane == 0) tma_store_wait_read<1>();   // the store that used this box two chunks ago has read it
+// First half of a chunk: waits until `box` (one of the warp's kBoxes boxes, used in turn) is free - at
+// most kBoxes - 1 earlier stores may still be reading the others - and turns the source values into
+// row ownership through it. After this the registers of `cq` are free for the next chunk's source.
+template <int kBoxes>
+__device__ __forceinline__ void stage_source_boxed(const EpilogueArgs& ep, const SourceQuads& cq, int lane, uint8_t* box) {
+  if (lane == 0) tma_store_wait_read<kBoxes - 1>();   // the store that used this box kBoxes chunks ago has read it
   __syncwarp();
-  const bool use_source = ep.beta != 0.f;
-  if (use_source) {
+  if (ep.beta != 0.f) {
+    // Row 4 j + lane / 8: the swizzle term (row % 8) takes two values, for even and for odd j, so
+    // every store is one of two per-lane bases plus a constant.
+    const uint32_t r = static_cast<uint32_t>(lane >> 3), quad = static_cast<uint32_t>(lane & 7);
+    uint8_t* even = box + r * 128u + ((quad ^ r) << 4);
+    uint8_t* odd = box + r * 128u + ((quad ^ (r + 4u)) << 4);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(box + box_offset(4 * j + (lane >> 3), lane & 7)) = cq.v[j];
+    for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(((j & 1) ? odd : even) + j * 512) = cq.v[j];
     __syncwarp();
   }
-  // From here on a lane touches its own row of the box only: it reads a granule of C and puts the
-  // finished values in its place.
+}
+
+// Second half: alpha * acc + beta * C + bias, activation, into the box, TMA store.
+template <int kAct>
+__device__ __forceinline__ void finish_chunk_boxed(const UmmaParams& p, const EpilogueArgs& ep, const uint32_t (&raw)[32],
+                                                   int row0, int col0, int lane, uint8_t* box) {
+  const bool use_source = ep.beta != 0.f;
+  // From here on a lane touches its own row of the box only: it reads the granules of C and puts
+  // the finished values in their place. Four granules at a time, all loads before the first store:
+  // the compiler cannot tell the swizzled slots apart, so a store between two loads would order
+  // them, and a lone warp then pays the shared-memory latency once per granule (880 cycles a chunk).
   const bool use_bias = ep.bias != nullptr;
+  uint8_t* row_base = box + static_cast<uint32_t>(lane) * 128u;
+  const uint32_t swz = static_cast<uint32_t>(lane & 7);
 #pragma unroll
-  for (int g = 0; g < 8; ++g) {
-    float4* slot = reinterpret_cast<float4*>(box + box_offset(lane, g));
-    const float4 src = use_source ? *slot : make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 v = make_float4(fmaf(ep.beta, src.x, ep.alpha * __uint_as_float(raw[4 * g + 0])),
-                           fmaf(ep.beta, src.y, ep.alpha * __uint_as_float(raw[4 * g + 1])),
-                           fmaf(ep.beta, src.z, ep.alpha * __uint_as_float(raw[4 * g + 2])),
-                           fmaf(ep.beta, src.w, ep.alpha * __uint_as_float(raw[4 * g + 3])));
-    if (use_bias && col0 + 4 * g < ep.n) {
-      const float4 bv = __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + 4 * g));
-      v.x += bv.x, v.y += bv.y, v.z += bv.z, v.w += bv.w;
+  for (int h = 0; h < 2; ++h) {
+    float4 v[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int g = 4 * h + q;
+      v[q] = use_source ? *reinterpret_cast<const float4*>(row_base + ((static_cast<uint32_t>(g) ^ swz) << 4))
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    *slot = make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int g = 4 * h + q;
+      v[q] = make_float4(fmaf(ep.beta, v[q].x, ep.alpha * __uint_as_float(raw[4 * g + 0])),
+                         fmaf(ep.beta, v[q].y, ep.alpha * __uint_as_float(raw[4 * g + 1])),
+                         fmaf(ep.beta, v[q].z, ep.alpha * __uint_as_float(raw[4 * g + 2])),
+                         fmaf(ep.beta, v[q].w, ep.alpha * __uint_as_float(raw[4 * g + 3])));
+      if (use_bias && col0 + 4 * g < ep.n) {
+        const float4 bv = __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + 4 * g));
+        v[q].x += bv.x, v[q].y += bv.y, v[q].z += bv.z, v[q].w += bv.w;
+      }
+      v[q] = make_float4(activate<kAct>(v[q].x), activate<kAct>(v[q].y), activate<kAct>(v[q].z), activate<kAct>(v[q].w));
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int g = 4 * h + q;
+      *reinterpret_cast<float4*>(row_base + ((static_cast<uint32_t>(g) ^ swz) << 4)) = v[q];
+    }
   }
   fence_proxy_async_smem();   // the box was written through the generic proxy, the store reads through the async one
   __syncwarp();
@@ -279,53 +303,66 @@ __device__ __forceinline__ void finish_chunk_boxed(const UmmaParams& p, const Ep
   }
 }
 
-// Epilogue of one 128 x BN tile for one warp through the boxes, software-pipelined: two named
-// register sets alternate, so while a chunk is finished the next chunk's accumulators are on their
-// way from TMEM and its source values from memory. `first` holds the source of chunk 0 (fetched by the
-// caller before it waited for the accumulator); `uses` counts the warp's box uses across tiles.
-template <int BN, int kAct>
+// Epilogue of one 128 x BN tile for one warp through its boxes. kShare warps serve each quarter of
+// the accumulator's rows (TMEM lanes); warp `part` of them takes the 32-column chunks part,
+// part + kShare, ... Software-pipelined: two named register sets of accumulator values alternate and
+// the source registers are refilled as soon as their values sit in the box, so while a chunk is
+// finished the warp's next chunk is on its way from TMEM and its source values from memory.
+// `src` arrives holding the source of the warp's first chunk (fetched by the caller before it
+// waited for the accumulator); `uses` counts the warp's box uses across tiles.
+template <int BN, int kAct, int kShare>
 __device__ __forceinline__ void epilogue_tile_boxed(const UmmaParams& p, const EpilogueArgs& ep, uint32_t tmem_acc, int quarter,
-                                                    int lane, int m0, int n0, const SourceQuads& first, uint8_t* boxes,
+                                                    int part, int lane, int m0, int n0, SourceQuads& src, uint8_t* boxes,
                                                     uint32_t& uses) {
-  constexpr int kChunks = BN / 32;
-  static_assert(kChunks % 2 == 0, "chunks are handled in pairs");
+  constexpr int kMine = BN / 32 / kShare;   // chunks of this warp
+  constexpr int kBoxes = 2 / kShare;        // boxes of this warp
+  static_assert(kShare == 1 || kShare == 2, "four or eight epilogue warps");
+  static_assert(kMine >= 1 && BN % (32 * kShare) == 0, "every warp has work");
   const int row0 = m0 + quarter * 32;
   const uint32_t tmem_row = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
   uint32_t raw_even[32], raw_odd[32];
-  SourceQuads src_even = first, src_odd;
-  tmem_ld_32x32(tmem_row, raw_even);
+  tmem_ld_32x32(tmem_row + part * 32, raw_even);
 #pragma unroll
-  for (int chunk = 0; chunk < kChunks; chunk += 2) {
+  for (int i = 0; i < kMine; i += 2) {
+    const int chunk = part + i * kShare;
     if (n0 + chunk * 32 >= ep.n) break;   // uniform across the warp
+    uint8_t* box = boxes + (uses++ % kBoxes) * kOutBoxBytes;
+    stage_source_boxed<kBoxes>(ep, src, lane, box);
     tmem_ld_wait();
-    tmem_ld_32x32(tmem_row + (chunk + 1) * 32, raw_odd);
-    fetch_source_coalesced(ep, src_odd, row0, n0 + (chunk + 1) * 32, lane);
-    finish_chunk_boxed<kAct>(p, ep, raw_even, src_even, row0, n0 + chunk * 32, lane, boxes + (uses++ & 1u) * kOutBoxBytes);
-    tmem_ld_wait();
-    if (chunk + 2 < kChunks) {
-      tmem_ld_32x32(tmem_row + (chunk + 2) * 32, raw_even);
-      fetch_source_coalesced(ep, src_even, row0, n0 + (chunk + 2) * 32, lane);
+    if (i + 1 < kMine) {
+      tmem_ld_32x32(tmem_row + (chunk + kShare) * 32, raw_odd);
+      fetch_source_coalesced(ep, src, row0, n0 + (chunk + kShare) * 32, lane);
     }
-    finish_chunk_boxed<kAct>(p, ep, raw_odd, src_odd, row0, n0 + (chunk + 1) * 32, lane, boxes + (uses++ & 1u) * kOutBoxBytes);
+    finish_chunk_boxed<kAct>(p, ep, raw_even, row0, n0 + chunk * 32, lane, box);
+    if (i + 1 < kMine) {
+      box = boxes + (uses++ % kBoxes) * kOutBoxBytes;
+      stage_source_boxed<kBoxes>(ep, src, lane, box);
+      tmem_ld_wait();
+      if (i + 2 < kMine) {
+        tmem_ld_32x32(tmem_row + (chunk + 2 * kShare) * 32, raw_even);
+        fetch_source_coalesced(ep, src, row0, n0 + (chunk + 2 * kShare) * 32, lane);
+      }
+      finish_chunk_boxed<kAct>(p, ep, raw_odd, row0, n0 + (chunk + kShare) * 32, lane, box);
+    }
   }
   tmem_ld_wait();   // nothing from TMEM is in flight when the accumulator is handed back
 }
 
-// Epilogue of one 128 x BN tile for one warp: TMEM lanes [32 * quarter, +32)
-// are rows m0 + 32 * quarter + lane. Each thread owns one row and walks it in
-// chunks of 32 columns.
-template <int BN, int kAct>
-__device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tmem_acc, int quarter, int lane, int m0,
-                                              int n0, float* stage) {
+// Epilogue of one 128 x BN tile for one warp, straight from registers: TMEM lanes [32 * quarter, +32)
+// are rows m0 + 32 * quarter + lane. Each thread owns one row and walks it in chunks of 32 columns;
+// warp `part` of the kShare that serve the quarter takes chunks part, part + kShare, ...
+template <int BN, int kAct, int kShare>
+__device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tmem_acc, int quarter, int part, int lane,
+                                              int m0, int n0, uint8_t* stage) {
   const int row = m0 + quarter * 32 + lane;
-  const bool stage_peers = p.peers.count > 0 && p.vector_io;   // `stage`: this warp's kPeerStageBytesPerWarp
+  const bool stage_peers = p.peers.count > 0 && p.vector_io;   // `stage`: one of this warp's boxes
   const bool row_ok = row < p.m;
   const bool use_c = p.beta != 0.f;
   const bool use_bias = p.bias != nullptr;
   const float* c_row = p.c + static_cast<int64_t>(row) * p.ldc;
   float* d_row = p.d + static_cast<int64_t>(row) * p.ldd;
 #pragma unroll 1
-  for (int chunk = 0; chunk < BN / 32; ++chunk) {
+  for (int chunk = part; chunk < BN / 32; chunk += kShare) {
     const int col0 = n0 + chunk * 32;
     if (col0 >= p.n) break;  // uniform across the warp
     uint32_t raw[32];
@@ -352,7 +389,7 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tm
             }
             v = make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
             *reinterpret_cast<float4*>(d_row + col) = v;
-            *reinterpret_cast<float4*>(stage + lane * kPeerStagePitch + 4 * g) = v;
+            *reinterpret_cast<float4*>(stage + box_offset(lane, g)) = v;
           }
         }
       }
@@ -365,7 +402,7 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tm
           const int r = 4 * j + (lane >> 3);
           const int out_row = m0 + quarter * 32 + r;
           if (out_row < p.m) {
-            const float4 v = *reinterpret_cast<const float4*>(stage + r * kPeerStagePitch + 4 * (lane & 7));
+            const float4 v = *reinterpret_cast<const float4*>(stage + box_offset(r, lane & 7));
             store_peers(p, static_cast<int64_t>(out_row) * p.ldd + quad_col, v);
           }
         }
@@ -471,15 +508,17 @@ __device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base
   }
 }
 
-// One of the four epilogue warps of the persistent single-CTA kernels.
-template <int BN, int kAct, bool kPipelinedEpilogue>
+// One of the 4 * kShare epilogue warps of the persistent single-CTA kernels: `quarter` is the warp's
+// quarter of the accumulator rows (its hardware warp index modulo four, which is what tcgen05.ld
+// lets it read), `part` in [0, kShare) its place among the warps of that quarter.
+template <int BN, int kAct, bool kPipelinedEpilogue, int kShare>
 __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCarve& sm, uint32_t tmem_base, int quarter,
-                                              int lane, int tiles, int tiles_m, int tiles_n) {
+                                              int part, int lane, int tiles, int tiles_m, int tiles_n) {
   const EpilogueArgs ep = epilogue_args(p);
   bool ok = true;
   int local = 0;
   const bool boxed = kPipelinedEpilogue && p.tma_store != 0 && ep.vector_io && ep.peers.count == 0;
-  uint8_t* boxes = reinterpret_cast<uint8_t*>(sm.peer_stage) + quarter * kOutStageBytesPerWarp;
+  uint8_t* boxes = reinterpret_cast<uint8_t*>(sm.peer_stage) + (part * 4 + quarter) * (kStagingBytes / (4 * kShare));
   uint32_t box_uses = 0;
   for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
     const int buf = local & 1;
@@ -487,24 +526,38 @@ __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCar
     int tm, tn;
     tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
     SourceQuads first;
-    if (boxed) fetch_source_coalesced(ep, first, tm * kTileM + quarter * 32, tn * BN, lane);   // before the wait
+    if (boxed) fetch_source_coalesced(ep, first, tm * kTileM + quarter * 32, tn * BN + part * 32, lane);   // before the wait
+    B200_PROBE(p, 2);
     if (!mbar_wait(&sm.acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
     tcgen05_fence_after_sync();
+    B200_PROBE(p, 3);
     if (boxed) {
-      epilogue_tile_boxed<BN, kAct>(p, ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN, first, boxes, box_uses);
+      epilogue_tile_boxed<BN, kAct, kShare>(p, ep, tmem_base + buf * BN, quarter, part, lane, tm * kTileM, tn * BN, first,
+                                            boxes, box_uses);
     } else {
-      epilogue_tile<BN, kAct>(ep, tmem_base + buf * BN, quarter, lane, tm * kTileM, tn * BN,
-                              sm.peer_stage + quarter * (kPeerStageBytesPerWarp / sizeof(float)));
+      epilogue_tile<BN, kAct, kShare>(ep, tmem_base + buf * BN, quarter, part, lane, tm * kTileM, tn * BN, boxes);
     }
     tcgen05_fence_before_sync();
     __syncwarp();
     if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
+    B200_PROBE(p, 4);
   }
   if (boxed && lane == 0) tma_store_wait_all<0>();   // every store has left shared memory and landed
+  B200_PROBE(p, 5);
 }
 
-// Threads of every TMA-fed kernel: warp 0 producer, warp 1 TMEM owner + MMA issuer, warps 2-5 epilogue.
+// Threads of the cluster kernels (split-K, operand-swapped): warp 0 producer, warp 1 TMEM owner +
+// MMA issuer, warps 2-5 epilogue.
 constexpr int kTmaThreads = 6 * 32;
+
+// Threads of the persistent TMA-fed tile kernels and the CTA-pair kernel: the same two warps and
+// eight epilogue warps, two per quarter of the accumulator rows. An epilogue warp has its
+// scheduler to itself and issues one dependent instruction every few cycles, so the epilogue of a
+// tile is bound by its instruction count per warp: with four warps a 32-column chunk took about
+// 1500 cycles (in-kernel time stamps: 2900 cycles for a 128 x 64 tile, 6400 for 128 x 128), all of
+// it exposed when a CTA has a single tile. Eight warps halve the chunks per warp.
+constexpr int kTileEpilogueShare = 2;
+constexpr int kTileThreads = (2 + 4 * kTileEpilogueShare) * 32;
 
 // ------------------------------------------------------------- host-side helpers
 
@@ -524,6 +577,9 @@ void fill_common(UmmaParams* p, const b200_gemm_problem& q, const PeerOutputs& p
   bool peers_ok = true;   // peer copies share the row pitch of D, only their bases can differ in alignment
   for (int i = 0; i < peers.count; ++i) peers_ok = peers_ok && aligned16(peers.ptr[i]);
   p->vector_io = (q.n % 4 == 0 && aligned16(q.d) && q.ldd % 4 == 0 && c_ok && bias_ok && peers_ok) ? 1 : 0;
+#ifdef B200_PROBE_TIMING
+  p->probe = b200_probe_buffer;
+#endif
 }
 
 }  // namespace
