@@ -337,6 +337,16 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t 
   return d;
 }
 
+// The descriptor of the same matrix `bytes` further on in shared memory (bytes a multiple of 16).
+// Only the start-address field changes, and it cannot carry out of its 14 bits while the operand
+// stays inside shared memory, so this is one 32-bit addition on the low word: the MMA-issuing
+// thread is a lone thread whose every instruction costs several cycles, and composing a descriptor
+// from scratch per instruction made it, not the tensor pipe, the limit of the main loops.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) {
+  const uint32_t lo = static_cast<uint32_t>(desc) + (bytes >> 4);
+  return (desc & 0xFFFFFFFF00000000ull) | lo;
+}
+
 // Instruction descriptor (32-bit) for kind::tf32 with FP32 accumulation.
 //   bits  4-5   accumulator format (1 = F32)
 //   bits  7-9   A format (2 = TF32)      bits 10-12  B format (2 = TF32)

@@ -157,6 +157,94 @@ __device__ __forceinline__ void exchange_finish(const EpilogueArgs& p, const flo
   }
 }
 
+// The same pass for a share that lies inside the matrix as a whole, with 128-bit rows and neither
+// bias nor peer outputs: the case of every large problem, and the one where the finishing pass is
+// most of what the split costs. The few warps of this kernel issue a dependent instruction every
+// five cycles or so, so the pass is bound by instructions per item: here a thread's items are one
+// column quad of rows `first`, `first` + step, ... (threads is a multiple of the quads per row), every
+// address advances by a constant, nothing is predicated but the end of the tile, and the source
+// quads of the next four items are requested before the current four are finished. The first four
+// are requested by `interior_sources` before the exchange. Sums run in source order and the
+// arithmetic is finish_quad's: the bits are those of the general pass.
+constexpr int kInteriorBatch = 4;
+
+struct InteriorCursor {
+  int row;                  // row of the tile of this thread's next item
+  int step;                 // rows between consecutive items
+  const float4* part;       // first source's partial of that item
+  const float* c;           // null when beta == 0
+  float* d;
+  int64_t c_step, d_step;   // elements per item step
+};
+
+__device__ __forceinline__ InteriorCursor interior_cursor(const EpilogueArgs& p, const float4* exchange, int quads_log2,
+                                                          int row0, int col_base, int t, int threads) {
+  const int quads = 1 << quads_log2;
+  const int quad = t & (quads - 1);
+  InteriorCursor cur;
+  cur.row = t >> quads_log2;
+  cur.step = threads >> quads_log2;
+  cur.part = exchange + quad * kExchangePitch + cur.row;
+  const int col = col_base + 4 * quad;
+  cur.c = p.beta != 0.f ? p.c + static_cast<int64_t>(row0 + cur.row) * p.ldc + col : nullptr;
+  cur.d = p.d + static_cast<int64_t>(row0 + cur.row) * p.ldd + col;
+  cur.c_step = static_cast<int64_t>(cur.step) * p.ldc;
+  cur.d_step = static_cast<int64_t>(cur.step) * p.ldd;
+  return cur;
+}
+
+__device__ __forceinline__ void interior_sources(const InteriorCursor& cur, int first_item, float4 (&out)[kInteriorBatch]) {
+#pragma unroll
+  for (int u = 0; u < kInteriorBatch; ++u) {
+    const bool wanted = cur.c != nullptr && cur.row + (first_item + u) * cur.step < kTileM;
+    out[u] = wanted ? __ldg(reinterpret_cast<const float4*>(cur.c + (first_item + u) * cur.c_step))
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+template <int kAct>
+__device__ __forceinline__ void exchange_finish_interior(const EpilogueArgs& p, InteriorCursor cur, float4 (&src)[kInteriorBatch],
+                                                         int sources, int quads_log2) {
+  const int source_stride = (1 << quads_log2) * kExchangePitch;
+#pragma unroll 1
+  while (cur.row < kTileM) {
+    float4 next[kInteriorBatch];
+    interior_sources(cur, kInteriorBatch, next);
+    float4 sum[kInteriorBatch];
+#pragma unroll
+    for (int u = 0; u < kInteriorBatch; ++u) {
+      sum[u] = cur.row + u * cur.step < kTileM ? cur.part[u * cur.step] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int s = 1; s < sources; ++s) {
+#pragma unroll
+      for (int u = 0; u < kInteriorBatch; ++u) {
+        if (cur.row + u * cur.step < kTileM) {
+          const float4 v = cur.part[s * source_stride + u * cur.step];
+          sum[u].x += v.x, sum[u].y += v.y, sum[u].z += v.z, sum[u].w += v.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kInteriorBatch; ++u) {
+      if (cur.row + u * cur.step < kTileM) {
+        float4 v = make_float4(p.alpha * sum[u].x, p.alpha * sum[u].y, p.alpha * sum[u].z, p.alpha * sum[u].w);
+        if (cur.c != nullptr) {
+          v.x = fmaf(p.beta, src[u].x, v.x), v.y = fmaf(p.beta, src[u].y, v.y);
+          v.z = fmaf(p.beta, src[u].z, v.z), v.w = fmaf(p.beta, src[u].w, v.w);
+        }
+        *reinterpret_cast<float4*>(cur.d + u * cur.d_step) =
+            make_float4(activate<kAct>(v.x), activate<kAct>(v.y), activate<kAct>(v.z), activate<kAct>(v.w));
+      }
+    }
+    cur.row += kInteriorBatch * cur.step;
+    cur.part += kInteriorBatch * cur.step;
+    if (cur.c != nullptr) cur.c += kInteriorBatch * cur.c_step;
+    cur.d += kInteriorBatch * cur.d_step;
+#pragma unroll
+    for (int u = 0; u < kInteriorBatch; ++u) src[u] = next[u];
+  }
+}
+
 // STAGES counts 32-wide K blocks of shared memory; KSUB of them form one pipeline stage (two when
 // the CTA has its SM to itself and the ring can be twice as large: one barrier round trip per 64 of K).
 template <int STAGES, int kAct, int KSUB = 1>
@@ -232,6 +320,7 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
     }
   } else if (warp == 1) {
     if (lane == 0 && has_work) {
+      const SubBlockDescs ring = sub_block_descs(smem_u32(sm.stages));   // of the ring's first sub-block
       int stage = 0;
       uint32_t phase = 0;
       bool fed = true;
@@ -240,8 +329,9 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
         tcgen05_fence_after_sync();
 #pragma unroll
         for (int sub = 0; sub < KSUB; ++sub) {
-          const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage * KSUB + sub) * stage_bytes<BN>());
-          issue_stage_mmas<BN>(tmem_base, a_addr, a_addr + kASlabBytes, (kb > kb_begin || sub > 0) ? 1u : 0u);
+          const uint32_t offset = static_cast<uint32_t>(stage * KSUB + sub) * stage_bytes<BN>();
+          const SubBlockDescs descs{umma_desc_advance(ring.a, offset), umma_desc_advance(ring.b, offset)};
+          issue_stage_mmas<BN>(tmem_base, descs, (kb > kb_begin || sub > 0) ? 1u : 0u);
         }
         umma_commit(&sm.empty[stage]);
         if (++stage == kRing) stage = 0, phase ^= 1u;
@@ -270,6 +360,15 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
   const int row_in_tile = quarter * 32 + lane;
   const bool warp_rows = tm * kTileM + quarter * 32 < p.m;   // any row of this warp inside the matrix
   const int quads_log2 = 31 - __clz(quads);
+  // The finishing pass of a share inside the matrix (see exchange_finish_interior): its first source
+  // quads are requested now and arrive during the exchange.
+  const EpilogueArgs args = epilogue_args(p);
+  const int col_base = tn * BN + rank * width;
+  const bool interior = args.vector_io && args.bias == nullptr && args.peers.count == 0 && (tm + 1) * kTileM <= p.m &&
+                        col_base + width <= p.n;
+  InteriorCursor cursor = interior_cursor(args, exchange, quads_log2, tm * kTileM, col_base, threadIdx.x, kTmaThreads);
+  float4 first_sources[kInteriorBatch];
+  if (interior) interior_sources(cursor, 0, first_sources);
   if (warp >= 2 && warp_rows) {
     // 2. Send this CTA's partial row, W columns to each CTA.
     send_partial_row<BN>(cluster, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), has_work && ok, exchange,
@@ -281,7 +380,11 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
   B200_PROBE(p, 5);
 
   // 3. Add the partials of this CTA's columns in rank order and finish them.
-  exchange_finish<kAct>(epilogue_args(p), exchange, ranks, quads_log2, tm * kTileM, tn * BN + rank * width, threadIdx.x, kTmaThreads);
+  if (interior) {
+    exchange_finish_interior<kAct>(args, cursor, first_sources, ranks, quads_log2);
+  } else {
+    exchange_finish<kAct>(args, exchange, ranks, quads_log2, tm * kTileM, col_base, threadIdx.x, kTmaThreads);
+  }
 
   B200_PROBE(p, 6);
   __syncthreads();
@@ -530,21 +633,23 @@ int splitk_max_clusters(int cluster_size) {
 }
 
 // Cluster size of the split-K kernel, from a cost model fitted to timings of the kernel on a B200
-// (microseconds). With f the fraction of the tile's 128 rows that exist, a 32-wide K block costs
-// 0.22 + 0.13 f when the CTA has its SM to itself and runs two sub-blocks per stage, 0.29 + 0.05 f
-// when the grid fits one CTA per SM but its clusters only fit the device at two (single-block
-// stages), and 0.43 + 0.10 f per CTA when two share an SM. Most of it is the MMA thread's
-// instruction stream and barrier round trips; with single-block stages a deeper ring changes
-// nothing. Barriers, exchange and the finishing pass cost 4.5 / 6.0 / 7.2 for
-// clusters of 2 / 4 / 8 when few rows exist and 7 / 8 / 9 when all 128 do (interpolated by the row
-// count), half as much again when two CTAs share an SM. A candidate must keep two K blocks per
-// range and fit the device in one wave (two CTAs per SM: twice the cluster count the occupancy
+// (microseconds, graph-timed, with a source and ReLU). With f the fraction of the tile's 128 rows
+// that exist, a 32-wide K block costs 0.15 + 0.09 f when the CTA has its SM to itself and runs two
+// sub-blocks per stage, 0.26 + 0.04 f when the grid fits one CTA per SM but its clusters only fit
+// the device at two (single-block stages), and 0.36 + 0.06 f per CTA when two share an SM. Most of
+// it is the MMA thread's instruction stream and barrier round trips; with single-block stages a
+// deeper ring changes nothing. Launch, pipeline fill, barriers, exchange and the finishing pass cost
+// 4.7 unsplit and 6.0 / 8.0 / 9.5 for clusters of 2 / 4 / 8 when few rows exist, 8.2 / 10.5 / 11.4 when
+// all 128 do (interpolated by the row count). Fitted to: 1024 x 1024 x K split in two 12.0 / 15.8 us
+// at K = 1024 / 2048, in four 25.0 / 39.7 at K = 4096 / 8192; 512 x 512 x 2048 in eight 13.3;
+// 768 x 768 x 4096 in four 20.7; 1280 x 1280 x 8192 in two 60.4. A candidate must keep two K blocks
+// per range and fit the device in one wave (two CTAs per SM: twice the cluster count the occupancy
 // query reports for one). `estimate_us` receives the modelled time of the choice.
 int splitk_ranks(const b200_gemm_problem& q, int sms, float* estimate_us = nullptr) {
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
-  constexpr float kExchangeFewRows[4] = {4.7f, 4.5f, 6.0f, 7.2f};
-  constexpr float kExchangeAllRows[4] = {4.7f, 7.0f, 8.0f, 9.0f};
+  constexpr float kExchangeFewRows[4] = {4.7f, 6.0f, 8.0f, 9.5f};
+  constexpr float kExchangeAllRows[4] = {4.7f, 8.2f, 10.5f, 11.4f};
   const float row_fraction = static_cast<float>(q.m < kTileM ? q.m : kTileM) / kTileM;
   int best = 1;
   float best_us = 1e30f;
@@ -556,10 +661,9 @@ int splitk_ranks(const b200_gemm_problem& q, int sms, float* estimate_us = nullp
     const bool shared_sm = ctas > sms;
     const bool deep = !shared_sm && (ranks == 1 || tiles <= splitk_max_clusters(ranks));   // as launch_splitk_for decides
     const float exchange = kExchangeFewRows[log2r] + row_fraction * (kExchangeAllRows[log2r] - kExchangeFewRows[log2r]);
-    const float per_block = shared_sm ? 0.43f + 0.10f * row_fraction
-                                      : (deep ? 0.22f + 0.13f * row_fraction : 0.29f + 0.05f * row_fraction);
-    const float us = static_cast<float>((k_blocks + ranks - 1) / ranks) * per_block +
-                     exchange * (shared_sm ? 1.5f : (deep ? 1.0f : 1.1f));
+    const float per_block = shared_sm ? 0.36f + 0.06f * row_fraction
+                                      : (deep ? 0.15f + 0.09f * row_fraction : 0.26f + 0.04f * row_fraction);
+    const float us = static_cast<float>((k_blocks + ranks - 1) / ranks) * per_block + exchange;
     if (us < best_us) best_us = us, best = ranks;
   }
   if (estimate_us != nullptr) *estimate_us = best_us;

@@ -128,6 +128,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) umma_pair_kernel(const __grid
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc_whole = umma_idesc_tf32(2 * kTileM, kPairN, /*a_mn_major=*/false, /*b_mn_major=*/true);
       constexpr uint32_t idesc_half = umma_idesc_tf32(2 * kTileM, kPairN / 2, /*a_mn_major=*/false, /*b_mn_major=*/true);
+      const SubBlockDescs ring = sub_block_descs(smem_u32(stages));   // of the ring's first sub-block
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -144,13 +145,12 @@ __global__ void __launch_bounds__(kTileThreads, 1) umma_pair_kernel(const __grid
           tcgen05_fence_after_sync();
 #pragma unroll
           for (int sub = 0; sub < KSUB; ++sub) {
-            const uint32_t a_addr = smem_u32(stages + static_cast<size_t>(stage) * kPairStageBytes + sub * kPairSubBytes);
-            const uint32_t b_addr = a_addr + kASlabBytes;
+            const uint32_t offset = static_cast<uint32_t>(stage) * kPairStageBytes + sub * kPairSubBytes;
 #pragma unroll
             for (int j = 0; j < kStageK / kInstK; ++j) {
-              const uint64_t desc_a = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
-              const uint64_t desc_b = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
-              umma_tf32_pair(tmem_acc, desc_a, desc_b, idesc, (kb > 0 || sub > 0 || j > 0) ? 1u : 0u);
+              umma_tf32_pair(tmem_acc, umma_desc_advance(ring.a, offset + j * (kInstK * 4)),
+                             umma_desc_advance(ring.b, offset + j * (kInstK * 128)), idesc,
+                             (kb > 0 || sub > 0 || j > 0) ? 1u : 0u);
             }
           }
           // The stage is reusable in both CTAs once these MMAs have read it.

@@ -178,21 +178,30 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   *tn = in_band / band_rows;
 }
 
-// Issues the four MMAs of one stage. `accumulate_first` is 0 only for the very
-// first MMA of an output tile.
+// Descriptors of the first MMA of a 32-wide K sub-block whose A slab starts at `a_addr` (B slab
+// right behind it).
+//   A: K-major, 8-row groups 1024 bytes apart (SBO); LBO is not used by the swizzled K-major form
+//      and carries the customary 16 bytes.
+//   B: N-major, 32-column groups 4096 bytes apart (LBO), 4-row k groups 512 bytes apart (SBO);
+//      one MMA spans two of them.
+struct SubBlockDescs {
+  uint64_t a, b;
+};
+__device__ __forceinline__ SubBlockDescs sub_block_descs(uint32_t a_addr) {
+  return SubBlockDescs{umma_smem_desc(a_addr, 16, 1024, kUmmaSwizzle128B),
+                       umma_smem_desc(a_addr + kASlabBytes, kBBoxBytes, 512, kUmmaSwizzle128B32BAtom)};
+}
+
+// Issues the four MMAs of one 32-wide K sub-block. `accumulate_first` is 0 only for the very
+// first MMA of an output tile. Successive MMAs advance 32 bytes along a row of A and eight rows
+// (1024 bytes) of B.
 template <int BN>
-__device__ __forceinline__ void issue_stage_mmas(uint32_t tmem_acc, uint32_t a_addr, uint32_t b_addr,
-                                                 uint32_t accumulate_first) {
+__device__ __forceinline__ void issue_stage_mmas(uint32_t tmem_acc, const SubBlockDescs& first, uint32_t accumulate_first) {
   constexpr uint32_t idesc = umma_idesc_tf32(kTileM, BN, /*a_mn_major=*/false, /*b_mn_major=*/true);
 #pragma unroll
   for (int j = 0; j < kStageK / kInstK; ++j) {
-    // A: K-major, 8-row groups 1024 bytes apart (SBO); LBO is not used by the
-    //    swizzled K-major form and carries the customary 16 bytes.
-    // B: N-major, 32-column groups 4096 bytes apart (LBO), 4-row k groups
-    //    512 bytes apart (SBO); one MMA spans two of them.
-    const uint64_t desc_a = umma_smem_desc(a_addr + j * (kInstK * 4), 16, 1024, kUmmaSwizzle128B);
-    const uint64_t desc_b = umma_smem_desc(b_addr + j * (kInstK * 128), kBBoxBytes, 512, kUmmaSwizzle128B32BAtom);
-    umma_tf32(tmem_acc, desc_a, desc_b, idesc, j == 0 ? accumulate_first : 1u);
+    umma_tf32(tmem_acc, umma_desc_advance(first.a, j * (kInstK * 4)), umma_desc_advance(first.b, j * (kInstK * 128)), idesc,
+              j == 0 ? accumulate_first : 1u);
   }
 }
 
@@ -480,6 +489,7 @@ __device__ __forceinline__ SmemCarve carve(uint8_t* raw) {
 // STAGES / KSUB stages, and `k_blocks` counts stages.
 template <int BN, int STAGES, int KSUB = 1>
 __device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base, int tiles, int k_blocks) {
+  const SubBlockDescs ring = sub_block_descs(smem_u32(sm.stages));   // of the ring's first sub-block
   static_assert(STAGES % KSUB == 0, "whole stages");
   constexpr int kRing = STAGES / KSUB;
   int stage = 0;
@@ -496,10 +506,12 @@ __device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base
     for (int kb = 0; kb < k_blocks; ++kb) {
       if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
+      const uint32_t stage_offset = static_cast<uint32_t>(stage * KSUB) * stage_bytes<BN>();
 #pragma unroll
       for (int sub = 0; sub < KSUB; ++sub) {
-        const uint32_t a_addr = smem_u32(sm.stages + static_cast<size_t>(stage * KSUB + sub) * stage_bytes<BN>());
-        issue_stage_mmas<BN>(tmem_acc, a_addr, a_addr + kASlabBytes, (kb > 0 || sub > 0) ? 1u : 0u);
+        const SubBlockDescs descs{umma_desc_advance(ring.a, stage_offset + sub * stage_bytes<BN>()),
+                                  umma_desc_advance(ring.b, stage_offset + sub * stage_bytes<BN>())};
+        issue_stage_mmas<BN>(tmem_acc, descs, (kb > 0 || sub > 0) ? 1u : 0u);
       }
       umma_commit(&sm.empty[stage]);  // stage reusable once these MMAs have read it
       if (++stage == kRing) stage = 0, phase ^= 1u;
