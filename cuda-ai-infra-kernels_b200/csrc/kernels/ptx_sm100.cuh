@@ -256,6 +256,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t ran
   return remote;
 }
 
+// 128-bit store to the shared memory of a CTA of the cluster (address from map_to_cta).
+__device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }

@@ -253,9 +253,6 @@ __device__ __forceinline__ bool produce_stage(const PipelineParams& p, ProducerC
   return true;
 }
 
-__device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, float x, float y, float z, float w) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
-}
 
 template <class Grid, int BK, int STAGES, bool kRegPrefetch, bool kPacked, bool kStreamK, int kCtasPerSm, bool kGather,
           int kSplit = 1>
@@ -400,7 +397,8 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
 #pragma unroll
           for (int cb = 0; cb < RN; ++cb) {
             st_shared_cluster_v4(remote + (i * RN + cb) * Grid::kConsumerThreads * static_cast<uint32_t>(sizeof(float4)),
-                                 acc[i][4 * cb], acc[i][4 * cb + 1], acc[i][4 * cb + 2], acc[i][4 * cb + 3]);
+                                 __float_as_uint(acc[i][4 * cb]), __float_as_uint(acc[i][4 * cb + 1]),
+                                 __float_as_uint(acc[i][4 * cb + 2]), __float_as_uint(acc[i][4 * cb + 3]));
           }
       }
       cluster_sync_all();

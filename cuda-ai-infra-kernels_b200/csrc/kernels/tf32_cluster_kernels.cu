@@ -73,30 +73,32 @@ constexpr int kExchangePitch = kTileM + 1;
 // TMEM at `tmem_row`): the columns of share s go to the CTA with cluster rank
 // s * rank_stride + rank_offset, into that CTA's buffer for source `my_slice`. The next 32 columns
 // are fetched from TMEM while the current ones are being sent; a share is at least 16 columns
-// wide, so each half chunk (four quads) has a single destination. `send_chunk` sends one chunk.
-__device__ __forceinline__ void send_chunk(cg::cluster_group& cluster, const uint32_t (&cur)[32], int chunk, float4* exchange,
-                                           int my_slice, int quads_log2, int rank_stride, int rank_offset,
-                                           int row_in_tile) {
+// wide, so each half chunk (four quads) has a single destination. `send_chunk` sends one chunk;
+// `exchange_addr` is the exchange buffer's shared-window address in this CTA (the same offset in
+// every CTA), destinations are 32-bit shared::cluster addresses: a `mapa` and four stores with
+// constant offsets per half chunk.
+__device__ __forceinline__ void send_chunk(const uint32_t (&cur)[32], int chunk, uint32_t exchange_addr, int my_slice,
+                                           int quads_log2, int rank_stride, int rank_offset, int row_in_tile) {
   const int quads = 1 << quads_log2;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int quad0 = chunk * 8 + half * 4;
     const int dest_slice = quad0 >> quads_log2, local_quad0 = quad0 & (quads - 1);
-    float4* dst = cluster.map_shared_rank(exchange, dest_slice * rank_stride + rank_offset) +
-                  (my_slice * quads + local_quad0) * kExchangePitch + row_in_tile;
+    const uint32_t dst = map_to_cta(exchange_addr, static_cast<uint32_t>(dest_slice * rank_stride + rank_offset)) +
+                         static_cast<uint32_t>((my_slice * quads + local_quad0) * kExchangePitch + row_in_tile) *
+                             static_cast<uint32_t>(sizeof(float4));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int e = half * 16 + j * 4;
-      dst[j * kExchangePitch] = make_float4(__uint_as_float(cur[e + 0]), __uint_as_float(cur[e + 1]),
-                                            __uint_as_float(cur[e + 2]), __uint_as_float(cur[e + 3]));
+      st_shared_cluster_v4(dst + j * kExchangePitch * static_cast<uint32_t>(sizeof(float4)), cur[e + 0], cur[e + 1], cur[e + 2],
+                           cur[e + 3]);
     }
   }
 }
 
 template <int kCols>
-__device__ __forceinline__ void send_partial_row(cg::cluster_group& cluster, uint32_t tmem_row, bool have_acc,
-                                                 float4* exchange, int my_slice, int quads_log2, int rank_stride,
-                                                 int rank_offset, int row_in_tile) {
+__device__ __forceinline__ void send_partial_row(uint32_t tmem_row, bool have_acc, uint32_t exchange_addr, int my_slice,
+                                                 int quads_log2, int rank_stride, int rank_offset, int row_in_tile) {
   constexpr int kChunks = kCols / 32;
   static_assert(kChunks % 2 == 0, "chunks are handled in pairs");
   // Two register sets, named rather than indexed so that both stay in registers.
@@ -113,12 +115,12 @@ __device__ __forceinline__ void send_partial_row(cg::cluster_group& cluster, uin
       tmem_ld_wait();
       tmem_ld_32x32(tmem_row + (chunk + 1) * 32, odd);
     }
-    send_chunk(cluster, even, chunk, exchange, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
+    send_chunk(even, chunk, exchange_addr, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
     if (have_acc) {
       tmem_ld_wait();
       if (chunk + 2 < kChunks) tmem_ld_32x32(tmem_row + (chunk + 2) * 32, even);
     }
-    send_chunk(cluster, odd, chunk + 1, exchange, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
+    send_chunk(odd, chunk + 1, exchange_addr, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
   }
 }
 
@@ -371,8 +373,8 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
   if (interior) interior_sources(cursor, 0, first_sources);
   if (warp >= 2 && warp_rows) {
     // 2. Send this CTA's partial row, W columns to each CTA.
-    send_partial_row<BN>(cluster, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), has_work && ok, exchange,
-                         rank, quads_log2, 1, 0, row_in_tile);
+    send_partial_row<BN>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), has_work && ok, smem_u32(exchange), rank,
+                         quads_log2, 1, 0, row_in_tile);
   }
   B200_PROBE(p, 4);
   tcgen05_fence_before_sync();

@@ -430,6 +430,32 @@ def test_pair_kernel_runs_a_short_last_round_as_half_tiles(abi, kernel, epilogue
     assert_device_clean(abi)
 
 
+# ------------------------------------------------------------ source and destination are one buffer
+# Every element's source value is read by the thread (or the warp) that later writes it, so an
+# accumulation in place must give what a separate source gives: through the boxes and TMA stores of
+# the tile kernels, through the split-K finishing passes (inside the matrix and at its edges).
+
+
+@pytest.mark.parametrize("entry", entries(), ids=lambda e: e[1])
+@pytest.mark.parametrize("shape", [(256, 384, 192), (200, 264, 96)])
+def test_source_may_be_the_destination(abi, entry, shape):
+    kernel_id, alias, epilogue, align = entry
+    m, n, k = (16, 256, shape[2]) if alias.startswith("swap") else shape
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randint(-4, 5, (m, k), generator=g).float()
+    b = torch.randint(-4, 5, (k, n), generator=g).float()
+    c = torch.randint(-4, 5, (m, n), generator=g).float()
+    d = c.clone().cuda()
+    a_dev, b_dev = a.cuda(), b.cuda()
+    q = GemmProblem(m, n, k, a_dev.data_ptr(), b_dev.data_ptr(), d.data_ptr(), d.data_ptr(), k, n, n, n, 1.0, 0.5, epilogue, None)
+    status = abi.b200_tf32_gemm_launch(kernel_id, ctypes.byref(q), current_stream_ptr())
+    assert status == 0, abi.b200_status_string(status)
+    expected = oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, EPILOGUE_NAME[epilogue])
+    tol = 1e-5 if epilogue == GELU else 0
+    torch.testing.assert_close(d.cpu(), expected, atol=tol, rtol=tol)
+    assert_device_clean(abi)
+
+
 # ------------------------------------------------ K that ends inside a pipeline stage
 # Stages hold two or four 32-wide K sub-blocks; a K that ends inside the first sub-block, between
 # sub-blocks or inside the last one must read the missing part as zeros.
