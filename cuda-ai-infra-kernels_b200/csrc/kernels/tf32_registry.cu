@@ -116,20 +116,20 @@ bool gate_pair(const b200_gemm_problem& q, int sms) {
 // tensor-core split-K entry takes over (16 x 4096 x 4096: 22.1 vs 14.7 us).
 bool gate_skinny(const b200_gemm_problem& q, int) { return q.m <= 4; }
 // Split K when the split-K kernel's model predicts a shorter run than the unsplit tile kernels. Those
-// take, graph-timed with a source and ReLU, about 0.185 us per 32-wide K block on top of 5.2 us
-// (128 x 64 tiles, when they fit the SMs in one round: 1024 x 1024 x K 11.0 / 17.3 / 28.8 / 55.9 us at
-// K = 1024 / 2048 / 4096 / 8192) or 0.235 us on top of 6.0 us (128 x 128: 1536^3 16.8,
-// 512 x 4096 x 4096 38.0, 1280 x 1280 x 8192 67.8). Split against unsplit, measured: 1024 x 1024 x 2048
-// 15.8 / 17.3 us, 1024 x 1024 x 8192 39.7 / 55.9, 512 x 512 x 2048 13.3 / 16.6, 768 x 768 x 4096 20.7 / 26.7,
-// 256 x 4096 x 4096 25.2 / 29.1, 64 x 4096 x 4096 16.2 / 29.0, 1280 x 1280 x 8192 60.4 / 67.8; unsplit is
-// ahead at 1024^3 (11.0 against 12.0), 1536^3 (16.8 / 20.2), 512 x 4096 x 4096 (38.0 / 39.5), 512^3 and
-// 768^3. The gate picks the faster side for all of these.
+// take, graph-timed with a source and ReLU, about 0.136 us per 32-wide K block on top of 5.4 us
+// (128 x 64 tiles, when they fit the SMs in one round: 1024 x 1024 x K 9.8 / 14.2 / 22.8 us at
+// K = 1024 / 2048 / 4096) or 0.235 us on top of 4.8 us (128 x 128: 1536^3 15.8, 512 x 4096 x 4096 35.8,
+// 1280 x 1280 x 8192 65.3). Split against unsplit, measured: 1024 x 1024 x 4096 22.1 / 22.8 us,
+// 512 x 512 x 2048 14.0 / 15.3 (before the second MMA issuer), 768 x 768 x 4096 21.0 / 25.8 (before),
+// 64 x 4096 x 4096 15.3 / 25.9, 1280 x 1280 x 8192 60.4 / 65.3; unsplit is ahead at 1024^3 (9.8 against
+// 11.7), 1024 x 1024 x 2048 (14.2 / 15.1), 1536^3 (15.8 / 20.1), 512 x 4096 x 4096 (35.8 / 38.8), 512^3
+// and 768^3.
 bool gate_splitk(const b200_gemm_problem& q, int sms) {
   float split_us = 0.f;
   if (tf32_splitk_plan(q, sms, &split_us) < 2) return false;
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
   const bool narrow = tiles_of(q, 64) <= sms;
-  const float unsplit_us = static_cast<float>(k_blocks) * (narrow ? 0.185f : 0.235f) + (narrow ? 5.2f : 6.0f);
+  const float unsplit_us = static_cast<float>(k_blocks) * (narrow ? 0.136f : 0.235f) + (narrow ? 5.4f : 4.8f);
   return split_us + 1.0f < unsplit_us;   // near ties go to the simpler kernel
 }
 // Measured against the split-K tile kernel: ahead up to 16 rows (16 x 8192 x 1024: 11.7 vs 16.5 us,

@@ -16,8 +16,9 @@ namespace {
 // STAGES counts 32-wide K blocks of shared memory; KSUB of them form one pipeline stage (the MMA
 // thread's barrier wait and commit cost about as much as four small MMAs, so narrow tiles, whose
 // MMAs are short, run two sub-blocks per stage).
-template <int BN, int STAGES, int kAct, int KSUB = 1>
-__global__ void __launch_bounds__(kTileThreads, 1) umma_tma_kernel(const __grid_constant__ UmmaParams p) {
+template <int BN, int STAGES, int kAct, int KSUB = 1, int kIssuers = 1>
+__global__ void __launch_bounds__(kIssuers == 2 ? kTileThreadsTwoIssuers : kTileThreads, 1)
+    umma_tma_kernel(const __grid_constant__ UmmaParams p) {
   constexpr int kRing = STAGES / KSUB;
   extern __shared__ uint8_t smem_raw[];
   const SmemCarve sm = carve<BN, STAGES>(smem_raw);
@@ -27,16 +28,16 @@ __global__ void __launch_bounds__(kTileThreads, 1) umma_tma_kernel(const __grid_
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&sm.full[s], 1);
-      mbar_init(&sm.empty[s], 1);
+      mbar_init(&sm.empty[s], kIssuers);   // one commit per MMA issuer
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&sm.acc_full[b], 1);
+      mbar_init(&sm.acc_full[b], kIssuers);
       mbar_init(&sm.acc_empty[b], 4 * kTileEpilogueShare);  // one arrive per epilogue warp
     }
     mbar_init_fence();
   }
   if (warp == 1) {
-    tmem_alloc<tmem_columns<BN>()>(sm.tmem_ptr);
+    tmem_alloc<tmem_columns<BN, kIssuers>()>(sm.tmem_ptr);
     tmem_relinquish();
   }
   tcgen05_fence_before_sync();
@@ -84,9 +85,14 @@ __global__ void __launch_bounds__(kTileThreads, 1) umma_tma_kernel(const __grid_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) mma_role<BN, STAGES, KSUB>(sm, tmem_base, tiles, k_blocks);
-  } else {
-    epilogue_role<BN, kAct, true, kTileEpilogueShare>(p, sm, tmem_base, warp & 3, (warp - 2) >> 2, lane, tiles, tiles_m, tiles_n);
+    if (lane == 0) mma_role<BN, STAGES, KSUB, kIssuers>(sm, tmem_base, tiles, k_blocks, 0);
+  } else if (warp < 2 + 4 * kTileEpilogueShare) {
+    epilogue_role<BN, kAct, true, kTileEpilogueShare, kIssuers>(p, sm, tmem_base, warp & 3, (warp - 2) >> 2, lane, tiles, tiles_m,
+                                                                tiles_n);
+  } else {   // the second MMA issuer's warp
+    if constexpr (kIssuers == 2) {
+      if (lane == 0) mma_role<BN, STAGES, KSUB, kIssuers>(sm, tmem_base, tiles, k_blocks, 1);
+    }
   }
 
   tcgen05_fence_before_sync();
@@ -94,7 +100,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) umma_tma_kernel(const __grid_
   B200_PROBE(p, 6);
   if (warp == 1) {
     tcgen05_fence_after_sync();
-    tmem_dealloc<tmem_columns<BN>()>(tmem_base);
+    tmem_dealloc<tmem_columns<BN, kIssuers>()>(tmem_base);
   }
 }
 
@@ -270,19 +276,23 @@ __global__ void __launch_bounds__(kGenericThreads, 1) umma_generic_kernel(const 
 
 template <int BN, int STAGES, int kAct>
 int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
-  // K sub-blocks per pipeline stage. The MMA thread pays about 380 cycles per stage (barrier wait,
-  // fence, commit) next to 54 per instruction, so a 128 x 64 tile (54 cycles of tensor pipe per
-  // instruction) wants four sub-blocks per stage and a 128 x 128 tile (71 cycles) two; the ring must
-  // still hold two or three such stages to cover the load latency. Measured on a B200, unsplit, with
-  // a source: 128 x 128 at 1280 x 1280 x 8192 takes 97 us with 2 stages of 2, 72 us with 3 of 2, 81 us
-  // with 2 of 3, 84 us with 6 of 1; 128 x 64 at 1024 x 1024 x 4096 takes 35.4 us with 3 stages of 2 or
-  // 4 of 2 and 29.4 us with 2 of 4. The 128 x 256 tile (134 cycles per instruction) is slower with two
-  // sub-blocks per stage (2048 x 2048 x 8192: 129-140 against 107-122 us): only two stages fit.
-  constexpr int KSUB = (BN == 64 && STAGES % 4 == 0 && STAGES >= 8) ? 4
-                       : (BN <= 128 && STAGES % 2 == 0 && STAGES >= 4) ? 2 : 1;
-  auto kernel = umma_tma_kernel<BN, STAGES, kAct, KSUB>;
+  // K sub-blocks per pipeline stage. An MMA thread pays about 300 cycles per stage (barrier wait,
+  // fence, commit) next to 58 per instruction, so the 128 x 64 and 128 x 128 tiles put two sub-blocks
+  // behind one pair of barriers and give each to its own issuing thread (kIssuers below); the ring
+  // must still hold three or four such stages to cover the load latency. Measured on a B200 with one
+  // issuer, unsplit, with a source: 128 x 128 at 1280 x 1280 x 8192 took 97 us with 2 stages of 2,
+  // 72 us with 3 of 2, 81 us with 2 of 3, 84 us with 6 of 1; 128 x 64 at 1024 x 1024 x 4096 took 35.4 us
+  // with 4 stages of 2 and 29.4 us with 2 of 4 - with two issuers 22.8 us with 4 of 2 against 26.2 with
+  // 2 of 4 (graph-timed). The 128 x 256 tile (134 cycles of tensor pipe per instruction: the pipe, not
+  // the thread, is its limit) is slower with two sub-blocks per stage (2048 x 2048 x 8192: 129-140
+  // against 107-122 us): only two stages fit.
+  constexpr int KSUB = (BN <= 128 && STAGES % 2 == 0 && STAGES >= 4) ? 2 : 1;
+  // Two MMA issuers (mma_role) wherever a stage has sub-blocks to share out and the tile leaves
+  // TMEM for a second accumulator: the 128 x 64 and 128 x 128 tiles.
+  constexpr int kIssuers = (BN <= 128 && KSUB % 2 == 0) ? 2 : 1;
+  auto kernel = umma_tma_kernel<BN, STAGES, kAct, KSUB, kIssuers>;
   constexpr size_t smem = smem_bytes<BN, STAGES>();
-  if (!ensure_dynamic_smem<umma_tma_kernel<BN, STAGES, kAct, KSUB>, smem>()) return B200_ERR_LAUNCH_FAILED;
+  if (!ensure_dynamic_smem<umma_tma_kernel<BN, STAGES, kAct, KSUB, kIssuers>, smem>()) return B200_ERR_LAUNCH_FAILED;
   const size_t launch_smem = smem;
   UmmaParams p;
   fill_common(&p, q, peers);
@@ -301,7 +311,7 @@ int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_
   if (sms <= 0) return B200_ERR_INTERNAL;
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + BN - 1) / BN);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  kernel<<<grid, kTileThreads, launch_smem, stream>>>(p);
+  kernel<<<grid, kIssuers == 2 ? kTileThreadsTwoIssuers : kTileThreads, launch_smem, stream>>>(p);
   return launch_status();
 }
 

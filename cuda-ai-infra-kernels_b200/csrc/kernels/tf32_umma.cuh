@@ -162,9 +162,10 @@ __host__ __device__ constexpr size_t smem_bytes() {
          kStagingBytes;
 }
 
-template <int BN>
+// Two accumulator buffers of kIssuers partial accumulators each; BN in {64,128,256} keeps this a power of two.
+template <int BN, int kIssuers = 1>
 __host__ __device__ constexpr uint32_t tmem_columns() {
-  return 2 * BN < 32 ? 32 : 2 * BN;  // two accumulator buffers; BN in {64,128,256} keeps this a power of two
+  return 2 * kIssuers * BN < 32 ? 32 : 2 * kIssuers * BN;
 }
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int* tm, int* tn) {
@@ -319,7 +320,16 @@ __device__ __forceinline__ void finish_chunk_boxed(const UmmaParams& p, const Ep
 // finished the warp's next chunk is on its way from TMEM and its source values from memory.
 // `src` arrives holding the source of the warp's first chunk (fetched by the caller before it
 // waited for the accumulator); `uses` counts the warp's box uses across tiles.
-template <int BN, int kAct, int kShare>
+// kIssuers == 2: the tile's accumulator is the sum of two partial ones, BN columns apart (mma_role).
+__device__ __forceinline__ void add_partial_accumulator(uint32_t (&raw)[32], uint32_t taddr) {
+  uint32_t other[32];
+  tmem_ld_32x32(taddr, other);
+  tmem_ld_wait();
+#pragma unroll
+  for (int e = 0; e < 32; ++e) raw[e] = __float_as_uint(__uint_as_float(raw[e]) + __uint_as_float(other[e]));
+}
+
+template <int BN, int kAct, int kShare, int kIssuers = 1>
 __device__ __forceinline__ void epilogue_tile_boxed(const UmmaParams& p, const EpilogueArgs& ep, uint32_t tmem_acc, int quarter,
                                                     int part, int lane, int m0, int n0, SourceQuads& src, uint8_t* boxes,
                                                     uint32_t& uses) {
@@ -338,6 +348,7 @@ __device__ __forceinline__ void epilogue_tile_boxed(const UmmaParams& p, const E
     uint8_t* box = boxes + (uses++ % kBoxes) * kOutBoxBytes;
     stage_source_boxed<kBoxes>(ep, src, lane, box);
     tmem_ld_wait();
+    if constexpr (kIssuers == 2) add_partial_accumulator(raw_even, tmem_row + BN + chunk * 32);
     if (i + 1 < kMine) {
       tmem_ld_32x32(tmem_row + (chunk + kShare) * 32, raw_odd);
       fetch_source_coalesced(ep, src, row0, n0 + (chunk + kShare) * 32, lane);
@@ -347,6 +358,7 @@ __device__ __forceinline__ void epilogue_tile_boxed(const UmmaParams& p, const E
       box = boxes + (uses++ % kBoxes) * kOutBoxBytes;
       stage_source_boxed<kBoxes>(ep, src, lane, box);
       tmem_ld_wait();
+      if constexpr (kIssuers == 2) add_partial_accumulator(raw_odd, tmem_row + BN + (chunk + kShare) * 32);
       if (i + 2 < kMine) {
         tmem_ld_32x32(tmem_row + (chunk + 2 * kShare) * 32, raw_even);
         fetch_source_coalesced(ep, src, row0, n0 + (chunk + 2 * kShare) * 32, lane);
@@ -360,7 +372,7 @@ __device__ __forceinline__ void epilogue_tile_boxed(const UmmaParams& p, const E
 // Epilogue of one 128 x BN tile for one warp, straight from registers: TMEM lanes [32 * quarter, +32)
 // are rows m0 + 32 * quarter + lane. Each thread owns one row and walks it in chunks of 32 columns;
 // warp `part` of the kShare that serve the quarter takes chunks part, part + kShare, ...
-template <int BN, int kAct, int kShare>
+template <int BN, int kAct, int kShare, int kIssuers = 1>
 __device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tmem_acc, int quarter, int part, int lane,
                                               int m0, int n0, uint8_t* stage) {
   const int row = m0 + quarter * 32 + lane;
@@ -377,6 +389,7 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueArgs& p, uint32_t tm
     uint32_t raw[32];
     tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 32, raw);
     tmem_ld_wait();
+    if constexpr (kIssuers == 2) add_partial_accumulator(raw, tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + BN + chunk * 32);
     if (!row_ok && !stage_peers) continue;
     if (stage_peers) {
       // Local copy straight from registers; peer copies row-wise from the staged chunk.
@@ -487,11 +500,20 @@ __device__ __forceinline__ SmemCarve carve(uint8_t* raw) {
 // then consumes the operand ring stage by stage.
 // `KSUB` 32-wide K sub-blocks share one pipeline stage (one barrier wait, one commit): the ring has
 // STAGES / KSUB stages, and `k_blocks` counts stages.
-template <int BN, int STAGES, int KSUB = 1>
-__device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base, int tiles, int k_blocks) {
-  const SubBlockDescs ring = sub_block_descs(smem_u32(sm.stages));   // of the ring's first sub-block
+// With kIssuers == 2 two threads (of different warps) run this role side by side: issuer i takes
+// the sub-blocks i, i + 2, ... of every stage and accumulates them into its own accumulator
+// (columns [i BN, (i + 1) BN) of the buffer), the epilogue adds the two. An issuing thread is alone
+// on its scheduler; the tensor pipe takes an MMA only when it has room, so the pipe stands idle
+// while its only issuer waits on a barrier or commits (about 300 of the 820 cycles of a
+// 128 x 128 stage, and a 128 x 64 MMA costs the thread the same 58 cycles as a 128 x 128 one for
+// half the pipe time). Two issuers fill each other's gaps. They must not share an accumulator:
+// MMAs of different threads are not ordered with respect to each other.
+template <int BN, int STAGES, int KSUB = 1, int kIssuers = 1>
+__device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base, int tiles, int k_blocks, int issuer = 0) {
   static_assert(STAGES % KSUB == 0, "whole stages");
+  static_assert(kIssuers == 1 || (kIssuers == 2 && KSUB % 2 == 0), "every issuer has sub-blocks in every stage");
   constexpr int kRing = STAGES / KSUB;
+  const SubBlockDescs ring = sub_block_descs(smem_u32(sm.stages));   // of the ring's first sub-block
   int stage = 0;
   uint32_t phase = 0;
   bool ok = true;
@@ -502,28 +524,28 @@ __device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base
     // The epilogue must have drained this accumulator buffer.
     if (!mbar_wait(&sm.acc_empty[buf], use_parity ^ 1u, kSiteUmmaAccEmpty)) { ok = false; break; }
     tcgen05_fence_after_sync();
-    const uint32_t tmem_acc = tmem_base + buf * BN;
+    const uint32_t tmem_acc = tmem_base + (buf * kIssuers + issuer) * BN;
     for (int kb = 0; kb < k_blocks; ++kb) {
       if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
-      const uint32_t stage_offset = static_cast<uint32_t>(stage * KSUB) * stage_bytes<BN>();
+      const uint32_t stage_offset = static_cast<uint32_t>(stage * KSUB + issuer) * stage_bytes<BN>();
 #pragma unroll
-      for (int sub = 0; sub < KSUB; ++sub) {
+      for (int sub = 0; sub < KSUB; sub += kIssuers) {
         const SubBlockDescs descs{umma_desc_advance(ring.a, stage_offset + sub * stage_bytes<BN>()),
                                   umma_desc_advance(ring.b, stage_offset + sub * stage_bytes<BN>())};
         issue_stage_mmas<BN>(tmem_acc, descs, (kb > 0 || sub > 0) ? 1u : 0u);
       }
-      umma_commit(&sm.empty[stage]);  // stage reusable once these MMAs have read it
+      umma_commit(&sm.empty[stage]);  // stage reusable once these MMAs have read it (one arrival per issuer)
       if (++stage == kRing) stage = 0, phase ^= 1u;
     }
-    if (ok) umma_commit(&sm.acc_full[buf]);
+    if (ok) umma_commit(&sm.acc_full[buf]);   // one arrival per issuer
   }
 }
 
 // One of the 4 * kShare epilogue warps of the persistent single-CTA kernels: `quarter` is the warp's
 // quarter of the accumulator rows (its hardware warp index modulo four, which is what tcgen05.ld
 // lets it read), `part` in [0, kShare) its place among the warps of that quarter.
-template <int BN, int kAct, bool kPipelinedEpilogue, int kShare>
+template <int BN, int kAct, bool kPipelinedEpilogue, int kShare, int kIssuers = 1>
 __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCarve& sm, uint32_t tmem_base, int quarter,
                                               int part, int lane, int tiles, int tiles_m, int tiles_n) {
   const EpilogueArgs ep = epilogue_args(p);
@@ -544,10 +566,11 @@ __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCar
     tcgen05_fence_after_sync();
     B200_PROBE(p, 3);
     if (boxed) {
-      epilogue_tile_boxed<BN, kAct, kShare>(p, ep, tmem_base + buf * BN, quarter, part, lane, tm * kTileM, tn * BN, first,
-                                            boxes, box_uses);
+      epilogue_tile_boxed<BN, kAct, kShare, kIssuers>(p, ep, tmem_base + buf * kIssuers * BN, quarter, part, lane, tm * kTileM,
+                                                      tn * BN, first, boxes, box_uses);
     } else {
-      epilogue_tile<BN, kAct, kShare>(ep, tmem_base + buf * BN, quarter, part, lane, tm * kTileM, tn * BN, boxes);
+      epilogue_tile<BN, kAct, kShare, kIssuers>(ep, tmem_base + buf * kIssuers * BN, quarter, part, lane, tm * kTileM, tn * BN,
+                                                boxes);
     }
     tcgen05_fence_before_sync();
     __syncwarp();
@@ -570,6 +593,8 @@ constexpr int kTmaThreads = 6 * 32;
 // it exposed when a CTA has a single tile. Eight warps halve the chunks per warp.
 constexpr int kTileEpilogueShare = 2;
 constexpr int kTileThreads = (2 + 4 * kTileEpilogueShare) * 32;
+// The tile kernels with two MMA issuers (mma_role) add one warp for the second.
+constexpr int kTileThreadsTwoIssuers = kTileThreads + 32;
 
 // ------------------------------------------------------------- host-side helpers
 
