@@ -96,7 +96,9 @@ __device__ __forceinline__ void send_chunk(const uint32_t (&cur)[32], int chunk,
   }
 }
 
-template <int kCols>
+// With kAccumulators == 2 the partial row is the sum of two accumulators kCols columns apart (two
+// MMA issuers, see mma_role in tf32_umma.cuh).
+template <int kCols, int kAccumulators = 1>
 __device__ __forceinline__ void send_partial_row(uint32_t tmem_row, bool have_acc, uint32_t exchange_addr, int my_slice,
                                                  int quads_log2, int rank_stride, int rank_offset, int row_in_tile) {
   constexpr int kChunks = kCols / 32;
@@ -113,11 +115,13 @@ __device__ __forceinline__ void send_partial_row(uint32_t tmem_row, bool have_ac
   for (int chunk = 0; chunk < kChunks; chunk += 2) {
     if (have_acc) {
       tmem_ld_wait();
+      if constexpr (kAccumulators == 2) add_partial_accumulator(even, tmem_row + kCols + chunk * 32);
       tmem_ld_32x32(tmem_row + (chunk + 1) * 32, odd);
     }
     send_chunk(even, chunk, exchange_addr, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
     if (have_acc) {
       tmem_ld_wait();
+      if constexpr (kAccumulators == 2) add_partial_accumulator(odd, tmem_row + kCols + (chunk + 1) * 32);
       if (chunk + 2 < kChunks) tmem_ld_32x32(tmem_row + (chunk + 2) * 32, even);
     }
     send_chunk(odd, chunk + 1, exchange_addr, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
@@ -249,9 +253,20 @@ __device__ __forceinline__ void exchange_finish_interior(const EpilogueArgs& p, 
 
 // STAGES counts 32-wide K blocks of shared memory; KSUB of them form one pipeline stage (two when
 // the CTA has its SM to itself and the ring can be twice as large: one barrier round trip per 64 of K).
+// With two sub-blocks per stage (the CTA has its SM to itself) two threads issue the MMAs, one
+// sub-block and one accumulator each (mma_role in tf32_umma.cuh says why); the second one's warp is
+// the kernel's seventh.
+template <int STAGES, int KSUB>
+__host__ __device__ constexpr int splitk_issuers() { return KSUB == 2 ? 2 : 1; }
+template <int STAGES, int KSUB>
+__host__ __device__ constexpr int splitk_threads() { return kTmaThreads + (splitk_issuers<STAGES, KSUB>() - 1) * 32; }
+
 template <int STAGES, int kAct, int KSUB = 1>
-__global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __grid_constant__ UmmaParams p) {
+__global__ void __launch_bounds__(splitk_threads<STAGES, KSUB>(), KSUB == 2 ? 1 : 2)
+    umma_splitk_kernel(const __grid_constant__ UmmaParams p) {
   constexpr int BN = kSplitN;
+  constexpr int kIssuers = splitk_issuers<STAGES, KSUB>();
+  constexpr int kThreads = splitk_threads<STAGES, KSUB>();
   static_assert(STAGES % KSUB == 0, "whole stages");
   constexpr int kRing = STAGES / KSUB;
   static_assert(static_cast<size_t>(STAGES) * stage_bytes<BN>() >= sizeof(float4) * kExchangePitch * (BN / 4),
@@ -267,13 +282,13 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&sm.full[s], 1);
-      mbar_init(&sm.empty[s], 1);
+      mbar_init(&sm.empty[s], empty_barrier_arrivals<KSUB, kIssuers>());   // one commit per MMA issuer of the stage
     }
-    mbar_init(&sm.acc_full[0], 1);
+    mbar_init(&sm.acc_full[0], kIssuers);
     mbar_init_fence();
   }
   if (warp == 1) {
-    tmem_alloc<BN>(sm.tmem_ptr);
+    tmem_alloc<kIssuers * BN>(sm.tmem_ptr);
     tmem_relinquish();
   }
   tcgen05_fence_before_sync();
@@ -320,8 +335,9 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
         if (++stage == kRing) stage = 0, phase ^= 1u;
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == kTmaThreads / 32) {   // (the second issuer's warp exists only with two issuers)
     if (lane == 0 && has_work) {
+      const int issuer = warp == 1 ? 0 : 1;
       const SubBlockDescs ring = sub_block_descs(smem_u32(sm.stages));   // of the ring's first sub-block
       int stage = 0;
       uint32_t phase = 0;
@@ -330,12 +346,12 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
         if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { fed = false; break; }
         tcgen05_fence_after_sync();
 #pragma unroll
-        for (int sub = 0; sub < KSUB; ++sub) {
-          const uint32_t offset = static_cast<uint32_t>(stage * KSUB + sub) * stage_bytes<BN>();
+        for (int sub = 0; sub < KSUB; sub += kIssuers) {
+          const uint32_t offset = static_cast<uint32_t>(stage * KSUB + sub + issuer) * stage_bytes<BN>();
           const SubBlockDescs descs{umma_desc_advance(ring.a, offset), umma_desc_advance(ring.b, offset)};
-          issue_stage_mmas<BN>(tmem_base, descs, (kb > kb_begin || sub > 0) ? 1u : 0u);
+          issue_stage_mmas<BN>(tmem_base + issuer * BN, descs, (kb > kb_begin || sub > 0) ? 1u : 0u);
         }
-        umma_commit(&sm.empty[stage]);
+        umma_commit(&sm.empty[stage]);   // one arrival per issuer
         if (++stage == kRing) stage = 0, phase ^= 1u;
       }
       if (fed) umma_commit(&sm.acc_full[0]);
@@ -368,13 +384,13 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
   const int col_base = tn * BN + rank * width;
   const bool interior = args.vector_io && args.bias == nullptr && args.peers.count == 0 && (tm + 1) * kTileM <= p.m &&
                         col_base + width <= p.n;
-  InteriorCursor cursor = interior_cursor(args, exchange, quads_log2, tm * kTileM, col_base, threadIdx.x, kTmaThreads);
+  InteriorCursor cursor = interior_cursor(args, exchange, quads_log2, tm * kTileM, col_base, threadIdx.x, kThreads);
   float4 first_sources[kInteriorBatch];
   if (interior) interior_sources(cursor, 0, first_sources);
-  if (warp >= 2 && warp_rows) {
+  if (warp >= 2 && warp < kTmaThreads / 32 && warp_rows) {
     // 2. Send this CTA's partial row, W columns to each CTA.
-    send_partial_row<BN>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), has_work && ok, smem_u32(exchange), rank,
-                         quads_log2, 1, 0, row_in_tile);
+    send_partial_row<BN, kIssuers>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), has_work && ok, smem_u32(exchange),
+                                   rank, quads_log2, 1, 0, row_in_tile);
   }
   B200_PROBE(p, 4);
   tcgen05_fence_before_sync();
@@ -385,14 +401,14 @@ __global__ void __launch_bounds__(kTmaThreads, 2) umma_splitk_kernel(const __gri
   if (interior) {
     exchange_finish_interior<kAct>(args, cursor, first_sources, ranks, quads_log2);
   } else {
-    exchange_finish<kAct>(args, exchange, ranks, quads_log2, tm * kTileM, col_base, threadIdx.x, kTmaThreads);
+    exchange_finish<kAct>(args, exchange, ranks, quads_log2, tm * kTileM, col_base, threadIdx.x, kThreads);
   }
 
   B200_PROBE(p, 6);
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after_sync();
-    tmem_dealloc<BN>(tmem_base);
+    tmem_dealloc<kIssuers * BN>(tmem_base);
   }
 }
 
@@ -636,22 +652,22 @@ int splitk_max_clusters(int cluster_size) {
 
 // Cluster size of the split-K kernel, from a cost model fitted to timings of the kernel on a B200
 // (microseconds, graph-timed, with a source and ReLU). With f the fraction of the tile's 128 rows
-// that exist, a 32-wide K block costs 0.15 + 0.09 f when the CTA has its SM to itself and runs two
-// sub-blocks per stage, 0.26 + 0.04 f when the grid fits one CTA per SM but its clusters only fit
-// the device at two (single-block stages), and 0.36 + 0.06 f per CTA when two share an SM. Most of
-// it is the MMA thread's instruction stream and barrier round trips; with single-block stages a
-// deeper ring changes nothing. Launch, pipeline fill, barriers, exchange and the finishing pass cost
-// 4.7 unsplit and 6.0 / 8.0 / 9.5 for clusters of 2 / 4 / 8 when few rows exist, 8.2 / 10.5 / 11.4 when
-// all 128 do (interpolated by the row count). Fitted to: 1024 x 1024 x K split in two 12.0 / 15.8 us
-// at K = 1024 / 2048, in four 25.0 / 39.7 at K = 4096 / 8192; 512 x 512 x 2048 in eight 13.3;
-// 768 x 768 x 4096 in four 20.7; 1280 x 1280 x 8192 in two 60.4. A candidate must keep two K blocks
-// per range and fit the device in one wave (two CTAs per SM: twice the cluster count the occupancy
-// query reports for one). `estimate_us` receives the modelled time of the choice.
+// that exist, a 32-wide K block costs 0.14 + 0.07 f when the CTA has its SM to itself and runs two
+// sub-blocks per stage (one per MMA issuer), 0.26 + 0.04 f when the grid fits one CTA per SM but
+// its clusters only fit the device at two (single-block stages), and 0.36 + 0.06 f per CTA when two
+// share an SM. Launch, pipeline fill, barriers, exchange and the finishing pass cost 6.0 / 6.0 / 8.0 /
+// 9.5 for clusters of 1 / 2 / 4 / 8 when few rows exist, 8.0 / 8.2 / 10.5 / 11.4 when all 128 do
+// (interpolated by the row count; a cluster of one still runs the exchange through its own
+// shared memory). Fitted to: 1024 x 1024 x K split in two 11.5 / 14.4 / 20.5 / 38.7 us at
+// K = 1024 / 2048 / 4096 / 8192, in four 39.8 at 8192; 512 x 512 x 2048 in eight 10.8; 768 x 768 x 4096
+// in four 20.8; 64 x 4096 x 4096 in four 15.1; 1280 x 1280 x 8192 in two 60.5. A candidate must keep two
+// K blocks per range and fit the device in one wave (two CTAs per SM: twice the cluster count the
+// occupancy query reports for one). `estimate_us` receives the modelled time of the choice.
 int splitk_ranks(const b200_gemm_problem& q, int sms, float* estimate_us = nullptr) {
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
-  constexpr float kExchangeFewRows[4] = {4.7f, 6.0f, 8.0f, 9.5f};
-  constexpr float kExchangeAllRows[4] = {4.7f, 8.2f, 10.5f, 11.4f};
+  constexpr float kExchangeFewRows[4] = {6.0f, 6.0f, 8.0f, 9.5f};
+  constexpr float kExchangeAllRows[4] = {8.0f, 8.2f, 10.5f, 11.4f};
   const float row_fraction = static_cast<float>(q.m < kTileM ? q.m : kTileM) / kTileM;
   int best = 1;
   float best_us = 1e30f;
@@ -664,7 +680,7 @@ int splitk_ranks(const b200_gemm_problem& q, int sms, float* estimate_us = nullp
     const bool deep = !shared_sm && (ranks == 1 || tiles <= splitk_max_clusters(ranks));   // as launch_splitk_for decides
     const float exchange = kExchangeFewRows[log2r] + row_fraction * (kExchangeAllRows[log2r] - kExchangeFewRows[log2r]);
     const float per_block = shared_sm ? 0.36f + 0.06f * row_fraction
-                                      : (deep ? 0.15f + 0.09f * row_fraction : 0.26f + 0.04f * row_fraction);
+                                      : (deep ? 0.14f + 0.07f * row_fraction : 0.26f + 0.04f * row_fraction);
     const float us = static_cast<float>((k_blocks + ranks - 1) / ranks) * per_block + exchange;
     if (us < best_us) best_us = us, best = ranks;
   }
@@ -694,7 +710,7 @@ int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStre
   if (tiles * ranks > 0x7fffffffLL) return B200_ERR_INVALID_PROBLEM;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(tiles * ranks));
-  cfg.blockDim = dim3(kTmaThreads);
+  cfg.blockDim = dim3(splitk_threads<STAGES, KSUB>());
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr;
@@ -777,6 +793,8 @@ int launch_splitk_for(const b200_gemm_problem& q, const PeerOutputs& peers, cuda
   const int ranks = splitk_ranks(q, sms);
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + kSplitN - 1) / kSplitN);
   const bool alone = tiles * ranks <= sms && (ranks == 1 || tiles <= splitk_max_clusters(ranks));
+  // (Single-block stages taken in turn by the two issuers, as in the 128 x 128 tile kernel for long
+  // K, were tried here too: no faster, 39.7 against 38.7 us at 1024 x 1024 x 8192 in two ranges.)
   return alone ? launch_splitk<6, kAct, 2>(q, peers, stream) : launch_splitk<3, kAct, 1>(q, peers, stream);
 }
 

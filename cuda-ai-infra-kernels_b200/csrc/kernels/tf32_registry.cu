@@ -117,19 +117,19 @@ bool gate_pair(const b200_gemm_problem& q, int sms) {
 bool gate_skinny(const b200_gemm_problem& q, int) { return q.m <= 4; }
 // Split K when the split-K kernel's model predicts a shorter run than the unsplit tile kernels. Those
 // take, graph-timed with a source and ReLU, about 0.136 us per 32-wide K block on top of 5.4 us
-// (128 x 64 tiles, when they fit the SMs in one round: 1024 x 1024 x K 9.8 / 14.2 / 22.8 us at
-// K = 1024 / 2048 / 4096) or 0.235 us on top of 4.8 us (128 x 128: 1536^3 15.8, 512 x 4096 x 4096 35.8,
-// 1280 x 1280 x 8192 65.3). Split against unsplit, measured: 1024 x 1024 x 4096 22.1 / 22.8 us,
-// 512 x 512 x 2048 14.0 / 15.3 (before the second MMA issuer), 768 x 768 x 4096 21.0 / 25.8 (before),
-// 64 x 4096 x 4096 15.3 / 25.9, 1280 x 1280 x 8192 60.4 / 65.3; unsplit is ahead at 1024^3 (9.8 against
-// 11.7), 1024 x 1024 x 2048 (14.2 / 15.1), 1536^3 (15.8 / 20.1), 512 x 4096 x 4096 (35.8 / 38.8), 512^3
-// and 768^3.
+// (128 x 64 tiles, when they fit the SMs in one round: 1024 x 1024 x K 9.8 / 14.2 / 22.8 / 41.5 us at
+// K = 1024 / 2048 / 4096 / 8192) or 0.22 us on top of 5.2 us (128 x 128: 1536^3 15.8, 512 x 4096 x 4096
+// 34.4, 1280 x 1280 x 8192 60.6). Split against unsplit, measured: 1024 x 1024 x 4096 20.5 / 22.8 us,
+// 1024 x 1024 x 8192 38.7 / 41.5, 1024 x 1024 x 16384 72.2 / 92.2, 512 x 512 x 2048 10.8 / 13.4,
+// 768 x 768 x 4096 20.8 / 22.0, 768 x 768 x 8192 30.8 / 40.5, 64 x 4096 x 4096 15.1 / 22.1; unsplit is
+// ahead at 1024^3 (9.8 against 11.5), 1536^3 (15.8 / 18.6), 512 x 4096 x 4096 (34.4 / 40.0), 512^3 and
+// 768^3, and level at 1024 x 1024 x 2048, 256 x 4096 x 4096 and 1280 x 1280 x 8192.
 bool gate_splitk(const b200_gemm_problem& q, int sms) {
   float split_us = 0.f;
   if (tf32_splitk_plan(q, sms, &split_us) < 2) return false;
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
   const bool narrow = tiles_of(q, 64) <= sms;
-  const float unsplit_us = static_cast<float>(k_blocks) * (narrow ? 0.136f : 0.235f) + (narrow ? 5.4f : 4.8f);
+  const float unsplit_us = static_cast<float>(k_blocks) * (narrow ? 0.136f : 0.22f) + (narrow ? 5.4f : 5.2f);
   return split_us + 1.0f < unsplit_us;   // near ties go to the simpler kernel
 }
 // Measured against the split-K tile kernel: ahead up to 16 rows (16 x 8192 x 1024: 11.7 vs 16.5 us,

@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(kIssuers == 2 ? kTileThreadsTwoIssuers : kTile
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&sm.full[s], 1);
-      mbar_init(&sm.empty[s], kIssuers);   // one commit per MMA issuer
+      mbar_init(&sm.empty[s], empty_barrier_arrivals<KSUB, kIssuers>());   // one commit per MMA issuer of the stage
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.acc_full[b], kIssuers);
@@ -49,7 +49,8 @@ __global__ void __launch_bounds__(kIssuers == 2 ? kTileThreadsTwoIssuers : kTile
   const int tiles_m = (p.m + kTileM - 1) / kTileM;
   const int tiles_n = (p.n + BN - 1) / BN;
   const int tiles = tiles_m * tiles_n;
-  const int k_blocks = (p.k + KSUB * kStageK - 1) / (KSUB * kStageK);   // stages per tile; K past the end reads as zeros
+  int k_blocks = (p.k + KSUB * kStageK - 1) / (KSUB * kStageK);   // stages per tile; K past the end reads as zeros
+  if constexpr (kIssuers == 2 && KSUB == 1) k_blocks = (k_blocks + 1) & ~1;   // issuers take alternate stages (mma_role)
 
   if (warp == 0) {
     if (lane == 0) {
@@ -274,22 +275,11 @@ __global__ void __launch_bounds__(kGenericThreads, 1) umma_generic_kernel(const 
 }
 // ------------------------------------------------------------------ launchers
 
-template <int BN, int STAGES, int kAct>
-int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
-  // K sub-blocks per pipeline stage. An MMA thread pays about 300 cycles per stage (barrier wait,
-  // fence, commit) next to 58 per instruction, so the 128 x 64 and 128 x 128 tiles put two sub-blocks
-  // behind one pair of barriers and give each to its own issuing thread (kIssuers below); the ring
-  // must still hold three or four such stages to cover the load latency. Measured on a B200 with one
-  // issuer, unsplit, with a source: 128 x 128 at 1280 x 1280 x 8192 took 97 us with 2 stages of 2,
-  // 72 us with 3 of 2, 81 us with 2 of 3, 84 us with 6 of 1; 128 x 64 at 1024 x 1024 x 4096 took 35.4 us
-  // with 4 stages of 2 and 29.4 us with 2 of 4 - with two issuers 22.8 us with 4 of 2 against 26.2 with
-  // 2 of 4 (graph-timed). The 128 x 256 tile (134 cycles of tensor pipe per instruction: the pipe, not
-  // the thread, is its limit) is slower with two sub-blocks per stage (2048 x 2048 x 8192: 129-140
-  // against 107-122 us): only two stages fit.
-  constexpr int KSUB = (BN <= 128 && STAGES % 2 == 0 && STAGES >= 4) ? 2 : 1;
+template <int BN, int STAGES, int kAct, int KSUB>
+int launch_tma_with(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   // Two MMA issuers (mma_role) wherever a stage has sub-blocks to share out and the tile leaves
   // TMEM for a second accumulator: the 128 x 64 and 128 x 128 tiles.
-  constexpr int kIssuers = (BN <= 128 && KSUB % 2 == 0) ? 2 : 1;
+  constexpr int kIssuers = (BN <= 128 && (KSUB % 2 == 0 || STAGES % 2 == 0)) ? 2 : 1;
   auto kernel = umma_tma_kernel<BN, STAGES, kAct, KSUB, kIssuers>;
   constexpr size_t smem = smem_bytes<BN, STAGES>();
   if (!ensure_dynamic_smem<umma_tma_kernel<BN, STAGES, kAct, KSUB, kIssuers>, smem>()) return B200_ERR_LAUNCH_FAILED;
@@ -313,6 +303,30 @@ int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
   kernel<<<grid, kIssuers == 2 ? kTileThreadsTwoIssuers : kTileThreads, launch_smem, stream>>>(p);
   return launch_status();
+}
+
+template <int BN, int STAGES, int kAct>
+int launch_tma(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  // K sub-blocks per pipeline stage. An MMA thread pays about 300 cycles per stage (barrier wait,
+  // fence, commit) next to 58 per instruction, so the 128 x 64 and 128 x 128 tiles put two sub-blocks
+  // behind one pair of barriers and give each to its own issuing thread (kIssuers below); the ring
+  // must still hold three or four such stages to cover the load latency. Measured on a B200 with one
+  // issuer, unsplit, with a source: 128 x 128 at 1280 x 1280 x 8192 took 97 us with 2 stages of 2,
+  // 72 us with 3 of 2, 81 us with 2 of 3, 84 us with 6 of 1; 128 x 64 at 1024 x 1024 x 4096 took 35.4 us
+  // with 4 stages of 2 and 29.4 us with 2 of 4 - with two issuers 22.8 us with 4 of 2 against 26.2 with
+  // 2 of 4 (graph-timed). The 128 x 256 tile (134 cycles of tensor pipe per instruction: the pipe, not
+  // the thread, is its limit) is slower with two sub-blocks per stage (2048 x 2048 x 8192: 129-140
+  // against 107-122 us): only two stages fit.
+  // With two issuers the 128 x 128 tile has two forms: two sub-blocks per stage, one per issuer
+  // (three stages), or single-block stages that the issuers take in turn (six stages: more bytes in
+  // flight, 0.21 instead of 0.235 us per K block, but 0.6 us more to get going). Graph-timed with a
+  // source and ReLU: 1536^3 15.8 against 16.4 us, 512 x 4096 x 4096 35.8 / 33.8, 1280 x 1280 x 8192
+  // 65.9 / 60.8.
+  if constexpr (BN == 128 && STAGES == 6) {
+    if (q.k > 2560) return launch_tma_with<BN, STAGES, kAct, 1>(q, peers, stream);
+  }
+  constexpr int KSUB = (BN <= 128 && STAGES % 2 == 0 && STAGES >= 4) ? 2 : 1;
+  return launch_tma_with<BN, STAGES, kAct, KSUB>(q, peers, stream);
 }
 
 template <int BN, int STAGES, int kAct>

@@ -500,21 +500,33 @@ __device__ __forceinline__ SmemCarve carve(uint8_t* raw) {
 // then consumes the operand ring stage by stage.
 // `KSUB` 32-wide K sub-blocks share one pipeline stage (one barrier wait, one commit): the ring has
 // STAGES / KSUB stages, and `k_blocks` counts stages.
-// With kIssuers == 2 two threads (of different warps) run this role side by side: issuer i takes
-// the sub-blocks i, i + 2, ... of every stage and accumulates them into its own accumulator
-// (columns [i BN, (i + 1) BN) of the buffer), the epilogue adds the two. An issuing thread is alone
-// on its scheduler; the tensor pipe takes an MMA only when it has room, so the pipe stands idle
-// while its only issuer waits on a barrier or commits (about 300 of the 820 cycles of a
-// 128 x 128 stage, and a 128 x 64 MMA costs the thread the same 58 cycles as a 128 x 128 one for
-// half the pipe time). Two issuers fill each other's gaps. They must not share an accumulator:
-// MMAs of different threads are not ordered with respect to each other.
+// With kIssuers == 2 two threads (of different warps) run this role side by side, each with its own
+// accumulator (columns [i BN, (i + 1) BN) of the buffer; the epilogue adds the two):
+//   KSUB even: issuer i takes the sub-blocks i, i + 2, ... of every stage, both commit every stage
+//              (`empty` barriers count two arrivals);
+//   KSUB == 1: issuer i takes the stages i, i + 2, ... of the ring (an even number of stages, and the
+//              caller passes an even `k_blocks`, padding K with a block that reads as zeros, so that
+//              the assignment is the same for every tile), one commit per stage.
+// An issuing thread is alone on its scheduler; the tensor pipe takes an MMA only when it has room,
+// so the pipe stands idle while its only issuer waits on a barrier or commits (about 300 of the 820
+// cycles of a 128 x 128 stage of two sub-blocks, and a 128 x 64 MMA costs the thread the same 58
+// cycles as a 128 x 128 one for half the pipe time). Two issuers fill each other's gaps. They must
+// not share an accumulator: MMAs of different threads are not ordered with respect to each other.
+template <int KSUB, int kIssuers>
+__host__ __device__ constexpr int empty_barrier_arrivals() {
+  return (kIssuers == 2 && KSUB > 1) ? 2 : 1;
+}
+
 template <int BN, int STAGES, int KSUB = 1, int kIssuers = 1>
 __device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base, int tiles, int k_blocks, int issuer = 0) {
   static_assert(STAGES % KSUB == 0, "whole stages");
-  static_assert(kIssuers == 1 || (kIssuers == 2 && KSUB % 2 == 0), "every issuer has sub-blocks in every stage");
+  static_assert(kIssuers == 1 || (kIssuers == 2 && (KSUB % 2 == 0 || (KSUB == 1 && STAGES % 2 == 0))),
+                "every issuer has work in every stage, or every other stage");
   constexpr int kRing = STAGES / KSUB;
+  constexpr bool kAlternate = kIssuers == 2 && KSUB == 1;   // issuers take alternate stages
+  constexpr int kStep = kAlternate ? 2 : 1;
   const SubBlockDescs ring = sub_block_descs(smem_u32(sm.stages));   // of the ring's first sub-block
-  int stage = 0;
+  int stage = kAlternate ? issuer : 0;
   uint32_t phase = 0;
   bool ok = true;
   int local = 0;
@@ -525,18 +537,20 @@ __device__ __forceinline__ void mma_role(const SmemCarve& sm, uint32_t tmem_base
     if (!mbar_wait(&sm.acc_empty[buf], use_parity ^ 1u, kSiteUmmaAccEmpty)) { ok = false; break; }
     tcgen05_fence_after_sync();
     const uint32_t tmem_acc = tmem_base + (buf * kIssuers + issuer) * BN;
-    for (int kb = 0; kb < k_blocks; ++kb) {
+    const int kb_first = kAlternate ? issuer : 0;
+    for (int kb = kb_first; kb < k_blocks; kb += kStep) {
       if (!mbar_wait(&sm.full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
-      const uint32_t stage_offset = static_cast<uint32_t>(stage * KSUB + issuer) * stage_bytes<BN>();
+      const uint32_t stage_offset = static_cast<uint32_t>(stage * KSUB + (kAlternate ? 0 : issuer)) * stage_bytes<BN>();
 #pragma unroll
-      for (int sub = 0; sub < KSUB; sub += kIssuers) {
+      for (int sub = 0; sub < KSUB; sub += (kAlternate ? 1 : kIssuers)) {
         const SubBlockDescs descs{umma_desc_advance(ring.a, stage_offset + sub * stage_bytes<BN>()),
                                   umma_desc_advance(ring.b, stage_offset + sub * stage_bytes<BN>())};
-        issue_stage_mmas<BN>(tmem_acc, descs, (kb > 0 || sub > 0) ? 1u : 0u);
+        issue_stage_mmas<BN>(tmem_acc, descs, (kb > kb_first || sub > 0) ? 1u : 0u);
       }
-      umma_commit(&sm.empty[stage]);  // stage reusable once these MMAs have read it (one arrival per issuer)
-      if (++stage == kRing) stage = 0, phase ^= 1u;
+      umma_commit(&sm.empty[stage]);  // stage reusable once these MMAs have read it
+      stage += kStep;
+      if (stage >= kRing) stage -= kRing, phase ^= 1u;
     }
     if (ok) umma_commit(&sm.acc_full[buf]);   // one arrival per issuer
   }
