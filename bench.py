@@ -801,8 +801,16 @@ def main() -> None:
     # The host link is shared with whatever else runs on the box (one run in a dozen was seen at half
     # its usual rate for a fraction of a second), so the 40-step region is timed five times and the
     # median is reported, with all five beside it.
+    # With several ranks the first hundred or so steps run slower (four ranks: 9.0, 6.3, 4.4, 3.8,
+    # 3.7 ms per step over five repeats after a four-step warm-up; one rank shows no such ramp), so the
+    # warm-up there is two untimed repeats.
     e2e_steps = max(args.steps, 40)
-    e2e_run(4)
+    if distributed:
+        for _ in range(2):
+            dist.barrier()
+            e2e_run(e2e_steps)
+    else:
+        e2e_run(4)
     e2e_samples = []
     for _ in range(5):
         if distributed:
