@@ -280,6 +280,8 @@ __global__ void __launch_bounds__(splitk_threads<STAGES, KSUB>(), KSUB == 2 ? 1 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    prefetch_tensormap(&p.map_a);   // first of all: the fetch is part of the first load's latency
+    prefetch_tensormap(p.b_strips == BN / 32 ? &p.map_b_strips : &p.map_b);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], empty_barrier_arrivals<KSUB, kIssuers>());   // one commit per MMA issuer of the stage
@@ -310,8 +312,6 @@ __global__ void __launch_bounds__(splitk_threads<STAGES, KSUB>(), KSUB == 2 ? 1 
 
   if (warp == 0) {
     if (lane == 0) {
-      prefetch_tensormap(&p.map_a);
-      prefetch_tensormap(p.b_strips == BN / 32 ? &p.map_b_strips : &p.map_b);
       int stage = 0;
       uint32_t phase = 0;
       for (int kb = kb_begin; kb < kb_end; ++kb) {

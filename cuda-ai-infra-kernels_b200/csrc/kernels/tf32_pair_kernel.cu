@@ -58,6 +58,12 @@ __global__ void __launch_bounds__(kTileThreads, 1) umma_pair_kernel(const __grid
   const uint32_t rank = cluster_cta_rank();  // 0: issues the MMAs, 1: peer
 
   if (threadIdx.x == 0) {
+    // The descriptors the copies will name, requested first of all (their fetch is part of the
+    // latency of the first load and of the first store).
+    prefetch_tensormap(&p.map_a);
+    prefetch_tensormap(&p.map_b);
+    if (p.b_strips == kPairN / 2 / 32) prefetch_tensormap(&p.map_b_strips);
+    if (p.tma_store != 0) prefetch_tensormap(&p.map_d);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);   // used in CTA 0 only: one expect_tx arrival, bytes of both CTAs
       mbar_init(&empty[s], 1);  // one tcgen05.commit per use, sent to each CTA
@@ -87,8 +93,6 @@ __global__ void __launch_bounds__(kTileThreads, 1) umma_pair_kernel(const __grid
 
   if (warp == 0) {
     if (lane == 0) {
-      prefetch_tensormap(&p.map_a);
-      prefetch_tensormap(&p.map_b);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -203,7 +207,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) umma_pair_kernel(const __grid
       // The MMA issuer (CTA 0) waits for the epilogues of both CTAs.
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
     }
-    if (boxed && lane == 0) tma_store_wait_all<0>();   // every store has left shared memory and landed
+    if (boxed && lane == 0) tma_store_wait_read<0>();   // every store has read its box (the writes land before the grid completes)
   }
 
   tcgen05_fence_before_sync();

@@ -26,6 +26,11 @@ __global__ void __launch_bounds__(kIssuers == 2 ? kTileThreadsTwoIssuers : kTile
   B200_PROBE(p, 0);
 
   if (threadIdx.x == 0) {
+    // The descriptors the copies will name, requested first of all: their fetch is part of the
+    // latency of the first load (and of the first store, which nothing hides).
+    prefetch_tensormap(&p.map_a);
+    prefetch_tensormap(p.b_strips == BN / 32 ? &p.map_b_strips : &p.map_b);
+    if (p.tma_store != 0) prefetch_tensormap(&p.map_d);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], empty_barrier_arrivals<KSUB, kIssuers>());   // one commit per MMA issuer of the stage
@@ -54,8 +59,6 @@ __global__ void __launch_bounds__(kIssuers == 2 ? kTileThreadsTwoIssuers : kTile
 
   if (warp == 0) {
     if (lane == 0) {
-      prefetch_tensormap(&p.map_a);
-      prefetch_tensormap(&p.map_b);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;

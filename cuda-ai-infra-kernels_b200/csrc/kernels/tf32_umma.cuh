@@ -591,7 +591,7 @@ __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCar
     if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
     B200_PROBE(p, 4);
   }
-  if (boxed && lane == 0) tma_store_wait_all<0>();   // every store has left shared memory and landed
+  if (boxed && lane == 0) tma_store_wait_read<0>();   // every store has read its box (the writes land before the grid completes)
   B200_PROBE(p, 5);
 }
 
