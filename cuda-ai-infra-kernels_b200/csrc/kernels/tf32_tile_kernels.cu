@@ -11,11 +11,12 @@ namespace {
 
 // ------------------------------------------------------- TMA, persistent kernel
 // warp 0: TMA producer (one lane)      warp 1: TMEM owner + MMA issuer (one lane)
-// warps 2-5: epilogue; warp w reads the TMEM lane quarter w % 4.
+// warps 2-9: epilogue; warp w reads the TMEM lane quarter w % 4, two warps per quarter.
+// warp 10 (kIssuers == 2): the second MMA issuer (one lane).
 
-// STAGES counts 32-wide K blocks of shared memory; KSUB of them form one pipeline stage (the MMA
-// thread's barrier wait and commit cost about as much as four small MMAs, so narrow tiles, whose
-// MMAs are short, run two sub-blocks per stage).
+// STAGES counts 32-wide K blocks of shared memory; KSUB of them form one pipeline stage (an MMA
+// thread's barrier wait and commit cost about as much as five MMAs at its issue rate); kIssuers
+// threads issue the MMAs, each into its own accumulator (mma_role in tf32_umma.cuh).
 template <int BN, int STAGES, int kAct, int KSUB = 1, int kIssuers = 1>
 __global__ void __launch_bounds__(kIssuers == 2 ? kTileThreadsTwoIssuers : kTileThreads, 1)
     umma_tma_kernel(const __grid_constant__ UmmaParams p) {
