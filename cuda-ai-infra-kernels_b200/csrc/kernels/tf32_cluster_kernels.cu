@@ -97,34 +97,36 @@ __device__ __forceinline__ void send_chunk(const uint32_t (&cur)[32], int chunk,
 }
 
 // With kAccumulators == 2 the partial row is the sum of two accumulators kCols columns apart (two
-// MMA issuers, see mma_role in tf32_umma.cuh).
-template <int kCols, int kAccumulators = 1>
+// MMA issuers, see mma_role in tf32_umma.cuh). kShare warps serve each quarter of the rows; warp
+// `part` of them sends the 32-column chunks part, part + kShare, ...
+template <int kCols, int kAccumulators = 1, int kShare = 1>
 __device__ __forceinline__ void send_partial_row(uint32_t tmem_row, bool have_acc, uint32_t exchange_addr, int my_slice,
-                                                 int quads_log2, int rank_stride, int rank_offset, int row_in_tile) {
-  constexpr int kChunks = kCols / 32;
-  static_assert(kChunks % 2 == 0, "chunks are handled in pairs");
+                                                 int quads_log2, int rank_stride, int rank_offset, int row_in_tile, int part = 0) {
+  constexpr int kMine = kCols / 32 / kShare;   // chunks of this warp
+  static_assert(kMine >= 2 && kMine % 2 == 0, "chunks are handled in pairs");
   // Two register sets, named rather than indexed so that both stay in registers.
   uint32_t even[32], odd[32];
   if (have_acc) {
-    tmem_ld_32x32(tmem_row, even);
+    tmem_ld_32x32(tmem_row + part * 32, even);
   } else {
 #pragma unroll
     for (int e = 0; e < 32; ++e) even[e] = odd[e] = 0u;   // an empty K range contributes zeros
   }
 #pragma unroll
-  for (int chunk = 0; chunk < kChunks; chunk += 2) {
+  for (int i = 0; i < kMine; i += 2) {
+    const int chunk = part + i * kShare;
     if (have_acc) {
       tmem_ld_wait();
       if constexpr (kAccumulators == 2) add_partial_accumulator(even, tmem_row + kCols + chunk * 32);
-      tmem_ld_32x32(tmem_row + (chunk + 1) * 32, odd);
+      tmem_ld_32x32(tmem_row + (chunk + kShare) * 32, odd);
     }
     send_chunk(even, chunk, exchange_addr, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
     if (have_acc) {
       tmem_ld_wait();
-      if constexpr (kAccumulators == 2) add_partial_accumulator(odd, tmem_row + kCols + (chunk + 1) * 32);
-      if (chunk + 2 < kChunks) tmem_ld_32x32(tmem_row + (chunk + 2) * 32, even);
+      if constexpr (kAccumulators == 2) add_partial_accumulator(odd, tmem_row + kCols + (chunk + kShare) * 32);
+      if (i + 2 < kMine) tmem_ld_32x32(tmem_row + (chunk + 2 * kShare) * 32, even);
     }
-    send_chunk(odd, chunk + 1, exchange_addr, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
+    send_chunk(odd, chunk + kShare, exchange_addr, my_slice, quads_log2, rank_stride, rank_offset, row_in_tile);
   }
 }
 
@@ -254,19 +256,27 @@ __device__ __forceinline__ void exchange_finish_interior(const EpilogueArgs& p, 
 // STAGES counts 32-wide K blocks of shared memory; KSUB of them form one pipeline stage (two when
 // the CTA has its SM to itself and the ring can be twice as large: one barrier round trip per 64 of K).
 // With two sub-blocks per stage (the CTA has its SM to itself) two threads issue the MMAs, one
-// sub-block and one accumulator each (mma_role in tf32_umma.cuh says why); the second one's warp is
-// the kernel's seventh.
+// sub-block and one accumulator each (mma_role in tf32_umma.cuh says why), and eight warps instead
+// of four send the partial rows, two per quarter of the rows: sending and finishing are bound by
+// instructions per warp (send 2.7 k and finishing pass 2.4 k cycles with four and seven warps).
+//   warp 0 producer, warp 1 first issuer, warps 2 .. 1 + 4 share: senders, then the second issuer.
 template <int STAGES, int KSUB>
 __host__ __device__ constexpr int splitk_issuers() { return KSUB == 2 ? 2 : 1; }
 template <int STAGES, int KSUB>
-__host__ __device__ constexpr int splitk_threads() { return kTmaThreads + (splitk_issuers<STAGES, KSUB>() - 1) * 32; }
+__host__ __device__ constexpr int splitk_send_share() { return KSUB == 2 ? 2 : 1; }
+template <int STAGES, int KSUB>
+__host__ __device__ constexpr int splitk_threads() {
+  return (2 + 4 * splitk_send_share<STAGES, KSUB>() + splitk_issuers<STAGES, KSUB>() - 1) * 32;
+}
 
 template <int STAGES, int kAct, int KSUB = 1>
 __global__ void __launch_bounds__(splitk_threads<STAGES, KSUB>(), KSUB == 2 ? 1 : 2)
     umma_splitk_kernel(const __grid_constant__ UmmaParams p) {
   constexpr int BN = kSplitN;
   constexpr int kIssuers = splitk_issuers<STAGES, KSUB>();
+  constexpr int kShare = splitk_send_share<STAGES, KSUB>();
   constexpr int kThreads = splitk_threads<STAGES, KSUB>();
+  constexpr int kSecondIssuerWarp = 2 + 4 * kShare;   // exists only with two issuers
   static_assert(STAGES % KSUB == 0, "whole stages");
   constexpr int kRing = STAGES / KSUB;
   static_assert(static_cast<size_t>(STAGES) * stage_bytes<BN>() >= sizeof(float4) * kExchangePitch * (BN / 4),
@@ -335,7 +345,7 @@ __global__ void __launch_bounds__(splitk_threads<STAGES, KSUB>(), KSUB == 2 ? 1 
         if (++stage == kRing) stage = 0, phase ^= 1u;
       }
     }
-  } else if (warp == 1 || warp == kTmaThreads / 32) {   // (the second issuer's warp exists only with two issuers)
+  } else if (warp == 1 || warp == kSecondIssuerWarp) {
     if (lane == 0 && has_work) {
       const int issuer = warp == 1 ? 0 : 1;
       const SubBlockDescs ring = sub_block_descs(smem_u32(sm.stages));   // of the ring's first sub-block
@@ -387,10 +397,10 @@ __global__ void __launch_bounds__(splitk_threads<STAGES, KSUB>(), KSUB == 2 ? 1 
   InteriorCursor cursor = interior_cursor(args, exchange, quads_log2, tm * kTileM, col_base, threadIdx.x, kThreads);
   float4 first_sources[kInteriorBatch];
   if (interior) interior_sources(cursor, 0, first_sources);
-  if (warp >= 2 && warp < kTmaThreads / 32 && warp_rows) {
+  if (warp >= 2 && warp < kSecondIssuerWarp && warp_rows) {
     // 2. Send this CTA's partial row, W columns to each CTA.
-    send_partial_row<BN, kIssuers>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), has_work && ok, smem_u32(exchange),
-                                   rank, quads_log2, 1, 0, row_in_tile);
+    send_partial_row<BN, kIssuers, kShare>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), has_work && ok,
+                                           smem_u32(exchange), rank, quads_log2, 1, 0, row_in_tile, (warp - 2) >> 2);
   }
   B200_PROBE(p, 4);
   tcgen05_fence_before_sync();
