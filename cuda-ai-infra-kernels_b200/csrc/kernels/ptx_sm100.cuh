@@ -159,11 +159,6 @@ __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
-template <int N>
-__device__ __forceinline__ void tma_store_wait_all() {
-  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
-}
-
 // Orders this thread's generic-proxy writes to shared memory before later
 // async-proxy reads of it (TMA store, tcgen05.mma operand fetch).
 __device__ __forceinline__ void fence_proxy_async_smem() {
