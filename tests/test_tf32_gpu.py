@@ -477,6 +477,29 @@ def test_k_tail_inside_a_stage(abi, entry, k):
     assert_device_clean(abi)
 
 
+# ------------------------------------------------ long K: the 128 x 128 tile's issuers take stages in turn
+# Above K = 2560 the 128 x 128 tile kernel runs single-block stages that its two MMA issuers take
+# alternately, padding K to an even number of 32-wide blocks that read as zeros: an odd block
+# count (83), an even one, and a K that ends inside a block.
+
+
+@pytest.mark.parametrize("entry", [e for e in entries(align=4) if e[1] in ("fast", "fast_relu", "fast_gelu")], ids=lambda e: e[1])
+@pytest.mark.parametrize("shape", [(256, 384, 2656), (130, 200, 2600), (128, 128, 2688)])
+def test_long_k_through_alternating_issuers(abi, entry, shape):
+    kernel_id, _, epilogue, _ = entry
+    m, n, k = shape
+    g = torch.Generator().manual_seed(k + m)
+    a = torch.randint(-4, 5, (m, k), generator=g).float()
+    b = torch.randint(-4, 5, (k, n), generator=g).float()
+    c = torch.randint(-4, 5, (m, n), generator=g).float()
+    status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c.cuda(), alpha=1.0, beta=0.5, epilogue=epilogue)
+    assert status == 0, abi.b200_status_string(status)
+    expected = oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, EPILOGUE_NAME[epilogue])
+    tol = 1e-5 if epilogue == GELU else 0
+    torch.testing.assert_close(d.cpu(), expected, atol=tol, rtol=tol)
+    assert_device_clean(abi)
+
+
 # ------------------------------------------------------- error-compensated TF32 (three products)
 
 
