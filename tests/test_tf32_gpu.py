@@ -500,6 +500,34 @@ def test_long_k_through_alternating_issuers(abi, entry, shape):
     assert_device_clean(abi)
 
 
+# ------------------------------------------------ more tiles than SMs: a CTA walks several tiles
+# The persistent tile kernels hand their two accumulator buffers (each with one accumulator per MMA
+# issuer) back and forth between the issuers and the epilogue warps; with more tiles than SMs some
+# CTAs take a second tile, and its partial sums must not meet the first tile's.
+
+
+@pytest.mark.parametrize("alias,shape", [("fast", (2048, 1280, 160)), ("fast_relu", (2048, 1280, 2720)),
+                                         ("narrow", (1280, 1024, 160)), ("narrow_relu", (2560, 1024, 96)),
+                                         ("wide", (2048, 2560, 96)), ("fast_stage3", (2048, 1280, 100))])
+def test_persistent_ctas_walk_several_tiles(abi, alias, shape):
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    kernel_id = abi.b200_tf32_kernel_from_name(alias.encode())
+    assert kernel_id > 0
+    epilogue = RELU if alias.endswith("relu") else LINEAR
+    m, n, k = shape
+    tile_n = {"fast": 128, "narrow": 64, "wide": 256}[alias.split("_")[0]]
+    assert (m // 128) * (n // tile_n) > sms, "the shape must give some CTA a second tile"
+    g = torch.Generator().manual_seed(m + k)
+    a = torch.randint(-4, 5, (m, k), generator=g).float()
+    b = torch.randint(-4, 5, (k, n), generator=g).float()
+    c = torch.randint(-4, 5, (m, n), generator=g).float()
+    status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c.cuda(), alpha=1.0, beta=0.5, epilogue=epilogue)
+    assert status == 0, abi.b200_status_string(status)
+    expected = oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, EPILOGUE_NAME[epilogue])
+    torch.testing.assert_close(d.cpu(), expected, atol=0, rtol=0)
+    assert_device_clean(abi)
+
+
 # ------------------------------------------------------- error-compensated TF32 (three products)
 
 
