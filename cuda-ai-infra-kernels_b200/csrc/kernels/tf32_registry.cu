@@ -97,11 +97,14 @@ int64_t tiles_of(const b200_gemm_problem& q, int tile_n) {
 }
 
 bool gate_always(const b200_gemm_problem&, int) { return true; }
-// 128 x 256 tiles move a third fewer operand bytes per flop through L2, which
-// is what bounds this kernel; worth it once they occupy three quarters of the
-// SMs (measured at 2048^3: 128 tiles on 148 SMs beat both 128 x 128 tiles and
-// 64 CTA pairs).
-bool gate_wide(const b200_gemm_problem& q, int sms) { return tiles_of(q, 256) * 4 >= sms * 3; }
+// 128 x 256 tiles move a third fewer operand bytes per flop through L2 and take about 1.45 times as
+// long as a 128 x 128 tile; they pay when they save a round: measured at 2048^3 (128 tiles in one
+// round against 256 in two: 27.9 against 34.2 us, and ahead of 64 CTA pairs) and at
+// 1792 x 1792 x 2048 (98 tiles in one round against 196 in two: 27.2 against 33.7 us).
+bool gate_wide(const b200_gemm_problem& q, int sms) {
+  const int64_t rounds_128 = (tiles_of(q, 128) + sms - 1) / sms, rounds_256 = (tiles_of(q, 256) + sms - 1) / sms;
+  return 100 * rounds_128 > 145 * rounds_256;
+}
 // 128 x 64 tiles when 128-wide ones would leave more than half the SMs idle.
 // CTA pairs (256 x 256 per pair) when they fill at least one round of pairs.
 // (Half tiles filling one round, e.g. 1536^3 with 72 halves on 74 pairs, measured level with the
