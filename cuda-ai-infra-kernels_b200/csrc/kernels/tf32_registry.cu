@@ -109,9 +109,15 @@ bool gate_wide(const b200_gemm_problem& q, int sms) {
 // CTA pairs (256 x 256 per pair) when they fill at least one round of pairs.
 // (Half tiles filling one round, e.g. 1536^3 with 72 halves on 74 pairs, measured level with the
 // 128 x 128 tile kernel, 21.7 against 20.6 us, and stay a matter of the forced "pair" entry.)
+// With K of 4096 or more they are also ahead of the 128 x 256 tile kernel when they fill two thirds
+// of one round (the wide tile streams half as many bytes again per flop, and with long K that is
+// what counts): 1280 x 2560 x 4096 (50 tiles) 49.1 against 56.5 us, 1792 x 1792 x 8192 (49) 99.6 / 111.2,
+// 1024 x 4096 x 4096 (64) 57.8 / 70.5, 2048 x 2048 x 8192 (64) 96.2 / 101.1; at K = 2048 the wide tile
+// is level or ahead (1024 x 4096 x 2048 28.0 against 29, 2048^3 27.6 / 29.5).
 bool gate_pair(const b200_gemm_problem& q, int sms) {
   const int64_t tiles = static_cast<int64_t>((q.m + 255) / 256) * ((q.n + 255) / 256);
-  return tiles >= sms / 2;
+  const int64_t pairs = sms / 2;
+  return tiles >= pairs || (q.k >= 4096 && 20 * tiles >= 13 * pairs);
 }
 // Up to four rows the FP32 stream over B is the fastest entry (1 x 4096 x 4096:
 // 8.0 us against 17.1 us for the split-K tensor-core tile); from eight rows on
