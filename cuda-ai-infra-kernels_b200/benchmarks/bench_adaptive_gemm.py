@@ -1,7 +1,7 @@
 """TF32 adaptive GEMM benchmark: registry kernels vs the cuBLAS baseline.
 
     python cuda-ai-infra-kernels_b200/benchmarks/bench_adaptive_gemm.py \
-        [--sizes 1024,4096,8192 | --shape MxNxK] [--kernel all|auto|fast|...] [--epilogue linear|relu] \
+        [--sizes 1024,4096,8192 | --shape MxNxK[,MxNxK...]] [--kernel all|auto|fast|...[,...]] [--epilogue linear|relu] \
         [--alpha 1.0] [--beta 0.5] [--timing graph|event] [--warmup 10] [--repeat 50] [--output FILE] [--profile]
 
 Follows the reference's benchmarks/bench_adaptive_gemm.py: each kernel is
@@ -9,7 +9,9 @@ checked first (here against the FP64 result computed on the device: relative
 Frobenius error <= 5e-3, plus the reference's atol = rtol = 3e-2 scaled by
 sqrt(K) for long reductions), then timed. With `--epilogue relu` the cuBLAS
 baseline is cuBLAS + a separate `torch.relu_` (`fused_relu: false`), as in the
-reference (:14-54). `--profile` runs one NVTX-ranged call per kernel and saves
+reference (:14-54); `cublaslt` is cuBLASLt with the ReLU (and bias) fused into its
+epilogue, the fair competitor of the fused kernels. `--kernel auto,cublaslt` with a list of shapes
+gives the sweep of automatic dispatch against the library. `--profile` runs one NVTX-ranged call per kernel and saves
 nothing. Throughput = 2*M*N*K / median time; the tensor roofline uses half the
 measured BF16 peak of MEASURED_PEAKS.json when that file is present.
 """
@@ -30,10 +32,11 @@ from cuda_ai_kernels.benchmark import cuda_event_benchmark, cuda_graph_benchmark
 from cuda_ai_kernels.env import collect_env  # noqa: E402
 
 # "skinny*" runs only M <= 16 and is reported as skipped elsewhere.
-LINEAR_KERNELS = ["auto", "skinny", "swap", "splitk", "pair", "wide", "narrow", "fast", "fallback", "fast_mwarp", "fallback_mwarp",
-                  "fast_stage3", "fast_stage2", "cublas"]
-RELU_KERNELS = ["auto", "skinny_relu", "swap_relu", "splitk_relu", "pair_relu", "wide_relu", "narrow_relu", "fast_relu", "fallback_relu", "cublas"]
-GELU_KERNELS = ["auto", "skinny_gelu", "swap_gelu", "splitk_gelu", "pair_gelu", "wide_gelu", "narrow_gelu", "fast_gelu", "fallback_gelu"]
+LINEAR_KERNELS = ["auto", "skinny", "swap", "splitk", "pair_mid", "pair", "wide", "narrow", "fast", "fallback", "fast_mwarp", "fallback_mwarp",
+                  "fast_stage3", "fast_stage2", "cublas", "cublaslt"]
+RELU_KERNELS = ["auto", "skinny_relu", "swap_relu", "splitk_relu", "pair_mid_relu", "pair_relu", "wide_relu", "narrow_relu", "fast_relu", "fallback_relu", "cublas",
+                "cublaslt"]
+GELU_KERNELS = ["auto", "skinny_gelu", "swap_gelu", "splitk_gelu", "pair_mid_gelu", "pair_gelu", "wide_gelu", "narrow_gelu", "fast_gelu", "fallback_gelu"]
 REL_FROBENIUS = 5e-3
 
 
@@ -73,7 +76,7 @@ def benchmark_problem(m: int, n: int, k: int, args) -> dict:
     elif args.epilogue == "gelu":
         expected = torch.nn.functional.gelu(expected)
     by_epilogue = {"linear": LINEAR_KERNELS, "relu": RELU_KERNELS, "gelu": GELU_KERNELS}
-    names = by_epilogue[args.epilogue] if args.kernel == "all" else [args.kernel]
+    names = by_epilogue[args.epilogue] if args.kernel == "all" else args.kernel.split(",")
     timer = cuda_graph_benchmark if args.timing == "graph" else cuda_event_benchmark
     peak, peak_source = tf32_peak_tflops()
     flops = 2.0 * m * n * k
@@ -106,9 +109,11 @@ def benchmark_problem(m: int, n: int, k: int, args) -> dict:
                      "roofline": {"bound": "tensor", "peak_tflops": peak, "peak_source": peak_source,
                                   "frac": flops / stats["p50_ms"] / 1e9 / peak}})
     base = next((r for r in rows if r["kernel"] == "cublas" and "stats" in r), None)
+    fused_base = next((r for r in rows if r["kernel"] == "cublaslt" and "stats" in r), None)
     for r in rows:
         if "stats" in r:
             r["speedup_vs_cublas"] = base["stats"]["p50_ms"] / r["stats"]["p50_ms"] if base else None
+            r["speedup_vs_cublaslt"] = fused_base["stats"]["p50_ms"] / r["stats"]["p50_ms"] if fused_base else None
     return {"m": m, "n": n, "k": k, "alpha": args.alpha, "beta": args.beta, "epilogue": args.epilogue, "results": rows}
 
 
@@ -133,7 +138,7 @@ def main(argv=None) -> dict:
         raise SystemExit("bench_adaptive_gemm.py needs a CUDA device")
     torch.manual_seed(args.seed)
     if args.shape:
-        problems = [tuple(int(v) for v in args.shape.lower().split("x"))]
+        problems = [tuple(int(v) for v in shape.split("x")) for shape in args.shape.lower().split(",")]
     else:
         problems = [(int(s),) * 3 for s in args.sizes.split(",")]
     payload = {"kernel": "adaptive_gemm", "dtype": "float32 in / TF32 multiply / FP32 accumulate", "timing": args.timing,
@@ -149,10 +154,10 @@ def main(argv=None) -> dict:
             if "skipped" in r:
                 print(f"  {r['kernel']:16} skipped: {r['skipped'][:70]}")
                 continue
-            vs = r["speedup_vs_cublas"]
+            vs, vs_lt = r["speedup_vs_cublas"], r["speedup_vs_cublaslt"]
             print(f"  {r['kernel']:16} {r['registry_name']:28} {r['stats']['p50_ms']:9.4f} ms {r['tflops_median']:8.1f} TFLOP/s "
                   f"{100 * r['roofline']['frac']:5.1f}% of peak  vs cuBLAS {(f'{vs:.2f}x' if vs else 'n/a')}  "
-                  f"rel_frob {r['correctness']['rel_frobenius']:.1e}")
+                  f"vs cuBLASLt fused {(f'{vs_lt:.2f}x' if vs_lt else 'n/a')}  rel_frob {r['correctness']['rel_frobenius']:.1e}")
     if not args.profile:
         out = args.output or f"results/raw/adaptive_gemm_{now_tag()}.json"
         save_json(out, payload)

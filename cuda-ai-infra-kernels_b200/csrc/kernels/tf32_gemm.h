@@ -19,6 +19,8 @@ cudaError_t tf32_tile_status_read_clear(uint32_t* word);
 
 // tf32_pair_kernel.cu: 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2).
 int launch_tf32_pair(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream);
+// The same on 256 x 128 tiles with two MMA issuers per pair.
+int launch_tf32_pair_mid(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream);
 cudaError_t tf32_pair_status_read_clear(uint32_t* word);
 
 // tf32_cluster_kernels.cu: K split over a thread-block cluster. `tf32_splitk_plan` is the cost model

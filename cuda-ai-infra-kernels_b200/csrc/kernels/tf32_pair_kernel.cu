@@ -218,6 +218,179 @@ __global__ void __launch_bounds__(kTileThreads, 1) umma_pair_kernel(const __grid
     tmem_dealloc_pair<512>(tmem_base);
   }
 }
+// ------------------------------------------- TMA, CTA-pair kernel, 256 x 128 tiles
+// The same machinery on 256 x 128 tiles with TWO MMA issuers (mma_role in tf32_umma.cuh says why):
+// CTA r of the pair holds rows [128 r, +128) of A and columns [64 r, +64) of B, 24 KiB per 32-wide
+// K sub-block where the single-CTA 128 x 128 tile streams 32 KiB for the same share of the product.
+// A stage holds two sub-blocks; issuer i (two threads of the even CTA) multiplies sub-block i of
+// every stage into accumulator i (128 TMEM columns each, two buffers of two: all 512 columns, which
+// is why the 256 x 256 kernel above cannot do the same) and both commit every stage to both CTAs.
+// For mid-sized problems with a long K, where the 128 x 128 tile kernel is bound by what an SM takes
+// in per K block.
+constexpr int kMidN = 128;
+constexpr uint32_t kMidSubBytes = kASlabBytes + (kMidN / 2 / 32) * kBBoxBytes;   // 24 KiB per 32 of K and CTA
+constexpr int kMidStages = 4;                                                       // of two sub-blocks: 192 KiB
+constexpr uint32_t kMidStageBytes = 2 * kMidSubBytes;
+constexpr size_t kMidSmemBytes = static_cast<size_t>(kMidStages) * kMidStageBytes + 1024 + 1024 + kStagingBytes;
+
+template <int kAct>
+__global__ void __launch_bounds__(kTileThreadsTwoIssuers, 1) umma_pair_mid_kernel(const __grid_constant__ UmmaParams p) {
+  constexpr int kIssuers = 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(kMidStages) * kMidStageBytes);
+  uint64_t* empty = full + kMidStages;
+  uint64_t* acc_full = empty + kMidStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint8_t* staging = stages + static_cast<size_t>(kMidStages) * kMidStageBytes + 1024;   // kStagingBytes
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();  // 0: issues the MMAs, 1: peer
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&p.map_a);
+    prefetch_tensormap(p.b_strips == kMidN / 2 / 32 ? &p.map_b_strips : &p.map_b);
+    if (p.tma_store != 0) prefetch_tensormap(&p.map_d);
+    for (int s = 0; s < kMidStages; ++s) {
+      mbar_init(&full[s], 1);           // used in CTA 0 only: one expect_tx arrival, bytes of both CTAs
+      mbar_init(&empty[s], kIssuers);   // one tcgen05.commit per issuer and use, sent to each CTA
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], kIssuers);
+      mbar_init(&acc_empty[b], 8 * kTileEpilogueShare);  // used in CTA 0 only: the epilogue warps of both CTAs
+    }
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair<512>(tmem_ptr);
+    tmem_relinquish_pair();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before any remote arrival
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  const int tiles_m = (p.m + 2 * kTileM - 1) / (2 * kTileM);
+  const int tiles_n = (p.n + kMidN - 1) / kMidN;
+  const int tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.k + 2 * kStageK - 1) / (2 * kStageK);   // stages per tile; K past the end reads as zeros
+  const int first_tile = blockIdx.x >> 1, tile_stride = gridDim.x >> 1;
+  constexpr int kSecondIssuerWarp = 2 + 4 * kTileEpilogueShare;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < tiles && ok; tile += tile_stride) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        const int row0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
+        const int col0 = tn * kMidN + static_cast<int>(rank) * (kMidN / 2);   // this CTA's share of the B columns
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, kSiteUmmaEmpty)) { ok = false; break; }
+          // Completion bytes of both CTAs are counted on CTA 0's barrier.
+          const uint32_t full_addr = map_to_cta(smem_u32(&full[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * kMidStageBytes);
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub) {
+            const int k0 = (kb * 2 + sub) * kStageK;
+            uint8_t* a_dst = stages + static_cast<size_t>(stage) * kMidStageBytes + sub * kMidSubBytes;
+            uint8_t* b_dst = a_dst + kASlabBytes;
+            tma_load_2d_pair(a_dst, &p.map_a, full_addr, k0, row0);
+            if (p.b_strips == kMidN / 2 / 32) {
+              tma_load_3d_pair(b_dst, &p.map_b_strips, full_addr, 0, k0, col0 / 32);
+            } else {
+#pragma unroll
+              for (int j = 0; j < kMidN / 2 / 32; ++j) {
+                tma_load_2d_pair(b_dst + j * kBBoxBytes, &p.map_b, full_addr, col0 + j * 32, k0);
+              }
+            }
+          }
+          if (++stage == kMidStages) stage = 0, phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1 || warp == kSecondIssuerWarp) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t issuer = warp == 1 ? 0u : 1u;
+      constexpr uint32_t idesc = umma_idesc_tf32(2 * kTileM, kMidN, /*a_mn_major=*/false, /*b_mn_major=*/true);
+      const SubBlockDescs ring = sub_block_descs(smem_u32(stages));   // of the ring's first sub-block
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = first_tile; tile < tiles && ok; tile += tile_stride, ++local) {
+        const int buf = local & 1;
+        const uint32_t use_parity = (local >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[buf], use_parity ^ 1u, kSiteUmmaAccEmpty)) { ok = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + (buf * kIssuers + issuer) * kMidN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, kSiteUmmaFull)) { ok = false; break; }
+          tcgen05_fence_after_sync();
+          const uint32_t offset = static_cast<uint32_t>(stage) * kMidStageBytes + issuer * kMidSubBytes;
+#pragma unroll
+          for (int j = 0; j < kStageK / kInstK; ++j) {
+            umma_tf32_pair(tmem_acc, umma_desc_advance(ring.a, offset + j * (kInstK * 4)),
+                           umma_desc_advance(ring.b, offset + j * (kInstK * 128)), idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          // The stage is reusable in both CTAs once both issuers' MMAs have read it.
+          umma_commit_pair(smem_u32(&empty[stage]));
+          umma_commit_pair(map_to_cta(smem_u32(&empty[stage]), 1));
+          if (++stage == kMidStages) stage = 0, phase ^= 1u;
+        }
+        if (ok) {
+          umma_commit_pair(smem_u32(&acc_full[buf]));
+          umma_commit_pair(map_to_cta(smem_u32(&acc_full[buf]), 1));
+        }
+      }
+    }
+  } else {
+    constexpr int kShare = kTileEpilogueShare;
+    const EpilogueArgs ep = epilogue_args(p);
+    const int quarter = warp & 3, part = (warp - 2) >> 2;
+    bool ok = true;
+    int local = 0;
+    const bool boxed = p.tma_store != 0 && ep.vector_io && ep.peers.count == 0;
+    uint8_t* boxes = staging + (part * 4 + quarter) * (kStagingBytes / (4 * kShare));
+    uint32_t box_uses = 0;
+    for (int tile = first_tile; tile < tiles && ok; tile += tile_stride, ++local) {
+      const int buf = local & 1;
+      const uint32_t use_parity = (local >> 1) & 1u;
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      const int n0 = tn * kMidN;
+      const int m0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
+      SourceQuads first;
+      if (boxed) fetch_source_coalesced(ep, first, m0 + quarter * 32, n0 + part * 32, lane);   // before the wait
+      if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
+      tcgen05_fence_after_sync();
+      const uint32_t tmem_acc = tmem_base + buf * kIssuers * kMidN;
+      if (boxed) {
+        epilogue_tile_boxed<kMidN, kAct, kShare, kIssuers>(p, ep, tmem_acc, quarter, part, lane, m0, n0, first, boxes, box_uses);
+      } else {
+        epilogue_tile<kMidN, kAct, kShare, kIssuers>(ep, tmem_acc, quarter, part, lane, m0, n0, boxes);
+      }
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      // The MMA issuers (CTA 0) wait for the epilogues of both CTAs.
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+    }
+    if (boxed && lane == 0) tma_store_wait_read<0>();   // every store has read its box (the writes land before the grid completes)
+  }
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer may still be signalling this CTA's barriers or reading its operands
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc_pair<512>(tmem_base);
+  }
+}
+
 // ------------------------------------------------------------------- launcher
 
 template <int STAGES, int kAct>
@@ -266,7 +439,51 @@ int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
+template <int kAct>
+int launch_pair_mid(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  auto kernel = umma_pair_mid_kernel<kAct>;
+  if (!ensure_dynamic_smem<umma_pair_mid_kernel<kAct>, kMidSmemBytes>()) return B200_ERR_LAUNCH_FAILED;
+  UmmaParams p;
+  fill_common(&p, q, peers);
+  if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
+      !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
+    return B200_ERR_MISALIGNED_OPERAND;
+  }
+  p.tma_store = (p.vector_io && make_tensor_map_2d(&p.map_d, q.d, q.m, q.n, q.ldd, 32, 32, Swizzle::k128B)) ? 1 : 0;
+  p.b_strips = (q.n % 32 == 0 && make_tensor_map_strips(&p.map_b_strips, q.b, q.k, q.n, q.ldb, kStageK, kMidN / 2 / 32,
+                                                        Swizzle::k128BAtom32B))
+                   ? kMidN / 2 / 32
+                   : 0;
+  const int sms = sm_count();
+  if (sms < 2) return B200_ERR_INTERNAL;
+  const int64_t tiles = static_cast<int64_t>((q.m + 2 * kTileM - 1) / (2 * kTileM)) * ((q.n + kMidN - 1) / kMidN);
+  const int64_t all_pairs = sms / 2;
+  const int64_t pairs = tiles < all_pairs ? tiles : all_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  cfg.blockDim = dim3(kTileThreadsTwoIssuers);
+  cfg.dynamicSmemBytes = kMidSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
+  return launch_status();
+}
 }  // namespace
+
+int launch_tf32_pair_mid(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  switch (act) {
+    case B200_EPILOGUE_LINEAR: return launch_pair_mid<B200_EPILOGUE_LINEAR>(q, peers, stream);
+    case B200_EPILOGUE_RELU: return launch_pair_mid<B200_EPILOGUE_RELU>(q, peers, stream);
+    case B200_EPILOGUE_GELU: return launch_pair_mid<B200_EPILOGUE_GELU>(q, peers, stream);
+    default: return B200_ERR_INVALID_ARGUMENT;
+  }
+}
 
 int launch_tf32_pair(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   switch (act) {

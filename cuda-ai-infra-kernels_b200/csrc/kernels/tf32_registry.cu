@@ -44,6 +44,10 @@ int pair_entry(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_
   return launch_tf32_pair(kAct, q, peers, stream);
 }
 template <int kAct>
+int pair_mid_entry(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  return launch_tf32_pair_mid(kAct, q, peers, stream);
+}
+template <int kAct>
 int splitk_entry(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   return launch_tf32_splitk(kAct, q, peers, stream);
 }
@@ -75,6 +79,11 @@ constexpr b200_tf32_kernel_meta meta(int id, const char* name, const char* alias
 constexpr b200_tf32_kernel_meta meta_pair(int id, const char* name, const char* alias, int epilogue, int stages) {
   return b200_tf32_kernel_meta{id, name, alias, epilogue, 2 * kTileM, kPairN, kStageK, 2 * kTileM, kPairN, kInstK,
                                stages, 4, 4, 4, 0};
+}
+
+// A CTA pair on 256 x 128 tiles (256 x 128 x 8 instructions), two MMA issuers.
+constexpr b200_tf32_kernel_meta meta_pair_mid(int id, const char* name, const char* alias, int epilogue) {
+  return b200_tf32_kernel_meta{id, name, alias, epilogue, 2 * kTileM, 128, kStageK, 2 * kTileM, 128, kInstK, 8, 4, 4, 4, 0};
 }
 
 // One 128 x 128 tile per cluster, K split over the cluster's CTAs.
@@ -141,6 +150,17 @@ bool gate_splitk(const b200_gemm_problem& q, int sms) {
   const float unsplit_us = static_cast<float>(k_blocks) * (narrow ? 0.136f : 0.22f) + (narrow ? 5.4f : 5.2f);
   return split_us + 1.0f < unsplit_us;   // near ties go to the simpler kernel
 }
+// CTA pairs on 256 x 128 tiles with two MMA issuers: where the 128 x 128 tile kernel would run one
+// round (more than half the SMs, so not the 128 x 64 tile's territory) and K is long enough for the
+// quarter fewer operand bytes per flop to outweigh the pair's start-up. Graph-timed with a source and
+// ReLU, against the 128 x 128 tile kernel: 1280 x 1280 x 4096 27.4 / 31.4 us, 1280 x 1280 x 8192 53.0 / 60.5,
+// 1536 x 1536 x 3072 24.3 / 26.0, 1536 x 1536 x 4096 32.3 / 39.0, 1024 x 2048 x 4096 30.0 / 33.3,
+// 512 x 4096 x 4096 32.8 / 33.7, 192 x 6144 x 6144 44.9 / 51.3; at K = 2048 and below the 128 x 128
+// tile is level or ahead (1536 x 1536 x 2048 19.0 against 18.7, 1536^3 15.7).
+bool gate_pair_mid(const b200_gemm_problem& q, int sms) {
+  const int64_t pair_tiles = static_cast<int64_t>((q.m + 2 * kTileM - 1) / (2 * kTileM)) * ((q.n + 127) / 128);
+  return q.k >= 2560 && q.m > kTileM && tiles_of(q, 128) * 2 > sms && pair_tiles <= sms / 2;
+}
 // Measured against the split-K tile kernel: ahead up to 16 rows (16 x 8192 x 1024: 11.7 vs 16.5 us,
 // 16 x 4096 x 4096: 12.7 vs 16.8, cuBLAS 12.9), level or behind from 32 rows on (64 x 4096 x 4096: 19.7 vs 18.2).
 bool gate_swap(const b200_gemm_problem& q, int) { return q.m <= 16; }
@@ -164,6 +184,9 @@ const RegistryEntry kRegistry[] = {
     {meta_splitk(30, "umma128x128stage3splitk", "splitk", B200_EPILOGUE_LINEAR, 3), &splitk_entry<B200_EPILOGUE_LINEAR>, &gate_splitk},
     {meta_splitk(31, "umma128x128stage3splitkRelu", "splitk_relu", B200_EPILOGUE_RELU, 3), &splitk_entry<B200_EPILOGUE_RELU>, &gate_splitk},
     {meta_splitk(32, "umma128x128stage3splitkGelu", "splitk_gelu", B200_EPILOGUE_GELU, 3), &splitk_entry<B200_EPILOGUE_GELU>, &gate_splitk},
+    {meta_pair_mid(39, "umma256x128stage8pair", "pair_mid", B200_EPILOGUE_LINEAR), &pair_mid_entry<B200_EPILOGUE_LINEAR>, &gate_pair_mid},
+    {meta_pair_mid(40, "umma256x128stage8pairRelu", "pair_mid_relu", B200_EPILOGUE_RELU), &pair_mid_entry<B200_EPILOGUE_RELU>, &gate_pair_mid},
+    {meta_pair_mid(41, "umma256x128stage8pairGelu", "pair_mid_gelu", B200_EPILOGUE_GELU), &pair_mid_entry<B200_EPILOGUE_GELU>, &gate_pair_mid},
     {meta_pair(20, "umma256x256stage6pair", "pair", B200_EPILOGUE_LINEAR, 6), &pair_entry<B200_EPILOGUE_LINEAR>, &gate_pair},
     {meta_pair(21, "umma256x256stage6pairRelu", "pair_relu", B200_EPILOGUE_RELU, 6), &pair_entry<B200_EPILOGUE_RELU>, &gate_pair},
     {meta(16, "umma128x256stage4tma", "wide", B200_EPILOGUE_LINEAR, 256, 4, 4), &tile_entry<256, 4, B200_EPILOGUE_LINEAR>, &gate_wide},
