@@ -451,6 +451,26 @@ def measure_extras(pkg, peaks: dict, device_index: int, warmup: int) -> dict:
             out[f"tf32_{label}_cublas_graph_us"], out[f"tf32_{label}_cublas_graph_min_us"] = gc["median_us"], gc["min_us"]
         del a, b
 
+    # Automatic dispatch against cuBLASLt with its ReLU fused over mid-sized and long-K shapes, where the
+    # choice of registry entry decides: D = relu(A B + 0.5 C), graph-timed, each arm measured twice in
+    # turn (the first measurement after fresh allocations runs at a clock that has not settled) and
+    # the second measurement reported.
+    sweep = []
+    for m_, n_, k_ in ((512, 512, 512), (1536, 1536, 1536), (2048, 2048, 2048), (2304, 2304, 2304), (3072, 3072, 3072),
+                       (1024, 1024, 4096), (1024, 4096, 4096), (512, 4096, 4096), (64, 4096, 4096), (1280, 1280, 8192),
+                       (1024, 2048, 4096), (4096, 4096, 512)):
+        a, b, c = (torch.randn(m_, k_, device=dev), torch.randn(k_, n_, device=dev), torch.randn(m_, n_, device=dev))
+        ours = lambda: pkg.adaptive_gemm(a, b, c=c, alpha=1.0, beta=0.5, epilogue="relu")
+        lt = lambda: pkg.adaptive_gemm(a, b, c=c, alpha=1.0, beta=0.5, epilogue="relu", kernel="cublaslt")
+        ours()
+        entry = _C.adaptive_gemm_last_kernel()
+        graph_us(ours), graph_us(lt)
+        t_ours, t_lt = graph_us(ours)["median_us"], graph_us(lt)["median_us"]
+        sweep.append({"shape": f"{m_}x{n_}x{k_}", "kernel": entry, "us": round(t_ours, 2), "cublaslt_fused_us": round(t_lt, 2),
+                      "speed_vs_cublaslt": round(t_lt / t_ours, 3)})
+        del a, b, c
+    out["tf32_dispatch_sweep"] = sweep
+
     # Row operators: bytes = one read of x + one write of y (+ weight once).
     rows, hidden = 16384, 4096
     xs = [torch.randn(rows, hidden, device=dev) for _ in range(2)]
