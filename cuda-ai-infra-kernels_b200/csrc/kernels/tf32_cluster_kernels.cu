@@ -422,6 +422,184 @@ __global__ void __launch_bounds__(splitk_threads<STAGES, KSUB>(), KSUB == 2 ? 1 
   }
 }
 
+// ------------------------------------------ TMA, CTA-pair split-K cluster kernel
+// The split-K kernel above on CTA pairs (tcgen05 cta_group::2) with two MMA issuers: a cluster of
+// 2 R CTAs shares one 256 x 128 output tile, pair r = cluster rank / 2 reduces the r-th range of K,
+// and within a pair CTA h = rank % 2 holds rows [128 h, +128) of A, columns [64 h, +64) of B and the
+// accumulator rows [128 h, +128). Per CTA a 32-wide K block is 16 KiB of A + 8 KiB of B for a
+// 128 x 128 share of the product, against 32 KiB in the single-CTA kernel: a quarter fewer operand
+// bytes per flop into the SM, which is what the main loop of these few-tile, long-K problems is bound
+// by. A stage holds two sub-blocks; issuer i (two threads of the pair's even CTA) multiplies
+// sub-block i into accumulator i and both commit every stage to both CTAs (with a single issuer
+// this form was no faster than the single-CTA kernel: 897 cycles per stage, 300 of them the
+// issuer's barrier round trip). The partial tiles then meet as above, among the R CTAs of the same
+// h (cluster ranks h, h + 2, ...): CTA (r, h) finishes columns [r W, (r + 1) W), W = 128 / R, of its
+// 128 rows. No multicast form is used anywhere.
+//   warp 0 producer, warp 1 first issuer, warps 2-9 send (two per quarter of the rows), warp 10
+//   second issuer; all eleven finish.
+constexpr int kPairSplitN = 128;
+constexpr uint32_t kPairSplitSubBytes = kASlabBytes + (kPairSplitN / 2 / 32) * kBBoxBytes;   // 24 KiB per 32 of K and CTA
+constexpr int kPairSplitStages = 4;    // of two sub-blocks: 192 KiB of ring
+constexpr uint32_t kPairSplitStageBytes = 2 * kPairSplitSubBytes;
+constexpr size_t kPairSplitSmemBytes = static_cast<size_t>(kPairSplitStages) * kPairSplitStageBytes + 1024 + 1024;
+constexpr int kPairSplitThreads = 11 * 32;
+static_assert(static_cast<size_t>(kPairSplitStages) * kPairSplitStageBytes >= sizeof(float4) * kExchangePitch * (kPairSplitN / 4),
+              "the idle operand ring must hold one exchanged tile");
+
+template <int kAct>
+__global__ void __launch_bounds__(kPairSplitThreads, 1) umma_pair_splitk_kernel(const __grid_constant__ UmmaParams p) {
+  constexpr int BN = kPairSplitN;
+  constexpr int kIssuers = 2;
+  constexpr int kSecondIssuerWarp = 10;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int ranks = static_cast<int>(cluster.num_blocks()) >> 1;   // K ranges = pairs in the cluster
+  const uint32_t cta = cluster.block_rank();
+  const int slice = static_cast<int>(cta >> 1);   // this pair's K range
+  const uint32_t half = cta & 1u;                 // rows [128 half, +128) of the tile
+  const uint32_t leader = cta & ~1u;              // cluster rank of the pair's even CTA, which issues the MMAs
+  extern __shared__ uint8_t smem_raw[];
+  // Same carve-up in every CTA: the MMA addresses the peer's shared memory by the same offsets as its own.
+  uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(kPairSplitStages) * kPairSplitStageBytes);
+  uint64_t* empty = full + kPairSplitStages;
+  uint64_t* acc_full = empty + kPairSplitStages;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_full + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&p.map_a);
+    prefetch_tensormap(p.b_strips == BN / 2 / 32 ? &p.map_b_strips : &p.map_b);
+    for (int s = 0; s < kPairSplitStages; ++s) {
+      mbar_init(&full[s], 1);           // used in the even CTA only: one expect_tx arrival, bytes of both CTAs
+      mbar_init(&empty[s], kIssuers);   // one tcgen05.commit per issuer and use, sent to each CTA
+    }
+    mbar_init(&acc_full[0], kIssuers);
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair<kIssuers * BN>(tmem_ptr);
+    tmem_relinquish_pair();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster.sync();   // every CTA's barriers exist before any remote arrival
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  const int tiles_m = (p.m + 2 * kTileM - 1) / (2 * kTileM);
+  const int tiles_n = (p.n + BN - 1) / BN;
+  int tm, tn;
+  tile_coords(static_cast<int>(blockIdx.x) / (2 * ranks), tiles_m, tiles_n, &tm, &tn);
+  const int row0 = tm * 2 * kTileM + static_cast<int>(half) * kTileM;   // this CTA's rows of A and of the output
+  const int k_stages = (p.k + 2 * kStageK - 1) / (2 * kStageK);   // K past the end reads as zeros
+  const int per_slice = (k_stages + ranks - 1) / ranks;
+  const int kb_begin = min(k_stages, slice * per_slice);
+  const int kb_end = min(k_stages, kb_begin + per_slice);
+  const bool has_work = kb_begin < kb_end;   // an empty range contributes zeros
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int col0 = tn * BN + static_cast<int>(half) * (BN / 2);   // this CTA's share of the B columns
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&empty[stage], phase ^ 1u, kSiteUmmaEmpty)) break;
+        // Completion bytes of both CTAs are counted on the even CTA's barrier.
+        const uint32_t full_addr = map_to_cta(smem_u32(&full[stage]), leader);
+        if (half == 0) mbar_expect_tx(&full[stage], 2 * kPairSplitStageBytes);
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+          const int k0 = (kb * 2 + sub) * kStageK;
+          uint8_t* a_dst = stages + static_cast<size_t>(stage) * kPairSplitStageBytes + sub * kPairSplitSubBytes;
+          uint8_t* b_dst = a_dst + kASlabBytes;
+          tma_load_2d_pair(a_dst, &p.map_a, full_addr, k0, row0);
+          if (p.b_strips == BN / 2 / 32) {
+            tma_load_3d_pair(b_dst, &p.map_b_strips, full_addr, 0, k0, col0 / 32);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 2 / 32; ++j) {
+              tma_load_2d_pair(b_dst + j * kBBoxBytes, &p.map_b, full_addr, col0 + j * 32, k0);
+            }
+          }
+        }
+        if (++stage == kPairSplitStages) stage = 0, phase ^= 1u;
+      }
+    }
+  } else if (warp == 1 || warp == kSecondIssuerWarp) {
+    if (lane == 0 && half == 0 && has_work) {
+      const uint32_t issuer = warp == 1 ? 0u : 1u;
+      constexpr uint32_t idesc = umma_idesc_tf32(2 * kTileM, BN, /*a_mn_major=*/false, /*b_mn_major=*/true);
+      const SubBlockDescs ring = sub_block_descs(smem_u32(stages));   // of the ring's first sub-block
+      int stage = 0;
+      uint32_t phase = 0;
+      bool fed = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&full[stage], phase, kSiteUmmaFull)) { fed = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t offset = static_cast<uint32_t>(stage) * kPairSplitStageBytes + issuer * kPairSplitSubBytes;
+#pragma unroll
+        for (int j = 0; j < kStageK / kInstK; ++j) {
+          umma_tf32_pair(tmem_base + issuer * BN, umma_desc_advance(ring.a, offset + j * (kInstK * 4)),
+                         umma_desc_advance(ring.b, offset + j * (kInstK * 128)), idesc, (kb > kb_begin || j > 0) ? 1u : 0u);
+        }
+        // The stage is reusable in both CTAs once both issuers' MMAs have read it.
+        umma_commit_pair(smem_u32(&empty[stage]));
+        umma_commit_pair(map_to_cta(smem_u32(&empty[stage]), leader + 1));
+        if (++stage == kPairSplitStages) stage = 0, phase ^= 1u;
+      }
+      if (fed) {
+        umma_commit_pair(smem_u32(&acc_full[0]));
+        umma_commit_pair(map_to_cta(smem_u32(&acc_full[0]), leader + 1));
+      }
+    }
+  } else if (has_work) {
+    ok = mbar_wait(&acc_full[0], 0, kSiteUmmaAccFull);
+    tcgen05_fence_after_sync();
+  }
+
+  // 1. Every CTA of the cluster is past its main loop: the operand rings become exchange buffers.
+  tcgen05_fence_before_sync();
+  cluster.sync();
+  tcgen05_fence_after_sync();
+
+  float4* exchange = reinterpret_cast<float4*>(stages);
+  const int width = BN / ranks;   // W: 128, 64 or 32 columns per CTA
+  const int quarter = warp & 3;
+  const int row_in_tile = quarter * 32 + lane;
+  const bool warp_rows = row0 + quarter * 32 < p.m;   // any row of this warp inside the matrix
+  const int quads_log2 = 31 - __clz(width / 4);
+  const EpilogueArgs args = epilogue_args(p);
+  const int col_base = tn * BN + slice * width;
+  const bool interior = args.vector_io && args.bias == nullptr && args.peers.count == 0 && row0 + kTileM <= p.m &&
+                        col_base + width <= p.n;
+  InteriorCursor cursor = interior_cursor(args, exchange, quads_log2, row0, col_base, threadIdx.x, kPairSplitThreads);
+  float4 first_sources[kInteriorBatch];
+  if (interior) interior_sources(cursor, 0, first_sources);
+  if (warp >= 2 && warp < kSecondIssuerWarp && warp_rows) {
+    // 2. This CTA's partial rows, W columns to each CTA with the same rows: cluster ranks half, half + 2, ...
+    send_partial_row<BN, kIssuers, 2>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), has_work && ok,
+                                      smem_u32(exchange), slice, quads_log2, 2, static_cast<int>(half), row_in_tile,
+                                      (warp - 2) >> 2);
+  }
+  tcgen05_fence_before_sync();
+  cluster.sync();
+
+  // 3. Add the partials of this CTA's columns in range order and finish them.
+  if (interior) {
+    exchange_finish_interior<kAct>(args, cursor, first_sources, ranks, quads_log2);
+  } else {
+    exchange_finish<kAct>(args, exchange, ranks, quads_log2, row0, col_base, threadIdx.x, kPairSplitThreads);
+  }
+
+  __syncthreads();
+  cluster.sync();   // the pair's TMEM is given back by both CTAs together
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc_pair<kIssuers * BN>(tmem_base);
+  }
+}
+
 // ---------------------------------------- TMA, operand-swapped kernel for few rows
 // Up to 64 rows (decode-like shapes): computing D^T = B^T * A^T puts the long
 // dimension N on the 128 rows of the MMA and the few rows of A on its N side, so
@@ -734,6 +912,95 @@ int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStre
   return launch_status();
 }
 
+// Most clusters of `cluster_ctas` (2, 4 or 8) CTAs of the CTA-pair split-K kernel that the device keeps
+// resident at once (cached per device), or 0 when the query fails.
+int pair_splitk_max_clusters(int cluster_ctas) {
+  static std::atomic<int> cache[64][3];   // [device][log2 cluster size - 1], 0 = not asked yet
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  const int slot = cluster_ctas == 2 ? 0 : cluster_ctas == 4 ? 1 : 2;
+  const int cached = cache[device][slot].load(std::memory_order_relaxed);
+  if (cached != 0) return cached > 0 ? cached : 0;
+  auto kernel = umma_pair_splitk_kernel<B200_EPILOGUE_LINEAR>;   // the activation does not change the footprint
+  if (!ensure_dynamic_smem<umma_pair_splitk_kernel<B200_EPILOGUE_LINEAR>, kPairSplitSmemBytes>()) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(cluster_ctas) * 64);
+  cfg.blockDim = dim3(kPairSplitThreads);
+  cfg.dynamicSmemBytes = kPairSplitSmemBytes;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(cluster_ctas);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) clusters = 0;
+  cache[device][slot].store(clusters > 0 ? clusters : -1, std::memory_order_relaxed);   // concurrent first calls compute the same value
+  return clusters > 0 ? clusters : 0;
+}
+
+// K ranges (pairs per cluster: 1, 2 or 4) of the CTA-pair split-K kernel for `q`, 0 when the occupancy
+// query fails. A range keeps at least two 64-wide stages; clusters beyond what the device keeps
+// resident at once run as further waves. The model (microseconds, fitted to graph timings on a B200
+// with a source and ReLU: 1024 x 1024 x K in two ranges 19.8 / 33.3 / 62.9 at K = 4096 / 8192 / 16384,
+// 256 x 4096 x 4096 in two 19.6, 768 x 768 x 4096 18.6, 512 x 512 x 2048 in four 10.8): a 64-wide stage
+// of a CTA's range costs 0.42; launch, pipeline fill, exchange and finishing pass 6.5 / 6.5 / 9.0 for
+// 1 / 2 / 4 ranges. `waves` receives the wave count of the choice.
+int pair_splitk_ranks(const b200_gemm_problem& q, float* estimate_us = nullptr, int* waves = nullptr) {
+  const int64_t tiles = static_cast<int64_t>((q.m + 2 * kTileM - 1) / (2 * kTileM)) * ((q.n + kPairSplitN - 1) / kPairSplitN);
+  const int k_stages = (q.k + 2 * kStageK - 1) / (2 * kStageK);
+  constexpr float kFixedUs[3] = {6.5f, 6.5f, 9.0f};
+  int best = 0, best_waves = 0;
+  float best_us = 1e30f;
+  for (int log2r = 0; log2r < 3; ++log2r) {
+    const int ranks = 1 << log2r;
+    if (ranks > 1 && k_stages / ranks < 2) break;
+    const int resident = pair_splitk_max_clusters(2 * ranks);
+    if (resident <= 0) continue;
+    const int64_t rounds = (tiles + resident - 1) / resident;
+    const float us = static_cast<float>(rounds) * (static_cast<float>((k_stages + ranks - 1) / ranks) * 0.42f + kFixedUs[log2r]);
+    if (us < best_us) best_us = us, best = ranks, best_waves = static_cast<int>(rounds < 0x7fffffff ? rounds : 0x7fffffff);
+  }
+  if (estimate_us != nullptr) *estimate_us = best_us;
+  if (waves != nullptr) *waves = best_waves;
+  return best;
+}
+
+template <int kAct>
+int launch_pair_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  auto kernel = umma_pair_splitk_kernel<kAct>;
+  if (!ensure_dynamic_smem<umma_pair_splitk_kernel<kAct>, kPairSplitSmemBytes>()) return B200_ERR_LAUNCH_FAILED;
+  const int ranks = pair_splitk_ranks(q);
+  if (ranks == 0) return B200_ERR_INTERNAL;   // the occupancy query failed
+  UmmaParams p;
+  fill_common(&p, q, peers);
+  if (!make_tensor_map_2d(&p.map_a, q.a, q.m, q.k, q.lda, kTileM, kStageK, Swizzle::k128B) ||
+      !make_tensor_map_2d(&p.map_b, q.b, q.k, q.n, q.ldb, kStageK, 32, Swizzle::k128BAtom32B)) {
+    return B200_ERR_MISALIGNED_OPERAND;
+  }
+  p.b_strips = (q.n % 32 == 0 && make_tensor_map_strips(&p.map_b_strips, q.b, q.k, q.n, q.ldb, kStageK,
+                                                        kPairSplitN / 2 / 32, Swizzle::k128BAtom32B))
+                   ? kPairSplitN / 2 / 32
+                   : 0;
+  const int64_t tiles = static_cast<int64_t>((q.m + 2 * kTileM - 1) / (2 * kTileM)) * ((q.n + kPairSplitN - 1) / kPairSplitN);
+  if (tiles * 2 * ranks > 0x7fffffffLL) return B200_ERR_INVALID_PROBLEM;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * 2 * ranks));
+  cfg.blockDim = dim3(kPairSplitThreads);
+  cfg.dynamicSmemBytes = kPairSplitSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(2 * ranks);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
+  return launch_status();
+}
+
 // Cluster size of the operand-swapped kernel: as many K ranges as keep every cluster resident at
 // once (one CTA per SM) with at least two pipeline stages each.
 int swap_ranks(int64_t tiles, int k_stages, int sms) {
@@ -828,6 +1095,18 @@ int launch_tf32_swap(int act, const b200_gemm_problem& q, const PeerOutputs& pee
   }
 }
 
+int launch_tf32_pair_splitk(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  switch (act) {
+    case B200_EPILOGUE_LINEAR: return launch_pair_splitk<B200_EPILOGUE_LINEAR>(q, peers, stream);
+    case B200_EPILOGUE_RELU: return launch_pair_splitk<B200_EPILOGUE_RELU>(q, peers, stream);
+    case B200_EPILOGUE_GELU: return launch_pair_splitk<B200_EPILOGUE_GELU>(q, peers, stream);
+    default: return B200_ERR_INVALID_ARGUMENT;
+  }
+}
+
 int tf32_splitk_plan(const b200_gemm_problem& q, int sms, float* estimate_us) { return splitk_ranks(q, sms, estimate_us); }
+int tf32_pair_splitk_plan(const b200_gemm_problem& q, float* estimate_us, int* waves) {
+  return pair_splitk_ranks(q, estimate_us, waves);
+}
 
 }  // namespace b200

@@ -27,6 +27,11 @@ cudaError_t tf32_pair_status_read_clear(uint32_t* word);
 // the dispatcher's gate consults: the cluster size the split-K entry would use for `q` (1 = it would
 // not split) and the modelled duration in microseconds.
 int launch_tf32_splitk(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream);
+// The same on CTA pairs with two MMA issuers: 256 x 128 tiles, clusters of 2, 4 or 8 CTAs.
+// `tf32_pair_splitk_plan` returns the K ranges it would use for `q` (0 = the occupancy query failed),
+// the modelled duration in microseconds and the number of waves of clusters that choice needs.
+int launch_tf32_pair_splitk(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream);
+int tf32_pair_splitk_plan(const b200_gemm_problem& q, float* estimate_us, int* waves);
 int launch_tf32_swap(int act, const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream);
 int tf32_splitk_plan(const b200_gemm_problem& q, int sms, float* estimate_us);
 cudaError_t tf32_cluster_status_read_clear(uint32_t* word);

@@ -52,6 +52,10 @@ int splitk_entry(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStrea
   return launch_tf32_splitk(kAct, q, peers, stream);
 }
 template <int kAct>
+int pair_splitk_entry(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
+  return launch_tf32_pair_splitk(kAct, q, peers, stream);
+}
+template <int kAct>
 int swap_entry(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t stream) {
   return launch_tf32_swap(kAct, q, peers, stream);
 }
@@ -89,6 +93,11 @@ constexpr b200_tf32_kernel_meta meta_pair_mid(int id, const char* name, const ch
 // One 128 x 128 tile per cluster, K split over the cluster's CTAs.
 constexpr b200_tf32_kernel_meta meta_splitk(int id, const char* name, const char* alias, int epilogue, int stages) {
   return b200_tf32_kernel_meta{id, name, alias, epilogue, kTileM, kSplitN, kStageK, kTileM, kSplitN, kInstK, stages, 4, 4, 4, 1};
+}
+
+// One 256 x 128 tile per cluster of CTA pairs, K split over the pairs.
+constexpr b200_tf32_kernel_meta meta_pair_splitk(int id, const char* name, const char* alias, int epilogue) {
+  return b200_tf32_kernel_meta{id, name, alias, epilogue, 2 * kTileM, kSplitN, kStageK, 2 * kTileM, kSplitN, kInstK, 8, 4, 4, 4, 1};
 }
 
 // Few rows on the tensor cores: D^T = B^T A^T, 128 columns of D per CTA, K split over a cluster.
@@ -150,6 +159,24 @@ bool gate_splitk(const b200_gemm_problem& q, int sms) {
   const float unsplit_us = static_cast<float>(k_blocks) * (narrow ? 0.136f : 0.22f) + (narrow ? 5.4f : 5.2f);
   return split_us + 1.0f < unsplit_us;   // near ties go to the simpler kernel
 }
+// The CTA-pair form of the split (two MMA issuers): when K is split at all (two ranges or more), all
+// its clusters are resident at once, both CTAs of a pair have rows to compute, and its model predicts
+// a shorter run than the single-CTA split and the unsplit tile kernels (the estimates of gate_splitk).
+// Graph-timed with a source and ReLU, pair split / single-CTA split / best unsplit: 1024 x 1024 x 8192
+// 33.3 / 37.4 / 41.5 us, 768 x 768 x 4096 18.6 / 20.7 / 22.1, 768 x 768 x 8192 28.2 / 30.8 / 40.5,
+// 256 x 4096 x 4096 19.6 / 23.6 / 22.9, 512 x 512 x 2048 10.8 / 13.4 / 13.7, 1024 x 1024 x 16384 62.9 / 68.7 /
+// 92.2; level at 1024 x 1024 x 4096 (19.8 / 19.6) and 512 x 2048 x 4096 (19.1 / 19.8).
+bool gate_pair_splitk(const b200_gemm_problem& q, int sms) {
+  if (q.m <= kTileM) return false;
+  float pair_us = 0.f, split_us = 0.f;
+  int waves = 0;
+  if (tf32_pair_splitk_plan(q, &pair_us, &waves) < 2 || waves != 1) return false;
+  tf32_splitk_plan(q, sms, &split_us);
+  const int k_blocks = (q.k + kStageK - 1) / kStageK;
+  const bool narrow = tiles_of(q, 64) <= sms;
+  const float unsplit_us = static_cast<float>(k_blocks) * (narrow ? 0.136f : 0.22f) + (narrow ? 5.4f : 5.2f);
+  return pair_us + 0.5f < (split_us < unsplit_us ? split_us : unsplit_us);
+}
 // CTA pairs on 256 x 128 tiles with two MMA issuers: where the 128 x 128 tile kernel would run one
 // round (more than half the SMs, so not the 128 x 64 tile's territory) and K is long enough for the
 // quarter fewer operand bytes per flop to outweigh the pair's start-up. Graph-timed with a source and
@@ -181,6 +208,9 @@ const RegistryEntry kRegistry[] = {
     {meta_swap(36, "umma64x128swap", "swap", B200_EPILOGUE_LINEAR), &swap_entry<B200_EPILOGUE_LINEAR>, &gate_swap},
     {meta_swap(37, "umma64x128swapRelu", "swap_relu", B200_EPILOGUE_RELU), &swap_entry<B200_EPILOGUE_RELU>, &gate_swap},
     {meta_swap(38, "umma64x128swapGelu", "swap_gelu", B200_EPILOGUE_GELU), &swap_entry<B200_EPILOGUE_GELU>, &gate_swap},
+    {meta_pair_splitk(42, "umma256x128pairsplitk", "pair_splitk", B200_EPILOGUE_LINEAR), &pair_splitk_entry<B200_EPILOGUE_LINEAR>, &gate_pair_splitk},
+    {meta_pair_splitk(43, "umma256x128pairsplitkRelu", "pair_splitk_relu", B200_EPILOGUE_RELU), &pair_splitk_entry<B200_EPILOGUE_RELU>, &gate_pair_splitk},
+    {meta_pair_splitk(44, "umma256x128pairsplitkGelu", "pair_splitk_gelu", B200_EPILOGUE_GELU), &pair_splitk_entry<B200_EPILOGUE_GELU>, &gate_pair_splitk},
     {meta_splitk(30, "umma128x128stage3splitk", "splitk", B200_EPILOGUE_LINEAR, 3), &splitk_entry<B200_EPILOGUE_LINEAR>, &gate_splitk},
     {meta_splitk(31, "umma128x128stage3splitkRelu", "splitk_relu", B200_EPILOGUE_RELU, 3), &splitk_entry<B200_EPILOGUE_RELU>, &gate_splitk},
     {meta_splitk(32, "umma128x128stage3splitkGelu", "splitk_gelu", B200_EPILOGUE_GELU, 3), &splitk_entry<B200_EPILOGUE_GELU>, &gate_splitk},
