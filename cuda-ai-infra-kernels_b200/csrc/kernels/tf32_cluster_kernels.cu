@@ -956,7 +956,10 @@ int pair_splitk_ranks(const b200_gemm_problem& q, float* estimate_us = nullptr, 
   for (int log2r = 0; log2r < 3; ++log2r) {
     const int ranks = 1 << log2r;
     if (ranks > 1 && k_stages / ranks < 2) break;
-    const int resident = pair_splitk_max_clusters(2 * ranks);
+    // Four fifths of what the occupancy query reports: on some GPUs of the same model the last few
+    // clusters of four did not find room beside the others and ran as a second wave (1024 x 1024 x 4096,
+    // 32 clusters: 20 us on most boxes, 35 on one).
+    const int resident = pair_splitk_max_clusters(2 * ranks) * 4 / 5;
     if (resident <= 0) continue;
     const int64_t rounds = (tiles + resident - 1) / resident;
     const float us = static_cast<float>(rounds) * (static_cast<float>((k_stages + ranks - 1) / ranks) * 0.42f + kFixedUs[log2r]);

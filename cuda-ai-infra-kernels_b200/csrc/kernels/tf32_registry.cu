@@ -159,23 +159,24 @@ bool gate_splitk(const b200_gemm_problem& q, int sms) {
   const float unsplit_us = static_cast<float>(k_blocks) * (narrow ? 0.136f : 0.22f) + (narrow ? 5.4f : 5.2f);
   return split_us + 1.0f < unsplit_us;   // near ties go to the simpler kernel
 }
-// The CTA-pair form of the split (two MMA issuers): when K is split at all (two ranges or more), all
-// its clusters are resident at once, both CTAs of a pair have rows to compute, and its model predicts
-// a shorter run than the single-CTA split and the unsplit tile kernels (the estimates of gate_splitk).
-// Graph-timed with a source and ReLU, pair split / single-CTA split / best unsplit: 1024 x 1024 x 8192
-// 33.3 / 37.4 / 41.5 us, 768 x 768 x 4096 18.6 / 20.7 / 22.1, 768 x 768 x 8192 28.2 / 30.8 / 40.5,
-// 256 x 4096 x 4096 19.6 / 23.6 / 22.9, 512 x 512 x 2048 10.8 / 13.4 / 13.7, 1024 x 1024 x 16384 62.9 / 68.7 /
-// 92.2; level at 1024 x 1024 x 4096 (19.8 / 19.6) and 512 x 2048 x 4096 (19.1 / 19.8).
+// The CTA-pair form of the split (two MMA issuers): when it splits K at all (two ranges or more), all
+// its clusters are resident at once, both CTAs of a pair have rows to compute, and either the
+// single-CTA split would be chosen (the pair form was ahead of it or level in every such case
+// measured) or its own model predicts a shorter run than the unsplit tile kernels. Graph-timed with a
+// source and ReLU, pair split / single-CTA split / best unsplit: 1024 x 1024 x 8192 33.3 / 37.4 / 41.5 us,
+// 768 x 768 x 4096 18.6 / 20.7 / 22.1, 768 x 768 x 8192 28.2 / 30.8 / 40.5, 256 x 4096 x 4096 19.6 / 23.6 / 22.9,
+// 512 x 512 x 2048 10.8 / 13.4 / 13.7, 1024 x 1024 x 16384 62.9 / 68.7 / 92.2; level at 1024 x 1024 x 4096
+// (19.8 / 19.6) and 512 x 2048 x 4096 (19.1 / 19.8).
 bool gate_pair_splitk(const b200_gemm_problem& q, int sms) {
   if (q.m <= kTileM) return false;
-  float pair_us = 0.f, split_us = 0.f;
+  float pair_us = 0.f;
   int waves = 0;
   if (tf32_pair_splitk_plan(q, &pair_us, &waves) < 2 || waves != 1) return false;
-  tf32_splitk_plan(q, sms, &split_us);
+  if (gate_splitk(q, sms)) return true;
   const int k_blocks = (q.k + kStageK - 1) / kStageK;
   const bool narrow = tiles_of(q, 64) <= sms;
   const float unsplit_us = static_cast<float>(k_blocks) * (narrow ? 0.136f : 0.22f) + (narrow ? 5.4f : 5.2f);
-  return pair_us + 0.5f < (split_us < unsplit_us ? split_us : unsplit_us);
+  return pair_us + 1.0f < unsplit_us;
 }
 // CTA pairs on 256 x 128 tiles with two MMA issuers: where the 128 x 128 tile kernel would run one
 // round (more than half the SMs, so not the 128 x 64 tile's territory) and K is long enough for the
