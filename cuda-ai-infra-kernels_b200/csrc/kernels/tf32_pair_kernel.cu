@@ -185,20 +185,26 @@ __global__ void __launch_bounds__(kTileThreads, 1) umma_pair_kernel(const __grid
       tile_coords(it.tile, tiles_m, tiles_n, &tm, &tn);
       const int n0 = tn * kPairN + (it.half < 0 ? 0 : it.half * (kPairN / 2));
       const int m0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
+      // Before the wait: the source of the warp's first chunk, fetched and turned in its box.
       SourceQuads first;
-      if (boxed) fetch_source_coalesced(ep, first, m0 + quarter * 32, n0 + part * 32, lane);   // before the wait
+      uint8_t* first_box = nullptr;
+      if (boxed) {
+        fetch_source_coalesced(ep, first, m0 + quarter * 32, n0 + part * 32, lane);
+        first_box = boxes + (box_uses++ % boxes_per_warp<kShare>()) * kOutBoxBytes;
+        stage_source_boxed<boxes_per_warp<kShare>()>(ep, first, lane, first_box);
+      }
       if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
       if (it.half < 0) {
         if (boxed) {
           epilogue_tile_boxed<kPairN, kAct, kShare>(p, ep, tmem_base + buf * kPairN, quarter, part, lane, m0, n0, first, boxes,
-                                                    box_uses);
+                                                    box_uses, first_box);
         } else {
           epilogue_tile<kPairN, kAct, kShare>(ep, tmem_base + buf * kPairN, quarter, part, lane, m0, n0, boxes);
         }
       } else if (boxed) {
         epilogue_tile_boxed<kPairN / 2, kAct, kShare>(p, ep, tmem_base + buf * kPairN, quarter, part, lane, m0, n0, first, boxes,
-                                                      box_uses);
+                                                      box_uses, first_box);
       } else {
         epilogue_tile<kPairN / 2, kAct, kShare>(ep, tmem_base + buf * kPairN, quarter, part, lane, m0, n0, boxes);
       }
@@ -365,12 +371,18 @@ __global__ void __launch_bounds__(kTileThreadsTwoIssuers, 1) umma_pair_mid_kerne
       const int n0 = tn * kMidN;
       const int m0 = tm * 2 * kTileM + static_cast<int>(rank) * kTileM;
       SourceQuads first;
-      if (boxed) fetch_source_coalesced(ep, first, m0 + quarter * 32, n0 + part * 32, lane);   // before the wait
+      uint8_t* first_box = nullptr;
+      if (boxed) {   // before the wait
+        fetch_source_coalesced(ep, first, m0 + quarter * 32, n0 + part * 32, lane);
+        first_box = boxes + (box_uses++ % boxes_per_warp<kShare>()) * kOutBoxBytes;
+        stage_source_boxed<boxes_per_warp<kShare>()>(ep, first, lane, first_box);
+      }
       if (!mbar_wait(&acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + buf * kIssuers * kMidN;
       if (boxed) {
-        epilogue_tile_boxed<kMidN, kAct, kShare, kIssuers>(p, ep, tmem_acc, quarter, part, lane, m0, n0, first, boxes, box_uses);
+        epilogue_tile_boxed<kMidN, kAct, kShare, kIssuers>(p, ep, tmem_acc, quarter, part, lane, m0, n0, first, boxes, box_uses,
+                                                           first_box);
       } else {
         epilogue_tile<kMidN, kAct, kShare, kIssuers>(ep, tmem_acc, quarter, part, lane, m0, n0, boxes);
       }

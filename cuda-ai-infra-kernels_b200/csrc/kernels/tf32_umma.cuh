@@ -329,26 +329,43 @@ __device__ __forceinline__ void add_partial_accumulator(uint32_t (&raw)[32], uin
   for (int e = 0; e < 32; ++e) raw[e] = __float_as_uint(__uint_as_float(raw[e]) + __uint_as_float(other[e]));
 }
 
+// `first_box`, when not null, is the box in which the caller has already staged the source of the
+// warp's first chunk (before it waited for the accumulator: the source does not depend on the
+// product, and a CTA with a single tile has nothing else to hide that step behind).
+template <int kShare>
+__host__ __device__ constexpr int boxes_per_warp() { return 2 / kShare; }
+
 template <int BN, int kAct, int kShare, int kIssuers = 1>
 __device__ __forceinline__ void epilogue_tile_boxed(const UmmaParams& p, const EpilogueArgs& ep, uint32_t tmem_acc, int quarter,
                                                     int part, int lane, int m0, int n0, SourceQuads& src, uint8_t* boxes,
-                                                    uint32_t& uses) {
+                                                    uint32_t& uses, uint8_t* first_box = nullptr) {
   constexpr int kMine = BN / 32 / kShare;   // chunks of this warp
-  constexpr int kBoxes = 2 / kShare;        // boxes of this warp
+  constexpr int kBoxes = boxes_per_warp<kShare>();
   static_assert(kShare == 1 || kShare == 2, "four or eight epilogue warps");
   static_assert(kMine >= 1 && BN % (32 * kShare) == 0, "every warp has work");
   const int row0 = m0 + quarter * 32;
   const uint32_t tmem_row = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
   uint32_t raw_even[32], raw_odd[32];
   tmem_ld_32x32(tmem_row + part * 32, raw_even);
+  if constexpr (kIssuers == 2) tmem_ld_32x32(tmem_row + BN + part * 32, raw_odd);   // the first chunk's other partial sum
 #pragma unroll
   for (int i = 0; i < kMine; i += 2) {
     const int chunk = part + i * kShare;
     if (n0 + chunk * 32 >= ep.n) break;   // uniform across the warp
-    uint8_t* box = boxes + (uses++ % kBoxes) * kOutBoxBytes;
-    stage_source_boxed<kBoxes>(ep, src, lane, box);
+    uint8_t* box = first_box;
+    if (i > 0 || first_box == nullptr) {
+      box = boxes + (uses++ % kBoxes) * kOutBoxBytes;
+      stage_source_boxed<kBoxes>(ep, src, lane, box);
+    }
     tmem_ld_wait();
-    if constexpr (kIssuers == 2) add_partial_accumulator(raw_even, tmem_row + BN + chunk * 32);
+    if constexpr (kIssuers == 2) {
+      if (i == 0) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) raw_even[e] = __float_as_uint(__uint_as_float(raw_even[e]) + __uint_as_float(raw_odd[e]));
+      } else {
+        add_partial_accumulator(raw_even, tmem_row + BN + chunk * 32);
+      }
+    }
     if (i + 1 < kMine) {
       tmem_ld_32x32(tmem_row + (chunk + kShare) * 32, raw_odd);
       fetch_source_coalesced(ep, src, row0, n0 + (chunk + kShare) * 32, lane);
@@ -573,15 +590,22 @@ __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCar
     const uint32_t use_parity = (local >> 1) & 1u;
     int tm, tn;
     tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+    // Before the wait for the accumulator: the source of the warp's first chunk is fetched and turned
+    // into row ownership in its box.
     SourceQuads first;
-    if (boxed) fetch_source_coalesced(ep, first, tm * kTileM + quarter * 32, tn * BN + part * 32, lane);   // before the wait
+    uint8_t* first_box = nullptr;
+    if (boxed) {
+      fetch_source_coalesced(ep, first, tm * kTileM + quarter * 32, tn * BN + part * 32, lane);
+      first_box = boxes + (box_uses++ % boxes_per_warp<kShare>()) * kOutBoxBytes;
+      stage_source_boxed<boxes_per_warp<kShare>()>(ep, first, lane, first_box);
+    }
     B200_PROBE(p, 2);
     if (!mbar_wait(&sm.acc_full[buf], use_parity, kSiteUmmaAccFull)) { ok = false; break; }
     tcgen05_fence_after_sync();
     B200_PROBE(p, 3);
     if (boxed) {
       epilogue_tile_boxed<BN, kAct, kShare, kIssuers>(p, ep, tmem_base + buf * kIssuers * BN, quarter, part, lane, tm * kTileM,
-                                                      tn * BN, first, boxes, box_uses);
+                                                      tn * BN, first, boxes, box_uses, first_box);
     } else {
       epilogue_tile<BN, kAct, kShare, kIssuers>(ep, tmem_base + buf * kIssuers * BN, quarter, part, lane, tm * kTileM, tn * BN,
                                                 boxes);
