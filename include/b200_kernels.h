@@ -205,7 +205,10 @@ typedef struct b200_gemm_problem {
  * are configurations that exist only here: 16-19 wider / narrower tiles,
  * 20-22 CTA pairs (256 x 256), 23-26 GELU forms, 27-29 "skinny" (up to 16 rows,
  * FP32 FMA stream over B; inst_* = 1), 30-32 "splitk" (one 128 x 128 tile per
- * cluster, K split over its CTAs; supports_split_k = 1). Automatic dispatch
+ * cluster, K split over its CTAs; supports_split_k = 1), 36-38 "swap" (operands
+ * swapped for up to 16 rows), 39-41 "pair_mid" (CTA pairs on 256 x 128 tiles),
+ * 42-44 "pair_splitk" (one 256 x 128 tile per cluster of CTA pairs, K split over
+ * the pairs; supports_split_k = 1). Automatic dispatch
  * tries them first, each behind a shape gate, and then walks the reference's
  * eight entries in the reference's order.
  */
