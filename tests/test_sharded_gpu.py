@@ -241,6 +241,9 @@ def test_sgemm_gather_fans_out_every_tile(abi):
     (8, (130, 136, 64)),       # 128 x 128 + ReLU
     (3, (33, 65, 17)),         # generic loader, scalar epilogue
     (30, (64, 256, 1024)),     # split-K cluster
+    (36, (12, 264, 512)),      # operands swapped, K split over a cluster
+    (39, (300, 264, 160)),     # CTA pair, 256 x 128 tiles, two issuers, ragged
+    (42, (300, 200, 1024)),    # CTA pairs with K split over the cluster
 ])
 def test_tf32_gather_fans_out_every_element(abi, kernel, shape):
     import ctypes
