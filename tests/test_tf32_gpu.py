@@ -591,3 +591,33 @@ def test_compensated_tf32_bias_integers_and_refusals(abi):
     assert abi.b200_tf32x3_gemm(ctypes.byref(q), scratch.data_ptr() + 4, need, current_stream_ptr()) == 4
     assert_device_clean(abi)
 
+
+# ------------------------------- CTA-pair kernel: whole 256 x 256 tiles, then 256 x 128 half tiles
+# A last round of tiles that would occupy at most half the pairs runs as half tiles. Their stages lie
+# differently in the operand ring (four of 48 KiB across the whole tiles' three of 64 KiB, starting
+# in the slot that comes free first) and their MMAs come from two threads with an accumulator each.
+
+
+@pytest.mark.parametrize("size,k", [(2304, 192), (2304, 256), (2304, 320), (2304, 200), (2304, 64), (2304, 1088),
+                                    (4096, 160)])
+def test_pair_kernel_goes_from_whole_tiles_to_half_tiles(abi, size, k):
+    # 2304: 81 tiles on 74 pairs, every pair multiplies a whole tile, fourteen of them a half tile
+    # after it; K sets the ring slot the whole tile ends on (3, 4 and 5 stages of 64 floats), a ragged
+    # K, a single stage and many stages. 4096: three whole tiles per pair before the half.
+    # Whole numbers: every element is exact.
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    m = n = size
+    tiles, pairs = (m // 256) * (n // 256), sms // 2
+    if not (pairs < tiles and 2 * (tiles % pairs) <= pairs):
+        pytest.skip("this part's SM count gives the shape no half tiles after whole ones")
+    kernel_id = abi.b200_tf32_kernel_from_name(b"pair_relu")
+    assert kernel_id > 0
+    g = torch.Generator().manual_seed(k)
+    a = torch.randint(-3, 4, (m, k), generator=g).float()
+    b = torch.randint(-3, 4, (k, n), generator=g).float()
+    c = torch.randint(-8, 9, (m, n), generator=g).float()
+    status, d, _ = run(abi, kernel_id, a.cuda(), b.cuda(), c.cuda(), alpha=1.0, beta=0.5, epilogue=RELU)
+    assert status == 0, abi.b200_status_string(status)
+    expected = oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, "relu")
+    torch.testing.assert_close(d.cpu(), expected, atol=0, rtol=0)
+    assert_device_clean(abi)
