@@ -454,7 +454,10 @@ def measure_extras(pkg, peaks: dict, device_index: int, warmup: int) -> dict:
     # Automatic dispatch against cuBLASLt with its ReLU fused over mid-sized and long-K shapes, where the
     # choice of registry entry decides: D = relu(A B + 0.5 C), graph-timed, each arm measured twice in
     # turn (the first measurement after fresh allocations runs at a clock that has not settled) and
-    # the second measurement reported.
+    # the second measurement reported. The timed measurement of each arm follows 0.6 s of idling: the
+    # clock the power cap left behind after the seconds of dense tensor work before it (about
+    # 1400 MHz, sw_power_cap) slows a 20 us problem by a third and the two arms unequally; the
+    # median SM clock of each arm's measurement is part of the row.
     sweep = []
     for m_, n_, k_ in ((512, 512, 512), (1536, 1536, 1536), (2048, 2048, 2048), (2304, 2304, 2304), (3072, 3072, 3072),
                        (1024, 1024, 4096), (1024, 4096, 4096), (512, 4096, 4096), (64, 4096, 4096), (1280, 1280, 8192),
@@ -465,9 +468,15 @@ def measure_extras(pkg, peaks: dict, device_index: int, warmup: int) -> dict:
         ours()
         entry = _C.adaptive_gemm_last_kernel()
         graph_us(ours), graph_us(lt)
-        t_ours, t_lt = graph_us(ours)["median_us"], graph_us(lt)["median_us"]
-        sweep.append({"shape": f"{m_}x{n_}x{k_}", "kernel": entry, "us": round(t_ours, 2), "cublaslt_fused_us": round(t_lt, 2),
-                      "speed_vs_cublaslt": round(t_lt / t_ours, 3)})
+        timed = {}
+        for arm, fn in (("ours", ours), ("lt", lt)):
+            time.sleep(0.6)
+            with ClockSampler(device_index) as clocks:
+                timed[arm] = graph_us(fn)["median_us"]
+            timed[arm + "_mhz"] = clocks.median_mhz()
+        sweep.append({"shape": f"{m_}x{n_}x{k_}", "kernel": entry, "us": round(timed["ours"], 2),
+                      "cublaslt_fused_us": round(timed["lt"], 2), "speed_vs_cublaslt": round(timed["lt"] / timed["ours"], 3),
+                      "mhz": timed["ours_mhz"], "cublaslt_mhz": timed["lt_mhz"]})
         del a, b, c
     out["tf32_dispatch_sweep"] = sweep
 

@@ -2,7 +2,7 @@
 
     python cuda-ai-infra-kernels_b200/benchmarks/bench_adaptive_gemm.py \
         [--sizes 1024,4096,8192 | --shape MxNxK[,MxNxK...]] [--kernel all|auto|fast|...[,...]] [--epilogue linear|relu] \
-        [--alpha 1.0] [--beta 0.5] [--timing graph|event] [--warmup 10] [--repeat 50] [--output FILE] [--profile]
+        [--alpha 1.0] [--beta 0.5] [--timing graph|event] [--warmup 10] [--repeat 50] [--idle SECONDS] [--output FILE] [--profile]
 
 Follows the reference's benchmarks/bench_adaptive_gemm.py: each kernel is
 checked first (here against the FP64 result computed on the device: relative
@@ -11,7 +11,9 @@ sqrt(K) for long reductions), then timed. With `--epilogue relu` the cuBLAS
 baseline is cuBLAS + a separate `torch.relu_` (`fused_relu: false`), as in the
 reference (:14-54); `cublaslt` is cuBLASLt with the ReLU (and bias) fused into its
 epilogue, the fair competitor of the fused kernels. `--kernel auto,cublaslt` with a list of shapes
-gives the sweep of automatic dispatch against the library. `--profile` runs one NVTX-ranged call per kernel and saves
+gives the sweep of automatic dispatch against the library; `--idle 0.6` lets the GPU idle before each
+timed kernel, so that a short problem is not timed at the clock the power cap left behind after a
+long one (about 1400 MHz, which slows the kernels here by up to a third and cuBLASLt's by less). `--profile` runs one NVTX-ranged call per kernel and saves
 nothing. Throughput = 2*M*N*K / median time; the tensor roofline uses half the
 measured BF16 peak of MEASURED_PEAKS.json when that file is present.
 """
@@ -20,6 +22,7 @@ from __future__ import annotations
 import argparse
 import json
 import sys
+import time
 from pathlib import Path
 
 import torch
@@ -101,6 +104,9 @@ def benchmark_problem(m: int, n: int, k: int, args) -> dict:
             torch.cuda.nvtx.range_pop()
             rows.append({"kernel": name, "registry_name": chosen, "correctness": correctness})
             continue
+        if args.idle > 0:
+            torch.cuda.synchronize()
+            time.sleep(args.idle)
         stats = timer(run, warmup=args.warmup, repeat=args.repeat)
         rows.append({"kernel": name, "registry_name": chosen, "fused_relu": fused, "correctness": correctness,
                      "stats": stats, "tflops_mean": flops / stats["mean_ms"] / 1e9,
@@ -129,6 +135,7 @@ def main(argv=None) -> dict:
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--repeat", type=int, default=50)
     parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--idle", type=float, default=0.0)
     parser.add_argument("--output", default="")
     parser.add_argument("--profile", action="store_true")
     args = parser.parse_args(argv)
