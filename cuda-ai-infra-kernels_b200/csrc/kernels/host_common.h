@@ -51,6 +51,32 @@ inline int launch_failed() {
   return B200_ERR_LAUNCH_FAILED;
 }
 
+// Launch attributes of the TF32 GEMM kernels: a cluster of `cluster_x` CTAs (1: none) and
+// programmatic stream serialization. With the latter a kernel may start while the kernel before it
+// in the stream is still running, once all CTAs of that kernel have executed
+// griddepcontrol.launch_dependents (the kernels here do after their set-up) or exited; the kernels
+// execute griddepcontrol.wait after their own set-up (barriers, TMEM, descriptor prefetch) and before
+// their first access to global memory, which returns when the earlier kernel has completed and
+// its writes are visible. Back-to-back calls overlap by about a microsecond that way.
+struct GemmLaunchAttributes {
+  cudaLaunchAttribute list[2];
+  unsigned count;
+};
+inline GemmLaunchAttributes gemm_launch_attributes(unsigned cluster_x) {
+  GemmLaunchAttributes a = {};
+  a.list[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.list[0].val.programmaticStreamSerializationAllowed = 1;
+  a.count = 1;
+  if (cluster_x > 1) {
+    a.list[1].id = cudaLaunchAttributeClusterDimension;
+    a.list[1].val.clusterDim.x = cluster_x;
+    a.list[1].val.clusterDim.y = 1;
+    a.list[1].val.clusterDim.z = 1;
+    a.count = 2;
+  }
+  return a;
+}
+
 // cudaFuncAttributeMaxDynamicSharedMemorySize for kernel `kKernel`, set once per device and process
 // (the attribute is per device; the call costs a few microseconds, which small problems notice).
 template <auto kKernel, size_t kBytes>

@@ -122,6 +122,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   return false;
 }
 
+// ------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still running: once every CTA of that kernel has executed
+// launch_dependents (or exited). It must then execute `wait` before its first access to global
+// memory: the wait returns when the earlier kernel has completed and its writes are visible. What
+// runs before the wait (barrier set-up, TMEM allocation, descriptor prefetch) overlaps the earlier
+// kernel's tail. Without the attribute, or after a kernel that never signals, both are no-ops.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ----------------------------------------------------------------------- TMA
 
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {

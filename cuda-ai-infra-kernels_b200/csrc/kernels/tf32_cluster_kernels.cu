@@ -307,6 +307,9 @@ __global__ void __launch_bounds__(splitk_threads<STAGES, KSUB>(), KSUB == 2 ? 1 
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *sm.tmem_ptr;
+  grid_launch_dependents();   // the next kernel of the stream may set itself up beside this one (not before this
+                              // kernel's TMEM is allocated: its CTAs could take the columns first)
+  grid_dependency_wait();     // the kernel before this one has completed: global memory may be touched
   B200_PROBE(p, 1);
 
   const int tiles_m = (p.m + kTileM - 1) / kTileM;
@@ -485,6 +488,9 @@ __global__ void __launch_bounds__(kPairSplitThreads, 1) umma_pair_splitk_kernel(
   cluster.sync();   // every CTA's barriers exist before any remote arrival
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
+  grid_launch_dependents();   // the next kernel of the stream may set itself up beside this one (not before this
+                              // kernel's TMEM is allocated: its CTAs could take the columns first)
+  grid_dependency_wait();     // the kernel before this one has completed: global memory may be touched
 
   const int tiles_m = (p.m + 2 * kTileM - 1) / (2 * kTileM);
   const int tiles_n = (p.n + BN - 1) / BN;
@@ -669,6 +675,9 @@ __global__ void __launch_bounds__(kTmaThreads, 1) umma_swap_kernel(const __grid_
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
+  grid_launch_dependents();   // the next kernel of the stream may set itself up beside this one (not before this
+                              // kernel's TMEM is allocated: its CTAs could take the columns first)
+  grid_dependency_wait();     // the kernel before this one has completed: global memory may be touched
   B200_PROBE(p, 1);
 
   // Tiles: blocks of NM rows of A by 128 columns of B; row blocks innermost.
@@ -901,13 +910,9 @@ int launch_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStre
   cfg.blockDim = dim3(splitk_threads<STAGES, KSUB>());
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = static_cast<unsigned>(ranks);
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  const GemmLaunchAttributes attrs = gemm_launch_attributes(static_cast<unsigned>(ranks));
+  cfg.attrs = const_cast<cudaLaunchAttribute*>(attrs.list);
+  cfg.numAttrs = attrs.count;
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
@@ -993,13 +998,9 @@ int launch_pair_splitk(const b200_gemm_problem& q, const PeerOutputs& peers, cud
   cfg.blockDim = dim3(kPairSplitThreads);
   cfg.dynamicSmemBytes = kPairSplitSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = static_cast<unsigned>(2 * ranks);
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  const GemmLaunchAttributes attrs = gemm_launch_attributes(static_cast<unsigned>(2 * ranks));
+  cfg.attrs = const_cast<cudaLaunchAttribute*>(attrs.list);
+  cfg.numAttrs = attrs.count;
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
@@ -1043,13 +1044,9 @@ int run_swap(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream_t 
   cfg.blockDim = dim3(kTmaThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = static_cast<unsigned>(ranks);
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  const GemmLaunchAttributes attrs = gemm_launch_attributes(static_cast<unsigned>(ranks));
+  cfg.attrs = const_cast<cudaLaunchAttribute*>(attrs.list);
+  cfg.numAttrs = attrs.count;
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }

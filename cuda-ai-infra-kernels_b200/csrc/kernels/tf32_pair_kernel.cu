@@ -142,6 +142,9 @@ __global__ void __launch_bounds__(kTileThreadsTwoIssuers, 1) umma_pair_kernel(co
   cluster_sync_all();  // both CTAs' barriers exist before any remote arrival
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
+  grid_launch_dependents();   // the next kernel of the stream may set itself up beside this one (not before this
+                              // kernel's TMEM is allocated: its CTAs could take the columns first)
+  grid_dependency_wait();     // the kernel before this one has completed: global memory may be touched
 
   const int tiles_m = (p.m + 2 * kTileM - 1) / (2 * kTileM);
   const int tiles_n = (p.n + kPairN - 1) / kPairN;
@@ -406,6 +409,9 @@ __global__ void __launch_bounds__(kTileThreadsTwoIssuers, 1) umma_pair_mid_kerne
   cluster_sync_all();  // both CTAs' barriers exist before any remote arrival
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
+  grid_launch_dependents();   // the next kernel of the stream may set itself up beside this one (not before this
+                              // kernel's TMEM is allocated: its CTAs could take the columns first)
+  grid_dependency_wait();     // the kernel before this one has completed: global memory may be touched
 
   const int tiles_m = (p.m + 2 * kTileM - 1) / (2 * kTileM);
   const int tiles_n = (p.n + kMidN - 1) / kMidN;
@@ -571,13 +577,9 @@ int launch_pair(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStream
   cfg.blockDim = dim3(kTileThreadsTwoIssuers);
   cfg.dynamicSmemBytes = launch_smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  const GemmLaunchAttributes attrs = gemm_launch_attributes(2);
+  cfg.attrs = const_cast<cudaLaunchAttribute*>(attrs.list);
+  cfg.numAttrs = attrs.count;
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
@@ -606,13 +608,9 @@ int launch_pair_mid(const b200_gemm_problem& q, const PeerOutputs& peers, cudaSt
   cfg.blockDim = dim3(kTileThreadsTwoIssuers);
   cfg.dynamicSmemBytes = kMidSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  const GemmLaunchAttributes attrs = gemm_launch_attributes(2);
+  cfg.attrs = const_cast<cudaLaunchAttribute*>(attrs.list);
+  cfg.numAttrs = attrs.count;
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }

@@ -50,6 +50,10 @@ __global__ void __launch_bounds__(kIssuers == 2 ? kTileThreadsTwoIssuers : kTile
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *sm.tmem_ptr;
+  // The next kernel of the stream may set itself up beside this one from here on: not earlier, or
+  // its CTAs could take TMEM columns that a CTA of this kernel is still about to ask for.
+  grid_launch_dependents();
+  grid_dependency_wait();     // from here on global memory is read and written
   B200_PROBE(p, 1);
 
   const int tiles_m = (p.m + kTileM - 1) / kTileM;
@@ -223,6 +227,9 @@ __global__ void __launch_bounds__(kGenericThreads, 1) umma_generic_kernel(const 
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *sm.tmem_ptr;
+  grid_launch_dependents();   // the next kernel of the stream may set itself up beside this one (not before this
+                              // kernel's TMEM is allocated: its CTAs could take the columns first)
+  grid_dependency_wait();     // the kernel before this one has completed: global memory may be touched
 
   const int tiles_m = (p.m + kTileM - 1) / kTileM;
   const int tiles_n = (p.n + BN - 1) / BN;
@@ -305,7 +312,15 @@ int launch_tma_with(const b200_gemm_problem& q, const PeerOutputs& peers, cudaSt
   if (sms <= 0) return B200_ERR_INTERNAL;
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + BN - 1) / BN);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  kernel<<<grid, kIssuers == 2 ? kTileThreadsTwoIssuers : kTileThreads, launch_smem, stream>>>(p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kIssuers == 2 ? kTileThreadsTwoIssuers : kTileThreads);
+  cfg.dynamicSmemBytes = launch_smem;
+  cfg.stream = stream;
+  const GemmLaunchAttributes attrs = gemm_launch_attributes(1);
+  cfg.attrs = const_cast<cudaLaunchAttribute*>(attrs.list);
+  cfg.numAttrs = attrs.count;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
 
@@ -345,7 +360,15 @@ int launch_generic(const b200_gemm_problem& q, const PeerOutputs& peers, cudaStr
   if (sms <= 0) return B200_ERR_INTERNAL;
   const int64_t tiles = static_cast<int64_t>((q.m + kTileM - 1) / kTileM) * ((q.n + BN - 1) / BN);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  kernel<<<grid, kGenericThreads, launch_smem, stream>>>(p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kGenericThreads);
+  cfg.dynamicSmemBytes = launch_smem;
+  cfg.stream = stream;
+  const GemmLaunchAttributes attrs = gemm_launch_attributes(1);
+  cfg.attrs = const_cast<cudaLaunchAttribute*>(attrs.list);
+  cfg.numAttrs = attrs.count;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
 }  // namespace
