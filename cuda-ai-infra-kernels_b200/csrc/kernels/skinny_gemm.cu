@@ -21,7 +21,6 @@
 #include <cuda_runtime.h>
 
 #include "host_common.h"
-#include "ptx_sm100.cuh"
 #include "tf32_gemm.h"
 
 namespace cg = cooperative_groups;
@@ -67,8 +66,6 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_gemm_kernel(const SkinnyPa
   const int rank = static_cast<int>(cluster.block_rank());
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int col0 = (blockIdx.x / ranks) * kCols;
-  grid_launch_dependents();   // the next kernel of the stream may be scheduled beside this one
-  grid_dependency_wait();     // the kernel before this one has completed: global memory may be touched
 
   extern __shared__ __align__(16) float skinny_smem[];
   float* a_stage = skinny_smem + warp * MR * kChunk;              // this warp's slice of A
@@ -164,9 +161,13 @@ int launch_rows(const SkinnyParams& p, int ranks, cudaStream_t stream) {
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  const GemmLaunchAttributes attrs = gemm_launch_attributes(static_cast<unsigned>(ranks));
-  cfg.attrs = const_cast<cudaLaunchAttribute*>(attrs.list);
-  cfg.numAttrs = attrs.count;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(ranks);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
