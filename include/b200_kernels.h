@@ -242,7 +242,14 @@ int b200_tf32_kernel_from_name(const char* name);
  */
 int b200_tf32_can_implement(int kernel_id, const b200_gemm_problem* problem);
 
-/* Launch exactly one registry entry (launch_gemm<Gemm>, kernel_launcher.h:7-29). */
+/*
+ * Launch exactly one registry entry (launch_gemm<Gemm>, kernel_launcher.h:7-29).
+ * Stream order holds as for any kernel. The tensor-core entries are launched with
+ * programmatic stream serialization: after another such kernel in the same stream
+ * their CTAs may become resident and set themselves up early, but they touch global
+ * memory only once that kernel has completed and its writes are visible, so a call
+ * may consume what the call before it produced.
+ */
 int b200_tf32_gemm_launch(int kernel_id, const b200_gemm_problem* problem,
                           b200_stream_t stream);
 
