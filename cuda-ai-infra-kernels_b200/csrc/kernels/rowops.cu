@@ -213,6 +213,8 @@ struct RowArgs {
 
 template <RowOp kOp, int VPT>
 __global__ void __launch_bounds__(kBlockThreads) row_warp_kernel(const RowArgs a) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= a.rows) return;
   const int nvec = static_cast<int>(a.cols / 4);
@@ -230,6 +232,8 @@ __global__ void __launch_bounds__(kBlockThreads) row_warp_kernel(const RowArgs a
 template <RowOp kOp, int VPT, int kThreads>
 __global__ void __launch_bounds__(kThreads) row_block_kernel(const RowArgs a) {
   __shared__ float scratch[2 * (kThreads / 32)];
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t row = blockIdx.x;
   const int nvec = static_cast<int>(a.cols / 4);
   const float4* x_row = reinterpret_cast<const float4*>(a.x + row * a.cols);
@@ -253,6 +257,8 @@ constexpr int64_t kStagedPartFloats = 24576;  // largest preferred share per CTA
 template <RowOp kOp, bool kCluster>
 __global__ void __launch_bounds__(kStagedThreads) row_staged_kernel(const RowArgs a) {
   extern __shared__ __align__(128) uint8_t staged_raw[];
+  grid_launch_dependents();
+  grid_dependency_wait();
   // This CTA's vectors [begin, begin + nvec) of row r.
   int64_t r = blockIdx.x;
   int begin = 0;
@@ -367,6 +373,8 @@ constexpr size_t staged_smem_bytes(int64_t share_floats) {
 template <RowOp kOp>
 __global__ void __launch_bounds__(kBlockThreads) row_stream_kernel(const RowArgs a) {
   __shared__ float scratch[2 * kWarpsPerBlock];
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t row = blockIdx.x;
   const float* x_row = a.x + row * a.cols;
   float* y_row = a.y + row * a.cols;
@@ -398,17 +406,32 @@ __global__ void __launch_bounds__(kBlockThreads) row_stream_kernel(const RowArgs
 
 // ------------------------------------------------------------------- dispatch
 
+// Launch under programmatic stream serialization: the CTAs of a kernel that follows another of
+// these in the stream are scheduled as that kernel's last CTAs drain, and wait (first statement of
+// the kernels) until it has completed, instead of being launched only then.
+template <typename Kernel>
+int launch_serialized(Kernel kernel, int64_t blocks, int threads, const RowArgs& a, cudaStream_t s, size_t smem = 0,
+                      unsigned cluster = 1) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+  cfg.blockDim = dim3(static_cast<unsigned>(threads));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  const GemmLaunchAttributes attrs = gemm_launch_attributes(cluster);   // serialization, and the cluster if there is one
+  cfg.attrs = const_cast<cudaLaunchAttribute*>(attrs.list);
+  cfg.numAttrs = attrs.count;
+  if (cudaLaunchKernelEx(&cfg, kernel, a) != cudaSuccess) return launch_failed();
+  return launch_status();
+}
+
 template <RowOp kOp, int VPT>
 int launch_warp(const RowArgs& a, cudaStream_t s) {
-  const int64_t blocks = (a.rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  row_warp_kernel<kOp, VPT><<<static_cast<unsigned>(blocks), kBlockThreads, 0, s>>>(a);
-  return launch_status();
+  return launch_serialized(row_warp_kernel<kOp, VPT>, (a.rows + kWarpsPerBlock - 1) / kWarpsPerBlock, kBlockThreads, a, s);
 }
 
 template <RowOp kOp, int VPT, int kThreads>
 int launch_block(const RowArgs& a, cudaStream_t s) {
-  row_block_kernel<kOp, VPT, kThreads><<<static_cast<unsigned>(a.rows), kThreads, 0, s>>>(a);
-  return launch_status();
+  return launch_serialized(row_block_kernel<kOp, VPT, kThreads>, a.rows, kThreads, a, s);
 }
 
 template <RowOp kOp>
@@ -457,30 +480,16 @@ int launch_rows(const RowArgs& a, cudaStream_t s) {
     constexpr size_t kMaxSmem = staged_smem_bytes(kStagedMaxFloats);
     if (a.cols <= 24576) {
       if (!ensure_dynamic_smem<row_staged_kernel<kOp, false>, kMaxSmem>()) return B200_ERR_LAUNCH_FAILED;
-      row_staged_kernel<kOp, false><<<static_cast<unsigned>(a.rows), kStagedThreads, staged_smem_bytes(a.cols), s>>>(a);
-      return launch_status();
+      return launch_serialized(row_staged_kernel<kOp, false>, a.rows, kStagedThreads, a, s, staged_smem_bytes(a.cols));
     }
     int ranks = 2;
     while (ranks < 8 && (a.cols + ranks - 1) / ranks > kStagedPartFloats) ranks *= 2;
     const int64_t share_vectors = (nvec + ranks - 1) / ranks;
     if (!ensure_dynamic_smem<row_staged_kernel<kOp, true>, kMaxSmem>()) return B200_ERR_LAUNCH_FAILED;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(a.rows * ranks));
-    cfg.blockDim = dim3(kStagedThreads);
-    cfg.dynamicSmemBytes = staged_smem_bytes(4 * share_vectors);
-    cfg.stream = s;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = ranks;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, row_staged_kernel<kOp, true>, a) != cudaSuccess) return launch_failed();
-    return launch_status();
+    return launch_serialized(row_staged_kernel<kOp, true>, a.rows * ranks, kStagedThreads, a, s,
+                             staged_smem_bytes(4 * share_vectors), static_cast<unsigned>(ranks));
   }
-  row_stream_kernel<kOp><<<static_cast<unsigned>(a.rows), kBlockThreads, 0, s>>>(a);
-  return launch_status();
+  return launch_serialized(row_stream_kernel<kOp>, a.rows, kBlockThreads, a, s);
 }
 
 }  // namespace
