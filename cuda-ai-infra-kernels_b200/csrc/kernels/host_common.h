@@ -51,7 +51,7 @@ inline int launch_failed() {
   return B200_ERR_LAUNCH_FAILED;
 }
 
-// Launch attributes of the tcgen05 GEMM kernels: a cluster of `cluster_x` CTAs (1: none) and
+// Launch attributes of the GEMM and row kernels: a cluster of `cluster_x` CTAs (1: none) and
 // programmatic stream serialization. With the latter a kernel may start while the kernel before it
 // in the stream is still running, once all CTAs of that kernel have executed
 // griddepcontrol.launch_dependents (the kernels here do after their set-up) or exited; the kernels

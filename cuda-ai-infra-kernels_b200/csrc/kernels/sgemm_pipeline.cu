@@ -286,6 +286,11 @@ __global__ void __launch_bounds__(Grid::kThreads, kCtasPerSm) sgemm_pipeline_ker
     mbar_init_fence();
   }
   __syncthreads();
+  // Launched under programmatic stream serialization (gemm_launch_attributes): the kernel after
+  // this one in the stream may be scheduled from here on, and this one touches global memory only
+  // once the kernel before it has completed.
+  grid_launch_dependents();
+  grid_dependency_wait();
 
   if (Grid::kProducerWarp && tid >= Grid::kConsumerThreads) {
     // ------------------------------------------------- dedicated producer warp
@@ -491,13 +496,9 @@ int launch_cluster_split(const PipelineParams& p, cudaStream_t stream) {
   cfg.blockDim = dim3(Grid::kThreads);
   cfg.dynamicSmemBytes = Layout::kBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = kSplit;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  const GemmLaunchAttributes attrs = gemm_launch_attributes(kSplit);
+  cfg.attrs = const_cast<cudaLaunchAttribute*>(attrs.list);
+  cfg.numAttrs = attrs.count;
   if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
@@ -575,7 +576,15 @@ int launch_pipeline(const float* a, const float* b, float* c, const PeerOutputs&
   const int64_t units = kStreamK ? tiles * p.k_blocks : tiles;
   const int64_t slots = static_cast<int64_t>(sms) * kCtasPerSm;
   const int grid = static_cast<int>(units < slots ? units : slots);
-  kernel<<<grid, Grid::kThreads, Layout::kBytes, stream>>>(p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(Grid::kThreads);
+  cfg.dynamicSmemBytes = Layout::kBytes;
+  cfg.stream = stream;
+  const GemmLaunchAttributes attrs = gemm_launch_attributes(1);
+  cfg.attrs = const_cast<cudaLaunchAttribute*>(attrs.list);
+  cfg.numAttrs = attrs.count;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return launch_failed();
   return launch_status();
 }
 
