@@ -112,3 +112,23 @@ def test_baseline_config_softmax_32768x1024(abi):
     torch.testing.assert_close(y.double().sum(dim=1), torch.ones(32768, dtype=torch.float64, device="cuda"),
                                atol=1e-5, rtol=0)
     assert bool((y > 0).all()) and bool((y <= 1).all())
+
+
+@pytest.mark.parametrize("shape", [(64, 1024), (16, 4096), (6, 16384), (3, 40000), (9, 1001)])
+def test_calls_in_a_row_read_what_the_last_one_wrote(abi, shape):
+    # The row kernels are launched under programmatic stream serialization (a kernel is scheduled
+    # while the one before it drains and waits for it before its first load): RMSNorm, softmax of
+    # its output, RMSNorm of that, with nothing between them in the stream.
+    x, w = oracle.rmsnorm_inputs(*shape, seed=3)
+    x_dev, w_dev = x.cuda(), w.cuda()
+    y = [torch.full_like(x_dev, float("nan")) for _ in range(3)]
+    torch.cuda.synchronize()
+    stream = current_stream_ptr()
+    assert abi.b200_rmsnorm(0, x_dev.data_ptr(), w_dev.data_ptr(), y[0].data_ptr(), shape[0], shape[1], 1e-6, stream) == 0
+    assert abi.b200_softmax(0, y[0].data_ptr(), y[1].data_ptr(), shape[0], shape[1], stream) == 0
+    assert abi.b200_rmsnorm(0, y[1].data_ptr(), w_dev.data_ptr(), y[2].data_ptr(), shape[0], shape[1], 1e-6, stream) == 0
+    step1 = oracle.rmsnorm_fp64(x, w, 1e-6)
+    check(y[0], step1)
+    step2 = oracle.softmax_fp64(y[0].cpu())
+    check(y[1], step2)
+    check(y[2], oracle.rmsnorm_fp64(y[1].cpu(), w, 1e-6))

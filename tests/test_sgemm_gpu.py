@@ -203,3 +203,26 @@ def test_cluster_split_is_exact_on_integers_and_matches_the_oracle(abi, impl, sh
     check_against_oracle(first, a_cpu, b_cpu)
     assert torch.equal(abi_sgemm(abi, impl, a_dev, b_dev), first)          # partial tiles are added in rank order
     assert_device_clean(abi)
+
+
+@pytest.mark.parametrize("name", PIPELINE)
+@pytest.mark.parametrize("n", [128, 512, 19 * 1024])
+def test_calls_in_a_row_read_what_the_last_one_wrote(abi, name, n):
+    # The pipeline kernel is launched under programmatic stream serialization (it may become resident
+    # while the kernel before it still runs and waits for it before touching global memory): three
+    # calls with nothing between them, C of one the B of the next. A in {-1, 0, 1}, K = 128: exact.
+    m = k = 128
+    g = torch.Generator().manual_seed(n)
+    a = torch.randint(-1, 2, (m, k), generator=g).float()
+    b = torch.randint(-2, 3, (k, n), generator=g).float()
+    a_dev = oracle.to_device_preserving_strides(a.t().contiguous().t(), "cuda")   # column-major [M, K]
+    outs = [b.cuda()] + [torch.full((m, n), float("nan"), device="cuda") for _ in range(3)]
+    impl = abi.b200_sgemm_impl_from_name(name.encode())
+    torch.cuda.synchronize()
+    for i in range(3):
+        assert abi.b200_sgemm(impl, a_dev.data_ptr(), outs[i].data_ptr(), outs[i + 1].data_ptr(), m, n, k, current_stream_ptr()) == 0
+    expected = b.double()
+    for i in range(3):
+        expected = a.double() @ expected
+    torch.testing.assert_close(outs[3].cpu().double(), expected, atol=0, rtol=0)
+    assert_device_clean(abi)

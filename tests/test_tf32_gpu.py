@@ -621,3 +621,37 @@ def test_pair_kernel_goes_from_whole_tiles_to_half_tiles(abi, size, k):
     expected = oracle.adaptive_gemm_fp64(a, b, c, 1.0, 0.5, "relu")
     torch.testing.assert_close(d.cpu(), expected, atol=0, rtol=0)
     assert_device_clean(abi)
+
+
+# ------------------------------------------------ calls in a row, each reading what the last one wrote
+# The tensor-core kernels are launched under programmatic stream serialization: a kernel may become
+# resident while the one before it still runs, and waits for it before touching global memory. Six
+# calls with nothing between them, each taking the previous output as its source C.
+
+
+@pytest.mark.parametrize("alias,shape", [("narrow_relu", (256, 256, 96)), ("fast_relu", (640, 512, 160)), ("wide_relu", (512, 1024, 64)),
+                                         ("pair_relu", (1024, 768, 128)), ("pair_mid_relu", (1024, 512, 192)),
+                                         ("splitk_relu", (128, 256, 1024)), ("pair_splitk_relu", (512, 256, 1024)),
+                                         ("swap_relu", (8, 512, 1024)), ("fallback_relu", (130, 132, 70))])
+def test_calls_in_a_row_read_what_the_last_one_wrote(abi, alias, shape):
+    kernel_id = abi.b200_tf32_kernel_from_name(alias.encode())
+    assert kernel_id > 0
+    m, n, k = shape
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randint(-2, 3, (m, k), generator=g).float()
+    b = torch.randint(-2, 3, (k, n), generator=g).float()
+    c = torch.randint(-8, 9, (m, n), generator=g).float()
+    a_dev, b_dev = a.cuda(), b.cuda()
+    outs = [c.cuda()] + [torch.full((m, n), float("nan"), device="cuda") for _ in range(6)]
+    torch.cuda.synchronize()
+    for i in range(6):   # nothing else enters the stream in between
+        q = GemmProblem(m, n, k, a_dev.data_ptr(), b_dev.data_ptr(), outs[i].data_ptr(), outs[i + 1].data_ptr(), k, n, n, n,
+                        1.0, 0.5, RELU, None)
+        assert abi.b200_tf32_gemm_launch(kernel_id, ctypes.byref(q), current_stream_ptr()) == 0
+    expected = c.double()
+    product = a.double() @ b.double()
+    for i in range(6):
+        expected = torch.relu(product + 0.5 * expected)
+    # Small whole numbers and halvings: every intermediate is exact in FP32.
+    torch.testing.assert_close(outs[6].cpu().double(), expected, atol=0, rtol=0)
+    assert_device_clean(abi)
