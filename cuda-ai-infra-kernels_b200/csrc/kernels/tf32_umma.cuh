@@ -162,10 +162,13 @@ __host__ __device__ constexpr size_t smem_bytes() {
          kStagingBytes;
 }
 
-// Two accumulator buffers of kIssuers partial accumulators each; BN in {64,128,256} keeps this a power of two.
+// Two accumulator buffers of kIssuers partial accumulators each, BN columns apart; the allocation
+// is the next power of two (a 192-wide tile's two buffers take 384 of 512 columns).
 template <int BN, int kIssuers = 1>
 __host__ __device__ constexpr uint32_t tmem_columns() {
-  return 2 * kIssuers * BN < 32 ? 32 : 2 * kIssuers * BN;
+  uint32_t columns = 32;
+  while (columns < 2u * kIssuers * BN) columns *= 2;
+  return columns;
 }
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int* tm, int* tn) {

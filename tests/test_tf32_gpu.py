@@ -508,14 +508,15 @@ def test_long_k_through_alternating_issuers(abi, entry, shape):
 
 @pytest.mark.parametrize("alias,shape", [("fast", (2048, 1280, 160)), ("fast_relu", (2048, 1280, 2720)),
                                          ("narrow", (1280, 1024, 160)), ("narrow_relu", (2560, 1024, 96)),
-                                         ("wide", (2048, 2560, 96)), ("fast_stage3", (2048, 1280, 100))])
+                                         ("wide", (2048, 2560, 96)), ("medium", (2048, 1920, 96)), ("medium_relu", (2048, 2000, 2080)),
+                                         ("fast_stage3", (2048, 1280, 100))])
 def test_persistent_ctas_walk_several_tiles(abi, alias, shape):
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     kernel_id = abi.b200_tf32_kernel_from_name(alias.encode())
     assert kernel_id > 0
     epilogue = RELU if alias.endswith("relu") else LINEAR
     m, n, k = shape
-    tile_n = {"fast": 128, "narrow": 64, "wide": 256}[alias.split("_")[0]]
+    tile_n = {"fast": 128, "narrow": 64, "wide": 256, "medium": 192}[alias.split("_")[0]]
     assert (m // 128) * (n // tile_n) > sms, "the shape must give some CTA a second tile"
     g = torch.Generator().manual_seed(m + k)
     a = torch.randint(-4, 5, (m, k), generator=g).float()
@@ -630,6 +631,7 @@ def test_pair_kernel_goes_from_whole_tiles_to_half_tiles(abi, size, k):
 
 
 @pytest.mark.parametrize("alias,shape", [("narrow_relu", (256, 256, 96)), ("fast_relu", (640, 512, 160)), ("wide_relu", (512, 1024, 64)),
+                                         ("medium_relu", (384, 768, 96)),
                                          ("pair_relu", (1024, 768, 128)), ("pair_mid_relu", (1024, 512, 192)),
                                          ("splitk_relu", (128, 256, 1024)), ("pair_splitk_relu", (512, 256, 1024)),
                                          ("swap_relu", (8, 512, 1024)), ("fallback_relu", (130, 132, 70))])
