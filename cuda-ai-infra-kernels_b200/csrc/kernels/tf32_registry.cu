@@ -123,14 +123,22 @@ bool gate_wide(const b200_gemm_problem& q, int sms) {
   const int64_t rounds_128 = (tiles_of(q, 128) + sms - 1) / sms, rounds_256 = (tiles_of(q, 256) + sms - 1) / sms;
   return 100 * rounds_128 > 145 * rounds_256;
 }
-// 128 x 192 tiles where they fit one round and 128 x 128 tiles do not: at these sizes a CTA's time is
-// set by the operand bytes it takes in per K block (16 KiB of A + 128 bytes per column of B), so of
-// the tile widths that run in one round the narrowest wins: 40 KiB against the 128 x 256 tile's 48.
+// Tile widths between the reference's: at sizes that run in one round a CTA's time is set by the
+// operand bytes it takes in per K block (16 KiB of A + 128 bytes per column of B), so of the widths
+// that fit one round the narrowest wins (128 x 96: 28 KiB, 128: 32, 160: 36, 192: 40, 224: 44, 256: 48).
 // Graph-timed with a source and ReLU, 128 x 192 / 128 x 256 / CTA pairs / cuBLASLt fused: 1792^3
 // 22.1 / 25.0 / 26.2 / 24.1 us, 1664^3 21.2 / 23.7 / 24.9 / 23.2, 1536 x 2048 x 2048 24.3 / 27.5 / 28.6 / 26.3,
 // 1280 x 2688 x 1024 15.7 / 17.7 / 18.9 / 17.7, 1792 x 1792 x 4096 46.7 / 50.0 / 50.0 / 46.6 (tried before
 // the CTA pairs for that reason).
-bool gate_medium(const b200_gemm_problem& q, int sms) { return tiles_of(q, 192) <= sms && tiles_of(q, 128) > sms; }
+int narrowest_one_round_width(const b200_gemm_problem& q, int sms) {
+  for (int width = 64; width <= 256; width += 32)
+    if (tiles_of(q, width) <= sms) return width;
+  return 0;
+}
+bool gate_width96(const b200_gemm_problem& q, int sms) { return narrowest_one_round_width(q, sms) == 96; }
+bool gate_width160(const b200_gemm_problem& q, int sms) { return narrowest_one_round_width(q, sms) == 160; }
+bool gate_medium(const b200_gemm_problem& q, int sms) { return narrowest_one_round_width(q, sms) == 192; }
+bool gate_width224(const b200_gemm_problem& q, int sms) { return narrowest_one_round_width(q, sms) == 224; }
 // 128 x 64 tiles when 128-wide ones would leave more than half the SMs idle.
 // CTA pairs (256 x 256 per pair) when they fill at least one round of pairs.
 // (Half tiles filling one round, e.g. 1536^3 with 72 halves on 74 pairs, measured level with the
@@ -226,6 +234,15 @@ const RegistryEntry kRegistry[] = {
     {meta_pair_mid(39, "umma256x128stage8pair", "pair_mid", B200_EPILOGUE_LINEAR), &pair_mid_entry<B200_EPILOGUE_LINEAR>, &gate_pair_mid},
     {meta_pair_mid(40, "umma256x128stage8pairRelu", "pair_mid_relu", B200_EPILOGUE_RELU), &pair_mid_entry<B200_EPILOGUE_RELU>, &gate_pair_mid},
     {meta_pair_mid(41, "umma256x128stage8pairGelu", "pair_mid_gelu", B200_EPILOGUE_GELU), &pair_mid_entry<B200_EPILOGUE_GELU>, &gate_pair_mid},
+    {meta(48, "umma128x96stage6tma", "width96", B200_EPILOGUE_LINEAR, 96, 6, 4), &tile_entry<96, 6, B200_EPILOGUE_LINEAR>, &gate_width96},
+    {meta(49, "umma128x96stage6tmaRelu", "width96_relu", B200_EPILOGUE_RELU, 96, 6, 4), &tile_entry<96, 6, B200_EPILOGUE_RELU>, &gate_width96},
+    {meta(50, "umma128x96stage6tmaGelu", "width96_gelu", B200_EPILOGUE_GELU, 96, 6, 4), &tile_entry<96, 6, B200_EPILOGUE_GELU>, &gate_width96},
+    {meta(51, "umma128x160stage5tma", "width160", B200_EPILOGUE_LINEAR, 160, 5, 4), &tile_entry<160, 5, B200_EPILOGUE_LINEAR>, &gate_width160},
+    {meta(52, "umma128x160stage5tmaRelu", "width160_relu", B200_EPILOGUE_RELU, 160, 5, 4), &tile_entry<160, 5, B200_EPILOGUE_RELU>, &gate_width160},
+    {meta(53, "umma128x160stage5tmaGelu", "width160_gelu", B200_EPILOGUE_GELU, 160, 5, 4), &tile_entry<160, 5, B200_EPILOGUE_GELU>, &gate_width160},
+    {meta(54, "umma128x224stage4tma", "width224", B200_EPILOGUE_LINEAR, 224, 4, 4), &tile_entry<224, 4, B200_EPILOGUE_LINEAR>, &gate_width224},
+    {meta(55, "umma128x224stage4tmaRelu", "width224_relu", B200_EPILOGUE_RELU, 224, 4, 4), &tile_entry<224, 4, B200_EPILOGUE_RELU>, &gate_width224},
+    {meta(56, "umma128x224stage4tmaGelu", "width224_gelu", B200_EPILOGUE_GELU, 224, 4, 4), &tile_entry<224, 4, B200_EPILOGUE_GELU>, &gate_width224},
     {meta(45, "umma128x192stage4tma", "medium", B200_EPILOGUE_LINEAR, 192, 4, 4), &tile_entry<192, 4, B200_EPILOGUE_LINEAR>, &gate_medium},
     {meta(46, "umma128x192stage4tmaRelu", "medium_relu", B200_EPILOGUE_RELU, 192, 4, 4), &tile_entry<192, 4, B200_EPILOGUE_RELU>, &gate_medium},
     {meta(47, "umma128x192stage4tmaGelu", "medium_gelu", B200_EPILOGUE_GELU, 192, 4, 4), &tile_entry<192, 4, B200_EPILOGUE_GELU>, &gate_medium},

@@ -342,10 +342,12 @@ template <int BN, int kAct, int kShare, int kIssuers = 1>
 __device__ __forceinline__ void epilogue_tile_boxed(const UmmaParams& p, const EpilogueArgs& ep, uint32_t tmem_acc, int quarter,
                                                     int part, int lane, int m0, int n0, SourceQuads& src, uint8_t* boxes,
                                                     uint32_t& uses, uint8_t* first_box = nullptr) {
-  constexpr int kMine = BN / 32 / kShare;   // chunks of this warp
+  constexpr int kChunks = BN / 32;
+  constexpr int kMine = (kChunks + kShare - 1) / kShare;   // chunks of this warp; one fewer for the later warps of a
+                                                            // quarter when the tile's chunks do not divide evenly
   constexpr int kBoxes = boxes_per_warp<kShare>();
   static_assert(kShare == 1 || kShare == 2, "four or eight epilogue warps");
-  static_assert(kMine >= 1 && BN % (32 * kShare) == 0, "every warp has work");
+  static_assert(BN % 32 == 0 && kChunks >= kShare, "every warp has work");
   const int row0 = m0 + quarter * 32;
   const uint32_t tmem_row = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
   uint32_t raw_even[32], raw_odd[32];
@@ -354,7 +356,10 @@ __device__ __forceinline__ void epilogue_tile_boxed(const UmmaParams& p, const E
 #pragma unroll
   for (int i = 0; i < kMine; i += 2) {
     const int chunk = part + i * kShare;
-    if (n0 + chunk * 32 >= ep.n) break;   // uniform across the warp
+    constexpr bool kEven = kChunks % kShare == 0;   // then every warp of a quarter has kMine chunks
+    if ((!kEven && chunk >= kChunks) || n0 + chunk * 32 >= ep.n) break;   // uniform across the warp
+    const bool second = i + 1 < kMine && (kEven || chunk + kShare < kChunks);       // the warp has a chunk after this one
+    const bool third = i + 2 < kMine && (kEven || chunk + 2 * kShare < kChunks);    // and one after that
     uint8_t* box = first_box;
     if (i > 0 || first_box == nullptr) {
       box = boxes + (uses++ % kBoxes) * kOutBoxBytes;
@@ -369,17 +374,17 @@ __device__ __forceinline__ void epilogue_tile_boxed(const UmmaParams& p, const E
         add_partial_accumulator(raw_even, tmem_row + BN + chunk * 32);
       }
     }
-    if (i + 1 < kMine) {
+    if (second) {
       tmem_ld_32x32(tmem_row + (chunk + kShare) * 32, raw_odd);
       fetch_source_coalesced(ep, src, row0, n0 + (chunk + kShare) * 32, lane);
     }
     finish_chunk_boxed<kAct>(p, ep, raw_even, row0, n0 + chunk * 32, lane, box);
-    if (i + 1 < kMine) {
+    if (second) {
       box = boxes + (uses++ % kBoxes) * kOutBoxBytes;
       stage_source_boxed<kBoxes>(ep, src, lane, box);
       tmem_ld_wait();
       if constexpr (kIssuers == 2) add_partial_accumulator(raw_odd, tmem_row + BN + (chunk + kShare) * 32);
-      if (i + 2 < kMine) {
+      if (third) {
         tmem_ld_32x32(tmem_row + (chunk + 2 * kShare) * 32, raw_even);
         fetch_source_coalesced(ep, src, row0, n0 + (chunk + 2 * kShare) * 32, lane);
       }

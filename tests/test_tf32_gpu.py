@@ -157,10 +157,16 @@ def test_auto_dispatch_order(abi):
     a, b, _ = oracle.adaptive_inputs(256 * 8, 256 * ((sms // 2 + 7) // 8), 64)
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 20              # pair
     assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 21
-    # In between: 128 x 256 tiles on at least three quarters of the SMs.
-    a, b, _ = oracle.adaptive_inputs(128 * 8, 256 * ((3 * sms // 4 + 7) // 8), 64)
+    # In between: the narrowest tile width (a multiple of 32 columns) whose tiles run in one round.
+    a, b, _ = oracle.adaptive_inputs(128 * 8, 256 * (sms // 8), 64)            # only 128 x 256 tiles do
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 16              # wide
     assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 17
+    for width, linear_id in ((224, 54), (192, 45), (160, 51), (96, 48)):
+        n = width * (sms // 8)                                                  # 8 x (sms // 8) tiles of that width
+        a, b, _ = oracle.adaptive_inputs(128 * 8, n, 64)
+        assert 8 * -(-n // (width - 32)) > sms                                  # one width narrower needs a second round
+        assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == linear_id
+        assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == linear_id + 1
     a, b, _ = oracle.adaptive_inputs(33, 65, 17)
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 3               # fallback
     assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 9  # fallback_relu
