@@ -244,6 +244,10 @@ def test_sgemm_gather_fans_out_every_tile(abi):
     (36, (12, 264, 512)),      # operands swapped, K split over a cluster
     (39, (300, 264, 160)),     # CTA pair, 256 x 128 tiles, two issuers, ragged
     (42, (300, 200, 1024)),    # CTA pairs with K split over the cluster
+    (48, (200, 296, 100)),     # 128 x 96 tiles, two MMA threads, three chunks on two epilogue warps
+    (51, (130, 488, 64)),      # 128 x 160 tiles
+    (45, (256, 388, 96)),      # 128 x 192 tiles
+    (54, (200, 676, 64)),      # 128 x 224 tiles
 ])
 def test_tf32_gather_fans_out_every_element(abi, kernel, shape):
     import ctypes
