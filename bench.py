@@ -459,7 +459,8 @@ def measure_extras(pkg, peaks: dict, device_index: int, warmup: int) -> dict:
     # 1400 MHz, sw_power_cap) slows a 20 us problem by a third and the two arms unequally; the
     # median SM clock of each arm's measurement is part of the row.
     sweep = []
-    for m_, n_, k_ in ((512, 512, 512), (1536, 1536, 1536), (2048, 2048, 2048), (2304, 2304, 2304), (3072, 3072, 3072),
+    for m_, n_, k_ in ((512, 512, 512), (1280, 1280, 1280), (1536, 1536, 1536), (1792, 1792, 1792), (2048, 2048, 2048),
+                       (2304, 2304, 2304), (3072, 3072, 3072),
                        (1024, 1024, 4096), (1024, 4096, 4096), (512, 4096, 4096), (64, 4096, 4096), (1280, 1280, 8192),
                        (1024, 2048, 4096), (4096, 4096, 512)):
         a, b, c = (torch.randn(m_, k_, device=dev), torch.randn(k_, n_, device=dev), torch.randn(m_, n_, device=dev))
