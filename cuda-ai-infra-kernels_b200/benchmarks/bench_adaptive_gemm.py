@@ -35,11 +35,11 @@ from cuda_ai_kernels.benchmark import cuda_event_benchmark, cuda_graph_benchmark
 from cuda_ai_kernels.env import collect_env  # noqa: E402
 
 # "skinny*" runs only M <= 16 and is reported as skipped elsewhere.
-LINEAR_KERNELS = ["auto", "skinny", "swap", "splitk", "pair_splitk", "pair_mid", "pair", "width96", "width160", "medium", "width224", "wide", "narrow", "fast", "fallback", "fast_mwarp", "fallback_mwarp",
+LINEAR_KERNELS = ["auto", "skinny", "swap", "splitk", "pair_splitk", "pair_mid", "pair", "width32", "width96", "width160", "medium", "width224", "wide", "narrow", "fast", "fallback", "fast_mwarp", "fallback_mwarp",
                   "fast_stage3", "fast_stage2", "cublas", "cublaslt"]
-RELU_KERNELS = ["auto", "skinny_relu", "swap_relu", "splitk_relu", "pair_splitk_relu", "pair_mid_relu", "pair_relu", "width96_relu", "width160_relu", "medium_relu", "width224_relu", "wide_relu", "narrow_relu", "fast_relu", "fallback_relu", "cublas",
+RELU_KERNELS = ["auto", "skinny_relu", "swap_relu", "splitk_relu", "pair_splitk_relu", "pair_mid_relu", "pair_relu", "width32_relu", "width96_relu", "width160_relu", "medium_relu", "width224_relu", "wide_relu", "narrow_relu", "fast_relu", "fallback_relu", "cublas",
                 "cublaslt"]
-GELU_KERNELS = ["auto", "skinny_gelu", "swap_gelu", "splitk_gelu", "pair_splitk_gelu", "pair_mid_gelu", "pair_gelu", "width96_gelu", "width160_gelu", "medium_gelu", "width224_gelu", "wide_gelu", "narrow_gelu", "fast_gelu", "fallback_gelu"]
+GELU_KERNELS = ["auto", "skinny_gelu", "swap_gelu", "splitk_gelu", "pair_splitk_gelu", "pair_mid_gelu", "pair_gelu", "width32_gelu", "width96_gelu", "width160_gelu", "medium_gelu", "width224_gelu", "wide_gelu", "narrow_gelu", "fast_gelu", "fallback_gelu"]
 REL_FROBENIUS = 5e-3
 
 

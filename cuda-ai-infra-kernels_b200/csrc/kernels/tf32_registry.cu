@@ -125,16 +125,19 @@ bool gate_wide(const b200_gemm_problem& q, int sms) {
 }
 // Tile widths between the reference's: at sizes that run in one round a CTA's time is set by the
 // operand bytes it takes in per K block (16 KiB of A + 128 bytes per column of B), so of the widths
-// that fit one round the narrowest wins (128 x 96: 28 KiB, 128: 32, 160: 36, 192: 40, 224: 44, 256: 48).
+// that fit one round the narrowest wins (128 x 32: 20 KiB, 64: 24, 96: 28, 128: 32, 160: 36, 192: 40,
+// 224: 44, 256: 48). 128 x 32 / 128 x 64 / cuBLASLt fused: 256^3 4.4 / 4.8 / 5.1-5.4 us, 512^3 5.5 / 6.0 / 5.7-5.8,
+// 640^3 6.1 / 6.7 / 6.4, 768^3 6.75 / 7.3 / 7.5.
 // Graph-timed with a source and ReLU, 128 x 192 / 128 x 256 / CTA pairs / cuBLASLt fused: 1792^3
 // 22.1 / 25.0 / 26.2 / 24.1 us, 1664^3 21.2 / 23.7 / 24.9 / 23.2, 1536 x 2048 x 2048 24.3 / 27.5 / 28.6 / 26.3,
 // 1280 x 2688 x 1024 15.7 / 17.7 / 18.9 / 17.7, 1792 x 1792 x 4096 46.7 / 50.0 / 50.0 / 46.6 (tried before
 // the CTA pairs for that reason).
 int narrowest_one_round_width(const b200_gemm_problem& q, int sms) {
-  for (int width = 64; width <= 256; width += 32)
+  for (int width = 32; width <= 256; width += 32)
     if (tiles_of(q, width) <= sms) return width;
   return 0;
 }
+bool gate_width32(const b200_gemm_problem& q, int sms) { return narrowest_one_round_width(q, sms) == 32; }
 bool gate_width96(const b200_gemm_problem& q, int sms) { return narrowest_one_round_width(q, sms) == 96; }
 bool gate_width160(const b200_gemm_problem& q, int sms) { return narrowest_one_round_width(q, sms) == 160; }
 bool gate_medium(const b200_gemm_problem& q, int sms) { return narrowest_one_round_width(q, sms) == 192; }
@@ -208,7 +211,9 @@ bool gate_pair_mid(const b200_gemm_problem& q, int sms) {
 // Measured against the split-K tile kernel: ahead up to 16 rows (16 x 8192 x 1024: 11.7 vs 16.5 us,
 // 16 x 4096 x 4096: 12.7 vs 16.8, cuBLAS 12.9), level or behind from 32 rows on (64 x 4096 x 4096: 19.7 vs 18.2).
 bool gate_swap(const b200_gemm_problem& q, int) { return q.m <= 16; }
-bool gate_narrow(const b200_gemm_problem& q, int sms) { return tiles_of(q, 128) * 2 <= sms && q.n > 64; }
+bool gate_narrow(const b200_gemm_problem& q, int sms) {
+  return (tiles_of(q, 128) * 2 <= sms && q.n > 64) || narrowest_one_round_width(q, sms) == 64;
+}
 
 // Dispatch order. Entries with ids >= 16 exist only here and are tried first by
 // automatic dispatch when their shape gate accepts the problem. The eight
@@ -234,6 +239,9 @@ const RegistryEntry kRegistry[] = {
     {meta_pair_mid(39, "umma256x128stage8pair", "pair_mid", B200_EPILOGUE_LINEAR), &pair_mid_entry<B200_EPILOGUE_LINEAR>, &gate_pair_mid},
     {meta_pair_mid(40, "umma256x128stage8pairRelu", "pair_mid_relu", B200_EPILOGUE_RELU), &pair_mid_entry<B200_EPILOGUE_RELU>, &gate_pair_mid},
     {meta_pair_mid(41, "umma256x128stage8pairGelu", "pair_mid_gelu", B200_EPILOGUE_GELU), &pair_mid_entry<B200_EPILOGUE_GELU>, &gate_pair_mid},
+    {meta(57, "umma128x32stage8tma", "width32", B200_EPILOGUE_LINEAR, 32, 8, 4), &tile_entry<32, 8, B200_EPILOGUE_LINEAR>, &gate_width32},
+    {meta(58, "umma128x32stage8tmaRelu", "width32_relu", B200_EPILOGUE_RELU, 32, 8, 4), &tile_entry<32, 8, B200_EPILOGUE_RELU>, &gate_width32},
+    {meta(59, "umma128x32stage8tmaGelu", "width32_gelu", B200_EPILOGUE_GELU, 32, 8, 4), &tile_entry<32, 8, B200_EPILOGUE_GELU>, &gate_width32},
     {meta(48, "umma128x96stage6tma", "width96", B200_EPILOGUE_LINEAR, 96, 6, 4), &tile_entry<96, 6, B200_EPILOGUE_LINEAR>, &gate_width96},
     {meta(49, "umma128x96stage6tmaRelu", "width96_relu", B200_EPILOGUE_RELU, 96, 6, 4), &tile_entry<96, 6, B200_EPILOGUE_RELU>, &gate_width96},
     {meta(50, "umma128x96stage6tmaGelu", "width96_gelu", B200_EPILOGUE_GELU, 96, 6, 4), &tile_entry<96, 6, B200_EPILOGUE_GELU>, &gate_width96},

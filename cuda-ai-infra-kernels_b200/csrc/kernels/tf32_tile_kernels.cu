@@ -390,6 +390,7 @@ int launch_tf32_tile(int tile_n, int stages, int act, const b200_gemm_problem& q
   B200_TILE_CASE(160, 5)
   B200_TILE_CASE(128, 6)
   B200_TILE_CASE(96, 6)
+  B200_TILE_CASE(32, 8)
   B200_TILE_CASE(64, 8)
 #undef B200_TILE_CASE
   // Configurations that exist with the linear epilogue only (the reference's stage and warp-shape variants).

@@ -347,10 +347,11 @@ __device__ __forceinline__ void epilogue_tile_boxed(const UmmaParams& p, const E
                                                             // quarter when the tile's chunks do not divide evenly
   constexpr int kBoxes = boxes_per_warp<kShare>();
   static_assert(kShare == 1 || kShare == 2, "four or eight epilogue warps");
-  static_assert(BN % 32 == 0 && kChunks >= kShare, "every warp has work");
+  static_assert(BN % 32 == 0 && kChunks >= 1, "whole 32-column chunks (a 32-wide tile leaves the later warps of a quarter idle)");
   const int row0 = m0 + quarter * 32;
   const uint32_t tmem_row = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
   uint32_t raw_even[32], raw_odd[32];
+  if (kChunks % kShare != 0 && part >= kChunks) return;   // a 32-wide tile: nothing for the later warps of a quarter
   tmem_ld_32x32(tmem_row + part * 32, raw_even);
   if constexpr (kIssuers == 2) tmem_ld_32x32(tmem_row + BN + part * 32, raw_odd);   // the first chunk's other partial sum
 #pragma unroll
@@ -602,7 +603,7 @@ __device__ __forceinline__ void epilogue_role(const UmmaParams& p, const SmemCar
     // into row ownership in its box.
     SourceQuads first;
     uint8_t* first_box = nullptr;
-    if (boxed) {
+    if (boxed && part < BN / 32) {   // (a 32-wide tile has a chunk for the first warp of each quarter only)
       fetch_source_coalesced(ep, first, tm * kTileM + quarter * 32, tn * BN + part * 32, lane);
       first_box = boxes + (box_uses++ % boxes_per_warp<kShare>()) * kOutBoxBytes;
       stage_source_boxed<boxes_per_warp<kShare>()>(ep, first, lane, first_box);

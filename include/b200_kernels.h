@@ -209,7 +209,8 @@ typedef struct b200_gemm_problem {
  * swapped for up to 16 rows), 39-41 "pair_mid" (CTA pairs on 256 x 128 tiles),
  * 42-44 "pair_splitk" (one 256 x 128 tile per cluster of CTA pairs, K split over
  * the pairs; supports_split_k = 1), 45-47 "medium" (128 x 192 tiles), 48-56
- * "width96" / "width160" / "width224" (128 x 96, 160 and 224 tiles). Automatic dispatch
+ * "width96" / "width160" / "width224" (128 x 96, 160 and 224 tiles), 57-59 "width32"
+ * (128 x 32 tiles). Automatic dispatch
  * tries them first, each behind a shape gate, and then walks the reference's
  * eight entries in the reference's order.
  */

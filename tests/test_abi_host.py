@@ -127,7 +127,7 @@ def test_registry_keeps_the_reference_ids_aliases_and_order(abi):
             assert (e.tile_m, e.tile_n, e.inst_m, e.inst_n, e.inst_k, e.supports_split_k) == (64, 128, 128, 64, 8, 1)
             continue
         assert e.tile_m in (128, 256) and e.inst_m == e.tile_m and e.inst_k == 8 and e.tile_k == 32
-        assert e.tile_n in (64, 96, 128, 160, 192, 224, 256) and e.inst_n == e.tile_n
+        assert e.tile_n in (32, 64, 96, 128, 160, 192, 224, 256) and e.inst_n == e.tile_n
         assert (e.tile_m == 256) == e.alias.decode().startswith("pair")   # 256 rows only as a CTA pair
         assert e.alignment_a == e.alignment_b == e.alignment_c and e.alignment_a in (1, 4)
         assert abi.b200_tf32_kernel_from_name(e.alias) == e.id

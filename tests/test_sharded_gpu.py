@@ -244,6 +244,7 @@ def test_sgemm_gather_fans_out_every_tile(abi):
     (36, (12, 264, 512)),      # operands swapped, K split over a cluster
     (39, (300, 264, 160)),     # CTA pair, 256 x 128 tiles, two issuers, ragged
     (42, (300, 200, 1024)),    # CTA pairs with K split over the cluster
+    (57, (200, 136, 100)),     # 128 x 32 tiles: one chunk, the second epilogue warp of a quarter idle
     (48, (200, 296, 100)),     # 128 x 96 tiles, two MMA threads, three chunks on two epilogue warps
     (51, (130, 488, 64)),      # 128 x 160 tiles
     (45, (256, 388, 96)),      # 128 x 192 tiles

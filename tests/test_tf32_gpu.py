@@ -149,8 +149,11 @@ def test_auto_dispatch_order(abi):
     a, b, _ = oracle.adaptive_inputs(m, 128, 64)
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 2               # fast
     assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 8  # fast_relu
-    # Small problem: 128-wide tiles would idle most SMs -> 64-wide tiles.
+    # Small problems: 128-wide tiles would idle most SMs -> the narrowest width that runs in one round.
     a, b, _ = oracle.adaptive_inputs(256, 256, 64)
+    assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 57              # width32
+    assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 58
+    a, b, _ = oracle.adaptive_inputs(128 * 8, 64 * (sms // 8), 64)             # 32-wide tiles would need two rounds
     assert run(abi, 0, a.cuda(), b.cuda(), dispatch=True)[2] == 18              # narrow
     assert run(abi, 0, a.cuda(), b.cuda(), epilogue=RELU, dispatch=True)[2] == 19
     # Large problem: 256 x 256 CTA pairs fill at least one round of pairs.
@@ -179,7 +182,7 @@ def test_strided_operands(abi):
     big_c = torch.randn(256, 640, device="cuda")
     a, b, c = big_a[:, :128], big_b[:128, :384], big_c[:, :384]
     status, d, chosen = run(abi, 0, a, b, c, alpha=0.5, beta=2.0, dispatch=True)
-    assert status == 0 and chosen in (2, 18)
+    assert status == 0 and chosen in (2, 18, 57)
     check(d, oracle.adaptive_gemm_fp64(a, b, c, 0.5, 2.0))
 
 
