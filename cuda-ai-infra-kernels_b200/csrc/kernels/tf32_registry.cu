@@ -142,7 +142,6 @@ bool gate_width96(const b200_gemm_problem& q, int sms) { return narrowest_one_ro
 bool gate_width160(const b200_gemm_problem& q, int sms) { return narrowest_one_round_width(q, sms) == 160; }
 bool gate_medium(const b200_gemm_problem& q, int sms) { return narrowest_one_round_width(q, sms) == 192; }
 bool gate_width224(const b200_gemm_problem& q, int sms) { return narrowest_one_round_width(q, sms) == 224; }
-// 128 x 64 tiles when 128-wide ones would leave more than half the SMs idle.
 // CTA pairs (256 x 256 per pair) when they fill at least one round of pairs.
 // (Half tiles filling one round, e.g. 1536^3 with 72 halves on 74 pairs, measured level with the
 // 128 x 128 tile kernel, 21.7 against 20.6 us, and stay a matter of the forced "pair" entry.)
@@ -211,6 +210,7 @@ bool gate_pair_mid(const b200_gemm_problem& q, int sms) {
 // Measured against the split-K tile kernel: ahead up to 16 rows (16 x 8192 x 1024: 11.7 vs 16.5 us,
 // 16 x 4096 x 4096: 12.7 vs 16.8, cuBLAS 12.9), level or behind from 32 rows on (64 x 4096 x 4096: 19.7 vs 18.2).
 bool gate_swap(const b200_gemm_problem& q, int) { return q.m <= 16; }
+// 128 x 64 tiles when 128-wide ones would leave more than half the SMs idle, or by the one-round rule above.
 bool gate_narrow(const b200_gemm_problem& q, int sms) {
   return (tiles_of(q, 128) * 2 <= sms && q.n > 64) || narrowest_one_round_width(q, sms) == 64;
 }
