@@ -13,7 +13,7 @@
 //   block  : one CTA per row, up to 4 vectors per thread: 256 or 512 threads
 //            (<= 4096 / 8192 floats); shuffle + one shared-memory hop.
 //   staged : rows of more than 8192 floats. The copy engine brings a row (up to
-//            24 576 floats: one CTA per row) or a CTA's share of it (beyond:
+//            28 672 floats: one CTA per row) or a CTA's share of it (beyond:
 //            clusters of 2/4/8 CTAs per row, partial statistics exchanged
 //            through distributed shared memory; up to 401 408 floats) into
 //            shared memory with one bulk copy, the threads take their
@@ -253,6 +253,10 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const RowArgs a) {
 constexpr int kStagedThreads = 512;
 constexpr int64_t kStagedMaxFloats = 50176;   // 196 KiB of row + barrier and reduction scratch inside 227 KiB
 constexpr int64_t kStagedPartFloats = 24576;  // largest preferred share per CTA of a cluster: 96 KiB, two CTAs per SM
+constexpr int64_t kStagedAloneFloats = 28672; // largest row one CTA takes alone: 112 KiB, two such CTAs still share an SM
+                                              // (2048 x 28672 softmax: 6200 GB/s alone, 4435 as clusters of two; at
+                                              // 32768 floats only one CTA fits an SM and the cluster form is ahead,
+                                              // 4500 against 4120)
 
 template <RowOp kOp, bool kCluster>
 __global__ void __launch_bounds__(kStagedThreads) row_staged_kernel(const RowArgs a) {
@@ -475,10 +479,10 @@ int launch_rows(const RowArgs& a, cudaStream_t s) {
   if (vector_ok && nvec <= 256 * kLightVec) return launch_by_vectors_block<kOp, 256>(static_cast<int>((nvec + 255) / 256), a, s);
   if (vector_ok && nvec <= 512 * kLightVec) return launch_by_vectors_block<kOp, 512>(static_cast<int>((nvec + 511) / 512), a, s);
   if (vector_ok && a.cols <= 8 * kStagedMaxFloats) {
-    // One CTA per row while two rows fit an SM side by side (24 576 floats); beyond that a cluster of
+    // One CTA per row while two rows fit an SM side by side (28 672 floats); beyond that a cluster of
     // 2, 4 or 8 CTAs per row, with shares of at most 16 384 floats where eight CTAs allow it.
     constexpr size_t kMaxSmem = staged_smem_bytes(kStagedMaxFloats);
-    if (a.cols <= 24576) {
+    if (a.cols <= kStagedAloneFloats) {
       if (!ensure_dynamic_smem<row_staged_kernel<kOp, false>, kMaxSmem>()) return B200_ERR_LAUNCH_FAILED;
       return launch_serialized(row_staged_kernel<kOp, false>, a.rows, kStagedThreads, a, s, staged_smem_bytes(a.cols));
     }

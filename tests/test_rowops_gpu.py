@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 # <= 65536 / 262144), streaming path, lengths that are not a multiple of four,
 # single row / single column.
 SHAPES = [(16, 128), (16, 768), (32, 1024), (33, 516), (8, 2048), (8, 4096), (5, 8192), (7, 8196), (4, 12288), (3, 16384),
-          (3, 32768), (3, 33000), (300, 20000), (3, 50176), (2, 50180), (2, 65536), (2, 70000), (2, 140000), (1, 262144),
+          (3, 28672), (3, 28676), (3, 32768), (3, 33000), (300, 20000), (3, 50176), (2, 50180), (2, 65536), (2, 70000), (2, 140000), (1, 262144),
           (1, 300000), (5, 1001), (7, 3), (1, 1), (300, 4), (0, 16)]
 
 
